@@ -1,0 +1,107 @@
+"""ctypes binding of libcoccl.so (the native runtime + sm_100a kernels).
+
+The library is loaded from coccl_b200/lib; if it is missing it is built in
+place. There is no Python fallback for a kernel: on a machine with a GPU a
+missing or stale library is an error, never a silent slow path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_ROOT = Path(__file__).resolve().parent
+_SO = _ROOT / "lib" / "libcoccl.so"
+_lib = None
+
+c_void_p, c_int, c_long, c_float, c_uint, c_ulonglong = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint, C.c_ulonglong
+
+MAX_RANKS = 8
+MAX_SLICES = 4096
+
+
+class Codec(C.Structure):
+    """Mirror of cocclkCodec (csrc/kernels/kernels_api.h)."""
+    _fields_ = [("kind", c_int), ("bits", c_int), ("group", c_int), ("asym", c_int), ("hadamard", c_int),
+                ("stochastic", c_int), ("paramBytes", c_int), ("seed", C.c_uint32)]
+
+
+class CollArgs(C.Structure):
+    """Mirror of cocclkCollArgs."""
+    _fields_ = [("op", c_int), ("nRanks", c_int), ("rankBase", c_int), ("dtype", c_int), ("count", c_long),
+                ("sliceTiles", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong), ("codec", Codec),
+                ("slotBytes", c_long), ("regionBOffset", c_long),
+                ("inp", c_void_p * MAX_RANKS), ("out", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
+                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS)]
+
+
+_PROTOS = {
+    # kernels_api.h
+    "cocclkEncodedChunkBytes": (c_long, [C.POINTER(Codec), c_long]),
+    "cocclkTileCodecSupported": (c_int, [C.POINTER(Codec)]),
+    "cocclkEncode": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_long, c_int, C.POINTER(Codec), c_void_p]),
+    "cocclkDecodeReduce": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_long, c_long, c_int,
+                                   C.POINTER(Codec), c_void_p]),
+    "cocclkDecodeReduceEncode": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_long, c_long,
+                                         C.POINTER(Codec), c_void_p]),
+    "cocclkFlagBytes": (c_long, []),
+    "cocclkSlotBytes": (c_long, [C.POINTER(Codec), c_long]),
+    "cocclkFusedCollective": (c_int, [C.POINTER(CollArgs), c_int, c_int, c_void_p]),
+    # gemm_api.h
+    "cocclkGemmBf16": (c_int, [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int,
+                               c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    # train_api.h
+    "cocclkLayerNormFwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_void_p]),
+    "cocclkLayerNormBwdGrid": (c_int, [c_int]),
+    "cocclkLayerNormBwd": (c_int, [c_void_p] * 9 + [c_int, c_void_p, c_int, c_int, c_void_p]),
+    "cocclkColSumBlocks": (c_int, [c_int]),
+    "cocclkColSum": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "cocclkGeluFwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
+    "cocclkGeluBwd": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_void_p]),
+    "cocclkCrossEntropy": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_long, c_float, c_void_p]),
+    "cocclkAdam": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_float, c_float, c_float,
+                           c_float, c_float, c_int, c_void_p, c_void_p]),
+    "cocclkSumSqBlocks": (c_int, [c_long]),
+    "cocclkSumSq": (c_int, [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_void_p]),
+    "cocclkClipCoef": (c_int, [c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p]),
+    "cocclkAccumBf16": (c_int, [c_void_p, c_void_p, c_long, c_int, c_void_p]),
+}
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not _SO.exists():
+            from . import _build
+            _build.build()
+        _lib = C.CDLL(str(_SO), mode=C.RTLD_GLOBAL)
+        for name, (res, args) in _PROTOS.items():
+            try:
+                fn = getattr(_lib, name)
+            except AttributeError as e:  # stale library
+                raise RuntimeError(f"{_SO} lacks symbol {name}; rebuild with `python -m coccl_b200._build`") from e
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+def declare(name: str, restype, argtypes):
+    """Attach a prototype for a symbol that is not in the static table (host runtime APIs)."""
+    fn = getattr(lib(), name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}" + (" (unsupported configuration)" if rc == -1 else ""))
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None passes NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def cur_stream() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream

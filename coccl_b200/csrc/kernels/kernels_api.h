@@ -1,0 +1,71 @@
+// C entry points of the device layer (libcoccl.so). Everything here takes raw
+// device pointers and a CUDA stream; nothing allocates unless stated.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Mirrors coccl::CodecCfg (kernels/codecs.cuh).
+typedef struct cocclkCodec {
+  int kind;        // 0 sdp4bit, 1 mxfp8
+  int bits;
+  int group;
+  int asym;
+  int hadamard;
+  int stochastic;
+  int paramBytes;
+  uint32_t seed;
+} cocclkCodec;
+
+// dtype: 0 fp32, 1 fp16, 2 bf16. All return a cudaError_t value (0 = ok) or
+// -1 for an unsupported configuration.
+long cocclkEncodedChunkBytes(const cocclkCodec* codec, long count);
+int cocclkTileCodecSupported(const cocclkCodec* codec);
+
+// `chunks` raw chunks of `count` elements (rawPitch elements apart) ->
+// `chunks` encoded chunks `encStride` bytes apart.
+int cocclkEncode(const void* in, void* out, long count, long chunks, long rawPitch, long encStride, int dtype,
+                 const cocclkCodec* codec, cudaStream_t stream);
+// out chunk j (j < chunks) = sum over i < reduce of decode(in chunk i*chunks + j).
+int cocclkDecodeReduce(const void* in, void* out, long count, long chunks, long reduce, long rawPitch,
+                       long encStride, int dtype, const cocclkCodec* codec, cudaStream_t stream);
+// encoded out chunk j = encode(sum over i < reduce of decode(in chunk i*chunks + j)).
+int cocclkDecodeReduceEncode(const void* in, void* out, long count, long chunks, long reduce, long encStrideIn,
+                             long encStrideOut, const cocclkCodec* codec, cudaStream_t stream);
+
+// Fused collectives. Mirrors coccl::CollArgs.
+enum { COCCLK_MAX_RANKS = 8, COCCLK_MAX_SLICES = 4096 };
+typedef struct cocclkCollArgs {
+  int op;        // 0 RS, 1 AG, 2 A2A, 3 AR one-shot, 4 AR two-shot
+  int nRanks;
+  int rankBase;
+  int dtype;
+  long count;
+  int sliceTiles;
+  unsigned int epoch;
+  unsigned long long timeoutNs;
+  cocclkCodec codec;
+  long slotBytes;
+  long regionBOffset;
+  const void* in[COCCLK_MAX_RANKS];
+  void* out[COCCLK_MAX_RANKS];
+  uint8_t* ws[COCCLK_MAX_RANKS];
+  unsigned int* flags[COCCLK_MAX_RANKS];
+  void* status[COCCLK_MAX_RANKS];
+} cocclkCollArgs;
+
+// Bytes of flag storage one rank needs (zero-initialised once).
+long cocclkFlagBytes(void);
+// Smallest slot size (16-byte aligned) for one encoded chunk of `count` elements.
+long cocclkSlotBytes(const cocclkCodec* codec, long count);
+// emulatedRanks == 1: production launch for rank `rankBase` (peer pointers in
+// ws/flags). emulatedRanks == nRanks: one cooperative launch plays every rank
+// on the current device. maxCtas <= 0 lets the library size the grid.
+int cocclkFusedCollective(const cocclkCollArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
