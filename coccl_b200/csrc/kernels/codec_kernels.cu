@@ -1,4 +1,5 @@
 // Launchers for the standalone codec kernels (see collective_kernels.cuh).
+#include "launch_count.h"
 #include "collective_kernels.cuh"
 #include "kernels_api.h"
 #include <type_traits>
@@ -62,6 +63,7 @@ extern "C" int cocclkEncode(const void* in, void* out, long count, long chunks, 
     });
   });
   if (!ok) return -1;
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -81,6 +83,7 @@ extern "C" int cocclkDecodeReduce(const void* in, void* out, long count, long ch
     });
   });
   if (!ok) return -1;
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -98,5 +101,6 @@ extern "C" int cocclkDecodeReduceEncode(const void* in, void* out, long count, l
     decodeReduceEncodeKernel<C><<<grid, kTileThreads, 0, stream>>>(a);
   });
   if (!ok) return -1;
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }

@@ -1,4 +1,5 @@
 // Launcher of the fused compressed collectives (see collective_kernels.cuh).
+#include "launch_count.h"
 #include "collective_kernels.cuh"
 #include "kernels_api.h"
 #include <string.h>
@@ -38,6 +39,7 @@ static int launchOne(const CollArgs& a, int emulatedRanks, int maxCtas, cudaStre
   int gx = (int)(items < cap ? items : cap);
   dim3 grid(gx, emulatedRanks, 1);
   CollArgs copy = a;
+  cocclkCountLaunches(1);
   void* params[] = {&copy};
   if (emulatedRanks > 1) {
     // the emulated ranks wait on one another: co-residency must be guaranteed

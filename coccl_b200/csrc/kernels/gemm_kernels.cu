@@ -10,6 +10,7 @@
 // epilogue (TMEM lane quadrant = warp % 4). Every mbarrier wait is bounded; on
 // a timeout the kernel raises the error word, drains its outstanding copies,
 // frees TMEM and returns.
+#include "launch_count.h"
 #include "gemm_tcgen05.cuh"
 #include "gemm_api.h"
 #include <stdio.h>
@@ -269,6 +270,10 @@ static EncodeTiledFn encodeTiled() {
 static int makeMap(CUtensorMap* m, const void* base, long inner, long outer, long ld, int boxInner, int boxOuter) {
   EncodeTiledFn f = encodeTiled();
   if (!f) return -2;
+  // The driver call needs a current context; a thread that has only ever been handed work (an
+  // autograd worker) may not have bound the primary context yet.
+  static thread_local bool ctxBound = false;
+  if (!ctxBound) { cudaFree(nullptr); ctxBound = true; }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * 2) & 15)) return -3;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -277,7 +282,12 @@ static int makeMap(CUtensorMap* m, const void* base, long inner, long outer, lon
   CUresult r = f(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -4;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "coccl: cuTensorMapEncodeTiled failed (%d): base=%p dims={%ld,%ld} ld=%ld box={%d,%d}\n", (int)r,
+            base, inner, outer, ld, boxInner, boxOuter);
+    return -4;
+  }
+  return 0;
 }
 
 }  // namespace coccl
@@ -314,5 +324,6 @@ extern "C" int cocclkGemmBf16(const void* A, long lda, int aMN, const void* B, l
   int grid = tiles < sms ? tiles : sms;
   if (maxCtas > 0 && grid > maxCtas) grid = maxCtas;
   gemmBf16Kernel<<<grid, kGemmThreads, smemBytes, stream>>>(ta, tb, g);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }

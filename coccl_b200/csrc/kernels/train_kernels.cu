@@ -6,6 +6,7 @@
 // The reference ships no trainer (its training layer is an empty submodule,
 // .gitmodules:1-3); these kernels belong to the framework layer that drives the
 // compressed collectives. Each kernel touches every byte once.
+#include "launch_count.h"
 #include "common.cuh"
 #include "train_api.h"
 #include <math.h>
@@ -400,6 +401,7 @@ extern "C" int cocclkLayerNormFwd(const void* x, const void* res, const void* ga
       (const bf16*)beta, (bf16*)y, (bf16*)xOut, mean, rstd, M, H, eps)
   if (nv <= 1) LN_FWD(1); else if (nv <= 2) LN_FWD(2); else if (nv <= 4) LN_FWD(4); else LN_FWD(8);
 #undef LN_FWD
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -418,6 +420,7 @@ extern "C" int cocclkLayerNormBwd(const void* dy, const void* x, const float* me
   // scratch rows are [dgamma | dbeta], 2H floats each
   colReduceKernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dgamma, grid, H, 2L * H, accumulate);
   colReduceKernel<<<(H + 255) / 256, 256, 0, s>>>(scratch + H, dbeta, grid, H, 2L * H, accumulate);
+  cocclkCountLaunches(3);
   return (int)cudaGetLastError();
 }
 
@@ -430,17 +433,20 @@ extern "C" int cocclkColSum(const void* x, float* out, int accumulate, float* sc
   dim3 grid((N / 8 + 255) / 256, by);
   colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
   colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
+  cocclkCountLaunches(2);
   return (int)cudaGetLastError();
 }
 
 extern "C" int cocclkGeluFwd(const void* z, const void* bias, void* y, void* zOut, long n, int N, cudaStream_t s) {
   if (n % 8 || N % 8) return -1;
   geluFwdKernel<<<gridForElems(n, 2048), 256, 0, s>>>((const bf16*)z, (const bf16*)bias, (bf16*)y, (bf16*)zOut, n, N);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 extern "C" int cocclkGeluBwd(const void* dy, const void* z, void* dz, long n, cudaStream_t s) {
   if (n % 8) return -1;
   geluBwdKernel<<<gridForElems(n, 2048), 256, 0, s>>>((const bf16*)dy, (const bf16*)z, (bf16*)dz, n);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -449,6 +455,7 @@ extern "C" int cocclkCrossEntropy(void* logits, const long* targets, float* loss
   if (V % 8 || V > kCeThreads * kCeMaxVec * 8 || ld % 8 || M <= 0) return -1;
   const int grid = M < 148 * 2 ? M : 148 * 2;
   crossEntropyKernel<<<grid, kCeThreads, 0, s>>>((bf16*)logits, targets, loss, M, V, ld, gscale);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -462,6 +469,7 @@ extern "C" int cocclkAdam(float* master, float* m, float* v, const void* grad, i
     adamKernel<bf16><<<grid, 256, 0, s>>>(master, m, v, (const bf16*)grad, (bf16*)param, n, lr, b1, b2, eps, wd, bc1, bc2, gradScale);
   else
     adamKernel<float><<<grid, 256, 0, s>>>(master, m, v, (const float*)grad, (bf16*)param, n, lr, b1, b2, eps, wd, bc1, bc2, gradScale);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
@@ -474,17 +482,20 @@ extern "C" int cocclkSumSq(const void* x, int isBf16, long n, float* out, int ac
   if (isBf16) sumSqPartialKernel<bf16><<<grid, 256, 0, s>>>((const bf16*)x, n, scratch);
   else sumSqPartialKernel<float><<<grid, 256, 0, s>>>((const float*)x, n, scratch);
   sumFinalKernel<<<1, 256, 0, s>>>(scratch, grid, out, accumulate);
+  cocclkCountLaunches(2);
   return (int)cudaGetLastError();
 }
 
 extern "C" int cocclkClipCoef(const float* sumsq, float maxNorm, float gradScaleIn, float* coef, float* normOut,
                               cudaStream_t s) {
   clipCoefKernel<<<1, 1, 0, s>>>(sumsq, maxNorm, gradScaleIn, coef, normOut);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
 
 extern "C" int cocclkAccumBf16(float* dst, const void* src, long n, int accumulate, cudaStream_t s) {
   if (n <= 0) return -1;
   accumBf16Kernel<<<gridForElems(n, 2048), 256, 0, s>>>(dst, (const bf16*)src, n, accumulate);
+  cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }

@@ -1,0 +1,251 @@
+"""Megatron-style GPT (pre-LN, learned positions, tanh-GELU MLP) built on the
+fused sm_100a ops, with tensor/sequence/pipeline-parallel hooks.
+
+The reference ships no model code; its training launcher drives an external
+Megatron trainer (examples/training_scripts/train_qwen_coccl.sh:1-131) and its
+classifier only recognises DP/TP/PP traffic
+(src/coccl-extend/core/training/coccl_training_classifier.cc:371-716). This
+module is the framework layer that produces that traffic.
+
+Activations are token-major [tokens, hidden] with tokens = batch*seq (batch
+outermost). Under sequence parallelism the residual stream is sharded over
+tokens; column-parallel linears see the all-gathered tokens and row-parallel
+linears reduce-scatter their partial sums back to the shard.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import fused
+
+
+@dataclass
+class GPTConfig:
+    n_layer: int = 32
+    hidden: int = 4096
+    n_head: int = 32
+    ffn: int = 16384
+    seq_len: int = 2048
+    vocab: int = 50304
+    eps: float = 1e-5
+    init_std: float = 0.02
+    dtype: torch.dtype = torch.bfloat16
+    # MoE (expert parallel) variant: every `moe_every`-th layer uses experts
+    n_experts: int = 0
+    moe_top_k: int = 2
+    moe_every: int = 1
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.n_head
+
+    def num_params(self) -> int:
+        h, f = self.hidden, self.ffn
+        per_layer = 4 * h * h + 4 * h + 2 * h * f + f + h + 4 * h
+        return self.n_layer * per_layer + self.vocab * h + self.seq_len * h + 2 * h
+
+    def flops_per_token(self) -> float:
+        """Training FLOPs per token (fwd+bwd = 3x fwd), causal attention counted at half."""
+        h, f, s = self.hidden, self.ffn, self.seq_len
+        per_layer = 2 * (4 * h * h + 2 * h * f) + 2 * 2 * s * h / 2 * 2 / 2 * 2
+        return 3.0 * (self.n_layer * per_layer + 2 * h * self.vocab)
+
+
+GPT_6P7B = GPTConfig()
+GPT_TINY = GPTConfig(n_layer=2, hidden=256, n_head=4, ffn=1024, seq_len=128, vocab=1024)
+
+
+class NoTP:
+    """Tensor-parallel context of size 1 (all hooks are identities)."""
+    size, rank = 1, 0
+    sequence_parallel = False
+
+    def gather_tokens(self, x): return x
+    def scatter_sum_tokens(self, x): return x
+    def all_reduce_sum(self, x): return x
+    def copy_to_tp(self, x): return x
+    def vocab_parallel_cross_entropy(self, logits, targets, scale): return fused.cross_entropy(logits, targets, scale)
+
+
+class ParamStore:
+    """Allocates every parameter of a pipeline stage as a view of one flat bf16 buffer,
+    and every gradient as a view (`p.main_grad`) of one flat fp32 buffer, so that the
+    distributed optimizer can reduce-scatter / all-gather contiguous shards."""
+
+    def __init__(self, dtype, device, pad_to: int = 1):
+        self.dtype, self.device, self.pad_to = dtype, device, pad_to
+        self.specs: list[tuple[str, tuple, str, float]] = []
+        self.params: dict[str, nn.Parameter] = {}
+        self.flat_param = None
+        self.flat_grad = None
+
+    def add(self, name, shape, init="normal", std=0.02):
+        self.specs.append((name, tuple(shape), init, std))
+
+    def materialise(self, generator=None, grad_dtype=torch.float32):
+        sizes = [math.prod(s) for _, s, _, _ in self.specs]
+        # every parameter starts on a 16-byte boundary of both buffers (8 elements)
+        offs, total = [], 0
+        for n in sizes:
+            offs.append(total)
+            total += -(-n // 8) * 8
+        total = -(-total // self.pad_to) * self.pad_to
+        self.flat_param = torch.zeros(total, dtype=self.dtype, device=self.device)
+        self.flat_grad = torch.zeros(total, dtype=grad_dtype, device=self.device)
+        for (name, shape, init, std), off, n in zip(self.specs, offs, sizes):
+            view = self.flat_param[off:off + n].view(shape)
+            if init == "normal":
+                view.copy_(torch.randn(shape, generator=generator, device=self.device, dtype=torch.float32) * std)
+            elif init == "ones":
+                view.fill_(1.0)
+            p = nn.Parameter(view, requires_grad=True)
+            p.main_grad = self.flat_grad[off:off + n].view(shape)
+            self.params[name] = p
+        return self
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, cfg: GPTConfig, idx: int, store: ParamStore, tp):
+        super().__init__()
+        self.cfg, self.idx, self.tp = cfg, idx, tp
+        h, f, t = cfg.hidden, cfg.ffn, tp.size
+        assert cfg.n_head % t == 0 and f % t == 0
+        self.prefix = f"layers.{idx}."
+        pre = self.prefix
+        out_std = cfg.init_std / math.sqrt(2.0 * cfg.n_layer)
+        store.add(pre + "ln1.weight", (h,), "ones")
+        store.add(pre + "ln1.bias", (h,), "zeros")
+        store.add(pre + "qkv.weight", (3 * h // t, h), "normal", cfg.init_std)
+        store.add(pre + "qkv.bias", (3 * h // t,), "zeros")
+        store.add(pre + "proj.weight", (h, h // t), "normal", out_std)
+        store.add(pre + "proj.bias", (h,), "zeros")
+        store.add(pre + "ln2.weight", (h,), "ones")
+        store.add(pre + "ln2.bias", (h,), "zeros")
+        store.add(pre + "fc1.weight", (f // t, h), "normal", cfg.init_std)
+        store.add(pre + "fc1.bias", (f // t,), "zeros")
+        store.add(pre + "fc2.weight", (h, f // t), "normal", out_std)
+        store.add(pre + "fc2.bias", (h,), "zeros")
+
+    def bind(self, params: dict):
+        for short in ("ln1.weight", "ln1.bias", "qkv.weight", "qkv.bias", "proj.weight", "proj.bias", "ln2.weight",
+                      "ln2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"):
+            self.register_parameter(short.replace(".", "_"), params[self.prefix + short])
+
+    def attention(self, qkv, batch, seq):
+        cfg, t = self.cfg, self.tp.size
+        nh, d = cfg.n_head // t, cfg.head_dim
+        qkv = qkv.view(batch, seq, nh, 3, d)
+        q, k, v = (qkv[:, :, :, i].transpose(1, 2) for i in range(3))  # [b, heads, s, d] views
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return o.transpose(1, 2).reshape(batch * seq, nh * d)
+
+    def forward(self, x, delta, batch, seq):
+        """x: residual stream, delta: pending update not yet added (or None). Returns (x, delta)."""
+        tp = self.tp
+        if delta is None:
+            y = fused.layer_norm(x, self.ln1_weight, self.ln1_bias, self.cfg.eps)
+        else:
+            y, x = fused.layer_norm(x, self.ln1_weight, self.ln1_bias, self.cfg.eps, residual=delta)
+        y = tp.gather_tokens(y)
+        qkv = fused.linear(y, self.qkv_weight, self.qkv_bias)
+        a = self.attention(qkv, batch, seq)
+        # row-parallel: the bias is added once, after the reduction (rank 0 carries it)
+        o = fused.linear(a, self.proj_weight, self.proj_bias if tp.rank == 0 else None)
+        o = tp.scatter_sum_tokens(o)
+        y, x = fused.layer_norm(x, self.ln2_weight, self.ln2_bias, self.cfg.eps, residual=o)
+        y = tp.gather_tokens(y)
+        z = fused.linear(y, self.fc1_weight, self.fc1_bias, gelu=True)
+        o = fused.linear(z, self.fc2_weight, self.fc2_bias if tp.rank == 0 else None)
+        o = tp.scatter_sum_tokens(o)
+        return x, o
+
+
+class GPTStage(nn.Module):
+    """Layers [first, last) of the model plus the embedding (first stage) and the head (last stage)."""
+
+    def __init__(self, cfg: GPTConfig, device, tp=None, first_layer=0, last_layer=None, pre=True, post=True,
+                 seed=1234, pad_to=1, layer_factory=None):
+        super().__init__()
+        self.cfg, self.tp = cfg, tp or NoTP()
+        last_layer = cfg.n_layer if last_layer is None else last_layer
+        self.pre, self.post = pre, post
+        tp_ = self.tp
+        store = ParamStore(cfg.dtype, device, pad_to)
+        vshard = cfg.vocab // tp_.size
+        assert cfg.vocab % tp_.size == 0
+        if pre or post:
+            # the output head shares the word embedding; under pipeline parallelism the last stage keeps
+            # its own copy whose gradient is summed with the first stage's (see parallel/pp.py)
+            store.add("wte", (vshard, cfg.hidden), "normal", cfg.init_std)
+        if pre:
+            store.add("wpe", (cfg.seq_len, cfg.hidden), "normal", cfg.init_std)
+        make = layer_factory or (lambda c, i, s, t: TransformerLayer(c, i, s, t))
+        self.layers = nn.ModuleList([make(cfg, i, store, tp_) for i in range(first_layer, last_layer)])
+        if post:
+            store.add("lnf.weight", (cfg.hidden,), "ones")
+            store.add("lnf.bias", (cfg.hidden,), "zeros")
+        # same seed on every TP rank would make shards identical: fold the rank in
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed + 7919 * tp_.rank + 104729 * first_layer)
+        store.materialise(gen)
+        self.store = store
+        for name, p in store.params.items():
+            if not name.startswith("layers."):
+                self.register_parameter(name.replace(".", "_"), p)
+        for layer in self.layers:
+            layer.bind(store.params)
+
+    # ---- embedding (vocab-parallel under TP)
+    def embed(self, tokens):
+        cfg, tp = self.cfg, self.tp
+        b, s = tokens.shape
+        flat = tokens.reshape(-1)
+        if tp.size == 1:
+            e = F.embedding(flat, self.wte)
+        else:
+            lo = tp.rank * (cfg.vocab // tp.size)
+            local = flat - lo
+            mask = (local < 0) | (local >= self.wte.shape[0])
+            e = F.embedding(local.masked_fill(mask, 0), self.wte)
+            e = e.masked_fill(mask[:, None], 0)
+        pos = self.wpe[:s].unsqueeze(0).expand(b, s, cfg.hidden).reshape(b * s, cfg.hidden)
+        if tp.size > 1:
+            e = e + pos / tp.size  # the position term is summed over ranks below
+            e = tp.scatter_sum_tokens(e) if tp.sequence_parallel else tp.all_reduce_sum(e)
+        else:
+            e = e + pos
+        return e.to(cfg.dtype)
+
+    def forward(self, tokens_or_hidden, targets=None, loss_scale: float = 1.0, batch=None, seq=None):
+        """First stage takes token ids [b, s]; later stages take (x, delta) from the previous stage.
+        The last stage returns the scaled summed loss; others return (x, delta)."""
+        if self.pre:
+            batch, seq = tokens_or_hidden.shape
+            x, delta = self.embed(tokens_or_hidden), None
+        else:
+            x, delta = tokens_or_hidden
+        for layer in self.layers:
+            x, delta = layer(x, delta, batch, seq)
+        if not self.post:
+            return x, delta
+        y, _ = fused.layer_norm(x, self.lnf_weight, self.lnf_bias, self.cfg.eps, residual=delta)
+        y = self.tp.gather_tokens(y)
+        y = self.tp.copy_to_tp(y)
+        logits = fused.linear(y, self.wte)
+        return self.tp.vocab_parallel_cross_entropy(logits, targets.reshape(-1), loss_scale)
+
+    # ---- utilities
+    def zero_grad_buffer(self):
+        self.store.flat_grad.zero_()
+
+    def post_backward_sync_autograd_grads(self):
+        """Parameters touched by stock autograd ops (embeddings) receive `.grad`; fold it into main_grad."""
+        for p in self.parameters():
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None

@@ -69,7 +69,6 @@ class _LayerNorm(torch.autograd.Function):
         ctx.has_res = has_res
         ctx.shape = x.shape
         if has_res:
-            ctx.mark_non_differentiable()
             return y.reshape(x.shape), xs.reshape(x.shape)
         return y.reshape(x.shape), None
 
@@ -206,7 +205,7 @@ def linear(x, w, bias=None, gelu: bool = False):
 # --------------------------------------------------------------------------- cross-entropy
 class _CrossEntropy(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, targets, scale):
+    def forward(ctx, logits, targets, scale, unit_grad):
         V = logits.shape[-1]
         lg = logits.reshape(-1, V)
         tg = targets.reshape(-1)
@@ -230,22 +229,23 @@ class _CrossEntropy(torch.autograd.Function):
             grad = (p * scale).to(lg.dtype)
         ctx.save_for_backward(grad)
         ctx.shape = logits.shape
+        ctx.unit_grad = unit_grad
         return loss.sum() * scale
 
     @staticmethod
     def backward(ctx, dloss):
         (grad,) = ctx.saved_tensors
-        # dloss is 1 in the training loop (the scale is already folded in); honour other values
-        return (grad * dloss.to(grad.dtype)).reshape(ctx.shape) if not _is_one(dloss) else grad.reshape(ctx.shape), None, None
+        if not ctx.unit_grad:
+            grad = grad * dloss.to(grad.dtype)
+        return grad.reshape(ctx.shape), None, None, None
 
 
-def _is_one(t):
-    return t.numel() == 1 and t.dtype == torch.float32 and not t.requires_grad and getattr(t, "_coccl_one", False)
+def cross_entropy(logits, targets, scale: float, unit_grad: bool = True):
+    """sum_i CE(logits_i, targets_i) * scale. On CUDA the logits buffer is consumed (turned into its gradient).
 
-
-def cross_entropy(logits, targets, scale: float):
-    """sum_i CE(logits_i, targets_i) * scale. On CUDA the logits buffer is consumed (turned into its gradient)."""
-    return _CrossEntropy.apply(logits, targets, scale)
+    unit_grad=True (the trainer's case) assumes the result is the root of backward(), i.e. the incoming
+    gradient is 1, and skips one pass over the [tokens, vocab] gradient."""
+    return _CrossEntropy.apply(logits, targets, scale, unit_grad)
 
 
 # --------------------------------------------------------------------------- optimizer kernels

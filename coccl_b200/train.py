@@ -1,0 +1,86 @@
+"""Training engine: micro-batch loop, (optional) pipeline schedule, sharded optimizer.
+
+`Trainer.train_step(tokens)` is the public entry point used by bench.py and the
+examples: it takes one global-batch slice of token ids for this data-parallel
+rank as a pinned host tensor [sequences, seq_len + 1], copies it to the device,
+runs forward/backward over all micro-batches, reduces gradients, steps the
+optimizer and returns the mean loss as a device scalar.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .models.gpt import GPTConfig, GPTStage
+from .parallel.dp import DistributedOptimizer
+
+
+@dataclass
+class ParallelConfig:
+    tp: int = 1
+    pp: int = 1
+    dp: int = 1
+    sequence_parallel: bool = True
+
+
+class Trainer:
+    def __init__(self, cfg: GPTConfig, device, *, micro_batch=2, parallel: ParallelConfig | None = None, groups=None,
+                 lr=1e-4, weight_decay=0.1, clip_grad=1.0, seed=1234):
+        self.cfg, self.device, self.micro_batch = cfg, device, micro_batch
+        self.parallel = parallel or ParallelConfig()
+        self.groups = groups  # coccl_b200.parallel.mesh.Mesh or None (single GPU)
+        g = groups
+        tp_ctx = g.tp_context() if g is not None else None
+        pp_rank = g.pp_rank if g is not None else 0
+        pp = self.parallel.pp
+        per = cfg.n_layer // pp
+        assert cfg.n_layer % pp == 0
+        dp = self.parallel.dp
+        self.stage = GPTStage(cfg, device, tp=tp_ctx, first_layer=pp_rank * per, last_layer=(pp_rank + 1) * per,
+                              pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * dp * 2048)
+        norm_groups = []
+        if g is not None:
+            if g.tp_comm is not None and g.tp_comm.size > 1:
+                norm_groups.append(g.tp_comm)
+            if g.pp_comm is not None and g.pp_comm.size > 1:
+                norm_groups.append(g.pp_comm)
+        self.opt = DistributedOptimizer(self.stage.store.flat_param, self.stage.store.flat_grad,
+                                        g.dp_comm if (g is not None and dp > 1) else None, lr=lr,
+                                        weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups)
+        self.schedule = None
+        if pp > 1:
+            from .parallel.pp import PipelineSchedule
+            self.schedule = PipelineSchedule(self.stage, g, cfg, micro_batch)
+        self._loss_acc = torch.zeros(1, dtype=torch.float32, device=device)
+        self._dev_tokens = None
+
+    def train_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens: [n_seq, seq_len+1] int64 (pinned host or device). Returns the mean token loss (device scalar)."""
+        cfg = self.cfg
+        n_seq = tokens.shape[0]
+        assert n_seq % self.micro_batch == 0
+        n_micro = n_seq // self.micro_batch
+        if tokens.device != self.device:
+            if self._dev_tokens is None or self._dev_tokens.shape != tokens.shape:
+                self._dev_tokens = torch.empty(tokens.shape, dtype=tokens.dtype, device=self.device)
+            self._dev_tokens.copy_(tokens, non_blocking=True)
+            tokens = self._dev_tokens
+        self.stage.zero_grad_buffer()
+        self._loss_acc.zero_()
+        # loss is summed over tokens of this rank's micro-batches and scaled so that the sum over
+        # all data-parallel ranks is the global mean
+        scale = 1.0 / (n_seq * cfg.seq_len * self.parallel.dp)
+        if self.schedule is not None:
+            self.schedule.run(tokens, n_micro, scale, self._loss_acc)
+        else:
+            for i in range(n_micro):
+                mb = tokens[i * self.micro_batch:(i + 1) * self.micro_batch]
+                loss = self.stage(mb[:, :-1], mb[:, 1:], scale)
+                loss.backward()
+                self._loss_acc += loss.detach()
+        self.stage.post_backward_sync_autograd_grads()
+        if self.groups is not None:
+            self.groups.sync_shared_grads(self.stage)
+        self.opt.step(grad_scale=1.0)
+        return self._loss_acc * self.parallel.dp  # this rank's mean loss
