@@ -9,6 +9,9 @@
 #include "launch_count.h"
 #include "common.cuh"
 #include "train_api.h"
+#include "no_alloc_api.h"
+#include <mutex>
+#include <stdio.h>
 #include <math.h>
 
 namespace coccl {
@@ -497,5 +500,63 @@ extern "C" int cocclkAccumBf16(float* dst, const void* src, long n, int accumula
   if (n <= 0) return -1;
   accumBf16Kernel<<<gridForElems(n, 2048), 256, 0, s>>>(dst, (const bf16*)src, n, accumulate);
   cocclkCountLaunches(1);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free column sum (see no_alloc_api.h). The scratch lives in the library
+// image; host code must not pass the symbol itself to a kernel (on the host the name
+// is only a stand-in), so the device address is looked up once per device.
+// ---------------------------------------------------------------------------
+namespace coccl {
+constexpr int kNoAllocRows = 64;  // == upper bound of cocclkColSumBlocks
+static __device__ __align__(256) float gColSumScratch[kNoAllocRows * COCCLK_NOALLOC_MAX_COLS];
+static float* gColSumScratchAddr[64];
+static std::mutex gNoAllocMutex;
+static thread_local char gNoAllocError[256] = "";
+}  // namespace coccl
+
+extern "C" const char* cocclkNoAllocLastError(void) { return coccl::gNoAllocError; }
+
+extern "C" int cocclkColSumNoAlloc(const void* x, float* out, int accumulate, int M, int N, cudaStream_t s) {
+  using namespace coccl;
+  gNoAllocError[0] = 0;
+  if (M <= 0 || N <= 0 || (N % 8) != 0) {
+    snprintf(gNoAllocError, sizeof(gNoAllocError), "cocclkColSumNoAlloc: need M > 0 and N a positive multiple of 8 (M=%d N=%d)", M, N);
+    return COCCLK_NOALLOC_BAD_SHAPE;
+  }
+  if (N > COCCLK_NOALLOC_MAX_COLS) {
+    snprintf(gNoAllocError, sizeof(gNoAllocError),
+             "cocclkColSumNoAlloc: N=%d exceeds the built-in scratch (max %d columns); use cocclkColSum with caller scratch",
+             N, COCCLK_NOALLOC_MAX_COLS);
+    return COCCLK_NOALLOC_TOO_LARGE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) {
+    snprintf(gNoAllocError, sizeof(gNoAllocError), "cocclkColSumNoAlloc: device index %d out of range", dev);
+    return COCCLK_NOALLOC_BAD_SHAPE;
+  }
+  float* scratch;
+  {
+    std::lock_guard<std::mutex> lock(gNoAllocMutex);
+    if (gColSumScratchAddr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, gColSumScratch);  // device `dev` is current
+      if (e != cudaSuccess) {
+        snprintf(gNoAllocError, sizeof(gNoAllocError), "cocclkColSumNoAlloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return (int)e;
+      }
+      gColSumScratchAddr[dev] = static_cast<float*>(p);
+    }
+    scratch = gColSumScratchAddr[dev];
+  }
+  const int by = cocclkColSumBlocks(M);  // <= kNoAllocRows
+  const int rowsPer = (M + by - 1) / by;
+  dim3 grid((N / 8 + 255) / 256, by);
+  colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
+  colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
+  cocclkCountLaunches(2);
   return (int)cudaGetLastError();
 }
