@@ -1,0 +1,80 @@
+// CUDA-IPC backend of the symmetric memory interface (symm.h).
+#include "symm.h"
+#include <string.h>
+#include <new>
+#include <vector>
+
+struct cocclSymmBuffer {
+  void* local = nullptr;
+  size_t bytes = 0;
+  int device = -1;
+  std::vector<void*> imported;  // by peer index; nullptr = not mapped
+};
+
+static_assert(sizeof(cudaIpcMemHandle_t) <= COCCL_SYMM_HANDLE_BYTES, "IPC handle does not fit");
+
+extern "C" int cocclSymmAlloc(size_t bytes, cocclSymmBuffer** out) {
+  if (out == nullptr || bytes == 0) return (int)cudaErrorInvalidValue;
+  cocclSymmBuffer* b = new (std::nothrow) cocclSymmBuffer();
+  if (!b) return (int)cudaErrorMemoryAllocation;
+  cudaError_t e = cudaGetDevice(&b->device);
+  if (e == cudaSuccess) e = cudaMalloc(&b->local, bytes);
+  if (e == cudaSuccess) e = cudaMemset(b->local, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (b->local) cudaFree(b->local);
+    delete b;
+    return (int)e;
+  }
+  b->bytes = bytes;
+  *out = b;
+  return 0;
+}
+
+extern "C" int cocclSymmExport(const cocclSymmBuffer* buf, void* handle) {
+  if (!buf || !handle) return (int)cudaErrorInvalidValue;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, buf->local);
+  if (e != cudaSuccess) return (int)e;
+  memset(handle, 0, COCCL_SYMM_HANDLE_BYTES);
+  memcpy(handle, &h, sizeof(h));
+  return 0;
+}
+
+extern "C" int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void* handle, void** mapped) {
+  if (!owner || !handle || !mapped || peerIndex < 0) return (int)cudaErrorInvalidValue;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return (int)e;
+  if ((size_t)peerIndex >= owner->imported.size()) owner->imported.resize(peerIndex + 1, nullptr);
+  owner->imported[peerIndex] = p;
+  *mapped = p;
+  return 0;
+}
+
+extern "C" void* cocclSymmLocalPtr(const cocclSymmBuffer* buf) { return buf ? buf->local : nullptr; }
+extern "C" size_t cocclSymmBytes(const cocclSymmBuffer* buf) { return buf ? buf->bytes : 0; }
+
+extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
+  if (!buf) return 0;
+  cudaError_t first = cudaSuccess;
+  for (void* p : buf->imported) {
+    if (p) {
+      cudaError_t e = cudaIpcCloseMemHandle(p);
+      if (first == cudaSuccess) first = e;
+    }
+  }
+  if (buf->local) {
+    cudaError_t e = cudaFree(buf->local);
+    if (first == cudaSuccess) first = e;
+  }
+  delete buf;
+  return (int)first;
+}
+
+// Small synchronous device->host read (status words).
+extern "C" int cocclHostRead32(const void* dev, unsigned int* out) {
+  return (int)cudaMemcpy(out, dev, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+}

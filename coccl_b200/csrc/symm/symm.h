@@ -1,0 +1,41 @@
+// Symmetric (peer-mapped) device memory for one NVSwitch domain.
+//
+// Every rank allocates a buffer of the same size, exports a handle, and maps
+// the buffers of all its peers, so that kernels can store encoded tiles
+// straight into a peer's receive slot and set flags there. This is what NCCL
+// builds for its P2P transport (src/transport/p2p.cc:199-284) and what COCCL's
+// VMM workspace grants to every peer-accessible device
+// (src/coccl-extend/core/memory/coccl_buffer_vmm.cc:85-102), reduced to the one
+// thing the fused kernels need. Handle exchange itself is left to the caller
+// (torch.distributed store, NCCL all-gather, a socket): handles are plain bytes.
+//
+// Two backends: "ipc" = cudaMalloc + CUDA IPC handles (64 bytes), and "vmm" =
+// cuMemCreate + POSIX file descriptors passed over a Unix-domain socket
+// (see symm_vmm.cc). Both sit behind the same functions.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { COCCL_SYMM_HANDLE_BYTES = 64 };
+
+typedef struct cocclSymmBuffer cocclSymmBuffer;
+
+// Allocate `bytes` of zero-initialised device memory on the current device that peers can map.
+int cocclSymmAlloc(size_t bytes, cocclSymmBuffer** out);
+// Copy this buffer's export handle (COCCL_SYMM_HANDLE_BYTES bytes).
+int cocclSymmExport(const cocclSymmBuffer* buf, void* handle);
+// Map a peer's buffer from its handle; returns the local device pointer of the mapping.
+int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void* handle, void** mapped);
+void* cocclSymmLocalPtr(const cocclSymmBuffer* buf);
+size_t cocclSymmBytes(const cocclSymmBuffer* buf);
+// Unmap every imported peer and free the local allocation.
+int cocclSymmFree(cocclSymmBuffer* buf);
+
+#ifdef __cplusplus
+}
+#endif

@@ -81,13 +81,16 @@ class ParamStore:
         self.dtype, self.device, self.pad_to = dtype, device, pad_to
         self.specs: list[tuple[str, tuple, str, float]] = []
         self.params: dict[str, nn.Parameter] = {}
+        self.replicated: dict[str, bool] = {}
         self.flat_param = None
         self.flat_grad = None
 
-    def add(self, name, shape, init="normal", std=0.02):
+    def add(self, name, shape, init="normal", std=0.02, replicated=False):
+        """replicated=True: identical on every tensor-parallel rank (its gradient is summed over the group)."""
         self.specs.append((name, tuple(shape), init, std))
+        self.replicated[name] = replicated
 
-    def materialise(self, generator=None, grad_dtype=torch.float32):
+    def materialise(self, seed=1234, tp_rank=0, grad_dtype=torch.float32):
         sizes = [math.prod(s) for _, s, _, _ in self.specs]
         # every parameter starts on a 16-byte boundary of both buffers (8 elements)
         offs, total = [], 0
@@ -100,7 +103,12 @@ class ParamStore:
         for (name, shape, init, std), off, n in zip(self.specs, offs, sizes):
             view = self.flat_param[off:off + n].view(shape)
             if init == "normal":
-                view.copy_(torch.randn(shape, generator=generator, device=self.device, dtype=torch.float32) * std)
+                # seeded by name so that a parameter gets the same values whichever pipeline stage holds it;
+                # sharded parameters fold the tensor-parallel rank in, replicated ones must not
+                import zlib
+                gen = torch.Generator(device=self.device)
+                gen.manual_seed(seed + zlib.crc32(name.encode()) + (0 if self.replicated[name] else 7919 * tp_rank))
+                view.copy_(torch.randn(shape, generator=gen, device=self.device, dtype=torch.float32) * std)
             elif init == "ones":
                 view.fill_(1.0)
             p = nn.Parameter(view, requires_grad=True)
@@ -118,18 +126,18 @@ class TransformerLayer(nn.Module):
         self.prefix = f"layers.{idx}."
         pre = self.prefix
         out_std = cfg.init_std / math.sqrt(2.0 * cfg.n_layer)
-        store.add(pre + "ln1.weight", (h,), "ones")
-        store.add(pre + "ln1.bias", (h,), "zeros")
+        store.add(pre + "ln1.weight", (h,), "ones", replicated=True)
+        store.add(pre + "ln1.bias", (h,), "zeros", replicated=True)
         store.add(pre + "qkv.weight", (3 * h // t, h), "normal", cfg.init_std)
         store.add(pre + "qkv.bias", (3 * h // t,), "zeros")
         store.add(pre + "proj.weight", (h, h // t), "normal", out_std)
-        store.add(pre + "proj.bias", (h,), "zeros")
-        store.add(pre + "ln2.weight", (h,), "ones")
-        store.add(pre + "ln2.bias", (h,), "zeros")
+        store.add(pre + "proj.bias", (h,), "zeros", replicated=True)
+        store.add(pre + "ln2.weight", (h,), "ones", replicated=True)
+        store.add(pre + "ln2.bias", (h,), "zeros", replicated=True)
         store.add(pre + "fc1.weight", (f // t, h), "normal", cfg.init_std)
         store.add(pre + "fc1.bias", (f // t,), "zeros")
         store.add(pre + "fc2.weight", (h, f // t), "normal", out_std)
-        store.add(pre + "fc2.bias", (h,), "zeros")
+        store.add(pre + "fc2.bias", (h,), "zeros", replicated=True)
 
     def bind(self, params: dict):
         for short in ("ln1.weight", "ln1.bias", "qkv.weight", "qkv.bias", "proj.weight", "proj.bias", "ln2.weight",
@@ -183,16 +191,13 @@ class GPTStage(nn.Module):
             # its own copy whose gradient is summed with the first stage's (see parallel/pp.py)
             store.add("wte", (vshard, cfg.hidden), "normal", cfg.init_std)
         if pre:
-            store.add("wpe", (cfg.seq_len, cfg.hidden), "normal", cfg.init_std)
+            store.add("wpe", (cfg.seq_len, cfg.hidden), "normal", cfg.init_std, replicated=True)
         make = layer_factory or (lambda c, i, s, t: TransformerLayer(c, i, s, t))
         self.layers = nn.ModuleList([make(cfg, i, store, tp_) for i in range(first_layer, last_layer)])
         if post:
-            store.add("lnf.weight", (cfg.hidden,), "ones")
-            store.add("lnf.bias", (cfg.hidden,), "zeros")
-        # same seed on every TP rank would make shards identical: fold the rank in
-        gen = torch.Generator(device=device)
-        gen.manual_seed(seed + 7919 * tp_.rank + 104729 * first_layer)
-        store.materialise(gen)
+            store.add("lnf.weight", (cfg.hidden,), "ones", replicated=True)
+            store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
+        store.materialise(seed, tp_.rank)
         self.store = store
         for name, p in store.params.items():
             if not name.startswith("layers."):

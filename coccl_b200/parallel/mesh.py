@@ -1,0 +1,84 @@
+"""3-D process mesh (tensor x data x pipeline) and the communicators of each axis.
+
+Rank order follows Megatron: tp fastest, then dp, then pp:
+    rank = tp_rank + tp * (dp_rank + dp * pp_rank)
+so tensor-parallel peers are adjacent GPUs.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .comm import NATIVE, Communicator, Policy
+from .tp import TPContext
+
+
+class Mesh:
+    def __init__(self, tp=1, pp=1, dp=1, device=None, compress=True, policy: Policy | None = None,
+                 sequence_parallel=True):
+        world, rank = dist.get_world_size(), dist.get_rank()
+        assert tp * pp * dp == world, (tp, pp, dp, world)
+        self.tp, self.pp, self.dp, self.device = tp, pp, dp, device
+        self.rank = rank
+        self.tp_rank = rank % tp
+        self.dp_rank = (rank // tp) % dp
+        self.pp_rank = rank // (tp * dp)
+        pol = (policy or Policy()) if compress else NATIVE
+        self.sequence_parallel = sequence_parallel
+
+        def make(groups):
+            mine = None
+            for ranks in groups:
+                g = dist.new_group(ranks) if len(ranks) > 1 else None
+                if rank in ranks:
+                    mine = (g, ranks)
+            return mine
+
+        tp_groups = [[t + tp * (d + dp * p) for t in range(tp)] for p in range(pp) for d in range(dp)]
+        dp_groups = [[t + tp * (d + dp * p) for d in range(dp)] for p in range(pp) for t in range(tp)]
+        pp_groups = [[t + tp * (d + dp * p) for p in range(pp)] for d in range(dp) for t in range(tp)]
+        (self.tp_group, self.tp_ranks) = make(tp_groups)
+        (self.dp_group, self.dp_ranks) = make(dp_groups)
+        (self.pp_group, self.pp_ranks) = make(pp_groups)
+        # first and last pipeline stage share the word embedding
+        emb_groups = [[r[0], r[-1]] for r in pp_groups] if pp > 1 else []
+        self.emb_group = None
+        for ranks in emb_groups:
+            g = dist.new_group(ranks)
+            if rank in ranks:
+                self.emb_group = g
+        self.tp_comm = Communicator(self.tp_group, device, pol, "tp") if tp > 1 else None
+        self.dp_comm = Communicator(self.dp_group, device, pol, "dp") if dp > 1 else None
+        self.pp_comm = Communicator(self.pp_group, device, NATIVE, "pp") if pp > 1 else None
+        self.pp_prev_global = self.pp_ranks[self.pp_rank - 1] if self.pp_rank > 0 else None
+        self.pp_next_global = self.pp_ranks[self.pp_rank + 1] if self.pp_rank < pp - 1 else None
+
+    def tp_context(self):
+        if self.tp_comm is None:
+            return None
+        return TPContext(self.tp_comm, self.sequence_parallel)
+
+    def sync_shared_grads(self, stage):
+        """Sum gradients of parameters that are replicated but see partial data:
+        tensor-parallel replicas (LayerNorm, row-parallel biases, positions) and the word
+        embedding shared by the first and last pipeline stage."""
+        store = stage.store
+        if self.tp_comm is not None:
+            names = [n for n in store.params if store.replicated.get(n)]
+            if not self.sequence_parallel:
+                names = [n for n in names if not (".ln" in n or n.startswith("lnf"))]
+            if names:
+                grads = [store.params[n].main_grad for n in names]
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=self.tp_group)
+                off = 0
+                for g in grads:
+                    g.copy_(flat[off:off + g.numel()].view_as(g))
+                    off += g.numel()
+        if self.emb_group is not None and (stage.pre or stage.post):
+            dist.all_reduce(store.params["wte"].main_grad, group=self.emb_group)
+
+    def close(self):
+        for c in (self.tp_comm, self.dp_comm, self.pp_comm):
+            if c is not None:
+                c.close()

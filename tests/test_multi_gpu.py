@@ -1,0 +1,103 @@
+"""Fused compressed collectives and the parallel trainer on real peer GPUs (one process per GPU, NCCL plumbing).
+Skipped when fewer than two GPUs are visible."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _collectives_worker(rank, world):
+    import torch.distributed as dist
+    from coccl_b200.ops import codec as C
+    from coccl_b200.parallel.comm import Communicator, Policy
+    dev = torch.device("cuda", rank)
+    pol = Policy(threshold_bytes=0, all_reduce_oneshot_max_bytes=1 << 16)
+    comm = Communicator(None, dev, pol, "default")
+    for dtype in (torch.float32, torch.bfloat16):
+        for numel in (world * 4096, world * 300000):
+            torch.manual_seed(100 + rank)
+            x = (torch.randn(numel, device=dev) * 0.01).to(dtype)
+            xs = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(xs, x)
+            cfg = pol.codec_for("default", "reduce_scatter")
+            c = numel // world
+            # reduce-scatter
+            out = torch.empty(c, dtype=dtype, device=dev)
+            comm.reduce_scatter(x, out)
+            ref = sum(C.reference_roundtrip(xq, cfg, world).reshape(world, c)[rank] for xq in xs)
+            bad = ((out.float() - ref.to(dtype).float()).abs() > 1e-5 + 2e-2 * ref.abs().max()).float().mean().item()
+            assert bad < 5e-3, ("rs", dtype, numel, bad)
+            # all-gather
+            out = torch.empty(numel * world, dtype=dtype, device=dev)
+            comm.all_gather(x, out)
+            ref = torch.cat([C.reference_roundtrip(xq, cfg, 1) for xq in xs])
+            bad = ((out.float() - ref.to(dtype).float()).abs() > 1e-5 + 2e-2 * ref.abs().max()).float().mean().item()
+            assert bad < 5e-3, ("ag", dtype, numel, bad)
+            # all-to-all
+            out = torch.empty(numel, dtype=dtype, device=dev)
+            comm.all_to_all(x, out)
+            ref = torch.cat([C.reference_roundtrip(xq, cfg, world).reshape(world, c)[rank] for xq in xs])
+            bad = ((out.float() - ref.to(dtype).float()).abs() > 1e-5 + 2e-2 * ref.abs().max()).float().mean().item()
+            assert bad < 5e-3, ("a2a", dtype, numel, bad)
+            # all-reduce (one-shot for the small size, two-shot for the large one)
+            y = x.clone()
+            comm.all_reduce(y)
+            exact = sum(xq.float() for xq in xs)
+            rel = ((y.float() - exact).norm() / exact.norm()).item()
+            assert rel < 0.3, ("ar", dtype, numel, rel)
+            ys = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(ys, y)
+            assert all(torch.equal(ys[0], t) for t in ys) or numel * x.element_size() <= pol.all_reduce_oneshot_max_bytes
+    assert comm.stats["compressed_calls"] == 16 and comm.stats["native_calls"] == 0
+    assert comm.status() == 0
+    comm.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_collectives_over_peer_memory():
+    run_distributed(_collectives_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
+
+
+def _trainer_worker(rank, world, tp, pp, dp, compress):
+    import torch.distributed as dist
+    from coccl_b200.models.gpt import GPTConfig
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.parallel.comm import Policy
+    from coccl_b200.train import ParallelConfig, Trainer
+    dev = torch.device("cuda", rank)
+    cfg = GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress, policy=Policy(threshold_bytes=0))
+    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=3e-4)
+    g = torch.Generator().manual_seed(5 + mesh.dp_rank)
+    tok = torch.randint(0, cfg.vocab, (8, cfg.seq_len + 1), generator=g).pin_memory()
+    losses = []
+    for _ in range(6):
+        t = tr.train_step(tok).clone()
+        dist.all_reduce(t)
+        losses.append(t.item() / (tp * dp))
+    assert losses[-1] < losses[0] - 0.2, losses
+    assert all(l == l for l in losses)
+    for c in (mesh.tp_comm, mesh.dp_comm):
+        if c is not None:
+            assert c.status() == 0
+            if compress:
+                assert c.stats["compressed_calls"] > 0
+    mesh.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("layout", ["tp2", "dp2", "pp2"])
+def test_trainer_two_gpus_compressed(layout):
+    tp, pp, dp = {"tp2": (2, 1, 1), "dp2": (1, 1, 2), "pp2": (1, 2, 1)}[layout]
+    run_distributed(_trainer_worker, 2, "nccl", (tp, pp, dp, True))
+
+
+@pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
+def test_trainer_3d_eight_gpus():
+    run_distributed(_trainer_worker, 8, "nccl", (2, 2, 2, True))

@@ -1,0 +1,57 @@
+"""3-D parallel trainer on CPU ranks (gloo): every parallel layout must reproduce the single-process loss."""
+import dataclasses
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _cfg():
+    from coccl_b200.models.gpt import GPTConfig
+    return GPTConfig(n_layer=4, hidden=64, n_head=4, ffn=256, seq_len=32, vocab=128, dtype=torch.float32)
+
+
+def _data(cfg, n_seq):
+    g = torch.Generator().manual_seed(7)
+    return torch.randint(0, cfg.vocab, (n_seq, cfg.seq_len + 1), generator=g)
+
+
+def _reference_losses(steps=3, n_seq=8):
+    from coccl_b200.train import Trainer
+    cfg = _cfg()
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2)
+    tok = _data(cfg, n_seq)
+    return tr, [tr.train_step(tok).item() for _ in range(steps)]
+
+
+def _worker(rank, world, tp, pp, dp, ref_losses, ref_params):
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    from coccl_b200.utils.checkpoint import shard_param
+    cfg = _cfg()
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=1e-2)
+    # load the single-process model's initial weights, re-sharded for this rank
+    for name, p in tr.stage.store.params.items():
+        p.data.copy_(shard_param(name, ref_params[name], mesh.tp_rank, tp))
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tok = _data(cfg, 8)
+    per = 8 // dp
+    mine = tok[mesh.dp_rank * per:(mesh.dp_rank + 1) * per]
+    for step, ref in enumerate(ref_losses):
+        loss = tr.train_step(mine)
+        # mean over DP ranks of the per-rank mean == global mean; only the last stage holds the loss
+        t = loss.clone()
+        dist.all_reduce(t)
+        total = t.item() / (tp * dp)
+        assert abs(total - ref) < 2e-3 * abs(ref) + 1e-4, (step, total, ref)
+
+
+@pytest.mark.parametrize("tp,pp,dp", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (2, 2, 2)])
+def test_parallel_layouts_match_single_process(tp, pp, dp):
+    tr, losses = _reference_losses()
+    tr2, _ = _reference_losses(steps=0)
+    params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
+    run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params))
