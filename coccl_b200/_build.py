@@ -109,7 +109,8 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
             name = src.stem.replace("_plugin", "")
             out = LIB / "plugins" / f"lib{name}.so"
             if _needs(src, out, hdr):
-                _run([NVCC, *NVCC_FLAGS, "-shared", src, "-o", out], verbose)
+                _run([NVCC, *NVCC_FLAGS, "-shared", src, "-o", out, f"-L{LIB}", "-lcoccl",
+                      "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."], verbose)
             return out
         with cf.ThreadPoolExecutor(jobs) as ex:
             list(ex.map(plug, sorted(PLUGIN_DIR.glob("*_plugin.cu"))))
