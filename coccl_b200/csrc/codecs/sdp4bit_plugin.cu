@@ -94,6 +94,7 @@ int gridFor(size_t n) { size_t b = (n + 255) / 256; return (int)(b > 148 * 16 ? 
 
 struct Sdp4Bit {
   using Config = Sdp4Config;
+  static constexpr bool kSeesPassthrough = true;  // the delta state is seeded from the raw first round
 
   static Status configure(coccl::ConfigReader& r, Config& c, const coccl::ConfigContext&) {
     static const coccl::EnumEntry<QuantType> qt[] = {{"Symmetric", QuantType::Symmetric}, {"Asymmetric", QuantType::Asymmetric}};

@@ -353,6 +353,7 @@ COCCL_SDK_DETECT(HasEncodedSizeBound, C::encodedSizeBound(std::declval<const Sha
 COCCL_SDK_FLAG(IsFramed, kFramed)
 COCCL_SDK_FLAG(HasFusedSwizzle, kFusedHierarchicalSwizzle)
 COCCL_SDK_FLAG(IsBytewiseLossless, kBytewiseLossless)
+COCCL_SDK_FLAG(SeesPassthrough, kSeesPassthrough)
 #undef COCCL_SDK_FLAG
 }  // namespace detail
 
@@ -370,7 +371,8 @@ struct PluginAdapter {
            (detail::HasDecompressReduceCompress<C>::value ? cocclCompressorCapabilityDecompressReduceCompress : 0) |
            (detail::IsFramed<C>::value ? cocclCompressorCapabilityFramed : 0) |
            (detail::HasFusedSwizzle<C>::value ? cocclCompressorCapabilityFusedHierarchicalSwizzle : 0) |
-           (detail::IsBytewiseLossless<C>::value ? cocclCompressorCapabilityBytewiseLossless : 0);
+           (detail::IsBytewiseLossless<C>::value ? cocclCompressorCapabilityBytewiseLossless : 0) |
+           (detail::SeesPassthrough<C>::value ? cocclCompressorCapabilitySeesPassthrough : 0);
   }
 
   static Status execute(cocclCompressorCall* call) {

@@ -38,6 +38,8 @@ enum cocclCompressorCapability : uint64_t {
   cocclCompressorCapabilityFramed = 1ULL << 4,                    // variable-length frames + metadata
   cocclCompressorCapabilityFusedHierarchicalSwizzle = 1ULL << 5,  // compress applies the rank swizzle itself
   cocclCompressorCapabilityBytewiseLossless = 1ULL << 6,          // any datatype may be routed through it
+  // extension of this runtime (bits the reference does not define are ignored by it):
+  cocclCompressorCapabilitySeesPassthrough = 1ULL << 7,           // decompress wants raw pass-through inputs too
 };
 constexpr uint64_t COCCL_COMPRESSOR_REQUIRED_CAPABILITIES =
     cocclCompressorCapabilityCompress | cocclCompressorCapabilityDecompress;

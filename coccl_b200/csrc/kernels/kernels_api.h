@@ -69,3 +69,15 @@ int cocclkFusedCollective(const cocclkCollArgs* args, int emulatedRanks, int max
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// Staged-pipeline helpers (kernels/reduce_kernels.cu). ncclType uses NCCL's datatype codes.
+int cocclkReduceChunks(const void* in, void* out, long count, int numChunks, long pitchElems, int ncclType,
+                       cudaStream_t stream);
+int cocclkPackSlice(const void* src, void* dst, long sliceBytes, long srcPitchBytes, long srcOffsetBytes, int chunks,
+                    int ranksPerNode, int nNodes, int unpack, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif
