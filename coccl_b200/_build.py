@@ -117,6 +117,11 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
 
     # tools and the host-test runner link against libcoccl.so
     rpath = ["-Wl,-rpath,$ORIGIN", f"-L{LIB}", "-lcoccl"]
+    shim = CSRC / "shim" / "nccl_shim.cc"
+    if shim.exists():
+        out = LIB / "libcoccl_nccl.so"
+        if _needs(shim, out, hdr) or so.stat().st_mtime > out.stat().st_mtime:
+            _run([CXX, *CXX_FLAGS, "-shared", shim, "-o", out, *rpath], verbose)
     if TOOLS_DIR.is_dir():
         for src in sorted(TOOLS_DIR.glob("*.cc")):
             out = LIB / src.stem.replace("_", "-")

@@ -1,0 +1,266 @@
+// Implementation of the public C API (include/coccl/coccl.h).
+// Every collective builds a CallInfo and asks the router first; when the router does not take the
+// call it runs on the native transport (the hook points the reference adds to NCCL's collectives,
+// src/collectives.cc:17-28,49-61,141-153,187-198,211-222,233-243, and to group end, src/group.cc:103-116).
+#include <mutex>
+#include <string>
+
+#include "coccl/coccl.h"
+#include "memory/buffer_manager.h"
+#include "runtime/log.h"
+#include "runtime/nccl_transport.h"
+#include "runtime/primitives.h"
+#include "runtime/runtime.h"
+#include "training/assist.h"
+#include "tuning/autotune.h"
+
+using namespace coccl;
+
+namespace {
+
+struct ApiState {
+  std::mutex mutex;
+  bool started = false;
+  BufferManager* buffers = nullptr;
+  FusedExecutor* executor = nullptr;
+  ModelStore models;
+  AutotuneSelector* selector = nullptr;
+  TrainingAssist* assist = nullptr;
+  int comms = 0;
+};
+ApiState& state() {
+  static ApiState* s = new ApiState();
+  return *s;
+}
+
+thread_local int tlsNativeInGroup = 0;  // native calls issued inside the current group
+thread_local std::string tlsLastError;
+
+Comm* unwrap(ncclComm_t c) { return reinterpret_cast<Comm*>(c); }
+
+// cocclInit: runs once per process when the first communicator is created; later communicators
+// only register themselves (core/runtime/coccl_init.cc:17-31).
+ncclResult_t runtimeStart(Comm* comm) {
+  ApiState& s = state();
+  std::lock_guard<std::mutex> lock(s.mutex);
+  Runtime& rt = globalRuntime();
+  if (!s.started) {
+    s.started = true;
+    const ProcessConfig& pc = processConfig();
+    if (pc.enabled) {
+      std::string err;
+      if (rt.enable(pc.config, comm->nNodes, comm->localRanks, &err) != ncclSuccess) {
+        COCCL_WARN("COCCL disabled for this process: %s", err.c_str());
+      } else {
+        if (logEnabled(kLevelInfo, kLogInit)) {
+          std::string text = formatConfig(pc.config);
+          COCCL_INFO(kLogInit, "effective configuration:\n%s", text.c_str());
+        }
+        BufferOptions bo;
+        bo.legacyBlockBytes = pc.config.legacyBlockBytes;
+        bo.physicalChunkBytes = pc.config.physicalChunkBytes;
+        bo.poolLimitBytes = pc.config.poolLimitBytes;
+        bo.vmm = cudaVmmDriverApi();
+        s.buffers = new BufferManager(bo);
+        s.executor = new FusedExecutor(s.buffers);
+        s.selector = new AutotuneSelector(&s.models);
+        rt.setExecutor(s.executor);
+        rt.setSelector(s.selector);
+        if (pc.config.mode == Mode::Training) {
+          s.assist = new TrainingAssist(ClassifierParams::from(pc.config), pc.config.observationIterations);
+          rt.setRoleOracle(s.assist);
+        }
+      }
+    }
+  }
+  ++s.comms;
+  if (!rt.enabled()) return ncclSuccess;
+  rt.commInit(comm);
+  if (s.buffers) s.buffers->commInit(comm);
+  if (s.assist) s.assist->registerComm(comm);
+  return ncclSuccess;
+}
+
+void runtimeStop(Comm* comm) {
+  ApiState& s = state();
+  std::lock_guard<std::mutex> lock(s.mutex);
+  Runtime& rt = globalRuntime();
+  if (rt.enabled()) {
+    if (s.executor) s.executor->releaseComm(comm);
+    if (s.assist) s.assist->unregisterComm(comm);
+    rt.commDestroy(comm);
+    if (s.buffers) s.buffers->commDestroy(comm);
+  }
+  if (--s.comms == 0 && rt.enabled()) destroyPipelineResources();
+}
+
+ncclResult_t route(CallInfo info) {
+  if (info.comm == nullptr) return ncclInvalidArgument;
+  Runtime& rt = globalRuntime();
+  bool taken = false;
+  ncclResult_t r = rt.enqueueCheck(info, &taken);
+  if (r != ncclSuccess) return r;
+  if (taken) return ncclSuccess;
+  if (rt.groupDepth() > 0) ++tlsNativeInGroup;
+  return rt.replayNative(info);
+}
+
+CallInfo makeInfo(Operation op, Func f, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t red, int peer, ncclComm_t c, cudaStream_t st) {
+  CallInfo i;
+  i.op = op; i.func = f; i.sendbuff = s; i.recvbuff = r; i.count = n; i.datatype = t; i.redOp = red; i.peer = peer;
+  i.comm = unwrap(c); i.stream = st;
+  return i;
+}
+
+ncclResult_t explicitCall(CallInfo info, Algorithm a) {
+  if (info.comm == nullptr) return ncclInvalidArgument;
+  return globalRuntime().enqueueExplicit(info, a);
+}
+
+}  // namespace
+
+extern "C" {
+
+ncclResult_t cocclApiGetUniqueId(ncclUniqueId* id) { return ncclTransport().uniqueId(id); }
+
+ncclResult_t cocclApiCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank) {
+  if (comm == nullptr) return ncclInvalidArgument;
+  Comm* c = nullptr;
+  ncclResult_t r = ncclTransport().initRank(&c, nranks, id, rank);
+  if (r != ncclSuccess) return r;
+  runtimeStart(c);
+  // measured models for the algorithm selector (collective: every rank is here)
+  Runtime& rt = globalRuntime();
+  if (rt.enabled() && rt.config().autotune && nranks > 1) {
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) == cudaSuccess) {
+      if (profileModels(&rt, c, &state().models, s) != ncclSuccess)
+        COCCL_WARN("autotune profiling failed; algorithm selection uses heuristics");
+      cudaStreamDestroy(s);
+    }
+  }
+  *comm = reinterpret_cast<ncclComm_t>(c);
+  return ncclSuccess;
+}
+
+ncclResult_t cocclApiCommDestroy(ncclComm_t comm) {
+  Comm* c = unwrap(comm);
+  if (c == nullptr) return ncclSuccess;
+  runtimeStop(c);
+  c->transport->destroy(c);
+  return ncclSuccess;
+}
+ncclResult_t cocclApiCommFinalize(ncclComm_t comm) {
+  Comm* c = unwrap(comm);
+  if (c == nullptr) return ncclInvalidArgument;
+  return cudaDeviceSynchronize() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+ncclResult_t cocclApiCommAbort(ncclComm_t comm) {
+  Comm* c = unwrap(comm);
+  if (c == nullptr) return ncclSuccess;
+  runtimeStop(c);
+  return ncclTransport().abort(c);
+}
+ncclResult_t cocclApiCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, void*) {
+  Comm* c = unwrap(comm);
+  if (c == nullptr || newcomm == nullptr) return ncclInvalidArgument;
+  Comm* child = nullptr;
+  ncclResult_t r = c->transport->split(c, color, key, &child);
+  if (r != ncclSuccess) return r;
+  runtimeStart(child);
+  *newcomm = reinterpret_cast<ncclComm_t>(child);
+  return ncclSuccess;
+}
+ncclResult_t cocclApiCommCount(ncclComm_t comm, int* n) { if (!comm || !n) return ncclInvalidArgument; *n = unwrap(comm)->nRanks; return ncclSuccess; }
+ncclResult_t cocclApiCommUserRank(ncclComm_t comm, int* r) { if (!comm || !r) return ncclInvalidArgument; *r = unwrap(comm)->rank; return ncclSuccess; }
+ncclResult_t cocclApiCommCuDevice(ncclComm_t comm, int* d) { if (!comm || !d) return ncclInvalidArgument; *d = unwrap(comm)->cudaDev; return ncclSuccess; }
+ncclResult_t cocclApiCommGetAsyncError(ncclComm_t comm, ncclResult_t* e) {
+  if (!comm || !e) return ncclInvalidArgument;
+  return ncclTransport().asyncError(unwrap(comm), e);
+}
+const char* cocclApiGetErrorString(ncclResult_t r) { return ncclTransport().errorString(r); }
+const char* cocclApiGetLastError(ncclComm_t) { return lastWarning(); }
+
+ncclResult_t cocclApiAllReduce(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::AllReduce, Func::Collective, s, r, n, t, op, -1, c, st));
+}
+ncclResult_t cocclApiReduceScatter(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::ReduceScatter, Func::Collective, s, r, n, t, op, -1, c, st));
+}
+ncclResult_t cocclApiAllGather(const void* s, void* r, size_t n, ncclDataType_t t, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::AllGather, Func::Collective, s, r, n, t, ncclSum, -1, c, st));
+}
+ncclResult_t cocclApiAllToAll(const void* s, void* r, size_t n, ncclDataType_t t, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::AllToAll, Func::Collective, s, r, n, t, ncclSum, -1, c, st));
+}
+ncclResult_t cocclApiSend(const void* s, size_t n, ncclDataType_t t, int peer, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::SendRecv, Func::Send, s, nullptr, n, t, ncclSum, peer, c, st));
+}
+ncclResult_t cocclApiRecv(void* r, size_t n, ncclDataType_t t, int peer, ncclComm_t c, cudaStream_t st) {
+  return route(makeInfo(Operation::SendRecv, Func::Recv, nullptr, r, n, t, ncclSum, peer, c, st));
+}
+ncclResult_t cocclApiBroadcast(const void* s, void* r, size_t n, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st) {
+  if (!c) return ncclInvalidArgument;
+  if (globalRuntime().groupDepth() > 0) ++tlsNativeInGroup;
+  return ncclTransport().broadcast(unwrap(c), s, r, n, t, root, st);
+}
+ncclResult_t cocclApiReduce(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t c, cudaStream_t st) {
+  if (!c) return ncclInvalidArgument;
+  if (globalRuntime().groupDepth() > 0) ++tlsNativeInGroup;
+  return ncclTransport().reduce(unwrap(c), s, r, n, t, op, root, st);
+}
+
+ncclResult_t cocclApiGroupStart(void) {
+  Runtime& rt = globalRuntime();
+  if (rt.groupDepth() == 0) tlsNativeInGroup = 0;
+  rt.groupStart();
+  return ncclTransport().groupStart();
+}
+ncclResult_t cocclApiGroupEnd(void) {
+  Runtime& rt = globalRuntime();
+  const bool nativePending = tlsNativeInGroup > 0;
+  ncclResult_t r = rt.groupEnd(&ncclTransport(), nativePending);
+  if (rt.groupDepth() == 0) tlsNativeInGroup = 0;
+  return r;
+}
+
+ncclResult_t cocclAllReduceCompOneShot(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::AllReduce, Func::Collective, s, r, n, t, op, -1, c, st), Algorithm::ArOneShot);
+}
+ncclResult_t cocclAllReduceCompTwoShot(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::AllReduce, Func::Collective, s, r, n, t, op, -1, c, st), Algorithm::ArTwoShot);
+}
+ncclResult_t cocclAllReduceCompTripleShot(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::AllReduce, Func::Collective, s, r, n, t, op, -1, c, st), Algorithm::ArTripleShot);
+}
+ncclResult_t cocclReduceScatterCompOneShot(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::ReduceScatter, Func::Collective, s, r, n, t, op, -1, c, st), Algorithm::RsOneShot);
+}
+ncclResult_t cocclReduceScatterCompTwoShot(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::ReduceScatter, Func::Collective, s, r, n, t, op, -1, c, st), Algorithm::RsTwoShot);
+}
+ncclResult_t cocclAllGatherComp(const void* s, void* r, size_t n, ncclDataType_t t, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::AllGather, Func::Collective, s, r, n, t, ncclSum, -1, c, st), Algorithm::None);
+}
+ncclResult_t cocclAllToAllComp(const void* s, void* r, size_t n, ncclDataType_t t, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::AllToAll, Func::Collective, s, r, n, t, ncclSum, -1, c, st), Algorithm::None);
+}
+ncclResult_t cocclSendComp(const void* s, size_t n, ncclDataType_t t, int peer, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::SendRecv, Func::Send, s, nullptr, n, t, ncclSum, peer, c, st), Algorithm::None);
+}
+ncclResult_t cocclRecvDecomp(void* r, size_t n, ncclDataType_t t, int peer, ncclComm_t c, cudaStream_t st) {
+  return explicitCall(makeInfo(Operation::SendRecv, Func::Recv, nullptr, r, n, t, ncclSum, peer, c, st), Algorithm::None);
+}
+
+void cocclApiGetStats(cocclApiStats* out) {
+  if (out == nullptr) return;
+  RouterStats& s = globalRuntime().stats();
+  out->nativeCalls = s.nativeCalls;
+  out->compressedCalls = s.compressedCalls;
+  out->deferredCalls = s.deferredCalls;
+  out->policyLookups = s.policyLookups;
+  out->fusedCalls = state().executor ? state().executor->fusedCalls : 0;
+  out->stagedCalls = state().executor ? state().executor->stagedCalls : 0;
+}
+
+}  // extern "C"

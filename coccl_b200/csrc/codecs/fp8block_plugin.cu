@@ -93,3 +93,9 @@ struct Fp8Block {
 }  // namespace
 
 COCCL_REGISTER_COMPRESSOR("fp8block", Fp8Block)
+
+extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecQuery(const void* config, int ncclDatatype, void* out) {
+  if (config == nullptr || out == nullptr || dtypeCode((ncclDataType_t)ncclDatatype) < 0) return 0;
+  *static_cast<cocclkCodec*>(out) = codec();
+  return 1;
+}

@@ -235,3 +235,11 @@ struct Sdp4Bit {
 }  // namespace
 
 COCCL_REGISTER_COMPRESSOR("sdp4bit", Sdp4Bit)
+
+// Fused-collective hook: every stateless configuration maps onto the library's tile codec.
+extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecQuery(const void* config, int ncclDatatype, void* out) {
+  const Sdp4Config* c = static_cast<const Sdp4Config*>(config);
+  if (c == nullptr || out == nullptr || c->subAdd || dtypeCode((ncclDataType_t)ncclDatatype) < 0) return 0;
+  *static_cast<cocclkCodec*>(out) = toCodec(*c, (ncclDataType_t)ncclDatatype);
+  return 1;
+}

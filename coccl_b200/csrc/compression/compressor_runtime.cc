@@ -216,6 +216,7 @@ bool CompressorRuntime::loadPlugin(const std::string& name, const std::string& d
   p->path = path;
   p->handle = h;
   p->descriptor = d;
+  p->fusedQuery = reinterpret_cast<int (*)(const void*, int, void*)>(dlsym(h, "cocclFusedCodecQuery"));
   plugins_.push_back(std::move(p));
   COCCL_INFO(kLogInit, "loaded compressor %s (capabilities 0x%llx) from %s", name.c_str(),
              (unsigned long long)d->capabilities, path.c_str());

@@ -34,6 +34,10 @@ struct LoadedPlugin {
   std::string path;
   void* handle = nullptr;                       // dlopen handle (null for built-in / test plugins)
   const cocclCompressorPlugin* descriptor = nullptr;
+  // Optional export `cocclFusedCodecQuery`: lets a codec whose kernels are the library's own tile codecs
+  // describe a parsed configuration as a kernel codec, which unlocks the fused collectives for it.
+  // Returns 1 and fills `out` (a cocclkCodec) when the configuration can run fused for `ncclDatatype`.
+  int (*fusedQuery)(const void* config, int ncclDatatype, void* out) = nullptr;
 };
 
 // Everything the pipeline needs to run one codec for one policy scope.

@@ -1,0 +1,64 @@
+// Public C API: the NCCL-compatible collective calls routed through the compression-aware
+// runtime, plus the explicit compressed calls.
+//
+// libcoccl.so exports every function under a `cocclApi` prefix (cocclApiAllReduce, ...), so that it
+// can live in a process that also holds the real NCCL. libcoccl_nccl.so is a thin shim that exports
+// the same functions under their NCCL names (ncclAllReduce, ..., and the p-prefixed profiling aliases),
+// for linking or preloading in place of libnccl.so. API surface: src/nccl.h.in:84-486 of the reference
+// (NCCL 2.21.5 calls + ncclAllToAll :437 + the nine coccl*Comp* calls :326-442).
+//
+// Environment: COCCL_ENABLE=0|1, COCCL_CONFIG_FILE=<policy.toml>; COCCL_DEBUG / COCCL_DEBUG_SUBSYS.
+#pragma once
+#include "coccl/nccl_compat.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+ncclResult_t cocclApiGetUniqueId(ncclUniqueId* id);
+ncclResult_t cocclApiCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank);
+ncclResult_t cocclApiCommDestroy(ncclComm_t comm);
+ncclResult_t cocclApiCommFinalize(ncclComm_t comm);
+ncclResult_t cocclApiCommAbort(ncclComm_t comm);
+ncclResult_t cocclApiCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, void* config);
+ncclResult_t cocclApiCommCount(ncclComm_t comm, int* count);
+ncclResult_t cocclApiCommUserRank(ncclComm_t comm, int* rank);
+ncclResult_t cocclApiCommCuDevice(ncclComm_t comm, int* device);
+// Also reports a bounded wait of a fused kernel that ran out (ncclRemoteError).
+ncclResult_t cocclApiCommGetAsyncError(ncclComm_t comm, ncclResult_t* asyncError);
+const char* cocclApiGetErrorString(ncclResult_t result);
+const char* cocclApiGetLastError(ncclComm_t comm);
+
+ncclResult_t cocclApiAllReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiAllToAll(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiBroadcast(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclApiGroupStart(void);
+ncclResult_t cocclApiGroupEnd(void);
+
+// Explicit compressed calls: bypass the size threshold, still need an enabled runtime and a policy for
+// the operation; an unsupported datatype runs natively and succeeds; no codec at the scopes the
+// algorithm uses is ncclInvalidUsage.
+ncclResult_t cocclAllReduceCompOneShot(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclAllReduceCompTwoShot(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclAllReduceCompTripleShot(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclReduceScatterCompOneShot(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclReduceScatterCompTwoShot(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclAllGatherComp(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclAllToAllComp(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclSendComp(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t cocclRecvDecomp(void* recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+
+// Router statistics of the process (native / compressed / deferred calls, fused vs staged).
+typedef struct cocclApiStats {
+  unsigned long long nativeCalls, compressedCalls, deferredCalls, policyLookups, fusedCalls, stagedCalls;
+} cocclApiStats;
+void cocclApiGetStats(cocclApiStats* out);
+
+#ifdef __cplusplus
+}
+#endif

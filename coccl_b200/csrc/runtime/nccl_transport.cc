@@ -1,0 +1,199 @@
+// Native transport: the system NCCL, resolved with dlopen so that libcoccl.so neither links
+// against it nor interposes it. Library lookup order: $COCCL_NCCL_LIBRARY, libnccl.so.2, libnccl.so.
+// Used for every call the router leaves native, for pipeline-parallel send/recv, and for the byte
+// exchanges of the staged pipeline.
+#include <dlfcn.h>
+#include <stdlib.h>
+#include <mutex>
+
+#include "runtime/log.h"
+#include "runtime/nccl_transport.h"
+
+namespace coccl {
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(void**, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(void*) = nullptr;
+  ncclResult_t (*CommAbort)(void*) = nullptr;
+  ncclResult_t (*CommSplit)(void*, int, int, void**, void*) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(void*, ncclResult_t*) = nullptr;
+  ncclResult_t (*CommCount)(void*, int*) = nullptr;
+  ncclResult_t (*CommUserRank)(void*, int*) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*Reduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, int, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, void*, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+
+NcclApi& api() {
+  static NcclApi a;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* names[] = {getenv("COCCL_NCCL_LIBRARY"), "libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+      if (n == nullptr || *n == '\0') continue;
+      a.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+      if (a.handle) break;
+    }
+    if (!a.handle) {
+      COCCL_WARN("native transport: no NCCL library found (set COCCL_NCCL_LIBRARY)");
+      return;
+    }
+#define LOAD(name) a.name = reinterpret_cast<decltype(a.name)>(dlsym(a.handle, "nccl" #name))
+    LOAD(GetUniqueId); LOAD(CommInitRank); LOAD(CommDestroy); LOAD(CommAbort); LOAD(CommSplit); LOAD(CommGetAsyncError); LOAD(CommCount); LOAD(CommUserRank);
+    LOAD(AllReduce); LOAD(ReduceScatter); LOAD(AllGather); LOAD(Broadcast); LOAD(Reduce); LOAD(Send); LOAD(Recv);
+    LOAD(GroupStart); LOAD(GroupEnd); LOAD(GetErrorString);
+#undef LOAD
+    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.ReduceScatter && a.AllGather && a.Send &&
+           a.Recv && a.GroupStart && a.GroupEnd;
+  });
+  return a;
+}
+
+int envInt(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : fallback;
+}
+
+}  // namespace
+
+bool NcclTransport::available() { return api().ok; }
+
+ncclResult_t NcclTransport::uniqueId(ncclUniqueId* id) { return api().ok ? api().GetUniqueId(id) : ncclSystemError; }
+
+const char* NcclTransport::errorString(ncclResult_t r) {
+  return (api().ok && api().GetErrorString) ? api().GetErrorString(r) : "NCCL library not loaded";
+}
+
+void NcclTransport::fillTopology(Comm* c) {
+  // One process per GPU; ranks are laid out node-major. LOCAL_WORLD_SIZE (torchrun) or
+  // COCCL_LOCAL_RANKS tells how many ranks share a node; default: all of them.
+  int local = envInt("COCCL_LOCAL_RANKS", envInt("LOCAL_WORLD_SIZE", c->nRanks));
+  if (local <= 0 || local > c->nRanks || c->nRanks % local != 0) local = c->nRanks;
+  c->localRanks = local;
+  c->nNodes = c->nRanks / local;
+  c->node = c->rank / local;
+  c->localRank = c->rank % local;
+  c->uniform = true;
+}
+
+ncclResult_t NcclTransport::initRank(Comm** out, int nRanks, ncclUniqueId id, int rank) {
+  if (!api().ok) return ncclSystemError;
+  void* native = nullptr;
+  ncclResult_t r = api().CommInitRank(&native, nRanks, id, rank);
+  if (r != ncclSuccess) return r;
+  Comm* c = new Comm();
+  c->rank = rank;
+  c->nRanks = nRanks;
+  cudaGetDevice(&c->cudaDev);
+  c->transport = this;
+  c->native = native;
+  static uint64_t nextId = 1;
+  c->id = nextId++;
+  fillTopology(c);
+  *out = c;
+  return ncclSuccess;
+}
+
+ncclResult_t NcclTransport::allGather(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, cudaStream_t st) {
+  return api().AllGather(s, r, n, t, c->native, st);
+}
+ncclResult_t NcclTransport::reduceScatter(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, cudaStream_t st) {
+  return api().ReduceScatter(s, r, n, t, op, c->native, st);
+}
+ncclResult_t NcclTransport::allReduce(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, cudaStream_t st) {
+  return api().AllReduce(s, r, n, t, op, c->native, st);
+}
+ncclResult_t NcclTransport::allToAll(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, cudaStream_t st) {
+  const size_t bytes = n * cocclTypeSize(t);
+  ncclResult_t res = api().GroupStart();
+  for (int p = 0; p < c->nRanks && res == ncclSuccess; ++p) {
+    res = api().Recv(static_cast<char*>(r) + (size_t)p * bytes, n, t, p, c->native, st);
+    if (res == ncclSuccess) res = api().Send(static_cast<const char*>(s) + (size_t)p * bytes, n, t, p, c->native, st);
+  }
+  ncclResult_t e = api().GroupEnd();
+  return res != ncclSuccess ? res : e;
+}
+ncclResult_t NcclTransport::send(Comm* c, const void* b, size_t n, ncclDataType_t t, int peer, cudaStream_t st) {
+  return api().Send(b, n, t, peer, c->native, st);
+}
+ncclResult_t NcclTransport::recv(Comm* c, void* b, size_t n, ncclDataType_t t, int peer, cudaStream_t st) {
+  return api().Recv(b, n, t, peer, c->native, st);
+}
+ncclResult_t NcclTransport::broadcast(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, int root, cudaStream_t st) {
+  return api().Broadcast ? api().Broadcast(s, r, n, t, root, c->native, st) : ncclInternalError;
+}
+ncclResult_t NcclTransport::reduce(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, cudaStream_t st) {
+  return api().Reduce ? api().Reduce(s, r, n, t, op, root, c->native, st) : ncclInternalError;
+}
+ncclResult_t NcclTransport::groupStart() { return api().GroupStart(); }
+ncclResult_t NcclTransport::groupEnd() { return api().GroupEnd(); }
+
+ncclResult_t NcclTransport::p2pBatch(Comm* c, const P2POp* ops, int n, cudaStream_t st) {
+  ncclResult_t res = api().GroupStart();
+  for (int i = 0; i < n && res == ncclSuccess; ++i) {
+    if (ops[i].bytes == 0) continue;
+    res = ops[i].send ? api().Send(ops[i].buffer, ops[i].bytes, ncclUint8, ops[i].peer, c->native, st)
+                      : api().Recv(ops[i].buffer, ops[i].bytes, ncclUint8, ops[i].peer, c->native, st);
+  }
+  ncclResult_t e = api().GroupEnd();
+  return res != ncclSuccess ? res : e;
+}
+
+ncclResult_t NcclTransport::split(Comm* parent, int color, int key, Comm** child) {
+  if (!api().CommSplit) return ncclInternalError;
+  void* native = nullptr;
+  ncclResult_t r = api().CommSplit(parent->native, color, key, &native, nullptr);
+  if (r != ncclSuccess) return r;
+  Comm* c = new Comm();
+  c->transport = this;
+  c->native = native;
+  c->cudaDev = parent->cudaDev;
+  c->id = parent->id * 1000003ull + (uint64_t)(unsigned)color + 1;
+  int count = 1, rank = 0;
+  if (api().CommCount) api().CommCount(native, &count);
+  if (api().CommUserRank) api().CommUserRank(native, &rank);
+  c->nRanks = count;
+  c->rank = rank;
+  // topology of the child is set by the caller (Runtime::hierarchy knows which split this is);
+  // default: treat it as one node
+  c->nNodes = 1; c->localRanks = count; c->localRank = rank; c->node = 0;
+  *child = c;
+  return ncclSuccess;
+}
+
+void NcclTransport::destroy(Comm* c) {
+  if (c == nullptr) return;
+  if (c->native && api().ok) api().CommDestroy(c->native);
+  delete c;
+}
+
+ncclResult_t NcclTransport::asyncError(Comm* c, ncclResult_t* out) {
+  if (api().CommGetAsyncError) return api().CommGetAsyncError(c->native, out);
+  *out = ncclSuccess;
+  return ncclSuccess;
+}
+
+ncclResult_t NcclTransport::abort(Comm* c) {
+  ncclResult_t r = (api().CommAbort && c->native) ? api().CommAbort(c->native) : ncclSuccess;
+  c->native = nullptr;
+  delete c;
+  return r;
+}
+
+NcclTransport& ncclTransport() {
+  static NcclTransport* t = new NcclTransport();
+  return *t;
+}
+
+}  // namespace coccl

@@ -254,11 +254,19 @@ ncclResult_t Runtime::hierarchy(Comm* owner, Comm** intra, Comm** inter) {
     ncclResult_t r = owner->transport->split(owner, owner->rank / owner->localRanks, owner->rank, &owner->intra);
     if (r != ncclSuccess) return r;
     owner->intra->isChild = true;
+    owner->intra->nNodes = 1;
+    owner->intra->localRanks = owner->intra->nRanks;
+    owner->intra->localRank = owner->intra->rank;
+    owner->intra->node = 0;
   }
   if (owner->inter == nullptr) {
     ncclResult_t r = owner->transport->split(owner, owner->rank % owner->localRanks, owner->rank, &owner->inter);
     if (r != ncclSuccess) return r;
     owner->inter->isChild = true;
+    owner->inter->nNodes = owner->inter->nRanks;
+    owner->inter->localRanks = 1;
+    owner->inter->localRank = 0;
+    owner->inter->node = owner->inter->rank;
   }
   if (intra) *intra = owner->intra;
   if (inter) *inter = owner->inter;
