@@ -109,7 +109,7 @@ Runtime::Runtime() {}
 Runtime::~Runtime() { disable(); }
 
 ncclResult_t Runtime::enable(const Config& cfg, int nodes, int devicesPerNode, std::string* error) {
-  disable();
+  if (enabled_) disable();  // plugins registered in-process before the first enable are kept
   std::string err;
   if (!compressors_.initialize(cfg, nodes, devicesPerNode, &err)) {
     if (error) *error = err;

@@ -90,44 +90,43 @@ bool detectIterations(const std::vector<TraceEvent>& events, int target, std::ve
   std::vector<uint64_t> tok(n);
   for (size_t i = 0; i < n; ++i) tok[i] = token(events[i]);
 
-  // smallest period whose last `target` cycles agree; a multiple of the true period would also
-  // match, so the search goes upward and stops at the first hit
-  size_t period = 0;
-  for (size_t p = kMinCycleEvents; p * (size_t)target <= n; ++p) {
-    if (periodMatch(tok, p, (size_t)target, true) < kSampledMatch) continue;
-    if (periodMatch(tok, p, (size_t)target, false) >= kCycleMatch) { period = p; break; }
-  }
-  if (period == 0) return false;
-
-  // how far back does the periodic suffix reach?
-  size_t cycles = (size_t)target;
-  while ((cycles + 1) * period <= n && periodMatch(tok, period, cycles + 1, false) >= kCycleMatch) ++cycles;
-
-  // phase: an iteration boundary is where the trace pauses (optimizer step, data loading). Among the
-  // `period` rotations take the one with the largest boundary-gap / median-gap score; without usable
-  // timestamps, or when no rotation stands out, keep the suffix-aligned phase.
-  size_t shift = 0;
   bool haveTime = false;
   for (size_t i = 1; i < n && !haveTime; ++i) haveTime = events[i].timestampNs != events[0].timestampNs;
-  if (haveTime && cycles >= 2) {
-    const size_t start = n - cycles * period;
+
+  // Candidate periods in ascending order. A candidate must repeat (>= 90 % agreement over the last
+  // `target` cycles) AND, when timestamps are available, show a pause at its boundaries: an inner loop
+  // (layers, micro-batches) repeats too, but only a training iteration ends in a gap (optimizer step,
+  // data loading) of at least twice the median gap.
+  size_t period = 0, cycles = 0, shift = 0;
+  for (size_t p = kMinCycleEvents; p * (size_t)target <= n && period == 0; ++p) {
+    if (periodMatch(tok, p, (size_t)target, true) < kSampledMatch) continue;
+    if (periodMatch(tok, p, (size_t)target, false) < kCycleMatch) continue;
+    size_t c = (size_t)target;
+    while ((c + 1) * p <= n && periodMatch(tok, p, c + 1, false) >= kCycleMatch) ++c;
+    if (!haveTime) { period = p; cycles = c; shift = 0; break; }
+    const size_t start = n - c * p;
     std::vector<double> gaps;
     for (size_t i = start + 1; i < n; ++i) gaps.push_back((double)(events[i].timestampNs - events[i - 1].timestampNs));
     const double med = std::max(1.0, medianOf(gaps));
     double bestScore = 0.0;
-    for (size_t r = 0; r < period; ++r) {
-      std::vector<double> b;
-      for (size_t c = 1; c < cycles; ++c) {
-        const size_t idx = start + c * period - r;  // boundary before event idx
+    size_t bestShift = 0;
+    for (size_t r = 0; r < p; ++r) {
+      std::vector<double> bnd;
+      for (size_t k = 1; k < c; ++k) {
+        const size_t idx = start + k * p - r;  // boundary before event idx
         if (idx <= start || idx >= n) continue;
-        b.push_back((double)(events[idx].timestampNs - events[idx - 1].timestampNs));
+        bnd.push_back((double)(events[idx].timestampNs - events[idx - 1].timestampNs));
       }
-      if (b.empty()) continue;
-      const double score = medianOf(b) / med;
-      if (score > bestScore) { bestScore = score; shift = r; }
+      if (bnd.empty()) continue;
+      const double score = medianOf(bnd) / med;
+      if (score > bestScore) { bestScore = score; bestShift = r; }
     }
-    if (bestScore < kBoundaryGapScore) shift = 0;
+    if (bestScore < kBoundaryGapScore) continue;  // repeats, but is not an iteration
+    // the rotation costs one cycle; keep at least `target`
+    if (bestShift != 0 && c < (size_t)target + 1) continue;
+    period = p; cycles = c; shift = bestShift;
   }
+  if (period == 0) return false;
   // a rotation by `shift` drops the incomplete iteration at the end
   const size_t usable = shift == 0 ? cycles : cycles - 1;
   if (usable < 2) { shift = 0; }
