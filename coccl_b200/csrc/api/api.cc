@@ -2,6 +2,7 @@
 // Every collective builds a CallInfo and asks the router first; when the router does not take the
 // call it runs on the native transport (the hook points the reference adds to NCCL's collectives,
 // src/collectives.cc:17-28,49-61,141-153,187-198,211-222,233-243, and to group end, src/group.cc:103-116).
+#include <algorithm>
 #include <mutex>
 #include <string>
 
@@ -264,3 +265,65 @@ void cocclApiGetStats(cocclApiStats* out) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Single-process codec harness: load one plugin, parse its options, and run
+// compress -> (decompressReduce | decompress) through the same glue the pipeline uses.
+// options: "key=value,key=value". Returns the encoded size through *encodedBytes.
+extern "C" ncclResult_t cocclApiCodecRoundTrip(const char* pluginDir, const char* name, const char* options,
+                                               const void* in, void* out, size_t elements, size_t chunks, int ncclDatatype,
+                                               size_t reduceChunks, int rounds, size_t* encodedBytes, cudaStream_t stream) {
+  if (!pluginDir || !name || !in || !out || chunks == 0 || elements % chunks != 0) return ncclInvalidArgument;
+  Config cfg;
+  cfg.mode = Mode::Normal;
+  cfg.compressors = {name};
+  cfg.libraryPath = pluginDir;
+  ScopeEntry& e = cfg.slots[(size_t)PolicyId::NormalAllGather].scopes[0];
+  e.configured = e.enabled = true;
+  e.compressor = name;
+  std::string opts = options ? options : "";
+  size_t pos = 0;
+  while (pos < opts.size()) {
+    size_t comma = opts.find(',', pos);
+    std::string kv = opts.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos);
+    size_t eq = kv.find('=');
+    if (eq != std::string::npos) e.options[kv.substr(0, eq)] = kv.substr(eq + 1);
+    if (comma == std::string::npos) break;
+    pos = comma + 1;
+  }
+  CompressorRuntime rt;
+  std::string err;
+  if (!rt.initialize(cfg, 1, 1, &err)) {
+    COCCL_WARN("codec harness: %s", err.c_str());
+    return ncclInvalidUsage;
+  }
+  CompressorPolicy* codec = rt.resolve(Role::Normal, Variant::Default, Operation::AllGather, Scope::Default);
+  if (codec == nullptr) return ncclInvalidUsage;
+  const ncclDataType_t dt = (ncclDataType_t)ncclDatatype;
+  const size_t width = cocclTypeSize(dt);
+  size_t bound = 0;
+  ncclResult_t r = encodedSizeBound(codec, cocclCompressorOperationCompress, elements, chunks, dt, &bound);
+  if (r != ncclSuccess) return r;
+  const bool framed = codec->has(cocclCompressorCapabilityFramed);
+  const size_t cap = std::max(bound, elements * width);
+  void* enc = nullptr;
+  void* meta = nullptr;
+  if (cudaMalloc(&enc, cap + 256) != cudaSuccess || cudaMalloc(&meta, chunks * 16 + 256) != cudaSuccess) return ncclUnhandledCudaError;
+  ExecEnv env;
+  env.stream = stream;
+  cudaGetDevice(&env.cudaDev);
+  const size_t red = reduceChunks ? reduceChunks : 1;
+  for (int round = 0; round < (rounds > 0 ? rounds : 1) && r == ncclSuccess; ++round) {
+    cocclCompressorView iv{const_cast<void*>(in), elements * width, elements * width, elements, chunks, dt, nullptr, 0};
+    cocclCompressorView ev{enc, cap, 0, cap, chunks, ncclInt8, framed ? (cocclCompressorFrameMetadata*)meta : nullptr, framed ? bound / chunks : 0};
+    r = compress(codec, iv, &ev, env);
+    if (r != ncclSuccess) break;
+    if (encodedBytes) *encodedBytes = ev.bytes;
+    cocclCompressorView ov{out, elements / red * width, 0, elements / red, chunks / red, dt, nullptr, 0};
+    r = red > 1 ? decompressReduce(codec, ev, &ov, red, env) : decompress(codec, ev, &ov, env);
+  }
+  if (cudaStreamSynchronize(stream) != cudaSuccess && r == ncclSuccess) r = ncclUnhandledCudaError;
+  cudaFree(enc);
+  cudaFree(meta);
+  return r;
+}

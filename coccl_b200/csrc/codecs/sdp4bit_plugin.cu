@@ -116,6 +116,8 @@ struct Sdp4Bit {
     if (s.chunks() == 0 || s.elements() % s.chunks() != 0 || dtypeCode(s.datatype()) < 0) return ncclInvalidUsage;
     cocclkCodec k = toCodec(sc.config<Config>(), s.datatype());
     *bytes = (size_t)cocclkEncodedChunkBytes(&k, (long)s.elementsPerChunk()) * s.chunks();
+    // the delta codec sends its seeding round raw: reserve room for it
+    if (sc.config<Config>().subAdd && *bytes < s.bytes()) *bytes = s.bytes();
     return ncclSuccess;
   }
 
