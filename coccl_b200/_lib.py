@@ -49,6 +49,8 @@ _PROTOS = {
     # gemm_api.h
     "cocclkGemmBf16": (c_int, [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cocclkGemmSetVariant": (None, [c_int]),
+    "cocclkGemmGetVariant": (c_int, []),
     # train_api.h
     "cocclkLayerNormFwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_void_p]),
     "cocclkLayerNormBwdGrid": (c_int, [c_int]),

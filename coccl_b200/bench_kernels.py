@@ -1,0 +1,110 @@
+"""Micro-benchmarks of single kernels (device-timed with CUDA events, L2 flushed between iterations).
+
+    python -m coccl_b200.bench_kernels gemm --m 4096 --n 4096 --k 4096 [--iters 20]
+    python -m coccl_b200.bench_kernels codec --codec sdp4bit --dtype fp32 --mib 1024
+    python -m coccl_b200.bench_kernels collective --op reduce_scatter --ranks 8 --mib 256   (ranks emulated on one GPU)
+
+Also the small, self-ending workloads used for ncu captures (see profiles/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from .ops import codec as C
+from .ops import collective as K
+from .ops import gemm as G
+
+
+def timed(fn, iters=20, warmup=5, flush_mib=256):
+    dev = torch.device("cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(flush_mib << 20, dtype=torch.uint8, device=dev)
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "codec", "collective"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="tn", choices=["tn", "nn", "nt"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--codec", default="sdp4bit", choices=["sdp4bit", "sdp4bit_sr", "mxfp8", "sdp8"])
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--mib", type=int, default=256)
+    ap.add_argument("--op", default="reduce_scatter")
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--variant", default="auto", choices=["auto", "1cta", "2cta"])
+    ap.add_argument("--cublas", action="store_true", help="time torch.matmul (cuBLAS) instead")
+    a = ap.parse_args()
+    dev = torch.device("cuda")
+    dt = torch.float32 if a.dtype == "fp32" else torch.bfloat16
+    cfgs = {"sdp4bit": C.SDP4BIT_G128, "sdp4bit_sr": C.CodecConfig("sdp4bit", 4, 128, False, True, True),
+            "mxfp8": C.MXFP8, "sdp8": C.CodecConfig("sdp4bit", 8, 2048, False, False)}
+    out = {"what": a.what}
+    if a.what == "gemm":
+        G.set_variant(a.variant)
+        x = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16)
+        if a.layout == "nn":      # dgrad-like: B stored [K, N]
+            w = w.t().contiguous().t()
+        if a.layout == "nt":      # wgrad-like: both operands stored with the contraction dimension outermost
+            x = x.t().contiguous().t()
+            w = w.t().contiguous().t()
+        fn = (lambda: x @ w.t()) if a.cublas else (lambda: G.gemm(x, w))
+        ms = timed(fn, a.iters, a.warmup)
+        G.check_errors()
+        out.update(m=a.m, n=a.n, k=a.k, layout=a.layout, impl="cublas" if a.cublas else "tcgen05-" + a.variant, ms=ms,
+                   tflops=2 * a.m * a.n * a.k / ms / 1e9)
+    elif a.what == "codec":
+        cfg = cfgs[a.codec]
+        n = (a.mib << 20) // (4 if dt == torch.float32 else 2)
+        x = (torch.randn(n, device=dev) * 0.01).to(dt)
+        enc = C.encode(x, cfg, 8)
+        t_enc = timed(lambda: C.encode(x, cfg, 8), a.iters, a.warmup)
+        t_dec = timed(lambda: C.decode(enc, cfg, n // 8, dt, 8), a.iters, a.warmup)
+        t_red = timed(lambda: C.decode_reduce(enc, cfg, n // 8, dt, 1, 8), a.iters, a.warmup)
+        raw = x.numel() * x.element_size()
+        out.update(codec=a.codec, dtype=a.dtype, raw_mib=a.mib, encoded_bytes=enc.numel(),
+                   encode_ms=t_enc, encode_gbs_traffic=(raw + enc.numel()) / t_enc / 1e6,
+                   decode_ms=t_dec, decode_gbs_traffic=(raw + enc.numel()) / t_dec / 1e6,
+                   decode_reduce8_ms=t_red, decode_reduce8_gbs_traffic=(raw / 8 + enc.numel()) / t_red / 1e6)
+    else:
+        cfg = cfgs[a.codec]
+        n = a.ranks
+        numel = (a.mib << 20) // (4 if dt == torch.float32 else 2)
+        if a.op == "all_gather":
+            numel //= n
+        numel = numel // (n * 2048) * (n * 2048)
+        xs = [(torch.randn(numel, device=dev) * 0.01).to(dt) for _ in range(n)]
+        st, ep = {}, [0]
+
+        def fn():
+            ep[0] += 1
+            K.emulate_collective(a.op, xs, cfg, state=st, epoch=ep[0])
+        ms = timed(fn, a.iters, a.warmup)
+        out.update(op=a.op, ranks=n, codec=a.codec, dtype=a.dtype, per_rank_input_mib=numel * xs[0].element_size() / 2**20,
+                   ms=ms, status=K.status_codes(st),
+                   note="all ranks emulated on one GPU: time covers the work of all ranks, HBM traffic only")
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+// Epilogue of one 128-row x 256-column fp32 accumulator held in TMEM: each of the four epilogue
+// warps drains its 32 lanes (rows), 32 columns at a time, applies the fused epilogue and stores.
+#pragma once
+#include "gemm_tcgen05.cuh"
+#include "gemm_api.h"
+
+namespace coccl {
+
+struct GemmArgs {
+  void* C;
+  void* Z;
+  const void* bias;
+  int M, N, K;
+  long ldc;
+  int epi;
+  int aMN, bMN;
+  unsigned int* err;
+};
+
+// tbase: TMEM address of (lane quadrant of this warp, first accumulator column); row: the global row
+// this thread owns; colBase: global column of accumulator column 0.
+__device__ __forceinline__ void epilogueStoreTile(const GemmArgs& g, uint32_t tbase, int row, int colBase) {
+  using namespace sm100;
+#pragma unroll 1
+  for (int c = 0; c < 256 / 32; ++c) {
+    uint32_t r[32];
+    tmemLd32x32(tbase + c * 32, r);
+    tmemLdWait();
+    const int col0 = colBase + c * 32;
+    if (row < g.M && col0 < g.N) {
+      const int ncols = min(32, g.N - col0);
+      if (g.epi == GEMM_EPI_F32 || g.epi == GEMM_EPI_F32_ACC) {
+        float* cp = reinterpret_cast<float*>(g.C) + (long)row * g.ldc + col0;
+        for (int j = 0; j < ncols; j += 4) {
+          float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                 __uint_as_float(r[j + 3]));
+          if (g.epi == GEMM_EPI_F32_ACC) {
+            float4 o = *reinterpret_cast<float4*>(cp + j);
+            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+          }
+          *reinterpret_cast<float4*>(cp + j) = v;
+        }
+      } else {
+        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(g.C) + (long)row * g.ldc + col0;
+        __nv_bfloat16* zp = g.Z ? reinterpret_cast<__nv_bfloat16*>(g.Z) + (long)row * g.ldc + col0 : nullptr;
+        const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(g.bias) + col0;
+        for (int j = 0; j < ncols; j += 8) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
+          if (g.epi == GEMM_EPI_BIAS || g.epi == GEMM_EPI_BIAS_GELU) {
+            uint4 bw = __ldg(reinterpret_cast<const uint4*>(bp + j));
+            const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              v[2 * i] += __uint_as_float(w[i] << 16);
+              v[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+          }
+          uint32_t o[4];
+          if (g.epi == GEMM_EPI_BIAS_GELU) {
+            if (zp) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                o[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(zp + j) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = geluTanh(v[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            o[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(cp + j) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace coccl

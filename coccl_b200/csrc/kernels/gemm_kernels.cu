@@ -11,10 +11,10 @@
 // a timeout the kernel raises the error word, drains its outstanding copies,
 // frees TMEM and returns.
 #include "launch_count.h"
-#include "gemm_tcgen05.cuh"
-#include "gemm_api.h"
+#include "gemm_epilogue.cuh"
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 namespace coccl {
 using namespace sm100;
@@ -28,16 +28,6 @@ constexpr int kGemmThreads = 192;
 constexpr int kGroupM = 16;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-struct GemmArgs {
-  void* C;
-  void* Z;
-  const void* bias;
-  int M, N, K;
-  long ldc;
-  int epi;
-  int aMN, bMN;
-  unsigned int* err;
-};
 
 struct __align__(8) GemmBarriers {
   uint64_t full[kStages];
@@ -173,65 +163,7 @@ gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tcFenceAfter();
       const int row = tm * BM + quad * 32 + lane;
       const uint32_t tbase = tmemBase + acc * BN + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmemLd32x32(tbase + c * 32, r);
-        tmemLdWait();
-        const int col0 = tn * BN + c * 32;
-        if (row < g.M && col0 < g.N) {
-          const int ncols = min(32, g.N - col0);
-          if (g.epi == GEMM_EPI_F32 || g.epi == GEMM_EPI_F32_ACC) {
-            float* cp = reinterpret_cast<float*>(g.C) + (long)row * g.ldc + col0;
-            for (int j = 0; j < ncols; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                     __uint_as_float(r[j + 3]));
-              if (g.epi == GEMM_EPI_F32_ACC) {
-                float4 o = *reinterpret_cast<float4*>(cp + j);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *reinterpret_cast<float4*>(cp + j) = v;
-            }
-          } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(g.C) + (long)row * g.ldc + col0;
-            __nv_bfloat16* zp = g.Z ? reinterpret_cast<__nv_bfloat16*>(g.Z) + (long)row * g.ldc + col0 : nullptr;
-            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(g.bias) + col0;
-            for (int j = 0; j < ncols; j += 8) {
-              float v[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
-              if (g.epi == GEMM_EPI_BIAS || g.epi == GEMM_EPI_BIAS_GELU) {
-                uint4 bw = __ldg(reinterpret_cast<const uint4*>(bp + j));
-                const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  v[2 * i] += __uint_as_float(w[i] << 16);
-                  v[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
-                }
-              }
-              uint32_t o[4];
-              if (g.epi == GEMM_EPI_BIAS_GELU) {
-                if (zp) {
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                    o[i] = *reinterpret_cast<uint32_t*>(&h);
-                  }
-                  *reinterpret_cast<uint4*>(zp + j) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = geluTanh(v[i]);
-              }
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                o[i] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(cp + j) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      }
+      epilogueStoreTile(g, tbase, row, tn * BN);
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(&bars->tmemEmpty[acc]);
@@ -290,11 +222,31 @@ static int makeMap(CUtensorMap* m, const void* base, long inner, long outer, lon
   return 0;
 }
 
+int makeBf16TensorMap(CUtensorMap* m, const void* base, long inner, long outer, long ld, int boxInner, int boxOuter) {
+  return makeMap(m, base, inner, outer, ld, boxInner, boxOuter);
+}
+
 }  // namespace coccl
 
 using namespace coccl;
 
-extern "C" int cocclkGemmBf16(const void* A, long lda, int aMN, const void* B, long ldb, int bMN, void* C, long ldc,
+extern "C" int cocclkGemmBf16Pair(const void* A, long lda, int aMN, const void* B, long ldb, int bMN, void* C, long ldc,
+                                  int M, int N, int K, int epi, const void* bias, void* Z, unsigned int* err, int maxCtas,
+                                  cudaStream_t stream);
+
+// 0 = choose by shape, 1 = always the single-CTA kernel, 2 = the CTA-pair kernel whenever the shape allows it.
+// The initial value comes from COCCL_GEMM_VARIANT ("1cta" / "2cta").
+static int gGemmVariant = -1;
+extern "C" void cocclkGemmSetVariant(int v) { gGemmVariant = v; }
+extern "C" int cocclkGemmGetVariant() {
+  if (gGemmVariant < 0) {
+    const char* e = getenv("COCCL_GEMM_VARIANT");
+    gGemmVariant = (e && !strcmp(e, "1cta")) ? 1 : (e && !strcmp(e, "2cta")) ? 2 : 0;
+  }
+  return gGemmVariant;
+}
+
+extern "C" int cocclkGemmBf16Single(const void* A, long lda, int aMN, const void* B, long ldb, int bMN, void* C, long ldc,
                               int M, int N, int K, int epi, const void* bias, void* Z, unsigned int* err,
                               int maxCtas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return -1;
@@ -326,4 +278,16 @@ extern "C" int cocclkGemmBf16(const void* A, long lda, int aMN, const void* B, l
   gemmBf16Kernel<<<grid, kGemmThreads, smemBytes, stream>>>(ta, tb, g);
   cocclkCountLaunches(1);
   return (int)cudaGetLastError();
+}
+
+extern "C" int cocclkGemmBf16(const void* A, long lda, int aMN, const void* B, long ldb, int bMN, void* C, long ldc,
+                              int M, int N, int K, int epi, const void* bias, void* Z, unsigned int* err,
+                              int maxCtas, cudaStream_t stream) {
+  const int v = cocclkGemmGetVariant();
+  // The pair kernel works on 256-row tiles: below that half of each pair would idle. A CTA limit of one
+  // cannot host a pair.
+  const bool pairOk = M > 128 && maxCtas != 1;
+  if (v != 1 && pairOk)
+    return cocclkGemmBf16Pair(A, lda, aMN, B, ldb, bMN, C, ldc, M, N, K, epi, bias, Z, err, maxCtas, stream);
+  return cocclkGemmBf16Single(A, lda, aMN, B, ldb, bMN, C, ldc, M, N, K, epi, bias, Z, err, maxCtas, stream);
 }

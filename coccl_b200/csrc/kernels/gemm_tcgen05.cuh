@@ -148,6 +148,56 @@ __host__ __device__ inline uint32_t makeInstrDescBf16(int M, int N, bool aMN, bo
   return d;
 }
 
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Cluster-window address of the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t mapToCta(uint32_t localAddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(localAddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbarArriveRemote(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ void stSharedRemote(uint32_t clusterAddr, int v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(clusterAddr), "r"(v) : "memory");
+}
+// TMA load issued by either CTA of a pair; the completion bytes are credited to the mbarrier at
+// cluster address `barClusterAddr` (the leader CTA's barrier). No multicast.
+__device__ __forceinline__ void tmaLoad2dPair(void* smemDst, const CUtensorMap* map, uint32_t barClusterAddr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smemAddr(smemDst)), "l"(map), "r"(barClusterAddr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmemAlloc2(uint32_t* smemSlot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(smemSlot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDealloc2(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// One MMA over the CTA pair: M = 256 (128 rows from each CTA), B halves from each CTA.
+__device__ __forceinline__ void umma2(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at the same offset in every CTA of `ctaMask` once all earlier MMAs are done.
+__device__ __forceinline__ void ummaCommit2(uint64_t* bar, uint16_t ctaMask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smemAddr(bar)), "h"(ctaMask) : "memory");
+}
+
 __device__ __forceinline__ float geluTanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * x * (1.f + k1 * x * x);

@@ -31,6 +31,16 @@ def check_errors(device=None) -> None:
             raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} reported error word {v & 0xFFFFFFFF:#x}")
 
 
+def set_variant(name: str) -> None:
+    """Pick the kernel: "auto" (by shape), "1cta" (128x256 tiles, one SM per tile) or "2cta"
+    (256x256 tiles on a CTA pair with tcgen05.mma.cta_group::2)."""
+    _lib.lib().cocclkGemmSetVariant({"auto": 0, "1cta": 1, "2cta": 2}[name])
+
+
+def get_variant() -> str:
+    return ("auto", "1cta", "2cta")[_lib.lib().cocclkGemmGetVariant()]
+
+
 def _operand(t: torch.Tensor, rows: int, k: int):
     """Return (ptr tensor, ld, mn_major) for a 2-D bf16 operand of logical shape [rows, k]."""
     assert t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape == (rows, k), (t.shape, rows, k)

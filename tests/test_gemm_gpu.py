@@ -7,6 +7,13 @@ from coccl_b200.ops import gemm as G
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["1cta", "2cta"], autouse=True)
+def variant(request):
+    G.set_variant(request.param)
+    yield request.param
+    G.set_variant("auto")
+
+
 def _ref(a, b):
     return a.float() @ b.float().t()
 
@@ -17,7 +24,7 @@ def _check(c, ref, k):
     assert err <= 2e-2 * scale + 1e-3, (err, scale)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (4096, 4096, 1024), (300, 264, 72), (1000, 50304 // 8, 128)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (4096, 4096, 1024), (300, 264, 72), (2048, 1024, 4096), (8192, 256, 64), (1000, 50304 // 8, 128)])
 def test_gemm_tn(cuda, M, N, K):
     torch.manual_seed(0)
     a = torch.randn(M, K, device=cuda, dtype=torch.bfloat16)
