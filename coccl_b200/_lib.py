@@ -44,6 +44,7 @@ _PROTOS = {
     "cocclkDecodeReduceEncode": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_long, c_long,
                                          C.POINTER(Codec), c_void_p]),
     "cocclkFlagBytes": (c_long, []),
+    "cocclkTileElems": (c_int, []),
     "cocclkSlotBytes": (c_long, [C.POINTER(Codec), c_long]),
     "cocclkFusedCollective": (c_int, [C.POINTER(CollArgs), c_int, c_int, c_void_p]),
     # gemm_api.h

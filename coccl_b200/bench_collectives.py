@@ -1,0 +1,148 @@
+"""Compressed-collective sweep: effective GB/s against message size, fused kernels vs native NCCL.
+
+Launch with one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 \
+        -m coccl_b200.bench_collectives --min-mib 1 --max-mib 1024 --out sweep.json
+
+Bandwidth follows the reference harness (tests/coccl-tests/doc/PERFORMANCE.md:16-145,
+tests/coccl-tests/src/all_reduce_comp_twoshot.cu:42-48, all_gather_comp.cu:62-68, alltoall_comp.cu:60-66): it is
+computed on UNCOMPRESSED logical bytes, algbw = S / t, busbw = algbw * 2(N-1)/N for all-reduce and
+algbw * (N-1)/N for reduce-scatter / all-gather / all-to-all, with S the all-reduce buffer or the N-rank total.
+Unlike the reference harness (host wall clock) every call is timed with CUDA events on the launching stream;
+a barrier precedes each timed call, L2 is flushed between calls, and the reported time is the median over
+iterations of the maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .ops.codec import MXFP8, SDP4BIT_G128
+from .parallel.comm import NATIVE, Communicator, Policy
+
+CODECS = {"sdp4bit": SDP4BIT_G128, "mxfp8": MXFP8}
+OPS = ("all_reduce", "reduce_scatter", "all_gather", "all_to_all")
+
+
+def _policy(codec) -> Policy:
+    p = Policy(threshold_bytes=0, all_reduce_oneshot_max_bytes=1 << 20)
+    p.codecs = {("default", op): codec for op in OPS}
+    return p
+
+
+def _buffers(op: str, total_bytes: int, dtype, n: int, dev):
+    """(input, output) for a call whose logical size S is `total_bytes`."""
+    es = torch.empty(0, dtype=dtype).element_size()
+    unit = n * 2048
+    if op == "all_reduce":
+        numel = max(unit, total_bytes // es // unit * unit)
+        x = (torch.randn(numel, device=dev) * 1e-2).to(dtype)
+        return x, x
+    per = max(2048, total_bytes // es // n // 2048 * 2048)
+    if op == "reduce_scatter":
+        return (torch.randn(per * n, device=dev) * 1e-2).to(dtype), torch.empty(per, device=dev, dtype=dtype)
+    if op == "all_gather":
+        return (torch.randn(per, device=dev) * 1e-2).to(dtype), torch.empty(per * n, device=dev, dtype=dtype)
+    return (torch.randn(per * n, device=dev) * 1e-2).to(dtype), torch.empty(per * n, device=dev, dtype=dtype)
+
+
+def _call(comm: Communicator, op: str, inp, out):
+    if op == "all_reduce":
+        comm.all_reduce(inp)
+    elif op == "reduce_scatter":
+        comm.reduce_scatter(inp, out)
+    elif op == "all_gather":
+        comm.all_gather(inp, out)
+    else:
+        comm.all_to_all(inp, out)
+
+
+def _time(comm: Communicator, op: str, inp, out, iters: int, warmup: int, flush) -> float:
+    for _ in range(warmup):
+        _call(comm, op, inp, out)
+    torch.cuda.synchronize()
+    tok = torch.zeros(1, device=inp.device)
+    ts = torch.zeros(iters, device=inp.device)
+    evs = []
+    for _ in range(iters):
+        flush.zero_()
+        dist.all_reduce(tok)  # lines the ranks up; not timed
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _call(comm, op, inp, out)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(evs):
+        ts[i] = a.elapsed_time(b)
+    dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+    return float(ts.median().item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-mib", type=float, default=1)
+    ap.add_argument("--max-mib", type=float, default=1024)
+    ap.add_argument("--ops", default=",".join(OPS))
+    ap.add_argument("--codecs", default="sdp4bit,mxfp8")
+    ap.add_argument("--dtypes", default="fp32,bf16")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--out", default="")
+    a = ap.parse_args()
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(1234 + rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    comms = {"native": Communicator(None, dev, NATIVE, "native")}
+    for c in a.codecs.split(","):
+        comms[c] = Communicator(None, dev, _policy(CODECS[c]), c)
+    dts = {"fp32": torch.float32, "bf16": torch.bfloat16}
+    rows = []
+    size = a.min_mib
+    sizes = []
+    while size <= a.max_mib:
+        sizes.append(int(size * (1 << 20)))
+        size *= 2
+    for op in a.ops.split(","):
+        bus = (2.0 * (world - 1) / world) if op == "all_reduce" else ((world - 1) / world)
+        for dn in a.dtypes.split(","):
+            for S in sizes:
+                inp, out = _buffers(op, S, dts[dn], world, dev)
+                logical = (inp.numel() if op != "all_gather" else out.numel()) * inp.element_size()
+                row = {"op": op, "dtype": dn, "bytes": logical, "n_gpus": world}
+                for name, comm in comms.items():
+                    ms = _time(comm, op, inp, out, a.iters, a.warmup, flush)
+                    row[name + "_ms"] = ms
+                    row[name + "_algbw_gbs"] = logical / ms / 1e6
+                    row[name + "_busbw_gbs"] = logical / ms / 1e6 * bus
+                for name in comms:
+                    if name != "native":
+                        row[name + "_speedup"] = row["native_ms"] / row[name + "_ms"]
+                        st = comms[name].status()
+                        if st:
+                            row[name + "_status"] = st
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+                del inp, out
+    if rank == 0 and a.out:
+        with open(a.out, "w") as f:
+            json.dump({"n_gpus": world, "timing": "cuda events, max over ranks, median of %d, L2 flushed" % a.iters,
+                       "rows": rows}, f, indent=1)
+    for c in comms.values():
+        c.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -27,7 +27,7 @@ static int smCount() {
 }
 
 static inline int gridFor(long items) {
-  long cap = (long)smCount() * 8;
+  long cap = (long)smCount() * 4;
   return (int)(items < cap ? (items > 0 ? items : 1) : cap);
 }
 

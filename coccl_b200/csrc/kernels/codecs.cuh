@@ -1,32 +1,35 @@
-// Tile-level codecs shared by the standalone codec kernels, the plugin
-// adapters and the fused collective kernels.
+// Tile-level codecs shared by the standalone codec kernels, the plugin adapters and the fused
+// collective kernels.
 //
-// A CTA of 256 threads owns a tile of 2048 consecutive elements of one chunk;
-// every thread owns 8 consecutive elements in registers. A codec turns those
-// registers into an `Enc` (packed payload words + the group parameters held by
-// the group's first lane) that can be stored to any number of destinations
-// (local scratch or a peer's receive slot), and back.
+// A CTA of 256 threads owns a tile of 8192 consecutive elements of one chunk; every thread owns one
+// aligned run of 32 elements in registers (tile_io.cuh). A codec turns a run into an `Enc` (packed payload
+// words + the parameters of the groups that start in the run) that can be stored to any number of
+// destinations (local scratch or a peer's receive slot), and back.
 //
 // Numerics follow the reference codecs:
-//  * SDP4Bit group quantisation: symmetric scale=(2^(b-1)-1)/absmax, stored
-//    parameter 1/scale, clamp to [-2^(b-1), 2^(b-1)-1]; asymmetric
-//    scale=2^b/(max-min), offset=(max+min)/2
-//    (sdp4bit/includes/quantization_utils.h:126-272), int4 pairs packed
-//    low nibble first (sdp4bit/includes/quantization.h:18-21), optional
-//    unnormalised 32-point Walsh-Hadamard on every aligned run of 32 elements,
-//    undone by a second transform and a 1/32 factor
+//  * SDP4Bit group quantisation: symmetric scale=(2^(b-1)-1)/absmax, stored parameter 1/scale, clamp to
+//    [-2^(b-1), 2^(b-1)-1]; asymmetric scale=2^b/(max-min), offset=(max+min)/2
+//    (sdp4bit/includes/quantization_utils.h:126-272), int4 pairs packed low nibble first
+//    (sdp4bit/includes/quantization.h:18-21), optional unnormalised 32-point Walsh-Hadamard on every
+//    aligned run of 32 elements, undone by a second transform and a 1/32 factor
 //    (sdp4bit/includes/fast_hadamard_transform_common.h:248-264).
-//  * Stochastic rounding uses a counter-based hash keyed by (seed, element)
-//    instead of the reference's per-element curand_init(clock())
-//    (quantization_utils.h:153-174); only the error statistics are comparable.
-//  * MX-FP8 (no counterpart in the reference; TACO, taco/taco.cu:89-295, is its
-//    behavioural model): 32-element blocks, UE8M0 power-of-two scale chosen so
-//    that the block maximum does not saturate, E4M3 payload.
+//  * Stochastic rounding uses a counter-based hash keyed by (seed, element) instead of the reference's
+//    per-element curand_init(clock()) (quantization_utils.h:153-174); only the error statistics are
+//    comparable.
+//  * MX-FP8 (no counterpart in the reference; TACO, taco/taco.cu:89-295, is its behavioural model):
+//    32-element blocks, UE8M0 power-of-two scale chosen so that the block maximum does not saturate, E4M3
+//    payload.
 //
-// Encoded chunk layout (all codecs): [payload bytes of every group][parameters
-// of every group]; the chunk is padded to whole groups in the encoded stream
-// only. Encoded sizes equal the reference's (544 B for 1024 fp32 elements in
-// 4 chunks at g128/q4, 576 B for 16-bit inputs;
+// Float <-> integer conversions go through the mantissa ("magic number") instead of the conversion unit:
+// adding 1.5 * 2^23 to y leaves round-to-nearest-even(y) in the low mantissa bits, and OR-ing an integer
+// n < 2^23 into the bits of 2^23 gives the float 2^23 + n. Packing eight 4-bit values is then one
+// multiply-add chain over the raw float bits: sum(bits_i * 16^i) = C + sum(q_i * 16^i), and adding
+// 0x88888888 turns the signed digits into offset-binary nibbles, which differ from two's-complement nibbles
+// by the XOR 0x88888888.
+//
+// Encoded chunk layout (all codecs): [payload bytes of every group][parameters of every group]; the chunk is
+// padded to whole groups in the encoded stream only. Encoded sizes equal the reference's (544 B for 1024
+// fp32 elements in 4 chunks at g128/q4, 576 B for 16-bit inputs;
 // tests/coccl-tests/src/coccl_fixed_compressor_test.cc:97-105).
 #pragma once
 #include "common.cuh"
@@ -67,43 +70,24 @@ __host__ __device__ inline ChunkLayout makeChunkLayout(const CodecCfg& c, long c
   return L;
 }
 
-struct Enc {
-  uint32_t w[2];  // payload: 4-bit -> w[0]; 8-bit / fp8 -> w[0..1]
-  float p0, p1;   // group parameters (valid on the group's first lane)
-};
-
 // ------------------------------------------------------------------ helpers
-__device__ __forceinline__ void hadamard8(float (&v)[8]) {
+// Unnormalised 32-point Walsh-Hadamard transform of one run, entirely in registers.
+__device__ __forceinline__ void hadamard32(float (&v)[32]) {
 #pragma unroll
-  for (int s = 1; s < 8; s <<= 1) {
+  for (int s = 1; s < 32; s <<= 1) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 32; ++i) {
       if ((i & s) == 0) {
-        float a = v[i], b = v[i | s];
+        const float a = v[i], b = v[i | s];
         v[i] = a + b;
         v[i | s] = a - b;
       }
     }
   }
 }
-// 32-point unnormalised WHT over 4 adjacent lanes x 8 registers.
-__device__ __forceinline__ void hadamard32(float (&v)[8]) {
-  hadamard8(v);
-  const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int s = 1; s <= 2; s <<= 1) {
-    const bool upper = (lane & s) != 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float o = __shfl_xor_sync(0xffffffffu, v[i], s);
-      v[i] = upper ? (o - v[i]) : (v[i] + o);
-    }
-  }
-}
 
-// Reduce over the `lpg` consecutive threads that share a group (lpg = group/8,
-// a power of two <= 256). For lpg > 32 the CTA cooperates through `sm` (needs
-// 2*8 floats) and every thread of the CTA must call this.
+// Reduce over the `lpg` consecutive threads that share a group (lpg = group/32, a power of two <= 64).
+// For lpg > 32 the CTA cooperates through `sm` (8 floats) and every thread of the CTA must call this.
 struct MaxOp { static __device__ __forceinline__ float f(float a, float b) { return fmaxf(a, b); } };
 struct MinOp { static __device__ __forceinline__ float f(float a, float b) { return fminf(a, b); } };
 
@@ -116,143 +100,261 @@ __device__ __forceinline__ float groupReduce(float x, int lpg, float* sm) {
     __syncthreads();
     if ((threadIdx.x & 31) == 0) sm[warp] = x;
     __syncthreads();
-    const int wpg = lpg >> 5;
-    const int base = warp / wpg * wpg;
-    x = sm[base];
-    for (int i = 1; i < wpg; ++i) x = Op::f(x, sm[base + i]);
+    x = Op::f(sm[warp & ~1], sm[warp | 1]);
   }
   return x;
 }
 
-__device__ __forceinline__ int quantRound(float y, bool stochastic, uint32_t word, int k) {
-  if (stochastic) return (int)floorf(y + rngUnit(word, k));
-  return __float2int_rn(y);
+constexpr float kRoundMagic = 12582912.f;          // 1.5 * 2^23
+constexpr uint32_t kRoundMagicBits = 0x4B400000u;  // its bit pattern
+constexpr uint32_t kIntMagicBits = 0x4B000000u;    // 2^23: OR an integer < 2^23 into the mantissa
+
+// (u - 0.5) for the k-th byte of a random word, u = (byte + 0.5) / 256, built in the mantissa of [1, 2).
+__device__ __forceinline__ float rngCentered(uint32_t word, int k) {
+  const uint32_t b = (word >> (8 * k)) & 0xffu;
+  return __uint_as_float(0x3F800000u | (b << 15)) - 1.498046875f;
 }
 
 // ------------------------------------------------------------------ SDP4Bit
-template <int BITS, bool ASYM, bool HAD>
+// SMALLG: groups of 8 or 16 elements (several per run, no rotation); otherwise group >= 32.
+template <int BITS, bool ASYM, bool HAD, bool SMALLG>
 struct SdpCodec {
+  static_assert(!(HAD && SMALLG), "the rotation needs groups of at least one run");
   static constexpr int kBits = BITS;
-  static constexpr int kWords = BITS / 4;  // u32 payload words per thread
+  static constexpr int kWords = BITS;          // payload words per run
+  static constexpr int kPerWord = 32 / BITS;   // elements per payload word
+  static constexpr int kParams = SMALLG ? 4 : 1;
   static constexpr bool kRotated = HAD;
+  static constexpr uint32_t kSignBits = BITS == 4 ? 0x88888888u : 0x80808080u;
+  static constexpr uint32_t kPackFix = kSignBits - kRoundMagicBits * (BITS == 4 ? 0x11111111u : 0x01010101u);
 
-  // v: 8 values of this thread (zero beyond the chunk). elem = chunk-relative
-  // index of v[0]. `rotate=false` when v is already in the rotated domain.
-  // rngElem = message-wide element index of v[0] (keys the rounding RNG).
-  static __device__ __forceinline__ Enc encode(float (&v)[8], const CodecCfg& c, long elem,
-                                               bool rotate, float* sm, uint64_t rngElem) {
-    if (HAD && rotate) hadamard32(v);
-    const int lpg = c.group >> 3;
-    Enc e;
-    float scale, offset = 0.f;
+  struct Enc {
+    uint32_t w[kWords];
+    float p0[kParams], p1[kParams];
+  };
+
+  template <bool ST>
+  static __device__ __forceinline__ void quantise(const float (&v)[32], const float (&scale)[kParams],
+                                                  const float (&offset)[kParams], const CodecCfg& c,
+                                                  uint64_t rngElem, Enc& e) {
+    constexpr float qlo = (float)(-(1 << (BITS - 1))), qhi = (float)((1 << (BITS - 1)) - 1);
+    uint32_t rw[8];
+    if (ST) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) rw[k] = rngWord(c.seed, (rngElem >> 2) + k);
+    }
+#pragma unroll
+    for (int k = 0; k < kWords; ++k) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int i = kPerWord - 1; i >= 0; --i) {
+        const int idx = k * kPerWord + i;
+        const int pj = SMALLG ? idx / 8 : 0;
+        // the product is rounded to fp32 before the rounding to an integer, as in the reference (no fma)
+        float y = __fmul_rn(ASYM ? v[idx] - offset[pj] : v[idx], scale[pj]);
+        if (ST) y = __fadd_rn(y, rngCentered(rw[idx >> 2], idx & 3));
+        // symmetric: |y| <= 2^(b-1)-1 by construction; asymmetric: the top of the range rounds to 2^(b-1)
+        if (ASYM) y = fminf(fmaxf(y, qlo), qhi);
+        const uint32_t b = __float_as_uint(__fadd_rn(y, kRoundMagic));
+        acc = (i == kPerWord - 1) ? b : acc * (1u << BITS) + b;
+      }
+      e.w[k] = (acc + kPackFix) ^ kSignBits;
+    }
+  }
+
+  static __device__ __forceinline__ void params(float mx, float mn, float& scale, float& offset, float& p0, float& p1) {
     constexpr float qmax = (float)((1 << (BITS - 1)) - 1);
-    constexpr int qlo = -(1 << (BITS - 1)), qhi = (1 << (BITS - 1)) - 1;
     if (!ASYM) {
-      float m = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
-      m = groupReduce<MaxOp>(m, lpg, sm);
-      scale = (m == 0.f) ? 1.f : qmax / m;
-      e.p0 = 1.f / scale;
-      e.p1 = 0.f;
+      scale = (mx == 0.f) ? 1.f : qmax / mx;
+      offset = 0.f;
     } else {
-      float mx = v[0], mn = v[0];
-#pragma unroll
-      for (int i = 1; i < 8; ++i) { mx = fmaxf(mx, v[i]); mn = fminf(mn, v[i]); }
-      mx = groupReduce<MaxOp>(mx, lpg, sm);
-      mn = groupReduce<MinOp>(mn, lpg, sm + 8);
       const float range = mx - mn;
       scale = (range == 0.f) ? 1.f : (float)(1 << BITS) / range;
       offset = 0.5f * (mx + mn);
-      e.p0 = 1.f / scale;
-      e.p1 = offset;
     }
-    int q[8];
-    const bool st = c.stochastic != 0;
-    uint32_t r0 = 0, r1 = 0;
-    if (st) {
-      r0 = rngWord(c.seed, rngElem >> 2);
-      r1 = rngWord(c.seed, (rngElem >> 2) + 1);
-    }
+    p0 = 1.f / scale;
+    p1 = offset;
+  }
+
+  // v: the run of this thread (zero beyond the chunk). `rotate=false` when v is already in the rotated
+  // domain. rngElem = message-wide element index of v[0] (keys the rounding RNG).
+  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& c, bool rotate, float* sm,
+                                               uint64_t rngElem) {
+    if (HAD && rotate) hadamard32(v);
+    Enc e;
+    float scale[kParams], offset[kParams];
+    if (!SMALLG) {
+      float mx, mn = 0.f;
+      if (!ASYM) {
+        mx = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int t = quantRound((v[i] - offset) * scale, st, i < 4 ? r0 : r1, i & 3);
-      q[i] = max(qlo, min(qhi, t));
-    }
-    if (BITS == 4) {
-      uint32_t w = 0;
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[i]));
+        mx = groupReduce<MaxOp>(mx, c.group >> 5, sm);
+      } else {
+        mx = v[0]; mn = v[0];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) w |= ((uint32_t)(q[i] & 0xf)) << (4 * i);
-      e.w[0] = w; e.w[1] = 0;
+        for (int i = 1; i < 32; ++i) { mx = fmaxf(mx, v[i]); mn = fminf(mn, v[i]); }
+        mx = groupReduce<MaxOp>(mx, c.group >> 5, sm);
+        mn = groupReduce<MinOp>(mn, c.group >> 5, sm);
+      }
+      params(mx, mn, scale[0], offset[0], e.p0[0], e.p1[0]);
     } else {
-      e.w[0] = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-      e.w[1] = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+      float mx[4], mn[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!ASYM) {
+          mx[j] = 0.f; mn[j] = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mx[j] = fmaxf(mx[j], fabsf(v[8 * j + i]));
+        } else {
+          mx[j] = v[8 * j]; mn[j] = v[8 * j];
+#pragma unroll
+          for (int i = 1; i < 8; ++i) { mx[j] = fmaxf(mx[j], v[8 * j + i]); mn[j] = fminf(mn[j], v[8 * j + i]); }
+        }
+      }
+      if (c.group == 16) {
+#pragma unroll
+        for (int j = 0; j < 4; j += 2) {
+          mx[j] = mx[j + 1] = fmaxf(mx[j], mx[j + 1]);
+          mn[j] = mn[j + 1] = fminf(mn[j], mn[j + 1]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kParams; ++j) params(mx[j], mn[j], scale[j], offset[j], e.p0[j], e.p1[j]);
     }
+    if (c.stochastic) quantise<true>(v, scale, offset, c, rngElem, e);
+    else quantise<false>(v, scale, offset, c, rngElem, e);
     return e;
   }
 
+  // elem = chunk-relative index of the run's first element
   static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L,
                                                const CodecCfg& c, long elem) {
-    if (elem >= L.groups * c.group) return;
-    uint32_t* pw = reinterpret_cast<uint32_t*>(chunk + elem * BITS / 8);
-    pw[0] = e.w[0];
-    if (BITS == 8) pw[1] = e.w[1];
-    if ((elem & (c.group - 1)) == 0) {
-      float* pp = reinterpret_cast<float*>(chunk + L.payloadBytes + (elem / c.group) * c.paramBytes);
-      pp[0] = e.p0;
-      if (c.paramBytes == 8) pp[1] = e.p1;
-    }
-  }
-
-  // Dequantise 8 values (still rotated when HAD) and ADD them into acc.
-  static __device__ __forceinline__ void loadAdd(const uint8_t* chunk, const ChunkLayout& L,
-                                                 const CodecCfg& c, long elem, float (&acc)[8]) {
-    if (elem >= L.groups * c.group) return;
-    const uint32_t* pw = reinterpret_cast<const uint32_t*>(chunk + elem * BITS / 8);
-    const float* pp = reinterpret_cast<const float*>(chunk + L.payloadBytes + (elem / c.group) * c.paramBytes);
-    // __ldcg: the bytes may have been written by a peer GPU during this launch
-    const float inv = __ldcg(pp);
-    const float off = ASYM ? __ldcg(pp + 1) : 0.f;
-    if (BITS == 4) {
-      const uint32_t w = __ldcg(pw);
+    const int gs = 31 - __clz(c.group);  // the group size is a power of two
+    const long padded = L.groups << gs;
+    if (elem >= padded) return;
+    uint8_t* pw = chunk + elem * BITS / 8;
+    if (elem + 32 <= padded && aligned16(pw)) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        int q = (int)(w << (28 - 4 * i)) >> 28;
-        acc[i] += (float)q * inv + off;
+      for (int q = 0; q < kWords / 4; ++q)
+        reinterpret_cast<uint4*>(pw)[q] = make_uint4(e.w[4 * q], e.w[4 * q + 1], e.w[4 * q + 2], e.w[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < kWords; ++k)
+        if (elem + k * kPerWord < padded) reinterpret_cast<uint32_t*>(pw)[k] = e.w[k];
+    }
+    uint8_t* pbase = chunk + L.payloadBytes;
+    if (!SMALLG) {
+      if ((elem & (c.group - 1)) == 0) {
+        float* pp = reinterpret_cast<float*>(pbase + (elem >> gs) * c.paramBytes);
+        pp[0] = e.p0[0];
+        if (c.paramBytes == 8) pp[1] = e.p1[0];
       }
     } else {
-      const uint32_t w0 = __ldcg(pw), w1 = __ldcg(pw + 1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[i] += (float)((int)(w0 << (24 - 8 * i)) >> 24) * inv + off;
-        acc[4 + i] += (float)((int)(w1 << (24 - 8 * i)) >> 24) * inv + off;
+      for (int j = 0; j < 4; ++j) {
+        const long ge = elem + 8 * j;
+        if ((ge & (c.group - 1)) == 0 && ge < padded) {
+          float* pp = reinterpret_cast<float*>(pbase + (ge >> gs) * c.paramBytes);
+          pp[0] = e.p0[j];
+          if (c.paramBytes == 8) pp[1] = e.p1[j];
+        }
       }
     }
   }
 
-  // Leave the rotated domain (after any reduction: the transform is linear).
-  static __device__ __forceinline__ void finish(float (&v)[8]) {
-    if (HAD) {
-      hadamard32(v);
+  // Encoded run as fetched from memory; `accumulate` dequantises it. Splitting the two lets a reduction
+  // keep the loads of several sources in flight.
+  struct Raw {
+    uint32_t w[kWords];
+    float inv[kParams], off[kParams];
+    bool valid;
+  };
+  static constexpr int kBatch = 2;
+
+  // `mul` scales the dequantised values (a power of two: exact); decoders that leave the rotated domain
+  // right afterwards pass 1/32 here instead of multiplying all 32 outputs.
+  static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c, long elem,
+                                              float mul) {
+    Raw r;
+    const int gs = 31 - __clz(c.group);
+    const long padded = L.groups << gs;
+    r.valid = elem < padded;
+    if (!r.valid) return r;
+    // __ldcg: the bytes may have been written by a peer GPU during this launch
+    const uint8_t* pw = chunk + elem * BITS / 8;
+    if (elem + 32 <= padded && aligned16(pw)) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] *= (1.f / 32.f);
+      for (int q = 0; q < kWords / 4; ++q) {
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(pw) + q);
+        r.w[4 * q] = t.x; r.w[4 * q + 1] = t.y; r.w[4 * q + 2] = t.z; r.w[4 * q + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < kWords; ++k)
+        r.w[k] = (elem + k * kPerWord < padded) ? __ldcg(reinterpret_cast<const uint32_t*>(pw) + k) : 0u;
     }
+    const uint8_t* pbase = chunk + L.payloadBytes;
+#pragma unroll
+    for (int j = 0; j < kParams; ++j) {
+      long g = (elem + 8 * j) >> gs;
+      if (g >= L.groups) g = L.groups - 1;
+      const float* pp = reinterpret_cast<const float*>(pbase + g * c.paramBytes);
+      r.inv[j] = __ldcg(pp) * mul;
+      r.off[j] = ASYM ? __ldcg(pp + 1) * mul : 0.f;
+    }
+    return r;
+  }
+
+  // Dequantise the run (still rotated when HAD) and ADD it into acc.
+  static __device__ __forceinline__ void accumulate(const Raw& r, float (&acc)[32]) {
+    if (!r.valid) return;
+#pragma unroll
+    for (int k = 0; k < kWords; ++k) {
+      const uint32_t x = r.w[k] ^ kSignBits;  // offset-binary digits: q + 2^(b-1)
+#pragma unroll
+      for (int i = 0; i < kPerWord; ++i) {
+        const int idx = k * kPerWord + i;
+        const int pj = SMALLG ? idx / 8 : 0;
+        float f;
+        if (BITS == 4) {
+          const uint32_t m = ((x >> (4 * i)) & 0xfu) | kIntMagicBits;
+          f = __uint_as_float(m) - 8388616.f;  // 2^23 + 8
+        } else {
+          const uint32_t m = __byte_perm(x, kIntMagicBits, 0x7650 + i);
+          f = __uint_as_float(m) - 8388736.f;  // 2^23 + 128
+        }
+        if (ASYM) acc[idx] += fmaf(f, r.inv[pj], r.off[pj]);
+        else acc[idx] = fmaf(f, r.inv[pj], acc[idx]);
+      }
+    }
+  }
+
+  // Leave the rotated domain (after any reduction: the transform is linear). The 1/32 of the inverse
+  // transform was applied by fetch (kFinishScale).
+  static constexpr float kFinishScale = HAD ? 1.f / 32.f : 1.f;
+  static __device__ __forceinline__ void finish(float (&v)[32]) {
+    if (HAD) hadamard32(v);
   }
 };
 
 // ------------------------------------------------------------------ MX-FP8
+// One 32-element block per run: the scale needs no cross-lane traffic at all.
 struct MxFp8Codec {
   static constexpr int kBits = 8;
-  static constexpr int kWords = 2;
+  static constexpr int kWords = 8;
   static constexpr bool kRotated = false;
 
-  static __device__ __forceinline__ Enc encode(float (&v)[8], const CodecCfg& c, long elem,
-                                               bool /*rotate*/, float* /*sm*/, uint64_t /*rngElem*/) {
+  struct Enc {
+    uint32_t w[8];
+    uint32_t scaleByte;
+  };
+
+  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& /*c*/, bool /*rotate*/, float* /*sm*/,
+                                               uint64_t /*rngElem*/) {
     float m = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(v[i]));
     // UE8M0: smallest power of two s with m / s <= 448.
     int biased = 0;
     if (m > 0.f && m < INFINITY) {
@@ -264,82 +366,114 @@ struct MxFp8Codec {
     }
     // 2^-(biased-127) as a float: exponent field 254 - biased (denormal-safe for biased in [1,253]).
     const int invExp = 254 - biased;
-    const float inv = invExp > 0 ? __uint_as_float((uint32_t)invExp << 23)
-                                 : __uint_as_float(0x00400000u);  // 2^-127
+    const float inv = invExp > 0 ? __uint_as_float((uint32_t)invExp << 23) : __uint_as_float(0x00400000u);  // 2^-127
     Enc e;
-    uint16_t h[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      h[i] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * i] * inv, v[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-    e.w[0] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-    e.w[1] = (uint32_t)h[2] | ((uint32_t)h[3] << 16);
-    e.p0 = __uint_as_float((uint32_t)biased);  // carries the scale byte
-    e.p1 = 0.f;
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * k] * inv, v[4 * k + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * k + 2] * inv, v[4 * k + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      e.w[k] = lo | (hi << 16);
+    }
+    e.scaleByte = (uint32_t)biased;
     return e;
   }
 
-  // Every lane of the warp must call this (it shuffles), valid or not.
-  static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L,
-                                               const CodecCfg& c, long elem) {
-    const bool valid = elem < L.groups * 32;
-    if (valid) {
-      uint32_t* pw = reinterpret_cast<uint32_t*>(chunk + elem);
-      pw[0] = e.w[0];
-      pw[1] = e.w[1];
+  static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/,
+                                               long elem) {
+    if (elem >= L.groups * 32) return;
+    uint8_t* pw = chunk + elem;
+    if (aligned16(pw)) {
+      reinterpret_cast<uint4*>(pw)[0] = make_uint4(e.w[0], e.w[1], e.w[2], e.w[3]);
+      reinterpret_cast<uint4*>(pw)[1] = make_uint4(e.w[4], e.w[5], e.w[6], e.w[7]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) reinterpret_cast<uint32_t*>(pw)[k] = e.w[k];
     }
-    // Gather the 8 scale bytes of this warp's 8 blocks (lanes 0,4,..,28) into
-    // lane 0 and write them with one 8-byte-aligned store when possible.
-    uint32_t b = __float_as_uint(e.p0) & 0xffu;
-    uint32_t t = b | (__shfl_down_sync(0xffffffffu, b, 4) << 8);
-    t = t | (__shfl_down_sync(0xffffffffu, t, 8) << 16);
-    uint32_t hi = __shfl_down_sync(0xffffffffu, t, 16);
-    if ((threadIdx.x & 31) == 0 && valid) {
-      uint8_t* ps = chunk + L.payloadBytes + elem / 32;
-      const long left = L.groups - elem / 32;
-      if (left >= 8 && ((reinterpret_cast<uintptr_t>(ps) & 7u) == 0)) {
-        *reinterpret_cast<uint2*>(ps) = make_uint2(t, hi);
-      } else {
-        for (int i = 0; i < 8 && i < left; ++i) ps[i] = (uint8_t)((i < 4 ? t >> (8 * i) : hi >> (8 * (i - 4))) & 0xff);
+    chunk[L.payloadBytes + elem / 32] = (uint8_t)e.scaleByte;
+  }
+
+  struct Raw {
+    uint32_t w[8];
+    uint32_t biased;
+    bool valid;
+  };
+  static constexpr int kBatch = 2;
+
+  static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/, long elem,
+                                              float /*mul*/) {
+    Raw r;
+    r.valid = elem < L.groups * 32;
+    if (!r.valid) return r;
+    const uint8_t* pw = chunk + elem;
+    if (aligned16(pw)) {
+      const uint4 a = __ldcg(reinterpret_cast<const uint4*>(pw)), b = __ldcg(reinterpret_cast<const uint4*>(pw) + 1);
+      r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r.w[k] = __ldcg(reinterpret_cast<const uint32_t*>(pw) + k);
+    }
+    r.biased = __ldcg(chunk + L.payloadBytes + elem / 32);
+    return r;
+  }
+
+  static __device__ __forceinline__ void accumulate(const Raw& r, float (&acc)[32]) {
+    if (!r.valid) return;
+    const float scale = r.biased > 0 ? __uint_as_float(r.biased << 23) : __uint_as_float(0x00400000u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint16_t pair = (uint16_t)(r.w[k] >> (16 * h));
+        __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+        acc[4 * k + 2 * h] = fmaf(f.x, scale, acc[4 * k + 2 * h]);
+        acc[4 * k + 2 * h + 1] = fmaf(f.y, scale, acc[4 * k + 2 * h + 1]);
       }
     }
   }
 
-  static __device__ __forceinline__ void loadAdd(const uint8_t* chunk, const ChunkLayout& L,
-                                                 const CodecCfg& c, long elem, float (&acc)[8]) {
-    if (elem >= L.groups * 32) return;
-    const uint32_t* pw = reinterpret_cast<const uint32_t*>(chunk + elem);
-    const uint32_t w[2] = {__ldcg(pw), __ldcg(pw + 1)};
-    const uint32_t biased = __ldcg(chunk + L.payloadBytes + elem / 32);
-    const float scale = biased > 0 ? __uint_as_float(biased << 23) : __uint_as_float(0x00400000u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint16_t pair = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
-      __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
-      float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
-      acc[2 * i] += f.x * scale;
-      acc[2 * i + 1] += f.y * scale;
-    }
-  }
-
-  static __device__ __forceinline__ void finish(float (&)[8]) {}
+  static constexpr float kFinishScale = 1.f;
+  static __device__ __forceinline__ void finish(float (&)[32]) {}
 };
 
-// Dispatch a generic lambda on the runtime codec configuration. The functor
-// receives a codec type tag; unsupported configurations return false.
+// acc += mul * sum over n encoded copies of the run at `elem`, copy i at base + i * stride. The loads of
+// Codec::kBatch copies are issued before any of them is unpacked.
+template <class Codec>
+__device__ __forceinline__ void decodeSum(const uint8_t* base, long stride, int n, const ChunkLayout& L,
+                                          const CodecCfg& c, long elem, float mul, float (&acc)[32]) {
+  for (int q = 0; q < n; q += Codec::kBatch) {
+    typename Codec::Raw r[Codec::kBatch];
+#pragma unroll
+    for (int j = 0; j < Codec::kBatch; ++j) {
+      if (q + j < n) r[j] = Codec::fetch(base + (long)(q + j) * stride, L, c, elem, mul);
+      else r[j].valid = false;
+    }
+#pragma unroll
+    for (int j = 0; j < Codec::kBatch; ++j) Codec::accumulate(r[j], acc);
+  }
+}
+
+// Dispatch a generic lambda on the runtime codec configuration. The functor receives a codec type tag;
+// unsupported configurations return false.
 template <class F>
 inline bool dispatchCodec(const CodecCfg& c, F&& f) {
   if (c.kind == kCodecMxfp8) { f(MxFp8Codec{}); return true; }
   if (c.kind != kCodecSdp4bit) return false;
-#define COCCL_SDP_CASE(B, A, H) \
-  if (c.bits == B && (c.asym != 0) == A && (c.hadamard != 0) == H) { f(SdpCodec<B, A, H>{}); return true; }
-  COCCL_SDP_CASE(4, false, true)
-  COCCL_SDP_CASE(4, false, false)
-  COCCL_SDP_CASE(8, false, true)
-  COCCL_SDP_CASE(8, false, false)
-  COCCL_SDP_CASE(4, true, true)
-  COCCL_SDP_CASE(4, true, false)
-  COCCL_SDP_CASE(8, true, true)
-  COCCL_SDP_CASE(8, true, false)
+  const bool small = c.group < 32;
+#define COCCL_SDP_CASE(B, A, H, S) \
+  if (c.bits == B && (c.asym != 0) == A && (c.hadamard != 0) == H && small == S) { f(SdpCodec<B, A, H, S>{}); return true; }
+  COCCL_SDP_CASE(4, false, true, false)
+  COCCL_SDP_CASE(4, false, false, false)
+  COCCL_SDP_CASE(8, false, true, false)
+  COCCL_SDP_CASE(8, false, false, false)
+  COCCL_SDP_CASE(4, true, true, false)
+  COCCL_SDP_CASE(4, true, false, false)
+  COCCL_SDP_CASE(8, true, true, false)
+  COCCL_SDP_CASE(8, true, false, false)
+  COCCL_SDP_CASE(4, false, false, true)
+  COCCL_SDP_CASE(8, false, false, true)
+  COCCL_SDP_CASE(4, true, false, true)
+  COCCL_SDP_CASE(8, true, false, true)
 #undef COCCL_SDP_CASE
   return false;
 }

@@ -11,6 +11,8 @@ static_assert(COCCLK_MAX_SLICES == kMaxSlices && COCCLK_MAX_RANKS == kMaxRanks, 
 
 extern "C" long cocclkFlagBytes(void) { return 2L * kMaxRanks * kMaxSlices * (long)sizeof(unsigned int); }
 
+extern "C" int cocclkTileElems(void) { return kTileElems; }
+
 extern "C" long cocclkSlotBytes(const cocclkCodec* codec, long count) {
   CodecCfg c;
   memcpy(&c, codec, sizeof(c));

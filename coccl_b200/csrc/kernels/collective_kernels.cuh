@@ -13,7 +13,7 @@
 // phases of one kernel; `pipeline.depth` becomes the slice granularity.
 //
 // Work decomposition: a chunk (the elements one rank owns / sends to one peer)
-// is cut into slices of `sliceTiles` tiles of 2048 elements. One CTA owns one
+// is cut into slices of `sliceTiles` tiles of 8192 elements. One CTA owns one
 // (peer, slice) item at a time; finishing it publishes flag[src][slice]=epoch
 // on the receiver with release semantics. Encode items never wait, so every
 // wait in a later phase depends only on work that cannot itself block.
@@ -25,6 +25,7 @@
 // gridDim.y == 1 and peer-mapped pointers.
 #pragma once
 #include "codecs.cuh"
+#include "tile_io.cuh"
 
 namespace coccl {
 
@@ -55,33 +56,18 @@ __device__ __forceinline__ unsigned int* flagPtr(unsigned int* base, int region,
   return base + ((long)region * kMaxRanks + src) * kMaxSlices + slice;
 }
 
-// Load 8 values of `chunk` at element `e` (zero beyond `count`).
-template <typename T>
-__device__ __forceinline__ void loadVals(const T* chunk, long count, long e, bool vec, float (&v)[8]) {
-  if (e < count) {
-    Vec8<T>::load(chunk + e, count - e, vec, v);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.f;
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ void storeVals(T* chunk, long count, long e, bool vec, const float (&v)[8]) {
-  if (e < count) Vec8<T>::store(chunk + e, count - e, vec, v);
-}
-
 // Encode the tiles [t0, t1) of one source chunk and store the result into
 // nDst destination chunk buffers.
 template <typename T, class Codec>
 __device__ __forceinline__ void encodeTiles(const T* src, const ChunkLayout& L, const CodecCfg& c, long t0, long t1,
-                                            uint8_t* const* dst, int nDst, float* sm, uint64_t rngBase) {
-  const bool vec = aligned16(src);
+                                            uint8_t* const* dst, int nDst, TileStage<T>& stage, float* sm,
+                                            uint64_t rngBase) {
   for (long t = t0; t < t1; ++t) {
-    const long e = t * kTileElems + (long)threadIdx.x * kElemsPerThread;
-    float v[8];
-    loadVals(src, L.count, e, vec, v);
-    Enc enc = Codec::encode(v, c, e, true, sm, rngBase + (uint64_t)e);
+    const long e0 = t * kTileElems;
+    const long e = e0 + (long)threadIdx.x * kElemsPerThread;
+    float v[32];
+    TileIO<T>::load(src, L.count, e0, TileIO<T>::fastTile(src, L.count, e0), stage, v);
+    const typename Codec::Enc enc = Codec::encode(v, c, true, sm, rngBase + (uint64_t)e);
     for (int d = 0; d < nDst; ++d) Codec::store(enc, dst[d], L, c, e);
   }
 }
@@ -108,8 +94,9 @@ __device__ __forceinline__ bool waitAll(unsigned int* const* flagAddrs, int n, u
 }
 
 template <typename T, class Codec>
-__global__ void __launch_bounds__(kTileThreads) fusedCollectiveKernel(const CollArgs a) {
-  __shared__ float sm[16];
+__global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const CollArgs a) {
+  __shared__ TileStage<T> stage;
+  __shared__ float sm[8];
   __shared__ uint8_t* sDst[kMaxRanks];
   __shared__ unsigned int* sFlag[kMaxRanks];
 
@@ -142,7 +129,7 @@ __global__ void __launch_bounds__(kTileThreads) fusedCollectiveKernel(const Coll
           sFlag[0] = flagPtr(a.flags[p], 0, rank, (int)s);
         }
         __syncthreads();
-        encodeTiles<T, Codec>(in + (long)p * a.count, L, c, t0, t1, sDst, 1, sm,
+        encodeTiles<T, Codec>(in + (long)p * a.count, L, c, t0, t1, sDst, 1, stage, sm,
                               ((uint64_t)(rank * N + p) << 40));
         publish(sFlag, 1, a.epoch);
       } else {
@@ -152,7 +139,7 @@ __global__ void __launch_bounds__(kTileThreads) fusedCollectiveKernel(const Coll
           sFlag[threadIdx.x] = flagPtr(a.flags[p], 0, rank, (int)s);
         }
         __syncthreads();
-        encodeTiles<T, Codec>(in, L, c, t0, t1, sDst, N, sm, ((uint64_t)rank << 40));
+        encodeTiles<T, Codec>(in, L, c, t0, t1, sDst, N, stage, sm, ((uint64_t)rank << 40));
         publish(sFlag, N, a.epoch);
       }
     }
@@ -182,21 +169,21 @@ __global__ void __launch_bounds__(kTileThreads) fusedCollectiveKernel(const Coll
         __syncthreads();
       }
       T* dstChunk = reduce ? out : out + (long)q0 * a.count;
-      const bool vec = aligned16(dstChunk);
       for (long t = t0; t < t1; ++t) {
-        const long e = t * kTileElems + (long)threadIdx.x * kElemsPerThread;
-        float acc[8];
+        const long e0 = t * kTileElems;
+        const long e = e0 + (long)threadIdx.x * kElemsPerThread;
+        float acc[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int q = 0; q < nq; ++q)
-          Codec::loadAdd(myWs + (long)(q0 + q) * a.slotBytes, L, c, e, acc);
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+        decodeSum<Codec>(myWs + (long)q0 * a.slotBytes, a.slotBytes, nq, L, c, e,
+                         a.op == kOpAllReduceTwoShot ? 1.f : Codec::kFinishScale, acc);
         if (a.op == kOpAllReduceTwoShot) {
           // stay in the rotated domain: the sum of rotated values is the rotation of the sum
-          Enc enc = Codec::encode(acc, c, e, false, sm, ((uint64_t)(0x80 + rank) << 40) + (uint64_t)e);
+          const typename Codec::Enc enc = Codec::encode(acc, c, false, sm, ((uint64_t)(0x80 + rank) << 40) + (uint64_t)e);
           for (int d = 0; d < N; ++d) Codec::store(enc, sDst[d], L, c, e);
         } else {
           Codec::finish(acc);
-          storeVals(dstChunk, L.count, e, vec, acc);
+          TileIO<T>::store(dstChunk, L.count, e0, TileIO<T>::fastTile(dstChunk, L.count, e0), stage, acc);
         }
       }
       if (a.op == kOpAllReduceTwoShot) publish(sFlag, N, a.epoch);
@@ -216,15 +203,15 @@ __global__ void __launch_bounds__(kTileThreads) fusedCollectiveKernel(const Coll
       __syncthreads();
       if (!waitAll(sFlag, 1, a.epoch, a.timeoutNs, st, 3, (int)s, failed)) failed = true;
       T* dstChunk = out + (long)q * a.count;
-      const bool vec = aligned16(dstChunk);
       for (long t = t0; t < t1; ++t) {
-        const long e = t * kTileElems + (long)threadIdx.x * kElemsPerThread;
-        float acc[8];
+        const long e0 = t * kTileElems;
+        const long e = e0 + (long)threadIdx.x * kElemsPerThread;
+        float acc[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        Codec::loadAdd(myWs + a.regionBOffset + (long)q * a.slotBytes, L, c, e, acc);
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+        decodeSum<Codec>(myWs + a.regionBOffset + (long)q * a.slotBytes, 0, 1, L, c, e, Codec::kFinishScale, acc);
         Codec::finish(acc);
-        storeVals(dstChunk, L.count, e, vec, acc);
+        TileIO<T>::store(dstChunk, L.count, e0, TileIO<T>::fastTile(dstChunk, L.count, e0), stage, acc);
       }
     }
   }
@@ -249,7 +236,8 @@ struct CodecArgs {
 
 template <typename T, class Codec>
 __global__ void __launch_bounds__(kTileThreads) encodeKernel(const CodecArgs a) {
-  __shared__ float sm[16];
+  __shared__ TileStage<T> stage;
+  __shared__ float sm[8];
   __shared__ uint8_t* sDst[1];
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
@@ -258,47 +246,49 @@ __global__ void __launch_bounds__(kTileThreads) encodeKernel(const CodecArgs a) 
     __syncthreads();
     if (threadIdx.x == 0) sDst[0] = reinterpret_cast<uint8_t*>(a.out) + ch * a.encStrideOut;
     __syncthreads();
-    encodeTiles<T, Codec>(reinterpret_cast<const T*>(a.in) + ch * a.rawPitch, L, a.codec, t, t + 1, sDst, 1, sm,
-                          (uint64_t)ch << 40);
+    encodeTiles<T, Codec>(reinterpret_cast<const T*>(a.in) + ch * a.rawPitch, L, a.codec, t, t + 1, sDst, 1, stage,
+                          sm, (uint64_t)ch << 40);
   }
 }
 
 // out chunk j = sum_{i<reduce} decode(in chunk i*chunks + j)
 template <typename T, class Codec>
 __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecArgs a) {
+  __shared__ TileStage<T> stage;
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
   const uint8_t* enc = reinterpret_cast<const uint8_t*>(a.in);
   for (long it = blockIdx.x; it < tiles * a.chunks; it += gridDim.x) {
     const long ch = it / tiles, t = it % tiles;
     T* dst = reinterpret_cast<T*>(a.out) + ch * a.rawPitch;
-    const bool vec = aligned16(dst);
-    const long e = t * kTileElems + (long)threadIdx.x * kElemsPerThread;
-    float acc[8];
+    const long e0 = t * kTileElems;
+    const long e = e0 + (long)threadIdx.x * kElemsPerThread;
+    float acc[32];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (long r = 0; r < a.reduce; ++r) Codec::loadAdd(enc + (r * a.chunks + ch) * a.encStrideIn, L, a.codec, e, acc);
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e,
+                     Codec::kFinishScale, acc);
     Codec::finish(acc);
-    storeVals(dst, L.count, e, vec, acc);
+    TileIO<T>::store(dst, L.count, e0, TileIO<T>::fastTile(dst, L.count, e0), stage, acc);
   }
 }
 
 // decode + reduce + re-encode without leaving registers
 // (reference kernel: sdp4bit/quantization/dequant_reduce_quant.cu:14-179).
 template <class Codec>
-__global__ void __launch_bounds__(kTileThreads) decodeReduceEncodeKernel(const CodecArgs a) {
-  __shared__ float sm[16];
+__global__ void __launch_bounds__(kTileThreads, 3) decodeReduceEncodeKernel(const CodecArgs a) {
+  __shared__ float sm[8];
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
   const uint8_t* enc = reinterpret_cast<const uint8_t*>(a.in);
   for (long it = blockIdx.x; it < tiles * a.chunks; it += gridDim.x) {
     const long ch = it / tiles, t = it % tiles;
     const long e = t * kTileElems + (long)threadIdx.x * kElemsPerThread;
-    float acc[8];
+    float acc[32];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (long r = 0; r < a.reduce; ++r) Codec::loadAdd(enc + (r * a.chunks + ch) * a.encStrideIn, L, a.codec, e, acc);
-    Enc o = Codec::encode(acc, a.codec, e, false, sm, ((uint64_t)(0x40 + ch) << 40) + (uint64_t)e);
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e, 1.f, acc);
+    const typename Codec::Enc o = Codec::encode(acc, a.codec, false, sm, ((uint64_t)(0x40 + ch) << 40) + (uint64_t)e);
     Codec::store(o, reinterpret_cast<uint8_t*>(a.out) + ch * a.encStrideOut, L, a.codec, e);
   }
 }

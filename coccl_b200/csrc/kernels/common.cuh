@@ -16,8 +16,8 @@ namespace coccl {
 
 constexpr int kMaxRanks = 8;          // one NVSwitch domain
 constexpr int kTileThreads = 256;     // threads per CTA in codec / collective kernels
-constexpr int kElemsPerThread = 8;
-constexpr int kTileElems = kTileThreads * kElemsPerThread;  // 2048
+constexpr int kElemsPerThread = 32;    // one aligned run of 32 elements (one Hadamard block) per thread
+constexpr int kTileElems = kTileThreads * kElemsPerThread;  // 8192
 
 enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
 

@@ -59,6 +59,8 @@ typedef struct cocclkCollArgs {
 
 // Bytes of flag storage one rank needs (zero-initialised once).
 long cocclkFlagBytes(void);
+/* Elements per CTA tile of the codec and collective kernels (slice sizes are given in tiles). */
+int cocclkTileElems(void);
 // Smallest slot size (16-byte aligned) for one encoded chunk of `count` elements.
 long cocclkSlotBytes(const cocclkCodec* codec, long count);
 // emulatedRanks == 1: production launch for rank `rankBase` (peer pointers in

@@ -136,10 +136,11 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   a.rankBase = comm->rank;
   a.dtype = kernelDtype(info.datatype);
   a.count = count;
-  long tiles = (count + 2047) / 2048;
-  long sliceTiles = tiles * n / (148 * 4);
+  const long tileElems = cocclkTileElems();
+  long tiles = (count + tileElems - 1) / tileElems;
+  long sliceTiles = tiles * n / (148 * 3);
   if (sliceTiles < 1) sliceTiles = 1;
-  if (sliceTiles > 64) sliceTiles = 64;
+  if (sliceTiles > 16) sliceTiles = 16;
   while ((tiles + sliceTiles - 1) / sliceTiles > COCCLK_MAX_SLICES) sliceTiles *= 2;
   a.sliceTiles = (int)sliceTiles;
   a.epoch = st.epoch & 0x7fffffffu;

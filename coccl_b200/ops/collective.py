@@ -16,17 +16,20 @@ from .codec import CodecConfig, DTYPE_CODE
 OP_RS, OP_AG, OP_A2A, OP_AR1, OP_AR2 = 0, 1, 2, 3, 4
 OP_NAMES = {"reduce_scatter": OP_RS, "all_gather": OP_AG, "all_to_all": OP_A2A, "all_reduce_oneshot": OP_AR1,
             "all_reduce_twoshot": OP_AR2}
-TILE = 2048
 
 
 def slot_bytes(cfg: CodecConfig, count: int, dtype) -> int:
     return _lib.lib().cocclkSlotBytes(cfg.to_c(dtype), count)
 
 
-def pick_slice_tiles(count: int, n_ranks: int, target_items: int = 148 * 4) -> int:
-    """Tiles per slice: enough items to fill the GPU, at most 4096 slices, at most 64 tiles per slice."""
-    tiles = -(-count // TILE)
-    st = max(1, min(64, tiles * n_ranks // max(1, target_items)))
+def tile_elems() -> int:
+    return _lib.lib().cocclkTileElems()
+
+
+def pick_slice_tiles(count: int, n_ranks: int, target_items: int = 148 * 3) -> int:
+    """Tiles per slice: enough items to fill the GPU, at most 4096 slices, at most 16 tiles per slice."""
+    tiles = -(-count // tile_elems())
+    st = max(1, min(16, tiles * n_ranks // max(1, target_items)))
     while -(-tiles // st) > _lib.MAX_SLICES:
         st *= 2
     return st

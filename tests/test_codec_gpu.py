@@ -29,7 +29,7 @@ def _step(x, cfg):
 
 @pytest.mark.parametrize("cfg", CFGS, ids=lambda c: f"{c.kind}{c.bits}g{c.group}{'a' if c.asym else 's'}{'h' if c.hadamard else ''}")
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("count,chunks", [(4096, 4), (1000, 3), (2048 * 5 + 136, 1)])
+@pytest.mark.parametrize("count,chunks", [(4096, 4), (1000, 3), (2048 * 5 + 136, 1), (8192 * 3 + 40, 2), (16384, 2)])
 def test_roundtrip_matches_oracle(cuda, cfg, dtype, count, chunks):
     torch.manual_seed(0)
     x = (torch.randn(chunks * count, device=cuda) * 0.01).to(dtype)
