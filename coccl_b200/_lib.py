@@ -34,6 +34,15 @@ class CollArgs(C.Structure):
                 ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS)]
 
 
+class TpArgs(C.Structure):
+    """Mirror of cocclkTpArgs (csrc/kernels/tp_api.h)."""
+    _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("epi", c_int),
+                ("epoch", c_uint), ("timeoutNs", c_ulonglong),
+                ("a", c_void_p * MAX_RANKS), ("b", c_void_p * MAX_RANKS), ("c", c_void_p * MAX_RANKS),
+                ("bias", c_void_p * MAX_RANKS), ("z", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
+                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS)]
+
+
 _PROTOS = {
     # kernels_api.h
     "cocclkEncodedChunkBytes": (c_long, [C.POINTER(Codec), c_long]),
@@ -52,6 +61,11 @@ _PROTOS = {
                                c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cocclkGemmSetVariant": (None, [c_int]),
     "cocclkGemmGetVariant": (c_int, []),
+    # tp_api.h
+    "cocclkAgGemmWorkspaceBytes": (c_long, [c_int, c_int]),
+    "cocclkGemmRsWorkspaceBytes": (c_long, [c_int, c_int, c_int]),
+    "cocclkAgGemm": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
+    "cocclkGemmRs": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
     # train_api.h
     "cocclkLayerNormFwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_void_p]),
     "cocclkLayerNormBwdGrid": (c_int, [c_int]),

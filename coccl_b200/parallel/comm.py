@@ -99,6 +99,10 @@ class Communicator:
         self._ws: _Symm | None = None
         self._ws_half = 0
         self._sig: _Symm | None = None
+        self._tp_ws: _Symm | None = None
+        self._tp_sig: _Symm | None = None
+        self._tp_half = 0
+        self._tp_epoch = 0
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
@@ -223,6 +227,84 @@ class Communicator:
             dist.all_to_all_single(out, inp, group=self.group)
         return out
 
+    # ------------------------------------------------------------------ tensor-parallel fusions
+    def _ensure_tp(self, half_bytes: int):
+        if self._tp_sig is None:
+            self._tp_flag_bytes = _lib.lib().cocclkFlagBytes()
+            self._tp_sig = _Symm(self, self._tp_flag_bytes + 256)
+            self._tp_err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self._tp_ws is None or self._tp_half < half_bytes:
+            if self._tp_ws is not None:
+                torch.cuda.synchronize()
+                dist.barrier(group=self.group)
+                self._tp_ws.free()
+            half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
+            self._tp_ws = _Symm(self, 2 * half)
+            self._tp_half = half
+            dist.barrier(group=self.group)
+
+    def _tp_args(self, M: int, N: int, K: int):
+        self._tp_epoch += 1
+        parity = self._tp_epoch & 1
+        a = _lib.TpArgs()
+        a.nRanks, a.rankBase, a.M, a.N, a.K = self.size, self.rank, M, N, K
+        a.epoch = self._tp_epoch & 0x7FFFFFFF
+        a.timeoutNs = int(self.policy.timeout_ms * 1e6)
+        for p in range(self.size):
+            a.ws[p] = self._tp_ws.ptrs[p] + parity * self._tp_half
+            a.flags[p] = self._tp_sig.ptrs[p]
+            a.status[p] = self._tp_sig.ptrs[p] + self._tp_flag_bytes
+        a.err[self.rank] = self._tp_err.data_ptr()
+        return a
+
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gelu: bool = False,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """concat_over_ranks(x_local) @ w.T (+ bias, GELU) in ONE kernel: the shards travel over peer memory
+        while the tensor cores already work on the local shard. x_local [m, K], w [N, K], both bf16."""
+        from ..ops import tp_fused as T
+        m, K = x_local.shape
+        N = w.shape[0]
+        M = m * self.size
+        assert x_local.is_contiguous() and w.is_contiguous() and x_local.dtype == torch.bfloat16
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
+        self._ensure_tp(T.ag_ws_bytes(M, K))
+        a = self._tp_args(M, N, K)
+        a.epi = T.EPI_NONE if bias is None else (T.EPI_BIAS_GELU if gelu else T.EPI_BIAS)
+        a.a[self.rank], a.b[self.rank], a.c[self.rank] = x_local.data_ptr(), w.data_ptr(), out.data_ptr()
+        a.bias[self.rank] = bias.data_ptr() if bias is not None else None
+        _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
+        self.stats["compressed_calls"] += 1
+        return out
+
+    def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """reduce_scatter over ranks of (a_mat @ w.T) along the rows, in ONE kernel: the partial products leave
+        the GEMM epilogue as block-scaled FP8 straight into the destination ranks' memory. a_mat [M, K], w [N, K]."""
+        from ..ops import tp_fused as T
+        M, K = a_mat.shape
+        N = w.shape[0]
+        assert a_mat.is_contiguous() and w.is_contiguous() and a_mat.dtype == torch.bfloat16
+        if out is None:
+            out = torch.empty(M // self.size, N, dtype=torch.bfloat16, device=a_mat.device)
+        self._ensure_tp(T.rs_ws_bytes(M, N, self.size))
+        a = self._tp_args(M, N, K)
+        a.epi = T.EPI_NONE
+        a.a[self.rank], a.b[self.rank], a.c[self.rank] = a_mat.data_ptr(), w.data_ptr(), out.data_ptr()
+        _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
+        self.stats["compressed_calls"] += 1
+        self.stats["compressed_raw_bytes"] += M * N * 2
+        return out
+
+    def tp_status(self) -> tuple[int, int]:
+        """(status word, pipeline error word) of the tensor-parallel fusions; synchronises the device."""
+        if self._tp_sig is None:
+            return 0, 0
+        torch.cuda.synchronize()
+        w = (C.c_uint * 1)()
+        rd = _lib.declare("cocclHostRead32", C.c_int, [C.c_void_p, C.POINTER(C.c_uint)])
+        _lib.check(rd(self._tp_sig.ptrs[self.rank] + self._tp_flag_bytes, w), "cocclHostRead32")
+        return int(w[0]), int(self._tp_err.item())
+
     def all_reduce_small(self, t: torch.Tensor, op=dist.ReduceOp.SUM):
         if self.size > 1:
             dist.all_reduce(t, op=op, group=self.group)
@@ -236,11 +318,11 @@ class Communicator:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
 
     def close(self):
-        if self._ws is not None or self._sig is not None:
+        if self._ws is not None or self._sig is not None or self._tp_ws is not None:
             torch.cuda.synchronize()
             if self.size > 1:
                 dist.barrier(group=self.group)
-        for s in (self._ws, self._sig):
+        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig):
             if s is not None:
                 s.free()
         self._ws = self._sig = None

@@ -101,3 +101,41 @@ def test_trainer_two_gpus_compressed(layout):
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
 def test_trainer_3d_eight_gpus():
     run_distributed(_trainer_worker, 8, "nccl", (2, 2, 2, True))
+
+
+def _tp_fused_worker(rank, world):
+    import torch.distributed as dist
+    from coccl_b200.ops import codec as C
+    from coccl_b200.parallel.comm import Communicator, Policy
+    dev = torch.device("cuda", rank)
+    comm = Communicator(None, dev, Policy(), "tp")
+    m, K, N = 256, 512, 768
+    for it in range(3):  # several calls: parity halves of the workspace and epochs are reused
+        torch.manual_seed(7 + rank + 10 * it)
+        x = torch.randn(m, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.1
+        b = torch.randn(N, device=dev, dtype=torch.bfloat16)
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x)
+        y = comm.ag_gemm(x, w, bias=b, gelu=True)
+        ref = torch.nn.functional.gelu(torch.cat(xs).float() @ w.float().t() + b.float(), approximate="tanh")
+        assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+        # second half of the MLP: y [M, N] @ w2[N2, N]^T, partial sums reduce-scattered as FP8
+        w2 = torch.randn(512, N, device=dev, dtype=torch.bfloat16) * 0.05
+        out = comm.gemm_rs(y, w2)
+        part = y.float() @ w2.float().t()
+        q = C.reference_roundtrip(part.contiguous(), C.MXFP8, 1)
+        parts = [torch.empty_like(q) for _ in range(world)]
+        dist.all_gather(parts, q)
+        rows = m  # M / world
+        refq = sum(parts)[rank * rows:(rank + 1) * rows]
+        d = (out.float() - refq).abs()
+        scale = refq.abs().max().item()
+        assert (d > 1e-2 * scale + 1e-3).float().mean().item() < 2e-3 and d.max().item() <= scale / 8 + 1e-3
+    assert comm.tp_status() == (0, 0)
+    comm.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_fusions_over_peer_memory():
+    run_distributed(_tp_fused_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")

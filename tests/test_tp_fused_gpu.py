@@ -1,0 +1,62 @@
+"""all-gather -> GEMM and GEMM -> FP8 reduce-scatter kernels, every rank emulated on one GPU, against fp32 PyTorch."""
+import pytest
+import torch
+
+from coccl_b200.ops import codec as C
+from coccl_b200.ops import tp_fused as T
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,m,N,K,bias,gelu", [(2, 128, 256, 64, False, False), (2, 256, 520, 192, True, False),
+                                               (4, 256, 512, 256, True, True), (2, 1024, 1024, 1024, False, False)])
+def test_ag_gemm_emulated(cuda, n, m, N, K, bias, gelu):
+    torch.manual_seed(0)
+    xs = [torch.randn(m, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
+    ws = [torch.randn(N, K, device=cuda, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
+    bs = [torch.randn(N, device=cuda, dtype=torch.bfloat16) for _ in range(n)] if bias else None
+    state = {}
+    for epoch in (1, 2):  # second call reuses flags and gather buffers
+        outs, state = T.emulate_ag_gemm(xs, ws, bias=bs, gelu=gelu, state=state, epoch=epoch, max_ctas=148 // n)
+        torch.cuda.synchronize()
+        T.check_state(state)
+        xf = torch.cat(xs).float()
+        for r in range(n):
+            ref = xf @ ws[r].float().t()
+            if bias:
+                ref = ref + bs[r].float()
+            if gelu:
+                ref = torch.nn.functional.gelu(ref, approximate="tanh")
+            err = (outs[r].float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-3, (r, err)
+        xs = [x * 0.5 for x in xs]
+
+
+@pytest.mark.parametrize("n,M,N,K", [(2, 256, 256, 64), (2, 512, 512, 320), (4, 1024, 768, 256), (2, 2048, 1024, 1024)])
+def test_gemm_rs_emulated(cuda, n, M, N, K):
+    torch.manual_seed(1)
+    As = [torch.randn(M, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
+    Ws = [torch.randn(N, K, device=cuda, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
+    state = {}
+    for epoch in (1, 2):
+        outs, state = T.emulate_gemm_rs(As, Ws, state=state, epoch=epoch, max_ctas=148 // n)
+        torch.cuda.synchronize()
+        T.check_state(state)
+        parts = [As[q].float() @ Ws[q].float().t() for q in range(n)]
+        exact = sum(parts)
+        # oracle of the transport: every partial product goes through the MX-FP8 codec (32 columns per block)
+        quant = sum(C.reference_roundtrip(p.contiguous(), C.MXFP8, 1) for p in parts)
+        rows = M // n
+        for r in range(n):
+            got = outs[r].float()
+            ref_q = quant[r * rows:(r + 1) * rows]
+            ref = exact[r * rows:(r + 1) * rows]
+            # the kernel's fp32 sums differ from torch's in the last bits, which can flip an E4M3 rounding
+            # decision: almost every element matches the oracle, a flipped one is off by one step (<= |x|/8)
+            d = (got - ref_q).abs()
+            scale = ref.abs().max().item()
+            assert (d > 1e-2 * scale + 1e-3).float().mean().item() < 2e-3
+            assert d.max().item() <= scale / 8 + 1e-3
+            rel = (got - ref).norm().item() / ref.norm().item()
+            assert rel < 0.05, rel
+        As = [a * 0.5 for a in As]
