@@ -43,6 +43,14 @@ class TpArgs(C.Structure):
                 ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS)]
 
 
+class MoeArgs(C.Structure):
+    """Mirror of cocclkMoeArgs (csrc/kernels/moe_api.h)."""
+    _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("tokens", c_int), ("hidden", c_int), ("topk", c_int),
+                ("experts", c_int), ("capacity", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong)] + \
+               [(n, c_void_p * MAX_RANKS) for n in ("x", "expertIds", "gates", "pos", "sendCounts", "recv", "recvOffsets",
+                                                   "recvCounts", "y", "out", "ws", "flags", "status")]
+
+
 _PROTOS = {
     # kernels_api.h
     "cocclkEncodedChunkBytes": (c_long, [C.POINTER(Codec), c_long]),
@@ -66,6 +74,11 @@ _PROTOS = {
     "cocclkGemmRsWorkspaceBytes": (c_long, [c_int, c_int, c_int]),
     "cocclkAgGemm": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
     "cocclkGemmRs": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
+    # moe_api.h
+    "cocclkMoeWorkspaceBytes": (c_long, [c_int, c_int, c_int, c_int]),
+    "cocclkMoeLayout": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "cocclkMoeDispatch": (c_int, [C.POINTER(MoeArgs), c_int, c_int, c_void_p]),
+    "cocclkMoeCombine": (c_int, [C.POINTER(MoeArgs), c_int, c_int, c_void_p]),
     # train_api.h
     "cocclkLayerNormFwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_void_p]),
     "cocclkLayerNormBwdGrid": (c_int, [c_int]),
