@@ -86,6 +86,50 @@ class _Symm:
             self.handle = None
 
 
+class _Arena:
+    """Parity-double-buffered symmetric workspace + flag/status block + epoch counter of one kernel family."""
+
+    def __init__(self, comm: "Communicator"):
+        self.comm = comm
+        self.flag_bytes = _lib.lib().cocclkFlagBytes()
+        self.sig = _Symm(comm, self.flag_bytes + 256)
+        self.ws: _Symm | None = None
+        self.half = 0
+        self.epoch = 0
+
+    def ensure(self, half_bytes: int):
+        if self.ws is None or self.half < half_bytes:
+            if self.ws is not None:
+                torch.cuda.synchronize()
+                dist.barrier(group=self.comm.group)
+                self.ws.free()
+            half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
+            self.ws = _Symm(self.comm, 2 * half)
+            self.half = half
+            dist.barrier(group=self.comm.group)
+
+    def next(self):
+        """(epoch, [workspace half of every rank], [flags], [status])"""
+        self.epoch += 1
+        off = (self.epoch & 1) * self.half
+        n = self.comm.size
+        return (self.epoch & 0x7FFFFFFF, [self.ws.ptrs[p] + off for p in range(n)], list(self.sig.ptrs),
+                [self.sig.ptrs[p] + self.flag_bytes for p in range(n)])
+
+    def status(self) -> int:
+        torch.cuda.synchronize()
+        w = (C.c_uint * 1)()
+        rd = _lib.declare("cocclHostRead32", C.c_int, [C.c_void_p, C.POINTER(C.c_uint)])
+        _lib.check(rd(self.sig.ptrs[self.comm.rank] + self.flag_bytes, w), "cocclHostRead32")
+        return int(w[0])
+
+    def free(self):
+        for s in (self.ws, self.sig):
+            if s is not None:
+                s.free()
+        self.ws = self.sig = None
+
+
 class Communicator:
     def __init__(self, group=None, device=None, policy: Policy | None = None, name: str = "default"):
         self.group = group
@@ -103,6 +147,7 @@ class Communicator:
         self._tp_sig: _Symm | None = None
         self._tp_half = 0
         self._tp_epoch = 0
+        self._moe: _Arena | None = None
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
@@ -305,6 +350,60 @@ class Communicator:
         _lib.check(rd(self._tp_sig.ptrs[self.rank] + self._tp_flag_bytes, w), "cocclHostRead32")
         return int(w[0]), int(self._tp_err.item())
 
+    # ------------------------------------------------------------------ expert parallelism
+    def _moe_args(self, tokens, hidden, topk, n_experts, capacity):
+        from ..ops import moe as M
+        if self._moe is None:
+            self._moe = _Arena(self)
+        self._moe.ensure(M.ws_bytes(self.size, capacity, hidden, n_experts // self.size))
+        epoch, ws, flags, status = self._moe.next()
+        a = _lib.MoeArgs()
+        a.nRanks, a.rankBase, a.tokens, a.hidden, a.topk = self.size, self.rank, tokens, hidden, topk
+        a.experts, a.capacity, a.epoch, a.timeoutNs = n_experts, capacity, epoch, int(self.policy.timeout_ms * 1e6)
+        for p in range(self.size):
+            a.ws[p], a.flags[p], a.status[p] = ws[p], flags[p], status[p]
+        return a
+
+    def moe_dispatch(self, x: torch.Tensor, expert_ids: torch.Tensor, n_experts: int, capacity: int | None = None):
+        """Send every token to the ranks of its top-k experts as block-scaled FP8 (one kernel: gather, quantise,
+        peer stores, dequantise on arrival). Returns (rows [R, hidden] bf16 grouped by local expert, handle);
+        handle.recv_offsets[e] .. [e+1] are the rows of local expert e."""
+        from ..ops import moe as M
+        tokens, hidden = x.shape
+        topk = expert_ids.shape[1]
+        capacity = capacity or tokens * topk
+        le = n_experts // self.size
+        pos, counts = M.route_layout(expert_ids, n_experts, self.size)
+        recv = torch.empty(self.size * capacity, hidden, dtype=torch.bfloat16, device=x.device)
+        roff = torch.zeros(le + 1, dtype=torch.int32, device=x.device)
+        rcnt = torch.zeros(self.size, le, dtype=torch.int32, device=x.device)
+        a = self._moe_args(tokens, hidden, topk, n_experts, capacity)
+        r = self.rank
+        a.x[r], a.expertIds[r], a.pos[r], a.sendCounts[r] = x.data_ptr(), expert_ids.data_ptr(), pos.data_ptr(), counts.data_ptr()
+        a.recv[r], a.recvOffsets[r], a.recvCounts[r] = recv.data_ptr(), roff.data_ptr(), rcnt.data_ptr()
+        _lib.check(_lib.lib().cocclkMoeDispatch(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeDispatch")
+        self.stats["compressed_calls"] += 1
+        self.stats["compressed_raw_bytes"] += tokens * topk * hidden * 2
+        h = M.Handle(expert_ids, pos, rcnt, roff, capacity, n_experts)
+        h.keep = (counts, x)
+        return recv, h
+
+    def moe_combine(self, y: torch.Tensor, gates: torch.Tensor, handle) -> torch.Tensor:
+        """Return the expert outputs (same row layout as moe_dispatch's result) to the token owners as bf16 and
+        form out[t] = sum_j gates[t, j] * y_j in one kernel."""
+        tokens, topk = gates.shape
+        hidden = y.shape[1]
+        out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=y.device)
+        a = self._moe_args(tokens, hidden, topk, handle.n_experts, handle.capacity)
+        r = self.rank
+        a.expertIds[r], a.pos[r], a.gates[r] = handle.expert_ids.data_ptr(), handle.pos.data_ptr(), gates.data_ptr()
+        a.recvCounts[r], a.y[r], a.out[r] = handle.recv_counts.data_ptr(), y.data_ptr(), out.data_ptr()
+        _lib.check(_lib.lib().cocclkMoeCombine(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeCombine")
+        return out
+
+    def moe_status(self) -> int:
+        return 0 if self._moe is None else self._moe.status()
+
     def all_reduce_small(self, t: torch.Tensor, op=dist.ReduceOp.SUM):
         if self.size > 1:
             dist.all_reduce(t, op=op, group=self.group)
@@ -318,11 +417,11 @@ class Communicator:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
 
     def close(self):
-        if self._ws is not None or self._sig is not None or self._tp_ws is not None:
+        if self._ws is not None or self._sig is not None or self._tp_ws is not None or self._moe is not None:
             torch.cuda.synchronize()
             if self.size > 1:
                 dist.barrier(group=self.group)
-        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig):
+        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig, self._moe):
             if s is not None:
                 s.free()
         self._ws = self._sig = None

@@ -139,3 +139,31 @@ def _tp_fused_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_tp_fusions_over_peer_memory():
     run_distributed(_tp_fused_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
+
+
+def _moe_worker(rank, world):
+    import torch.distributed as dist
+    from coccl_b200.models.moe import MoELayer
+    from coccl_b200.parallel.comm import NATIVE, Communicator, Policy
+    dev = torch.device("cuda", rank)
+    comm = Communicator(None, dev, Policy(), "ep")
+    layer = MoELayer(comm, hidden=512, ffn=1024, n_experts=4 * world, topk=2, seed=3)
+    # the same model with every expert on one rank
+    solo = Communicator.__new__(Communicator)
+    solo.size, solo.rank, solo.device = 1, 0, dev
+    ref_layer = MoELayer(solo, hidden=512, ffn=1024, n_experts=4 * world, topk=2, seed=3, device=dev)
+    for it in range(2):
+        torch.manual_seed(50 + rank + it)
+        x = torch.randn(384, 512, device=dev, dtype=torch.bfloat16)
+        y = layer.forward(x)
+        ids, gates = layer.route(x)
+        ref = ref_layer.forward_local(x, ids, gates)
+        rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+        assert rel < 0.06, rel  # FP8 on the dispatched activations
+    assert comm.moe_status() == 0
+    comm.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_moe_layer_expert_parallel():
+    run_distributed(_moe_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
