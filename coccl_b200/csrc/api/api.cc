@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "coccl/coccl.h"
 #include "memory/buffer_manager.h"
@@ -323,6 +324,15 @@ extern "C" ncclResult_t cocclApiCodecRoundTrip(const char* pluginDir, const char
     r = red > 1 ? decompressReduce(codec, ev, &ov, red, env) : decompress(codec, ev, &ov, env);
   }
   if (cudaStreamSynchronize(stream) != cudaSuccess && r == ncclSuccess) r = ncclUnhandledCudaError;
+  if (r == ncclSuccess && framed && encodedBytes) {
+    // a framed codec reserves fixed slots; what it actually produced is in the frame metadata
+    std::vector<cocclCompressorFrameMetadata> hm(chunks);
+    if (cudaMemcpy(hm.data(), meta, chunks * sizeof(cocclCompressorFrameMetadata), cudaMemcpyDeviceToHost) == cudaSuccess) {
+      size_t total = 0;
+      for (const auto& m : hm) total += (size_t)m.payloadBytes;
+      *encodedBytes = total;
+    }
+  }
   cudaFree(enc);
   cudaFree(meta);
   return r;

@@ -1,0 +1,175 @@
+// ZFP fixed-rate coder for 1-D blocks of four floats, written once for host and device: the device kernels of
+// the zfp plugin and the CPU oracle compile this same code, so their streams are bit-identical.
+//
+// Algorithm (public ZFP specification; reference files zfp/src/cuda_zfp/encode.cuh:73-231, decode.cuh,
+// zfp/src/zfp.c:773-803): common exponent of the block (9 header bits: 1 "non-zero" bit + 8 exponent bits),
+// block-floating-point conversion to int32 with 30 fraction bits, the reversible-up-to-rounding decorrelating
+// lift, negabinary, then the bit planes from the most significant one down, each coded as "the bits of the
+// values already known to be significant" + a unary run-length code of the rest, until the block's budget of
+// maxbits = max(round(4 * rate), 9) bits is used up; short blocks are padded with zeros. Block i starts at
+// bit i * maxbits of a stream of 32-bit little-endian words.
+#pragma once
+#include <stdint.h>
+#include <math.h>
+
+#if defined(__CUDACC__)
+#define COCCL_HD __host__ __device__ __forceinline__
+#else
+#define COCCL_HD inline
+#endif
+
+namespace coccl {
+namespace zfp1d {
+
+constexpr int kBlock = 4;
+constexpr int kEbias = 127;
+constexpr int kMaxWords = 6;  // rate <= 32: a block of up to 128 bits starting at any bit of a word spans 5 words; one spare
+
+COCCL_HD int maxBits(int rate) {
+  const int b = 4 * rate;
+  return b < 9 ? 9 : b;
+}
+
+// Bits are appended LSB-first into a zero-initialised window of words, starting at bit `pos`.
+struct BitWindow {
+  uint32_t w[kMaxWords];
+  int pos;
+};
+
+COCCL_HD void putBits(BitWindow& s, uint64_t v, int n) {
+  for (int done = 0; done < n;) {
+    const int word = s.pos >> 5, off = s.pos & 31;
+    const int take = (32 - off) < (n - done) ? (32 - off) : (n - done);
+    const uint32_t piece = (uint32_t)((v >> done) & ((take == 32) ? 0xffffffffull : ((1ull << take) - 1)));
+    s.w[word] |= piece << off;
+    s.pos += take;
+    done += take;
+  }
+}
+COCCL_HD uint64_t getBits(BitWindow& s, int n) {
+  uint64_t v = 0;
+  for (int done = 0; done < n;) {
+    const int word = s.pos >> 5, off = s.pos & 31;
+    const int take = (32 - off) < (n - done) ? (32 - off) : (n - done);
+    const uint64_t piece = (s.w[word] >> off) & ((take == 32) ? 0xffffffffu : ((1u << take) - 1));
+    v |= piece << done;
+    s.pos += take;
+    done += take;
+  }
+  return v;
+}
+
+COCCL_HD int blockExponent(const float* x) {
+  float m = 0.f;
+  for (int i = 0; i < kBlock; ++i) { const float a = fabsf(x[i]); if (a > m) m = a; }
+  if (!(m > 0.f) || !(m < INFINITY)) return -kEbias;
+  int e;
+  frexpf(m, &e);            // m = f * 2^e, f in [0.5, 1)
+  return e < 1 - kEbias ? 1 - kEbias : e;
+}
+
+COCCL_HD void forwardLift(int32_t* p) {
+  int32_t x = p[0], y = p[1], z = p[2], w = p[3];
+  x += w; x >>= 1; w -= x;
+  z += y; z >>= 1; y -= z;
+  x += z; x >>= 1; z -= x;
+  w += y; w >>= 1; y -= w;
+  w += y >> 1; y -= w >> 1;
+  p[0] = x; p[1] = y; p[2] = z; p[3] = w;
+}
+COCCL_HD void inverseLift(int32_t* p) {
+  int32_t x = p[0], y = p[1], z = p[2], w = p[3];
+  y += w >> 1; w -= y >> 1;
+  y += w; w <<= 1; w -= y;
+  z += x; x <<= 1; x -= z;
+  y += z; z <<= 1; z -= y;
+  w += x; x <<= 1; x -= w;
+  p[0] = x; p[1] = y; p[2] = z; p[3] = w;
+}
+COCCL_HD uint32_t toNegabinary(int32_t v) { return ((uint32_t)v + 0xaaaaaaaau) ^ 0xaaaaaaaau; }
+COCCL_HD int32_t fromNegabinary(uint32_t v) { return (int32_t)((v ^ 0xaaaaaaaau) - 0xaaaaaaaau); }
+
+// Encode one block into `s` (window zeroed by the caller, s.pos = first bit of the block).
+COCCL_HD void encodeBlock(const float* x, int maxbits, BitWindow& s) {
+  const int start = s.pos;
+  const int emax = blockExponent(x);
+  if (emax == -kEbias) {  // all zero (or not finite): a single 0 bit, the rest of the budget is padding
+    s.pos = start + maxbits;
+    return;
+  }
+  putBits(s, (uint64_t)(2 * (emax + kEbias) + 1), 9);
+  int32_t q[kBlock];
+  const float scale = ldexpf(1.f, 30 - emax);
+  for (int i = 0; i < kBlock; ++i) q[i] = (int32_t)(x[i] * scale);
+  forwardLift(q);
+  uint32_t u[kBlock];
+  for (int i = 0; i < kBlock; ++i) u[i] = toNegabinary(q[i]);
+  int bits = maxbits - 9;
+  int n = 0;
+  for (int k = 32; bits && k-- > 0;) {
+    uint32_t plane = 0;
+    for (int i = 0; i < kBlock; ++i) plane |= ((u[i] >> k) & 1u) << i;
+    const int m = n < bits ? n : bits;
+    bits -= m;
+    putBits(s, plane, m);
+    plane >>= m;
+    // unary run-length code of the values that are not yet significant
+    while (n < kBlock && bits) {
+      --bits;
+      const uint32_t any = plane != 0;
+      putBits(s, any, 1);
+      if (!any) break;
+      while (n < kBlock - 1 && bits) {
+        --bits;
+        const uint32_t bit = plane & 1u;
+        putBits(s, bit, 1);
+        if (bit) break;
+        plane >>= 1;
+        ++n;
+      }
+      plane >>= 1;
+      ++n;
+    }
+  }
+  s.pos = start + maxbits;
+}
+
+// Decode one block from `s` (s.pos = first bit of the block).
+COCCL_HD void decodeBlock(BitWindow& s, int maxbits, float* x) {
+  const int start = s.pos;
+  if (getBits(s, 1) == 0) {
+    for (int i = 0; i < kBlock; ++i) x[i] = 0.f;
+    s.pos = start + maxbits;
+    return;
+  }
+  const int emax = (int)getBits(s, 8) - kEbias;
+  uint32_t u[kBlock] = {0, 0, 0, 0};
+  int bits = maxbits - 9;
+  int n = 0;
+  for (int k = 32; bits && k-- > 0;) {
+    const int m = n < bits ? n : bits;
+    bits -= m;
+    uint32_t plane = (uint32_t)getBits(s, m);
+    while (n < kBlock && bits) {
+      --bits;
+      if (!getBits(s, 1)) break;
+      while (n < kBlock - 1 && bits) {
+        --bits;
+        if (getBits(s, 1)) break;
+        ++n;
+      }
+      plane |= 1u << n;
+      ++n;
+    }
+    for (int i = 0; plane; ++i, plane >>= 1) u[i] |= (plane & 1u) << k;
+  }
+  int32_t q[kBlock];
+  for (int i = 0; i < kBlock; ++i) q[i] = fromNegabinary(u[i]);
+  inverseLift(q);
+  const float scale = ldexpf(1.f, emax - 30);
+  for (int i = 0; i < kBlock; ++i) x[i] = (float)q[i] * scale;
+  s.pos = start + maxbits;
+}
+
+}  // namespace zfp1d
+}  // namespace coccl
