@@ -177,10 +177,11 @@ def main():
     e2e_s = time.perf_counter() - t0
     barrier()
 
-    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    # the loss lives on the last pipeline stage: take the maximum over ranks (it is positive)
+    t = torch.tensor([ms, e2e_s * 1e3, last if last is not None else 0.0], dtype=torch.float64, device=dev)
     if n > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = t.tolist()
+    ms, e2e_ms, last = t.tolist()
     from coccl_b200.ops import gemm as G
     G.check_errors()
     if rank == 0:
@@ -190,7 +191,9 @@ def main():
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
+            # published: 163.2 model TFLOP/s per GPU for GPT-6.7B with COCCL on 32 x H800 (reference README.md:334-340),
+            # converted to tokens/s with the same FLOPs-per-token formula and scaled to n GPUs
+            "vs_baseline": value / (n * 163.2e12 / cfg.flops_per_token()), "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
             "config": {"model": f"{args.model}: L{cfg.n_layer} h{cfg.hidden} heads{cfg.n_head} ffn{cfg.ffn} gelu "
                                 f"seq{cfg.seq_len} vocab{cfg.vocab}", "global_batch": global_batch,
                        "seq_len": cfg.seq_len, "micro_batch": 2, "parallelism": f"tp{tp}pp{pp}dp{dp}",

@@ -31,7 +31,7 @@ class CollArgs(C.Structure):
                 ("sliceTiles", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong), ("codec", Codec),
                 ("slotBytes", c_long), ("regionBOffset", c_long),
                 ("inp", c_void_p * MAX_RANKS), ("out", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
-                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS)]
+                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("trace", c_void_p * MAX_RANKS)]
 
 
 class TpArgs(C.Structure):

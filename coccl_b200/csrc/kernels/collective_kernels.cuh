@@ -50,7 +50,13 @@ struct CollArgs {
   uint8_t* ws[kMaxRanks];          // workspace of every rank as mapped here (parity offset applied)
   unsigned int* flags[kMaxRanks];  // [2 regions][kMaxRanks sources][kMaxSlices]
   StatusWord* status[kMaxRanks];
+  unsigned long long* trace[kMaxRanks];  // optional phase timestamps, 4 per CTA
 };
+
+constexpr int kTraceMaxCtas = 2048;
+__device__ __forceinline__ void tracePhase(unsigned long long* tr, int phase) {
+  if (tr != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceMaxCtas) tr[blockIdx.x * 4 + phase] = globalTimerNs();
+}
 
 __device__ __forceinline__ unsigned int* flagPtr(unsigned int* base, int region, int src, int slice) {
   return base + ((long)region * kMaxRanks + src) * kMaxSlices + slice;
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
   uint8_t* myWs = a.ws[rank];
   unsigned int* myFlags = a.flags[rank];
   StatusWord* st = a.status[rank];
+  unsigned long long* tr = a.trace[rank];
+  tracePhase(tr, 0);
   bool failed = false;
   const bool perPeer = (a.op == kOpReduceScatter || a.op == kOpAllToAll || a.op == kOpAllReduceTwoShot);
 
@@ -145,6 +153,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
     }
   }
 
+  tracePhase(tr, 1);
   // ---------------- phase 2: wait + decode ----------------
   const bool reduce = (a.op == kOpReduceScatter || a.op == kOpAllReduceOneShot || a.op == kOpAllReduceTwoShot);
   {
@@ -190,6 +199,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
     }
   }
 
+  tracePhase(tr, 2);
   // ---------------- phase 3 (two-shot all-reduce): gather reduced chunks ----------------
   if (a.op == kOpAllReduceTwoShot) {
     const long items = slices * N;
@@ -215,6 +225,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
       }
     }
   }
+  tracePhase(tr, 3);
 }
 
 // ---------------------------------------------------------------------------

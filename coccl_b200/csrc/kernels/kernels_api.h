@@ -37,7 +37,7 @@ int cocclkDecodeReduceEncode(const void* in, void* out, long count, long chunks,
                              long encStrideOut, const cocclkCodec* codec, cudaStream_t stream);
 
 // Fused collectives. Mirrors coccl::CollArgs.
-enum { COCCLK_MAX_RANKS = 8, COCCLK_MAX_SLICES = 4096 };
+enum { COCCLK_MAX_RANKS = 8, COCCLK_MAX_SLICES = 4096, COCCLK_TRACE_MAX_CTAS = 2048 };
 typedef struct cocclkCollArgs {
   int op;        // 0 RS, 1 AG, 2 A2A, 3 AR one-shot, 4 AR two-shot
   int nRanks;
@@ -55,6 +55,10 @@ typedef struct cocclkCollArgs {
   uint8_t* ws[COCCLK_MAX_RANKS];
   unsigned int* flags[COCCLK_MAX_RANKS];
   void* status[COCCLK_MAX_RANKS];
+  /* Optional per-rank phase trace (NULL = off): CTA c writes four globaltimer values (ns) at
+     trace[rank][4 c + {0: kernel start, 1: encode+push done, 2: decode(-reduce) done, 3: gather done}].
+     Needs 32 bytes per CTA of the launch (COCCLK_TRACE_MAX_CTAS CTAs at most are recorded). */
+  unsigned long long* trace[COCCLK_MAX_RANKS];
 } cocclkCollArgs;
 
 // Bytes of flag storage one rank needs (zero-initialised once).

@@ -83,6 +83,8 @@ def emulate_collective(op: str, inputs: list[torch.Tensor], cfg: CodecConfig, *,
         assert inputs[r].is_contiguous() and inputs[r].numel() == numel
         a.inp[r], a.out[r] = inputs[r].data_ptr(), outs[r].data_ptr()
         a.ws[r], a.flags[r], a.status[r] = state["ws"][r].data_ptr(), state["flags"][r].data_ptr(), state["status"][r].data_ptr()
+        if state.get("trace") is not None:  # list of int64 [TRACE_MAX_CTAS, 4] tensors, one per rank
+            a.trace[r] = state["trace"][r].data_ptr()
     rc = _lib.lib().cocclkFusedCollective(a, n, max_ctas, _lib.cur_stream())
     _lib.check(rc, f"cocclkFusedCollective({op})")
     return outs

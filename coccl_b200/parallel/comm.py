@@ -20,6 +20,9 @@ import torch.distributed as dist
 from .. import _lib
 from ..ops import collective as K
 from ..ops.codec import MXFP8, SDP4BIT_G128, CodecConfig, DTYPE_CODE
+from ..utils.trace import nvtx_range
+
+K_NAMES = {0: "reduce_scatter", 1: "all_gather", 2: "all_to_all", 3: "all_reduce_oneshot", 4: "all_reduce_twoshot"}
 
 
 @dataclass
@@ -148,6 +151,7 @@ class Communicator:
         self._tp_half = 0
         self._tp_epoch = 0
         self._moe: _Arena | None = None
+        self._trace: torch.Tensor | None = None
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
@@ -187,10 +191,27 @@ class Communicator:
             a.ws[p] = self._ws.ptrs[p] + parity * self._ws_half
             a.flags[p] = self._sig.ptrs[p]
             a.status[p] = self._sig.ptrs[p] + self._flag_bytes
-        rc = _lib.lib().cocclkFusedCollective(a, 1, self.policy.max_ctas, _lib.cur_stream())
+        if self._trace is not None:
+            self._trace.zero_()
+            a.trace[self.rank] = self._trace.data_ptr()
+        with nvtx_range(f"coccl.fused.{K_NAMES.get(opc, opc)}.{cfg.kind}"):
+            rc = _lib.lib().cocclkFusedCollective(a, 1, self.policy.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkFusedCollective")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += inp.numel() * inp.element_size()
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Record per-CTA phase timestamps of every following fused collective (see utils.trace)."""
+        from ..utils.trace import TRACE_MAX_CTAS
+        self._trace = torch.zeros(TRACE_MAX_CTAS, 4, dtype=torch.int64, device=self.device) if on else None
+
+    def phase_times(self) -> dict:
+        """Phase durations (us) of the last fused collective on this rank; synchronises the device."""
+        from ..utils.trace import summarise
+        if self._trace is None:
+            return {}
+        torch.cuda.synchronize()
+        return summarise(self._trace)
 
     def status(self) -> int:
         """Error word written by bounded waits (0 = ok). Synchronises the device."""
@@ -230,7 +251,8 @@ class Communicator:
             self._fused(K.OP_RS, inp, out, cfg)
         else:
             self._native(nbytes)
-            dist.reduce_scatter_tensor(out, inp, group=self.group)
+            with nvtx_range("coccl.native.reduce_scatter"):
+                dist.reduce_scatter_tensor(out, inp, group=self.group)
         return out
 
     def all_gather(self, inp: torch.Tensor, out: torch.Tensor, role: str = "default"):
@@ -243,7 +265,8 @@ class Communicator:
             self._fused(K.OP_AG, inp, out, cfg)
         else:
             self._native(nbytes)
-            dist.all_gather_into_tensor(out, inp, group=self.group)
+            with nvtx_range("coccl.native.all_gather"):
+                dist.all_gather_into_tensor(out, inp, group=self.group)
         return out
 
     def all_reduce(self, x: torch.Tensor, role: str = "default"):
@@ -256,7 +279,8 @@ class Communicator:
             self._fused(op, x, x, cfg)
         else:
             self._native(nbytes)
-            dist.all_reduce(x, group=self.group)
+            with nvtx_range("coccl.native.all_reduce"):
+                dist.all_reduce(x, group=self.group)
         return x
 
     def all_to_all(self, inp: torch.Tensor, out: torch.Tensor, role: str = "default"):
@@ -269,7 +293,8 @@ class Communicator:
             self._fused(K.OP_A2A, inp, out, cfg)
         else:
             self._native(nbytes)
-            dist.all_to_all_single(out, inp, group=self.group)
+            with nvtx_range("coccl.native.all_to_all"):
+                dist.all_to_all_single(out, inp, group=self.group)
         return out
 
     # ------------------------------------------------------------------ tensor-parallel fusions

@@ -113,3 +113,21 @@ def test_bounded_wait_reports_missing_peer(cuda):
     assert (code >> 23) & 0xFF == 2 and (code >> 15) & 0xFF == 1  # phase 2 waited for peer 1
     # the context is still usable
     assert torch.isfinite(torch.ones(4, device=cuda).sum()).item()
+
+
+def test_phase_trace_records_ordered_timestamps(cuda):
+    """Device-side phase trace: every CTA stamps kernel start <= encode done <= decode done <= gather done."""
+    from coccl_b200.utils.trace import TRACE_MAX_CTAS, summarise
+    n, numel = 4, 4 * 70000
+    xs = [torch.randn(numel, device=cuda) * 0.01 for _ in range(n)]
+    state = {"trace": [torch.zeros(TRACE_MAX_CTAS, 4, dtype=torch.int64, device=cuda) for _ in range(n)]}
+    K.emulate_collective("all_reduce_twoshot", xs, CFGS["sdp4bit"], state=state)
+    torch.cuda.synchronize()
+    assert K.status_codes(state) == [0] * n
+    for r in range(n):
+        t = state["trace"][r].cpu()
+        rows = t[t[:, 0] != 0]
+        assert rows.shape[0] > 0
+        assert (rows[:, 0] <= rows[:, 1]).all() and (rows[:, 1] <= rows[:, 2]).all() and (rows[:, 2] <= rows[:, 3]).all()
+        s = summarise(state["trace"][r])
+        assert s["total_us"] > 0 and s["ctas"] == rows.shape[0]
