@@ -148,7 +148,9 @@ class TransformerLayer(nn.Module):
         cfg, t = self.cfg, self.tp.size
         nh, d = cfg.n_head // t, cfg.head_dim
         qkv = qkv.view(batch, seq, nh, 3, d)
-        q, k, v = (qkv[:, :, :, i].transpose(1, 2) for i in range(3))  # [b, heads, s, d] views
+        # unbind: its backward is ONE stack of dq/dk/dv into the packed gradient (three selects would each
+        # materialise a zero-filled copy of the whole tensor and add them up)
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(3))  # [b, heads, s, d] views
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return o.transpose(1, 2).reshape(batch * seq, nh * d)
 
