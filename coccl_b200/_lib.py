@@ -64,6 +64,9 @@ _PROTOS = {
     "cocclkTileElems": (c_int, []),
     "cocclkSlotBytes": (c_long, [C.POINTER(Codec), c_long]),
     "cocclkFusedCollective": (c_int, [C.POINTER(CollArgs), c_int, c_int, c_void_p]),
+    "cocclkNvlsFlagBytes": (c_long, []),
+    "cocclkNvlsAllReduce": (c_int, [c_void_p, c_long, c_int, c_int, c_int, C.POINTER(c_void_p), c_void_p, c_uint, c_ulonglong,
+                                    c_int, c_void_p]),
     # gemm_api.h
     "cocclkGemmBf16": (c_int, [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),

@@ -84,6 +84,14 @@ int cocclkReduceChunks(const void* in, void* out, long count, int numChunks, lon
                        cudaStream_t stream);
 int cocclkPackSlice(const void* src, void* dst, long sliceBytes, long srcPitchBytes, long srcOffsetBytes, int chunks,
                     int ranksPerNode, int nNodes, int unpack, cudaStream_t stream);
+/* Uncompressed all-reduce of a symmetric buffer through the NVSwitch (multimem.ld_reduce / multimem.st).
+   multicastPtr: multicast address of element 0 of a buffer every rank has bound to the same multicast object;
+   flags[r]: cocclkNvlsFlagBytes() zero-initialised bytes on rank r as mapped here. count * size must be a multiple of
+   16 * nRanks. The result replaces the buffer's contents on every rank. */
+long cocclkNvlsFlagBytes(void);
+int cocclkNvlsAllReduce(void* multicastPtr, long count, int dtype, int nRanks, int rank, unsigned int* const* flags,
+                        void* status, unsigned int epoch, unsigned long long timeoutNs, int maxCtas, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

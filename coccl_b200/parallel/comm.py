@@ -44,6 +44,7 @@ class Policy:
         ("default", "all_to_all"): SDP4BIT_G128,
     })
     all_reduce_oneshot_max_bytes: int = 1 << 20
+    nvls_all_reduce: bool = False   # uncompressed all-reduce below the threshold through multimem instead of NCCL
     timeout_ms: float = 20000.0
     max_ctas: int = 0
 
@@ -151,6 +152,7 @@ class Communicator:
         self._tp_half = 0
         self._tp_epoch = 0
         self._moe: _Arena | None = None
+        self._nvls: dict | None = None
         self._trace: torch.Tensor | None = None
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
@@ -269,11 +271,61 @@ class Communicator:
                 dist.all_gather_into_tensor(out, inp, group=self.group)
         return out
 
+    # ------------------------------------------------------------------ NVSwitch (multimem) all-reduce
+    def _ensure_nvls(self, nbytes: int) -> bool:
+        """Symmetric buffer bound to a multicast object (torch symmetric memory does the allocation and the
+        binding; the reduction kernel is csrc/kernels/nvls_kernels.cu). False when the fabric has no multicast."""
+        if self._nvls is not None and self._nvls["bytes"] >= nbytes:
+            return self._nvls["mc"] != 0
+        if self._nvls is not None and self._nvls["mc"] == 0:
+            return False
+        import torch.distributed._symmetric_memory as symm_mem
+        size = max(nbytes, 64 << 20)
+        try:
+            t = symm_mem.empty(size, dtype=torch.uint8, device=self.device)
+            h = symm_mem.rendezvous(t, (self.group or dist.group.WORLD).group_name)
+            mc = int(h.multicast_ptr or 0)
+        except Exception:  # noqa: BLE001 - no symmetric memory support in this build / on this fabric
+            t, h, mc = None, None, 0
+        ok = torch.tensor([1 if mc else 0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            mc = 0
+        flags = self._nvls["flags"] if self._nvls is not None else _Symm(self, _lib.lib().cocclkNvlsFlagBytes() + 256)
+        epoch = self._nvls["epoch"] if self._nvls is not None else 0
+        self._nvls = {"t": t, "h": h, "mc": mc, "bytes": size, "flags": flags, "epoch": epoch}
+        return mc != 0
+
+    def all_reduce_nvls(self, x: torch.Tensor) -> bool:
+        """In-place sum over ranks through the switch. Returns False (x untouched) when multicast is unavailable or
+        the size does not split into 16-byte vectors per rank."""
+        nbytes = x.numel() * x.element_size()
+        if x.dtype not in DTYPE_CODE or nbytes % (16 * self.size) != 0 or not x.is_contiguous():
+            return False
+        if not self._ensure_nvls(nbytes):
+            return False
+        st = self._nvls
+        buf = st["t"][:nbytes].view(x.dtype)
+        buf.copy_(x.view(-1))
+        st["epoch"] += 1
+        fl = (C.c_void_p * self.size)(*[st["flags"].ptrs[p] for p in range(self.size)])
+        status = st["flags"].ptrs[self.rank] + _lib.lib().cocclkNvlsFlagBytes()
+        with nvtx_range("coccl.nvls.all_reduce"):
+            rc = _lib.lib().cocclkNvlsAllReduce(st["mc"], x.numel(), DTYPE_CODE[x.dtype], self.size, self.rank, fl, status,
+                                                st["epoch"] & 0x7FFFFFFF, int(self.policy.timeout_ms * 1e6),
+                                                self.policy.max_ctas, _lib.cur_stream())
+        _lib.check(rc, "cocclkNvlsAllReduce")
+        x.view(-1).copy_(buf)
+        self.stats["nvls_calls"] = self.stats.get("nvls_calls", 0) + 1
+        return True
+
     def all_reduce(self, x: torch.Tensor, role: str = "default"):
         if self.size == 1:
             return x
         nbytes = x.numel() * x.element_size()
         cfg = self._route(role, "all_reduce", x, nbytes, divisible=(x.numel() % self.size == 0))
+        if cfg is None and self.policy.nvls_all_reduce and self.cuda and x.is_cuda and self.all_reduce_nvls(x):
+            return x
         if cfg is not None:
             op = K.OP_AR1 if nbytes <= self.policy.all_reduce_oneshot_max_bytes else K.OP_AR2
             self._fused(op, x, x, cfg)
@@ -446,7 +498,7 @@ class Communicator:
             torch.cuda.synchronize()
             if self.size > 1:
                 dist.barrier(group=self.group)
-        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig, self._moe):
+        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig, self._moe, self._nvls["flags"] if self._nvls else None):
             if s is not None:
                 s.free()
         self._ws = self._sig = None

@@ -167,3 +167,37 @@ def _moe_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_moe_layer_expert_parallel():
     run_distributed(_moe_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
+
+
+def _nvls_worker(rank, world):
+    import torch.distributed as dist
+    from coccl_b200.parallel.comm import Communicator, Policy
+    dev = torch.device("cuda", rank)
+    comm = Communicator(None, dev, Policy(nvls_all_reduce=True, threshold_bytes=1 << 30), "nvls")
+    used, bad = 0, []
+    for dtype, n in ((torch.float32, 4096 * world), (torch.bfloat16, 1 << 20), (torch.float32, (1 << 22) + 64 * world)):
+        for it in range(2):
+            torch.manual_seed(11 + rank + it)
+            x = torch.randn(n, device=dev).to(dtype)
+            ref = x.clone()
+            dist.all_reduce(ref)
+            comm.all_reduce(x)  # below the threshold: multimem path when the fabric offers multicast, else NCCL
+            tol = 1e-5 if dtype == torch.float32 else 3e-2
+            if not torch.allclose(x.float(), ref.float(), atol=tol * ref.float().abs().max().item(), rtol=0):
+                bad.append((str(dtype), n, it))
+    used = comm.stats.get("nvls_calls", 0)
+    if rank == 0:
+        print(f"nvls_calls={used} (0 means the fabric offers no multicast and NCCL served the calls)")
+    # leave in order before judging the result: no rank exits while its memory is still bound to the multicast object
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.close()
+    comm._nvls = None
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert not bad, bad
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_nvls_all_reduce_or_native_fallback():
+    run_distributed(_nvls_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
