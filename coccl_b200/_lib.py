@@ -37,7 +37,7 @@ class CollArgs(C.Structure):
 class TpArgs(C.Structure):
     """Mirror of cocclkTpArgs (csrc/kernels/tp_api.h)."""
     _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("epi", c_int),
-                ("epoch", c_uint), ("timeoutNs", c_ulonglong),
+                ("bMN", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong),
                 ("a", c_void_p * MAX_RANKS), ("b", c_void_p * MAX_RANKS), ("c", c_void_p * MAX_RANKS),
                 ("bias", c_void_p * MAX_RANKS), ("z", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
                 ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS)]

@@ -21,10 +21,11 @@ typedef struct {
   int nRanks, rankBase;
   int M, N, K;        // ag_gemm: C[M,N] = gather(A)[M,K] * B[N,K]^T; gemm_rs: out[M/nRanks,N] = reduce_scatter(A[M,K] * B[N,K]^T)
   int epi;            // ag_gemm: GEMM_EPI_NONE | GEMM_EPI_BIAS | GEMM_EPI_BIAS_GELU
+  int bMN;            // 0: B is [N, K] with K contiguous; 1: B is stored [K, N] with N contiguous (backward passes)
   unsigned int epoch; // strictly increasing per workspace; flags carry it
   unsigned long long timeoutNs;
   const void* a[COCCLK_TP_MAX_RANKS];     // ag_gemm: own shard [M/nRanks, K] bf16; gemm_rs: A [M, K] bf16
-  const void* b[COCCLK_TP_MAX_RANKS];     // [N, K] bf16, K contiguous
+  const void* b[COCCLK_TP_MAX_RANKS];     // bf16 weights, layout per bMN
   void* c[COCCLK_TP_MAX_RANKS];           // ag_gemm: [M, N] bf16; gemm_rs: [M/nRanks, N] bf16
   const void* bias[COCCLK_TP_MAX_RANKS];  // ag_gemm, optional
   void* z[COCCLK_TP_MAX_RANKS];           // ag_gemm with GELU: optional pre-activation output

@@ -103,6 +103,15 @@ __device__ __forceinline__ void pipeTeardown(const Pipe& p, unsigned int* err, u
   if (threadIdx.x == 0 && p.bars->abortFlag && err) atomicExch(err, code);
 }
 
+// B tile of one stage: 256 weight rows x 64 k (K-major), or four 64-column x 64-k boxes (stored [K, N])
+__device__ __forceinline__ void loadB(uint8_t* sb, const CUtensorMap* tmB, uint64_t* bar, int kb, int tn, bool bMN) {
+  if (!bMN) {
+    tmaLoad2d(sb, tmB, bar, kb * BK, tn * BN);
+  } else {
+    for (int i = 0; i < BN / 64; ++i) tmaLoad2d(sb + i * 8192, tmB, bar, tn * BN + i * 64, kb * BK);
+  }
+}
+
 // give copies already issued a bounded time to land before the CTA may leave
 __device__ __forceinline__ void drainProducer(const Pipe& p, uint32_t it) {
   for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
@@ -115,8 +124,8 @@ __device__ __forceinline__ void drainProducer(const Pipe& p, uint32_t it) {
 }
 
 // MMA issuer: identical for both kernels (K-major operands).
-__device__ __forceinline__ void mmaRole(const Pipe& p, int numTiles, int kBlocks) {
-  const uint32_t idesc = makeInstrDescBf16(BM, BN, false, false);
+__device__ __forceinline__ void mmaRole(const Pipe& p, int numTiles, int kBlocks, bool bMN) {
+  const uint32_t idesc = makeInstrDescBf16(BM, BN, false, bMN);
   uint32_t it = 0, tileIdx = 0;
   bool ok = true;
   for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileIdx) {
@@ -133,8 +142,10 @@ __device__ __forceinline__ void mmaRole(const Pipe& p, int numTiles, int kBlocks
       const uint32_t sa = smemAddr(p.smem + s * kStageBytes);
       const uint32_t sb = sa + kABytes;
 #pragma unroll
-      for (int k = 0; k < BK / 16; ++k)
-        umma(dTmem, makeSmemDesc(sa + k * 32, 16, 1024), makeSmemDesc(sb + k * 32, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+      for (int k = 0; k < BK / 16; ++k) {
+        const uint64_t db = bMN ? makeSmemDesc(sb + k * 2048, 8192, 1024) : makeSmemDesc(sb + k * 32, 16, 1024);
+        umma(dTmem, makeSmemDesc(sa + k * 32, 16, 1024), db, idesc, (kb | k) != 0 ? 1u : 0u);
+      }
       ummaCommit(&p.bars->empty[s]);
       if (kb == kBlocks - 1) ummaCommit(&p.bars->tmemFull[acc]);
     }
@@ -194,13 +205,13 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmKernel(const __grid_constan
           uint8_t* sa = p.smem + s * kStageBytes;
           mbarArriveExpectTx(&p.bars->full[s], kStageBytes);
           tmaLoad2d(sa, tmA, &p.bars->full[s], kb * BK, arow);
-          tmaLoad2d(sa + kABytes, tmB, &p.bars->full[s], kb * BK, tn * BN);
+          loadB(sa + kABytes, tmB, &p.bars->full[s], kb, tn, a.bMN != 0);
         }
       }
       if (!ok) drainProducer(p, it);
     }
   } else if (warp == 1) {
-    if (lane == 0) mmaRole(p, numTiles, kBlocks);
+    if (lane == 0) mmaRole(p, numTiles, kBlocks, a.bMN != 0);
   } else if (warp < 6) {
     GemmArgs g;
     g.C = a.c[rank]; g.Z = a.z[rank]; g.bias = a.bias[rank]; g.M = a.M; g.N = a.N; g.K = a.K; g.ldc = a.N;
@@ -302,13 +313,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemmRsKernel(const __grid_constan
           uint8_t* sa = p.smem + s * kStageBytes;
           mbarArriveExpectTx(&p.bars->full[s], kStageBytes);
           tmaLoad2d(sa, tmA, &p.bars->full[s], kb * BK, arow);
-          tmaLoad2d(sa + kABytes, tmB, &p.bars->full[s], kb * BK, tn * BN);
+          loadB(sa + kABytes, tmB, &p.bars->full[s], kb, tn, a.bMN != 0);
         }
       }
       if (!ok) drainProducer(p, it);
     }
   } else if (warp == 1) {
-    if (lane == 0) mmaRole(p, numTiles, kBlocks);
+    if (lane == 0) mmaRole(p, numTiles, kBlocks, a.bMN != 0);
   } else if (warp < 6) {
     // ---------------- epilogue: quantise, stage, push to the destination's slot ----------------
     const int quad = warp & 3;
@@ -502,7 +513,8 @@ extern "C" int cocclkAgGemm(const cocclkTpArgs* args, int emulatedRanks, int max
     if (rc) return rc;
     rc = makeBf16TensorMap(&P.maps[e][1], args->a[r], args->K, rowsPerShard, args->K, BK, BM);
     if (rc) return rc;
-    rc = makeBf16TensorMap(&P.maps[e][2], args->b[r], args->K, args->N, args->K, BK, BN);
+    rc = args->bMN ? makeBf16TensorMap(&P.maps[e][2], args->b[r], args->N, args->K, args->N, 64, 64)
+                   : makeBf16TensorMap(&P.maps[e][2], args->b[r], args->K, args->N, args->K, BK, BN);
     if (rc) return rc;
   }
   const long tiles = (long)(args->M / BM) * ((args->N + BN - 1) / BN);
@@ -521,7 +533,8 @@ extern "C" int cocclkGemmRs(const cocclkTpArgs* args, int emulatedRanks, int max
     int rc = makeBf16TensorMap(&P.maps[e][0], args->a[r], args->K, args->M, args->K, BK, BM);
     if (rc) return rc;
     P.maps[e][1] = P.maps[e][0];
-    rc = makeBf16TensorMap(&P.maps[e][2], args->b[r], args->K, args->N, args->K, BK, BN);
+    rc = args->bMN ? makeBf16TensorMap(&P.maps[e][2], args->b[r], args->N, args->K, args->N, 64, 64)
+                   : makeBf16TensorMap(&P.maps[e][2], args->b[r], args->K, args->N, args->K, BK, BN);
     if (rc) return rc;
   }
   const long tiles = (long)(args->M / BM) * (args->N / BN);

@@ -78,3 +78,10 @@ extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
 extern "C" int cocclHostRead32(const void* dev, unsigned int* out) {
   return (int)cudaMemcpy(out, dev, sizeof(unsigned int), cudaMemcpyDeviceToHost);
 }
+
+// Stream-ordered device-to-device copy between raw addresses (e.g. out of a symmetric workspace, which has no
+// framework tensor behind it).
+extern "C" int cocclDeviceCopy(void* dst, const void* src, size_t bytes, cudaStream_t stream) {
+  if (bytes == 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);
+}

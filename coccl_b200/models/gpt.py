@@ -69,6 +69,8 @@ class NoTP:
     def scatter_sum_tokens(self, x): return x
     def all_reduce_sum(self, x): return x
     def copy_to_tp(self, x): return x
+    def gather_linear(self, x, w, bias=None, gelu=False): return fused.linear(x, w, bias, gelu=gelu)
+    def linear_scatter(self, x, w, bias=None): return fused.linear(x, w, bias)
     def vocab_parallel_cross_entropy(self, logits, targets, scale): return fused.cross_entropy(logits, targets, scale)
 
 
@@ -161,17 +163,14 @@ class TransformerLayer(nn.Module):
             y = fused.layer_norm(x, self.ln1_weight, self.ln1_bias, self.cfg.eps)
         else:
             y, x = fused.layer_norm(x, self.ln1_weight, self.ln1_bias, self.cfg.eps, residual=delta)
-        y = tp.gather_tokens(y)
-        qkv = fused.linear(y, self.qkv_weight, self.qkv_bias)
+        # column-parallel: gather the token shards (fused into the GEMM kernel when the shapes allow it)
+        qkv = tp.gather_linear(y, self.qkv_weight, self.qkv_bias)
         a = self.attention(qkv, batch, seq)
-        # row-parallel: the bias is added once, after the reduction (rank 0 carries it)
-        o = fused.linear(a, self.proj_weight, self.proj_bias if tp.rank == 0 else None)
-        o = tp.scatter_sum_tokens(o)
+        # row-parallel: partial sums are reduce-scattered over the token shards; the bias is added once
+        o = tp.linear_scatter(a, self.proj_weight, self.proj_bias)
         y, x = fused.layer_norm(x, self.ln2_weight, self.ln2_bias, self.cfg.eps, residual=o)
-        y = tp.gather_tokens(y)
-        z = fused.linear(y, self.fc1_weight, self.fc1_bias, gelu=True)
-        o = fused.linear(z, self.fc2_weight, self.fc2_bias if tp.rank == 0 else None)
-        o = tp.scatter_sum_tokens(o)
+        z = tp.gather_linear(y, self.fc1_weight, self.fc1_bias, gelu=True)
+        o = tp.linear_scatter(z, self.fc2_weight, self.fc2_bias)
         return x, o
 
 

@@ -50,17 +50,18 @@ def check_state(state) -> None:
 
 
 def emulate_ag_gemm(x_shards, w_shards, *, bias=None, gelu=False, state=None, epoch=1, max_ctas=0,
-                    timeout_ms=5000.0):
-    """C_r = concat(x_shards) @ w_shards[r].T (+ bias_r, GELU) for every emulated rank r."""
+                    timeout_ms=5000.0, b_mn=False):
+    """C_r = concat(x_shards) @ w_shards[r].T (+ bias_r, GELU) for every emulated rank r (w [K, N] with b_mn)."""
     n = len(x_shards)
     m, K = x_shards[0].shape
-    N = w_shards[0].shape[0]
+    N = w_shards[0].shape[1] if b_mn else w_shards[0].shape[0]
     dev = x_shards[0].device
     state = _state(state if state is not None else {}, n, dev, ag_ws_bytes(m * n, K))
     outs = [torch.empty(m * n, N, dtype=torch.bfloat16, device=dev) for _ in range(n)]
     a = _lib.TpArgs()
     a.nRanks, a.rankBase, a.M, a.N, a.K = n, 0, m * n, N, K
     a.epi = EPI_NONE if bias is None else (EPI_BIAS_GELU if gelu else EPI_BIAS)
+    a.bMN = int(b_mn)
     a.epoch, a.timeoutNs = epoch, int(timeout_ms * 1e6)
     _fill(a, state, n)
     for r in range(n):
@@ -71,17 +72,18 @@ def emulate_ag_gemm(x_shards, w_shards, *, bias=None, gelu=False, state=None, ep
     return outs, state
 
 
-def emulate_gemm_rs(a_list, w_list, *, state=None, epoch=1, max_ctas=0, timeout_ms=5000.0):
+def emulate_gemm_rs(a_list, w_list, *, state=None, epoch=1, max_ctas=0, timeout_ms=5000.0, b_mn=False):
     """out_r = rows r of sum_q (a_list[q] @ w_list[q].T), the partial products sent as block-scaled FP8."""
     n = len(a_list)
     M, K = a_list[0].shape
-    N = w_list[0].shape[0]
+    N = w_list[0].shape[1] if b_mn else w_list[0].shape[0]
     dev = a_list[0].device
     state = _state(state if state is not None else {}, n, dev, rs_ws_bytes(M, N, n))
     outs = [torch.empty(M // n, N, dtype=torch.bfloat16, device=dev) for _ in range(n)]
     a = _lib.TpArgs()
     a.nRanks, a.rankBase, a.M, a.N, a.K = n, 0, M, N, K
     a.epi, a.epoch, a.timeoutNs = EPI_NONE, epoch, int(timeout_ms * 1e6)
+    a.bMN = int(b_mn)
     _fill(a, state, n)
     for r in range(n):
         assert a_list[r].is_contiguous() and w_list[r].is_contiguous()

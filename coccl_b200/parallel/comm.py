@@ -380,12 +380,15 @@ class Communicator:
         return a
 
     def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gelu: bool = False,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, *, b_mn: bool = False, save_preact: bool = False,
+                gathered: torch.Tensor | None = None):
         """concat_over_ranks(x_local) @ w.T (+ bias, GELU) in ONE kernel: the shards travel over peer memory
-        while the tensor cores already work on the local shard. x_local [m, K], w [N, K], both bf16."""
+        while the tensor cores already work on the local shard. x_local [m, K] bf16; w [N, K], or [K, N] with
+        b_mn=True (then the product is gather(x) @ w). save_preact: also return the pre-activation (GELU only).
+        gathered: optional [M, K] tensor that receives the gathered input (for a later weight gradient)."""
         from ..ops import tp_fused as T
         m, K = x_local.shape
-        N = w.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
         M = m * self.size
         assert x_local.is_contiguous() and w.is_contiguous() and x_local.dtype == torch.bfloat16
         if out is None:
@@ -393,29 +396,58 @@ class Communicator:
         self._ensure_tp(T.ag_ws_bytes(M, K))
         a = self._tp_args(M, N, K)
         a.epi = T.EPI_NONE if bias is None else (T.EPI_BIAS_GELU if gelu else T.EPI_BIAS)
+        a.bMN = int(b_mn)
         a.a[self.rank], a.b[self.rank], a.c[self.rank] = x_local.data_ptr(), w.data_ptr(), out.data_ptr()
         a.bias[self.rank] = bias.data_ptr() if bias is not None else None
-        _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
+        z = None
+        if save_preact and gelu and bias is not None:
+            z = torch.empty_like(out)
+            a.z[self.rank] = z.data_ptr()
+        with nvtx_range("coccl.fused.ag_gemm"):
+            _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
         self.stats["compressed_calls"] += 1
-        return out
+        if gathered is not None:
+            # the peers' shards are in this call's half of the workspace, the own shard never left x_local
+            cp = _lib.declare("cocclDeviceCopy", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p])
+            row = K * 2
+            ws, r, st = a.ws[self.rank], self.rank, _lib.cur_stream()
+            if r > 0:
+                _lib.check(cp(gathered.data_ptr(), ws, r * m * row, st), "cocclDeviceCopy")
+            if r + 1 < self.size:
+                off = (r + 1) * m * row
+                _lib.check(cp(gathered.data_ptr() + off, ws + off, (self.size - r - 1) * m * row, st), "cocclDeviceCopy")
+            gathered[r * m:(r + 1) * m].copy_(x_local)
+        return (out, z) if save_preact else out
 
-    def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, b_mn: bool = False) -> torch.Tensor:
         """reduce_scatter over ranks of (a_mat @ w.T) along the rows, in ONE kernel: the partial products leave
-        the GEMM epilogue as block-scaled FP8 straight into the destination ranks' memory. a_mat [M, K], w [N, K]."""
+        the GEMM epilogue as block-scaled FP8 straight into the destination ranks' memory. a_mat [M, K]; w [N, K],
+        or [K, N] with b_mn=True (then the product is a_mat @ w)."""
         from ..ops import tp_fused as T
         M, K = a_mat.shape
-        N = w.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
         assert a_mat.is_contiguous() and w.is_contiguous() and a_mat.dtype == torch.bfloat16
         if out is None:
             out = torch.empty(M // self.size, N, dtype=torch.bfloat16, device=a_mat.device)
         self._ensure_tp(T.rs_ws_bytes(M, N, self.size))
         a = self._tp_args(M, N, K)
         a.epi = T.EPI_NONE
+        a.bMN = int(b_mn)
         a.a[self.rank], a.b[self.rank], a.c[self.rank] = a_mat.data_ptr(), w.data_ptr(), out.data_ptr()
-        _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
+        with nvtx_range("coccl.fused.gemm_rs"):
+            _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += M * N * 2
         return out
+
+    def tp_fusable(self, rows_total: int, n_out_rs: int | None = None) -> bool:
+        """Whether the one-kernel TP fusions accept a problem with `rows_total` gathered rows (and, for gemm_rs,
+        `n_out_rs` output columns)."""
+        if not (self.cuda and self.policy.enabled and 1 < self.size <= _lib.MAX_RANKS):
+            return False
+        if rows_total % (self.size * 128) != 0:
+            return False
+        return n_out_rs is None or n_out_rs % 256 == 0
 
     def tp_status(self) -> tuple[int, int]:
         """(status word, pipeline error word) of the tensor-parallel fusions; synchronises the device."""

@@ -115,6 +115,82 @@ class _VocabParallelCE(torch.autograd.Function):
         return g, None, None, None
 
 
+def _gelu_bwd(dy2, z):
+    from .. import _lib
+    dz = torch.empty_like(dy2)
+    _lib.check(_lib.lib().cocclkGeluBwd(dy2.data_ptr(), z.data_ptr(), dz.data_ptr(), dz.numel(), _lib.cur_stream()), "cocclkGeluBwd")
+    return dz
+
+
+def _col_sum(bias, dy2):
+    from .. import _lib
+    M, N = dy2.shape
+
+    def run(out, acc):
+        sc = fused.scratch(dy2.device, _lib.lib().cocclkColSumBlocks(M) * N, "colsum")
+        _lib.check(_lib.lib().cocclkColSum(dy2.data_ptr(), out.data_ptr(), int(acc), sc.data_ptr(), M, N, _lib.cur_stream()),
+                   "cocclkColSum")
+    return fused._accum_param_grad(bias, None, run)
+
+
+class _GatherLinear(torch.autograd.Function):
+    """Column-parallel linear on sequence shards as ONE kernel per direction:
+    forward  y = act(gather(x) @ w.T + b)      (all-gather -> GEMM, csrc/kernels/tp_kernels.cu agGemmKernel)
+    backward dx = reduce_scatter(dy @ w)        (GEMM -> FP8 reduce-scatter, gemmRsKernel)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, gelu, comm):
+        m, K = x.shape
+        xg = torch.empty(m * comm.size, K, dtype=x.dtype, device=x.device)
+        if gelu:
+            y, z = comm.ag_gemm(x.contiguous(), w, bias, True, save_preact=True, gathered=xg)
+        else:
+            y, z = comm.ag_gemm(x.contiguous(), w, bias, False, gathered=xg), None
+        ctx.save_for_backward(xg, w, bias, z)
+        ctx.comm, ctx.gelu = comm, gelu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, w, bias, z = ctx.saved_tensors
+        from ..ops import gemm as G
+        dy2 = dy.contiguous()
+        if ctx.gelu:
+            dy2 = _gelu_bwd(dy2, z)
+        dx = ctx.comm.gemm_rs(dy2, w, b_mn=True) if ctx.needs_input_grad[0] else None   # w [N, K] is "[contraction, out]"
+        dw = fused._accum_param_grad(w, None, lambda out, acc: G.gemm(dy2.t(), xg.t(), out=out, accumulate=acc))
+        db = _col_sum(bias, dy2) if bias is not None else None
+        return dx, dw, db, None, None
+
+
+class _LinearScatter(torch.autograd.Function):
+    """Row-parallel linear whose partial sums are reduce-scattered over the token shards, ONE kernel per direction:
+    forward  o = reduce_scatter(x @ w.T) + b    (gemmRsKernel, FP8 on the wire)
+    backward dx = gather(do) @ w                 (agGemmKernel)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, comm):
+        x2 = x.contiguous()
+        o = comm.gemm_rs(x2, w)
+        if bias is not None:
+            o += bias  # every rank adds it to its own rows; its gradient is summed over the group with the other replicated ones
+        ctx.save_for_backward(x2, w, bias)
+        ctx.comm = comm
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        x2, w, bias = ctx.saved_tensors
+        from ..ops import gemm as G
+        comm = ctx.comm
+        d2 = do.contiguous()
+        dg = torch.empty(d2.shape[0] * comm.size, d2.shape[1], dtype=d2.dtype, device=d2.device)
+        dx = comm.ag_gemm(d2, w, b_mn=True, gathered=dg)   # w [h, f/t] is "[contraction, out]"
+        dw = fused._accum_param_grad(w, None, lambda out, acc: G.gemm(dg.t(), x2.t(), out=out, accumulate=acc))
+        db = _col_sum(bias, d2) if bias is not None else None
+        return dx, dw, db, None
+
+
 class TPContext:
     """Hooks the model calls; `comm` is the Communicator of the tensor-parallel group."""
 
@@ -122,6 +198,25 @@ class TPContext:
         self.comm = comm
         self.size, self.rank = comm.size, comm.rank
         self.sequence_parallel = sequence_parallel and comm.size > 1
+        self.fuse_gemm = True   # use the one-kernel all-gather->GEMM / GEMM->reduce-scatter fusions when they apply
+
+    def can_fuse(self, x_shard, n_out_rs=None) -> bool:
+        return (self.fuse_gemm and self.sequence_parallel and x_shard.is_cuda and x_shard.dim() == 2 and
+                self.comm.tp_fusable(x_shard.shape[0] * self.size, n_out_rs))
+
+    def gather_linear(self, x_shard, w, bias=None, gelu=False):
+        """act(gather_tokens(x_shard) @ w.T + bias) for a column-parallel weight shard."""
+        if self.can_fuse(x_shard, w.shape[1]):  # the backward reduce-scatters w.shape[1] columns
+            return _GatherLinear.apply(x_shard, w, bias, gelu, self.comm)
+        return fused.linear(self.gather_tokens(x_shard), w, bias, gelu=gelu)
+
+    def linear_scatter(self, x_full, w, bias=None):
+        """scatter_sum_tokens(x_full @ w.T) + bias for a row-parallel weight shard."""
+        if self.size > 1 and self.fuse_gemm and self.sequence_parallel and x_full.is_cuda and x_full.dim() == 2 and \
+                self.comm.tp_fusable(x_full.shape[0], w.shape[0]):
+            return _LinearScatter.apply(x_full, w, bias, self.comm)
+        o = fused.linear(x_full, w, bias if self.rank == 0 else None)
+        return self.scatter_sum_tokens(o)
 
     def gather_tokens(self, x):
         if self.size == 1:

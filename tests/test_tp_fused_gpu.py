@@ -60,3 +60,26 @@ def test_gemm_rs_emulated(cuda, n, M, N, K):
             rel = (got - ref).norm().item() / ref.norm().item()
             assert rel < 0.05, rel
         As = [a * 0.5 for a in As]
+
+
+def test_weights_stored_contraction_major(cuda):
+    """b_mn: the weight is stored [K, N] (the layout the backward passes meet); same products as with its transpose."""
+    torch.manual_seed(2)
+    n, m, N, K = 2, 256, 512, 320
+    xs = [torch.randn(m, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
+    ws = [torch.randn(K, N, device=cuda, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
+    outs, st = T.emulate_ag_gemm(xs, ws, b_mn=True, max_ctas=74)
+    torch.cuda.synchronize()
+    T.check_state(st)
+    xf = torch.cat(xs).float()
+    for r in range(n):
+        ref = xf @ ws[r].float()
+        assert (outs[r].float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+    As = [torch.randn(n * m, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
+    outs, st = T.emulate_gemm_rs(As, ws, b_mn=True, max_ctas=74)
+    torch.cuda.synchronize()
+    T.check_state(st)
+    exact = sum(As[q].float() @ ws[q].float() for q in range(n))
+    for r in range(n):
+        ref = exact[r * m:(r + 1) * m]
+        assert ((outs[r].float() - ref).norm() / ref.norm()).item() < 0.05
