@@ -48,7 +48,8 @@ class MoeArgs(C.Structure):
     _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("tokens", c_int), ("hidden", c_int), ("topk", c_int),
                 ("experts", c_int), ("capacity", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong)] + \
                [(n, c_void_p * MAX_RANKS) for n in ("x", "expertIds", "gates", "pos", "sendCounts", "recv", "recvOffsets",
-                                                   "recvCounts", "y", "out", "ws", "flags", "status")]
+                                                   "recvCounts", "y", "out", "rowScale", "dotWith", "dotOut", "ws", "flags",
+                                                   "status")]
 
 
 _PROTOS = {

@@ -198,7 +198,9 @@ extern "C" int cocclkGemmBf16Pair(const void* A, long lda, int aMN, const void* 
                                   int M, int N, int K, int epi, const void* bias, void* Z, unsigned int* err, int maxCtas,
                                   cudaStream_t stream) {
   using namespace pair;
-  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return -1;
+  // K-major operands have rows of K elements (16-byte multiples for TMA); operands stored with M / N contiguous put
+  // no constraint on K (rows past K read as zeros)
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || ((!aMN || !bMN) && (K & 7))) return -1;
   if ((epi == GEMM_EPI_BIAS || epi == GEMM_EPI_BIAS_GELU) && bias == nullptr) return -1;
   CUtensorMap ta, tb;
   int rc = aMN ? makeBf16TensorMap(&ta, A, M, K, lda, 64, 64) : makeBf16TensorMap(&ta, A, K, M, lda, BK, BM);

@@ -249,7 +249,9 @@ extern "C" int cocclkGemmGetVariant() {
 extern "C" int cocclkGemmBf16Single(const void* A, long lda, int aMN, const void* B, long ldb, int bMN, void* C, long ldc,
                               int M, int N, int K, int epi, const void* bias, void* Z, unsigned int* err,
                               int maxCtas, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return -1;
+  // K-major operands have rows of K elements (16-byte multiples for TMA); operands stored with M / N contiguous put
+  // no constraint on K (rows past K read as zeros)
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || ((!aMN || !bMN) && (K & 7))) return -1;
   if ((epi == GEMM_EPI_BIAS || epi == GEMM_EPI_BIAS_GELU) && bias == nullptr) return -1;
   CUtensorMap ta, tb;
   int rc;

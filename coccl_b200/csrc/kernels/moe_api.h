@@ -38,6 +38,9 @@ typedef struct {
   int* recvCounts[COCCLK_MOE_MAX_RANKS];         // dispatch out / combine in: [nRanks, localExperts] rows per (source, expert)
   const void* y[COCCLK_MOE_MAX_RANKS];           // combine: expert outputs, same layout as recv
   void* out[COCCLK_MOE_MAX_RANKS];               // combine out: [tokens, hidden] bf16
+  const float* rowScale[COCCLK_MOE_MAX_RANKS];   // dispatch, optional: [tokens, topk] factor applied to the row of every entry
+  const void* dotWith[COCCLK_MOE_MAX_RANKS];     // combine, optional: [tokens, hidden] bf16 ...
+  float* dotOut[COCCLK_MOE_MAX_RANKS];           // ... dotOut[t, j] = <returned row of entry (t, j), dotWith[t]> (gate gradients)
   void* ws[COCCLK_MOE_MAX_RANKS];                // cocclkMoeWorkspaceBytes() bytes
   unsigned int* flags[COCCLK_MOE_MAX_RANKS];     // cocclkFlagBytes() bytes
   void* status[COCCLK_MOE_MAX_RANKS];

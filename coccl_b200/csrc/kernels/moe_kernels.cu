@@ -175,11 +175,13 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x[rank]);
     const int* ids = a.expertIds[rank];
     const int* pos = a.pos[rank];
+    const float* rowScale = a.rowScale[rank];
     const int entries = a.tokens * a.topk;
     for (int en = gw; en < entries; en += GW) {
       const int t = en / a.topk, e = ids[en], p = pos[en];
       const int d = e / LE;
       if (p >= cap) continue;  // over capacity: dropped (cannot happen with capacity = tokens * topk)
+      const float rs = rowScale ? rowScale[en] : 1.f;
       const uint4* src = reinterpret_cast<const uint4*>(x + (long)t * H);
       uint8_t* wsd = reinterpret_cast<uint8_t*>(a.ws[d]);
       uint2* dp = reinterpret_cast<uint2*>(wsd + L.payloadOff + ((long)rank * cap + p) * H);
@@ -190,8 +192,8 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
         float v[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          v[2 * i] = __uint_as_float(w[i] << 16);
-          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+          v[2 * i] = __uint_as_float(w[i] << 16) * rs;
+          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u) * rs;
         }
         float m = 0.f;
 #pragma unroll
@@ -318,12 +320,29 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
   const int* pos = a.pos[rank];
   const float* gates = a.gates[rank];
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out[rank]);
+  const __nv_bfloat16* dotWith = reinterpret_cast<const __nv_bfloat16*>(a.dotWith[rank]);
+  float* dotOut = a.dotOut[rank];
   for (int t = gw; t < a.tokens; t += GW) {
+    float dots[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dots[j] = 0.f;
     for (int it = 0; it < H / 256; ++it) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int j = 0; j < a.topk; ++j) {
+      float dw[8];
+      if (dotOut != nullptr) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(dotWith + (long)t * H) + it * 32 + lane);
+        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dw[2 * i] = __uint_as_float(qw[i] << 16);
+          dw[2 * i + 1] = __uint_as_float(qw[i] & 0xffff0000u);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j >= a.topk) break;
         const int en = t * a.topk + j;
         const int p = pos[en];
         if (p >= cap) continue;
@@ -333,8 +352,10 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          acc[2 * i] = fmaf(g, __uint_as_float(w[i] << 16), acc[2 * i]);
-          acc[2 * i + 1] = fmaf(g, __uint_as_float(w[i] & 0xffff0000u), acc[2 * i + 1]);
+          const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xffff0000u);
+          acc[2 * i] = fmaf(g, lo, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(g, hi, acc[2 * i + 1]);
+          if (dotOut != nullptr) dots[j] = fmaf(lo, dw[2 * i], fmaf(hi, dw[2 * i + 1], dots[j]));
         }
       }
       uint32_t o[4];
@@ -344,6 +365,15 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
         o[i] = *reinterpret_cast<uint32_t*>(&h);
       }
       reinterpret_cast<uint4*>(out + (long)t * H)[it * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    if (dotOut != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j >= a.topk) break;
+        float d = dots[j];
+        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (lane == 0) dotOut[t * a.topk + j] = d;
+      }
     }
   }
 }

@@ -1,6 +1,8 @@
 """Expert-parallel MoE feed-forward layer: top-k router, FP8 dispatch, per-expert MLP on the tcgen05 GEMM,
-bf16 gate-weighted combine. Forward path (serving / evaluation); the token exchange kernels are in
-csrc/kernels/moe_kernels.cu.
+bf16 gate-weighted combine; the token exchange kernels are in csrc/kernels/moe_kernels.cu. The exchange is
+differentiable: the backward of the dispatch is a combine with unit gates, the backward of the combine is a
+dispatch of the output gradient scaled by the gates (FP8 on the wire) plus the gate gradients, which the combine
+kernel computes as dot products on the token side.
 
 The reference has no model code; its hook for this traffic is the compressed AllToAll
 (extensions/primitives/coccl_alltoall.cc:12-21) selected by the `normal.all_to_all` policy slot.
@@ -9,8 +11,54 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import fused
 from ..ops import gemm as G
 from ..parallel.comm import Communicator
+
+
+class _Exchange:
+    """Routing of one forward pass, shared by the dispatch and the combine."""
+
+    def __init__(self, comm, ids, n_experts):
+        from ..ops import moe as M
+        self.comm, self.ids, self.n_experts = comm, ids, n_experts
+        self.layout = M.route_layout(ids, n_experts, comm.size)
+        self.handle = None
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ex):
+        rows, h = ex.comm.moe_dispatch(x.contiguous(), ex.ids, ex.n_experts, layout=ex.layout)
+        ex.handle = h
+        ctx.ex = ex
+        ctx.tokens = x.shape[0]
+        return rows
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        ex = ctx.ex
+        ones = torch.ones(ctx.tokens, ex.ids.shape[1], dtype=torch.float32, device=d_rows.device)
+        return ex.comm.moe_combine(d_rows.contiguous(), ones, ex.handle), None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, gates, ex):
+        ctx.ex = ex
+        ctx.save_for_backward(y, gates)
+        return ex.comm.moe_combine(y.contiguous(), gates.contiguous(), ex.handle)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        y, gates = ctx.saved_tensors
+        ex = ctx.ex
+        d_out = d_out.contiguous()
+        # dy[row(t, j)] = gates[t, j] * d_out[t]: the same routing, rows scaled per entry
+        d_y, _ = ex.comm.moe_dispatch(d_out, ex.ids, ex.n_experts, row_scale=gates.contiguous(), layout=ex.layout)
+        # d_gates[t, j] = <y[row(t, j)], d_out[t]>: send the expert outputs back once more and dot them on arrival
+        _, d_g = ex.comm.moe_combine(y.contiguous(), gates.contiguous(), ex.handle, dot_with=d_out)
+        return d_y, d_g, None
 
 
 class MoELayer:
@@ -36,28 +84,40 @@ class MoELayer:
             self.b_up.append(torch.zeros(ffn, device=dev, dtype=torch.bfloat16))
             self.w_down.append((torch.randn(hidden, ffn, generator=ge) * 0.02).to(dev, torch.bfloat16))
 
+    def parameters(self):
+        return [self.router, *self.w_up, *self.b_up, *self.w_down]
+
+    def requires_grad_(self, on: bool = True):
+        for p in self.parameters():
+            p.requires_grad_(on)
+        return self
+
     def route(self, x: torch.Tensor):
-        logits = G.gemm(x, self.router, out_dtype=torch.float32)
+        logits = fused.linear(x, self.router).float()
         top = logits.topk(self.topk, dim=1)
         return top.indices.to(torch.int32).contiguous(), torch.softmax(top.values, dim=1).contiguous()
 
     def experts(self, rows: torch.Tensor, offsets: list[int]) -> torch.Tensor:
-        y = torch.empty_like(rows)
+        outs, total = [], rows.shape[0]
         for le in range(self.local):
             lo, hi = offsets[le], offsets[le + 1]
             if hi > lo:
-                h = G.gemm(rows[lo:hi], self.w_up[le], bias=self.b_up[le], gelu=True)
-                G.gemm(h, self.w_down[le], out=y[lo:hi])
-        return y
+                h = fused.linear(rows[lo:hi], self.w_up[le], self.b_up[le], gelu=True)
+                outs.append(fused.linear(h, self.w_down[le]))
+        used = offsets[self.local]
+        if used < total:  # unused tail of the receive buffer
+            outs.append(rows.new_zeros(total - used, rows.shape[1]))
+        return torch.cat(outs) if outs else rows.new_zeros(total, rows.shape[1])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [tokens, hidden] bf16 -> [tokens, hidden] bf16."""
+        """x [tokens, hidden] bf16 -> [tokens, hidden] bf16 (differentiable)."""
         ids, gates = self.route(x)
         if self.comm.size == 1:
             return self.forward_local(x, ids, gates)
-        rows, h = self.comm.moe_dispatch(x, ids, self.n_experts)
-        y = self.experts(rows, h.recv_offsets.tolist())
-        return self.comm.moe_combine(y, gates, h)
+        ex = _Exchange(self.comm, ids, self.n_experts)
+        rows = _Dispatch.apply(x, ex)
+        y = self.experts(rows, ex.handle.recv_offsets.tolist())
+        return _Combine.apply(y, gates, ex)
 
     def forward_local(self, x, ids, gates) -> torch.Tensor:
         """Single-rank path (all experts local): same arithmetic, plain indexing instead of the exchange."""
@@ -66,7 +126,7 @@ class MoELayer:
             for j in range(self.topk):
                 tok = (ids[:, j] == e).nonzero()[:, 0]
                 if tok.numel():
-                    h = G.gemm(x[tok].contiguous(), self.w_up[e], bias=self.b_up[e], gelu=True)
-                    y = G.gemm(h, self.w_down[e])
-                    out[tok] += gates[tok, j:j + 1] * y.float()
+                    h = fused.linear(x[tok].contiguous(), self.w_up[e], self.b_up[e], gelu=True)
+                    y = fused.linear(h, self.w_down[e])
+                    out = out.index_add(0, tok, gates[tok, j:j + 1] * y.float())
         return out.to(torch.bfloat16)

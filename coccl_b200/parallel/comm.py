@@ -473,7 +473,8 @@ class Communicator:
             a.ws[p], a.flags[p], a.status[p] = ws[p], flags[p], status[p]
         return a
 
-    def moe_dispatch(self, x: torch.Tensor, expert_ids: torch.Tensor, n_experts: int, capacity: int | None = None):
+    def moe_dispatch(self, x: torch.Tensor, expert_ids: torch.Tensor, n_experts: int, capacity: int | None = None,
+                     row_scale: torch.Tensor | None = None, layout=None):
         """Send every token to the ranks of its top-k experts as block-scaled FP8 (one kernel: gather, quantise,
         peer stores, dequantise on arrival). Returns (rows [R, hidden] bf16 grouped by local expert, handle);
         handle.recv_offsets[e] .. [e+1] are the rows of local expert e."""
@@ -482,7 +483,7 @@ class Communicator:
         topk = expert_ids.shape[1]
         capacity = capacity or tokens * topk
         le = n_experts // self.size
-        pos, counts = M.route_layout(expert_ids, n_experts, self.size)
+        pos, counts = layout if layout is not None else M.route_layout(expert_ids, n_experts, self.size)
         recv = torch.empty(self.size * capacity, hidden, dtype=torch.bfloat16, device=x.device)
         roff = torch.zeros(le + 1, dtype=torch.int32, device=x.device)
         rcnt = torch.zeros(self.size, le, dtype=torch.int32, device=x.device)
@@ -490,16 +491,21 @@ class Communicator:
         r = self.rank
         a.x[r], a.expertIds[r], a.pos[r], a.sendCounts[r] = x.data_ptr(), expert_ids.data_ptr(), pos.data_ptr(), counts.data_ptr()
         a.recv[r], a.recvOffsets[r], a.recvCounts[r] = recv.data_ptr(), roff.data_ptr(), rcnt.data_ptr()
+        if row_scale is not None:
+            assert row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.shape == expert_ids.shape
+            a.rowScale[r] = row_scale.data_ptr()
         _lib.check(_lib.lib().cocclkMoeDispatch(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeDispatch")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += tokens * topk * hidden * 2
         h = M.Handle(expert_ids, pos, rcnt, roff, capacity, n_experts)
-        h.keep = (counts, x)
+        h.keep = (counts, x, row_scale)
+        h.counts = counts
         return recv, h
 
-    def moe_combine(self, y: torch.Tensor, gates: torch.Tensor, handle) -> torch.Tensor:
+    def moe_combine(self, y: torch.Tensor, gates: torch.Tensor, handle, dot_with: torch.Tensor | None = None):
         """Return the expert outputs (same row layout as moe_dispatch's result) to the token owners as bf16 and
-        form out[t] = sum_j gates[t, j] * y_j in one kernel."""
+        form out[t] = sum_j gates[t, j] * y_j in one kernel. With dot_with [tokens, hidden] the kernel also returns
+        dots[t, j] = <y_j, dot_with[t]> (the gate gradients when dot_with is the output gradient)."""
         tokens, topk = gates.shape
         hidden = y.shape[1]
         out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=y.device)
@@ -507,8 +513,13 @@ class Communicator:
         r = self.rank
         a.expertIds[r], a.pos[r], a.gates[r] = handle.expert_ids.data_ptr(), handle.pos.data_ptr(), gates.data_ptr()
         a.recvCounts[r], a.y[r], a.out[r] = handle.recv_counts.data_ptr(), y.data_ptr(), out.data_ptr()
+        dots = None
+        if dot_with is not None:
+            assert dot_with.dtype == torch.bfloat16 and dot_with.is_contiguous() and dot_with.shape == (tokens, hidden)
+            dots = torch.empty(tokens, topk, dtype=torch.float32, device=y.device)
+            a.dotWith[r], a.dotOut[r] = dot_with.data_ptr(), dots.data_ptr()
         _lib.check(_lib.lib().cocclkMoeCombine(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeCombine")
-        return out
+        return out if dot_with is None else (out, dots)
 
     def moe_status(self) -> int:
         return 0 if self._moe is None else self._moe.status()

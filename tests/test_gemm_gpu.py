@@ -69,3 +69,16 @@ def test_gemm_epilogues(cuda):
     _check(f, _ref(a, b), K)
     torch.cuda.synchronize()
     G.check_errors()
+
+
+def test_gemm_wgrad_layout_with_ragged_contraction(cuda):
+    """dW = dY^T @ X with a token count that is not a multiple of 8: both operands are stored token-major, so the
+    contraction length is unconstrained (rows past it read as zeros)."""
+    torch.manual_seed(3)
+    tokens, n_out, n_in = 97, 256, 192
+    dy = torch.randn(tokens, n_out, device=cuda, dtype=torch.bfloat16)
+    x = torch.randn(tokens, n_in, device=cuda, dtype=torch.bfloat16)
+    dw = G.gemm(dy.t(), x.t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    G.check_errors()
+    _check(dw, dy.float().t() @ x.float(), tokens)

@@ -160,6 +160,39 @@ def _moe_worker(rank, world):
         ref = ref_layer.forward_local(x, ids, gates)
         rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
         assert rel < 0.06, rel  # FP8 on the dispatched activations
+    # training: gradients through the exchange (dispatch <-> combine are each other's backward) against the local model
+    layer.requires_grad_(True)
+    ref_layer.requires_grad_(True)
+    torch.manual_seed(90 + rank)
+    x = torch.randn(384, 512, device=dev, dtype=torch.bfloat16)
+    probe = torch.randn(384, 512, device=dev)
+    xa = x.clone().requires_grad_(True)
+    (layer.forward(xa).float() * probe).sum().backward()
+    xb = x.clone().requires_grad_(True)
+    ids, _ = ref_layer.route(x)
+    logits = torch.nn.functional.linear(xb, ref_layer.router).float()
+    gates = torch.softmax(logits.gather(1, ids.long()), dim=1)
+    (ref_layer.forward_local(xb, ids, gates).float() * probe).sum().backward()
+    rel = ((xa.grad.float() - xb.grad.float()).norm() / xb.grad.float().norm()).item()
+    assert rel < 0.12, ("dx", rel)
+    le = layer.local
+    for k in range(le):
+        e = rank * le + k
+        # an expert's weight gradient collects the tokens of every rank
+        gref = ref_layer.w_up[e].grad.float().clone() if ref_layer.w_up[e].grad is not None else torch.zeros_like(ref_layer.w_up[e]).float()
+        for other in range(world):
+            for kk in range(le):
+                ee = other * le + kk
+                g = ref_layer.w_up[ee].grad
+                buf = g.float().clone() if g is not None else torch.zeros(ref_layer.w_up[ee].shape, device=dev)
+                dist.all_reduce(buf)
+                if ee == e:
+                    gref = buf
+        got = layer.w_up[k].grad.float()
+        rel = ((got - gref).norm() / (gref.norm() + 1e-6)).item()
+        assert rel < 0.15, ("dw_up", e, rel)
+    rr = ((layer.router.grad.float() - ref_layer.router.grad.float()).norm() / (ref_layer.router.grad.float().norm() + 1e-6)).item()
+    assert rr < 0.2, ("drouter", rr)
     assert comm.moe_status() == 0
     comm.close()
 
