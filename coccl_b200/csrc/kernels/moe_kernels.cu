@@ -186,8 +186,17 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
       uint8_t* wsd = reinterpret_cast<uint8_t*>(a.ws[d]);
       uint2* dp = reinterpret_cast<uint2*>(wsd + L.payloadOff + ((long)rank * cap + p) * H);
       uint8_t* ds = wsd + L.scalesOff + ((long)rank * cap + p) * scalesPerRow;
-      for (int it = 0; it < H / 256; ++it) {
-        const uint4 raw = __ldg(src + it * 32 + lane);
+      // four 256-value pieces per pass: their loads are in flight together
+      for (int it0 = 0; it0 < H / 256; it0 += 4) {
+        uint4 rawv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (it0 + u < H / 256) rawv[u] = __ldg(src + (it0 + u) * 32 + lane);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+        const int it = it0 + u;
+        if (it >= H / 256) break;
+        const uint4 raw = rawv[u];
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
         float v[8];
 #pragma unroll
@@ -218,6 +227,7 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
         }
         dp[it * 32 + lane] = make_uint2(o[0], o[1]);
         if ((lane & 3) == 0) ds[it * 8 + (lane >> 2)] = (uint8_t)biased;
+        }
       }
     }
     if (blockIdx.x == 0) {
@@ -259,9 +269,18 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
     const uint2* pp = reinterpret_cast<const uint2*>(myWs + L.payloadOff + sp * H);
     const uint8_t* ps = myWs + L.scalesOff + sp * scalesPerRow;
     uint4* out = reinterpret_cast<uint4*>(recv + (long)r * H);
-    for (int it = 0; it < H / 256; ++it) {
-      const uint2 q = __ldcg(pp + it * 32 + lane);
-      const uint32_t biased = __ldcg(ps + it * 8 + (lane >> 2));
+    for (int it0 = 0; it0 < H / 256; it0 += 4) {
+      uint2 qv[4];
+      uint32_t bv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (it0 + u < H / 256) { qv[u] = __ldcg(pp + (it0 + u) * 32 + lane); bv[u] = __ldcg(ps + (it0 + u) * 8 + (lane >> 2)); }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u;
+      if (it >= H / 256) break;
+      const uint2 q = qv[u];
+      const uint32_t biased = bv[u];
       const float scale = biased > 0 ? __uint_as_float(biased << 23) : __uint_as_float(0x00400000u);
       const uint32_t qw[2] = {q.x, q.y};
       uint32_t o[4];
@@ -274,6 +293,7 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
         o[k] = *reinterpret_cast<uint32_t*>(&h);
       }
       out[it * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
   }
 }

@@ -1,7 +1,7 @@
 // Tensor-parallel fusions on sm_100a: one persistent tcgen05 kernel per operation, with the collective
 // inside the kernel.
 //
-//  agGemmKernel  C = gather(A) * B^T. Two spare warps of every CTA copy the local activation shard into the
+//  agGemmKernel  C = gather(A) * B^T. Six extra warps of every CTA copy the local activation shard into the
 //                peers' gather buffers (plain peer stores, 16-row parts, one release flag per part) while the
 //                tensor cores already work on the local shard; the TMA producer waits for the flags of a
 //                remote shard's rows right before it loads them (from LOCAL memory, no multicast). Shards are
@@ -33,7 +33,9 @@ constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;       // gemmRsKernel: producer, MMA, 4 epilogue warps, 2 spare
+constexpr int kAgThreads = 384;     // agGemmKernel: the same roles + 6 warps that push the local shard
+constexpr int kAgCommWarps = (kAgThreads - 192) / 32;
 constexpr int kParts = 8;                 // flag granularity of the gather: 16 rows
 constexpr int kPartRows = BM / kParts;
 constexpr int kFlagStride = 4096;         // flags per source rank
@@ -155,7 +157,7 @@ __device__ __forceinline__ void mmaRole(const Pipe& p, int numTiles, int kBlocks
 // ---------------------------------------------------------------------------------------------
 // all-gather -> GEMM
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1) agGemmKernel(const __grid_constant__ Params P) {
+__global__ void __launch_bounds__(kAgThreads, 1) agGemmKernel(const __grid_constant__ Params P) {
   extern __shared__ uint8_t smemRaw[];
   const cocclkTpArgs& a = P.a;
   const int e = blockIdx.y;
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmKernel(const __grid_constan
     }
   } else {
     // ---------------- gather push: this rank's shard -> every peer's gather buffer ----------------
-    const int cw = blockIdx.x * 2 + (warp - 6), W = gridDim.x * 2;
+    const int cw = blockIdx.x * kAgCommWarps + (warp - 6), W = gridDim.x * kAgCommWarps;
     const long items = (long)(N - 1) * tps * kParts;
     const long partVecs = (long)kPartRows * a.K * 2 / 16;  // uint4 per 16-row part
     const uint4* src0 = reinterpret_cast<const uint4*>(a.a[rank]);
@@ -470,7 +472,7 @@ extern "C" long cocclkGemmRsWorkspaceBytes(int M, int N, int nRanks) {
 }
 
 template <class Kern>
-static int launchTp(Kern kern, Params& P, int emulatedRanks, int maxCtas, long tilesPerRank, cudaStream_t stream) {
+static int launchTp(Kern kern, int threads, Params& P, int emulatedRanks, int maxCtas, long tilesPerRank, cudaStream_t stream) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -487,8 +489,8 @@ static int launchTp(Kern kern, Params& P, int emulatedRanks, int maxCtas, long t
   void* params[] = {&P};
   cocclkCountLaunches(1);
   if (emulatedRanks > 1)
-    return (int)cudaLaunchCooperativeKernel((const void*)kern, grid, dim3(kThreads), params, kSmemBytes, stream);
-  return (int)cudaLaunchKernel((const void*)kern, grid, dim3(kThreads), params, kSmemBytes, stream);
+    return (int)cudaLaunchCooperativeKernel((const void*)kern, grid, dim3(threads), params, kSmemBytes, stream);
+  return (int)cudaLaunchKernel((const void*)kern, grid, dim3(threads), params, kSmemBytes, stream);
 }
 
 static int checkCommon(const cocclkTpArgs* a, int emulatedRanks) {
@@ -518,7 +520,7 @@ extern "C" int cocclkAgGemm(const cocclkTpArgs* args, int emulatedRanks, int max
     if (rc) return rc;
   }
   const long tiles = (long)(args->M / BM) * ((args->N + BN - 1) / BN);
-  return launchTp(agGemmKernel, P, emulatedRanks, maxCtas, tiles, stream);
+  return launchTp(agGemmKernel, kAgThreads, P, emulatedRanks, maxCtas, tiles, stream);
 }
 
 extern "C" int cocclkGemmRs(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
@@ -538,5 +540,5 @@ extern "C" int cocclkGemmRs(const cocclkTpArgs* args, int emulatedRanks, int max
     if (rc) return rc;
   }
   const long tiles = (long)(args->M / BM) * (args->N / BN);
-  return launchTp(gemmRsKernel, P, emulatedRanks, maxCtas, tiles, stream);
+  return launchTp(gemmRsKernel, kThreads, P, emulatedRanks, maxCtas, tiles, stream);
 }
