@@ -22,7 +22,7 @@ constexpr int BM = 128;        // rows per CTA (256 per pair)
 constexpr int BN = 256;        // accumulator columns
 constexpr int BNH = 128;       // B rows loaded per CTA
 constexpr int BK = 64;
-constexpr int kStages = 7;
+constexpr int kStages = 7;      // bf16 outputs; fp32 outputs run with 6 and give the space to the TMA boxes
 constexpr int kABytes = BM * BK * 2;    // 16 KiB
 constexpr int kBBytes = BNH * BK * 2;   // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -51,11 +51,15 @@ __device__ __forceinline__ void tileCoord(int t, int numM, int numN, int& tm, in
 }  // namespace pair
 
 __global__ void __launch_bounds__(pair::kThreads, 1)
-gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   using namespace pair;
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * kStageBytes);
+  const int stages = g.stages;  // 6 or 7, the same in both CTAs
+  const bool f32 = g.epi == GEMM_EPI_F32 || g.epi == GEMM_EPI_F32_ACC;
+  uint8_t* epiStage = smem + stages * kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(epiStage + (f32 ? kEpiStageBytes : 0));
   volatile int* abortFlag = &bars->abortFlag;
 
   const int warp = threadIdx.x >> 5;
@@ -97,8 +101,8 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int m0 = tm * 2 * BM + (int)cta * BM;
         const int n0 = tn * BN + (int)cta * BNH;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
           if (!mbarWait(&bars->empty[s], ph ^ 1, abortFlag, kWaitLimitNs)) { ok = false; raiseAbort(); break; }
           if (*abortFlag) { ok = false; break; }
           uint8_t* sa = smem + s * kStageBytes;
@@ -137,8 +141,8 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         tcFenceAfter();
         const uint32_t dTmem = tmemBase + acc * BN;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
           if (!mbarWait(&bars->full[s], ph, abortFlag, kWaitLimitNs)) { ok = false; raiseAbort(); break; }
           tcFenceAfter();
           const uint32_t sa = smemAddr(smem + s * kStageBytes);
@@ -157,7 +161,7 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else {
     // ------------------------------------------------ epilogue warps (both CTAs)
     const int quad = warp & 3;
-    uint32_t tileIdx = 0;
+    uint32_t tileIdx = 0, boxes = 0;
     bool ok = true;
     for (int t = clusterId; t < numTiles && ok; t += numClusters, ++tileIdx) {
       int tm, tn;
@@ -168,13 +172,19 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       ok = __all_sync(0xffffffffu, ok) != 0;
       if (!ok) { if (lane == 0) raiseAbort(); break; }
       tcFenceAfter();
-      const int row = tm * 2 * BM + (int)cta * BM + quad * 32 + lane;
+      const int row0 = tm * 2 * BM + (int)cta * BM + quad * 32;
       const uint32_t tbase = tmemBase + acc * BN + ((uint32_t)(quad * 32) << 16);
-      epilogueStoreTile(g, tbase, row, tn * BN);
+      if (f32) {
+        if (row0 < g.M)
+          epilogueTmaTileF32(&tmC, g.epi == GEMM_EPI_F32_ACC, tbase, row0, tn * BN, g.N, epiStage + quad * kEpiStageBytesPerWarp, boxes);
+      } else {
+        epilogueStoreTile(g, tbase, row0 + lane, tn * BN);
+      }
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArriveRemote(mapToCta(smemAddr(&bars->tmemEmpty[acc]), 0));
     }
+    if (f32 && lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
   }
 
   __syncwarp();
@@ -188,6 +198,7 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 // shared with gemm_kernels.cu
+int makeF32OutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld);
 int makeBf16TensorMap(CUtensorMap* m, const void* base, long inner, long outer, long ld, int boxInner, int boxOuter);
 
 }  // namespace coccl
@@ -209,19 +220,28 @@ extern "C" int cocclkGemmBf16Pair(const void* A, long lda, int aMN, const void* 
   if (rc) return rc;
   static int maxClusters = 0;
   static bool attrSet = false;
-  const int smemBytes = kStages * kStageBytes + (int)sizeof(Barriers) + 1024;
+  const bool f32 = epi == GEMM_EPI_F32 || epi == GEMM_EPI_F32_ACC;
+  CUtensorMap tc = ta;  // placeholder unless the epilogue writes fp32 through the TMA unit
+  if (f32) {
+    rc = makeF32OutputMap(&tc, C, N, M, ldc);
+    if (rc) return rc;
+  }
+  const int stages = f32 ? kStages - 1 : kStages;
+  const int smemMax = kStages * kStageBytes + (int)sizeof(Barriers) + 1024;   // the attribute is set once, for the larger layout
+  const int smemBytes = stages * kStageBytes + (f32 ? kEpiStageBytes : 0) + (int)sizeof(Barriers) + 1024;
   if (!attrSet) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(gemmBf16PairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemmBf16PairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smemMax > smemBytes ? smemMax : smemBytes);
     if (e != cudaSuccess) return (int)e;
     maxClusters = sms / 2;
     // how many pairs the device can hold at once (SMs pair up inside a GPC)
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3((unsigned)(sms / 2) * 2, 1, 1);
     q.blockDim = dim3(kThreads, 1, 1);
-    q.dynamicSmemBytes = (size_t)smemBytes;
+    q.dynamicSmemBytes = (size_t)(smemMax > smemBytes ? smemMax : smemBytes);
     cudaLaunchAttribute qa[1];
     qa[0].id = cudaLaunchAttributeClusterDimension;
     qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
@@ -249,7 +269,8 @@ extern "C" int cocclkGemmBf16Pair(const void* A, long lda, int aMN, const void* 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemmBf16PairKernel, ta, tb, g);
+  g.stages = stages;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemmBf16PairKernel, ta, tb, tc, g);
   cocclkCountLaunches(1);
   return (int)e;
 }

@@ -15,6 +15,7 @@ struct GemmArgs {
   int epi;
   int aMN, bMN;
   unsigned int* err;
+  int stages;  // pair kernel: ring depth of this launch (fp32 epilogues give one stage to the TMA boxes)
 };
 
 // tbase: TMEM address of (lane quadrant of this warp, first accumulator column); row: the global row
@@ -79,6 +80,45 @@ __device__ __forceinline__ void epilogueStoreTile(const GemmArgs& g, uint32_t tb
         }
       }
     }
+  }
+}
+
+// fp32 outputs (weight gradients, fp32 products): each epilogue warp drains its 32 rows, 32 columns at a time, into a
+// 4 KiB shared-memory box laid out for SWIZZLE_128B (16-byte chunk j of row i sits at chunk j ^ (i & 7): the 32 lanes,
+// one row each, write without bank conflicts) and one lane hands the box to the TMA unit: a plain store, or with
+// `accumulate` a reduce-add that the L2 performs, so the previous gradient never travels to the SM. Two boxes per warp
+// alternate; the TMA unit clips rows and columns past the matrix.
+constexpr int kEpiBoxBytes = 32 * 128;
+constexpr int kEpiStageBytesPerWarp = 2 * kEpiBoxBytes;
+constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;
+
+// stage: this warp's two boxes (1024-byte aligned); boxCounter: running count of boxes this warp has issued.
+__device__ __forceinline__ void epilogueTmaTileF32(const CUtensorMap* tmC, bool accumulate, uint32_t tbase, int row0,
+                                                  int colBase, int nCols, uint8_t* stage, uint32_t& boxCounter) {
+  using namespace sm100;
+  const int lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int c = 0; c < 256 / 32; ++c) {
+    uint32_t r[32];
+    tmemLd32x32(tbase + c * 32, r);
+    tmemLdWait();
+    const int col0 = colBase + c * 32;
+    if (col0 >= nCols) continue;  // uniform over the warp
+    uint8_t* box = stage + (boxCounter & 1u) * kEpiBoxBytes;
+    // the box was handed to the TMA unit two boxes ago: wait until that transfer has read it
+    if (lane == 0) bulkWaitGroupRead<1>();
+    __syncwarp();
+    uint4* rowp = reinterpret_cast<uint4*>(box + lane * 128);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) rowp[j ^ (lane & 7)] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    fenceProxyAsyncShared();
+    __syncwarp();
+    if (lane == 0) {
+      if (accumulate) tmaReduceAdd2d(tmC, box, col0, row0);
+      else tmaStore2d(tmC, box, col0, row0);
+      bulkCommitGroup();
+    }
+    ++boxCounter;
   }
 }
 

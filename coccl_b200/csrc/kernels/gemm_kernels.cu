@@ -49,10 +49,12 @@ __device__ __forceinline__ void tileCoord(int t, int numM, int numN, int& tm, in
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
-  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + kStages * kStageBytes);
+  uint8_t* epiStage = smem + kStages * kStageBytes;  // TMA boxes of the fp32 epilogues
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epiStage + kEpiStageBytes);
   volatile int* abortFlag = &bars->abortFlag;
 
   const int warp = threadIdx.x >> 5;
@@ -150,7 +152,8 @@ gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------------------------ epilogue warps
     const int quad = warp & 3;
-    uint32_t tileIdx = 0;
+    const bool f32 = g.epi == GEMM_EPI_F32 || g.epi == GEMM_EPI_F32_ACC;
+    uint32_t tileIdx = 0, boxes = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileIdx) {
       int tm, tn;
@@ -161,13 +164,19 @@ gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok) != 0;  // tcgen05.ld below needs the whole warp
       if (!ok) break;
       tcFenceAfter();
-      const int row = tm * BM + quad * 32 + lane;
+      const int row0 = tm * BM + quad * 32;
       const uint32_t tbase = tmemBase + acc * BN + ((uint32_t)(quad * 32) << 16);
-      epilogueStoreTile(g, tbase, row, tn * BN);
+      if (f32) {
+        if (row0 < g.M)
+          epilogueTmaTileF32(&tmC, g.epi == GEMM_EPI_F32_ACC, tbase, row0, tn * BN, g.N, epiStage + quad * kEpiStageBytesPerWarp, boxes);
+      } else {
+        epilogueStoreTile(g, tbase, row0 + lane, tn * BN);
+      }
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(&bars->tmemEmpty[acc]);
     }
+    if (f32 && lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
   }
 
   tcFenceBefore();
@@ -196,6 +205,26 @@ static EncodeTiledFn encodeTiled() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   }
   return fn;
+}
+
+// 2-D fp32 tensor map of an output matrix for the epilogue boxes (32 columns x 32 rows, 128-byte swizzle).
+int makeF32OutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld) {
+  EncodeTiledFn f = encodeTiled();
+  if (!f) return -2;
+  static thread_local bool ctxBound = false;
+  if (!ctxBound) { cudaFree(nullptr); ctxBound = true; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * 4) & 15)) return -3;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t es[2] = {1, 1};
+  CUresult r = f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "coccl: cuTensorMapEncodeTiled (fp32 output) failed (%d): base=%p dims={%ld,%ld} ld=%ld\n", (int)r, base, cols, rows, ld);
+    return -4;
+  }
+  return 0;
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows `ld` elements apart.
@@ -262,7 +291,12 @@ extern "C" int cocclkGemmBf16Single(const void* A, long lda, int aMN, const void
   if (rc) return rc;
   static int sms = 0;
   static bool attrSet = false;
-  const int smemBytes = kStages * kStageBytes + (int)sizeof(GemmBarriers) + 1024;
+  CUtensorMap tc = ta;  // placeholder unless the epilogue writes fp32 through the TMA unit
+  if (epi == GEMM_EPI_F32 || epi == GEMM_EPI_F32_ACC) {
+    rc = makeF32OutputMap(&tc, C, N, M, ldc);
+    if (rc) return rc;
+  }
+  const int smemBytes = kStages * kStageBytes + kEpiStageBytes + (int)sizeof(GemmBarriers) + 1024;
   if (!attrSet) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -277,7 +311,8 @@ extern "C" int cocclkGemmBf16Single(const void* A, long lda, int aMN, const void
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < sms ? tiles : sms;
   if (maxCtas > 0 && grid > maxCtas) grid = maxCtas;
-  gemmBf16Kernel<<<grid, kGemmThreads, smemBytes, stream>>>(ta, tb, g);
+  g.stages = kStages;
+  gemmBf16Kernel<<<grid, kGemmThreads, smemBytes, stream>>>(ta, tb, tc, g);
   cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }

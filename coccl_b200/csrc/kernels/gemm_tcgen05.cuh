@@ -198,6 +198,29 @@ __device__ __forceinline__ void ummaCommit2(uint64_t* bar, uint16_t ctaMask) {
                ::"r"(smemAddr(bar)), "h"(ctaMask) : "memory");
 }
 
+// ------------------------------------------------------------------ TMA stores / reductions (shared -> global)
+// Make generic-proxy writes to shared memory visible to the async proxy (TMA) before it reads them.
+__device__ __forceinline__ void fenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Write a box from shared memory to the tensor at (x, y); parts outside the tensor are clipped.
+__device__ __forceinline__ void tmaStore2d(const CUtensorMap* map, const void* smemSrc, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smemAddr(smemSrc)), "r"(x), "r"(y) : "memory");
+}
+// Add a box from shared memory into the tensor at (x, y) (element type from the tensor map); the addition runs in L2.
+__device__ __forceinline__ void tmaReduceAdd2d(const CUtensorMap* map, const void* smemSrc, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smemAddr(smemSrc)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N> __device__ __forceinline__ void bulkWaitGroupRead() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Wait until at most N of this thread's bulk groups are still in flight at all.
+template <int N> __device__ __forceinline__ void bulkWaitGroup() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ float geluTanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * x * (1.f + k1 * x * x);
