@@ -1,6 +1,6 @@
 // CTA-pair variant of the bf16 GEMM: two CTAs of a cluster (two SMs) work on one 256x256 output
 // tile with tcgen05.mma.cta_group::2 (M = 256). Each CTA loads its 128 rows of A and its 128-row half
-// of B, so a stage is 32 KiB per SM instead of 48 KiB: seven stages fit and the L2->SM traffic per FLOP
+// of B, so a stage is 32 KiB per SM instead of 48 KiB: six stages and the epilogue boxes fit and the L2->SM traffic per FLOP
 // drops by a third, which is what limited the single-CTA kernel (tensor pipe ~72 % busy).
 //
 // Per CTA: warp 0 = TMA producer (both CTAs; completion bytes are credited to the LEADER's "full"
@@ -22,7 +22,7 @@ constexpr int BM = 128;        // rows per CTA (256 per pair)
 constexpr int BN = 256;        // accumulator columns
 constexpr int BNH = 128;       // B rows loaded per CTA
 constexpr int BK = 64;
-constexpr int kStages = 7;      // bf16 outputs; fp32 outputs run with 6 and give the space to the TMA boxes
+constexpr int kStages = 6;      // 6 x 32 KiB ring + 32 KiB of epilogue boxes for the TMA stores
 constexpr int kABytes = BM * BK * 2;    // 16 KiB
 constexpr int kBBytes = BNH * BK * 2;   // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -56,10 +56,10 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   using namespace pair;
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
-  const int stages = g.stages;  // 6 or 7, the same in both CTAs
+  constexpr int stages = kStages;  // compile-time: the ring index is a division by a constant
   const bool f32 = g.epi == GEMM_EPI_F32 || g.epi == GEMM_EPI_F32_ACC;
   uint8_t* epiStage = smem + stages * kStageBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(epiStage + (f32 ? kEpiStageBytes : 0));
+  Barriers* bars = reinterpret_cast<Barriers*>(epiStage + kEpiStageBytes);
   volatile int* abortFlag = &bars->abortFlag;
 
   const int warp = threadIdx.x >> 5;
@@ -177,14 +177,14 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (f32) {
         if (row0 < g.M)
           epilogueTmaTileF32(&tmC, g.epi == GEMM_EPI_F32_ACC, tbase, row0, tn * BN, g.N, epiStage + quad * kEpiStageBytesPerWarp, boxes);
-      } else {
-        epilogueStoreTile(g, tbase, row0 + lane, tn * BN);
+      } else if (row0 < g.M) {
+        epilogueTmaTileBf16(g, &tmC, tbase, row0, tn * BN, epiStage + quad * kEpiStageBytesPerWarp, boxes);
       }
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArriveRemote(mapToCta(smemAddr(&bars->tmemEmpty[acc]), 0));
     }
-    if (f32 && lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
+    if (lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
   }
 
   __syncwarp();
@@ -198,7 +198,7 @@ gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 // shared with gemm_kernels.cu
-int makeF32OutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld);
+int makeOutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld, bool f32);
 int makeBf16TensorMap(CUtensorMap* m, const void* base, long inner, long outer, long ld, int boxInner, int boxOuter);
 
 }  // namespace coccl
@@ -221,14 +221,12 @@ extern "C" int cocclkGemmBf16Pair(const void* A, long lda, int aMN, const void* 
   static int maxClusters = 0;
   static bool attrSet = false;
   const bool f32 = epi == GEMM_EPI_F32 || epi == GEMM_EPI_F32_ACC;
-  CUtensorMap tc = ta;  // placeholder unless the epilogue writes fp32 through the TMA unit
-  if (f32) {
-    rc = makeF32OutputMap(&tc, C, N, M, ldc);
-    if (rc) return rc;
-  }
-  const int stages = f32 ? kStages - 1 : kStages;
-  const int smemMax = kStages * kStageBytes + (int)sizeof(Barriers) + 1024;   // the attribute is set once, for the larger layout
-  const int smemBytes = stages * kStageBytes + (f32 ? kEpiStageBytes : 0) + (int)sizeof(Barriers) + 1024;
+  CUtensorMap tc;
+  rc = makeOutputMap(&tc, C, N, M, ldc, f32);
+  if (rc) return rc;
+  const int stages = kStages;
+  const int smemMax = kStages * kStageBytes + kEpiStageBytes + (int)sizeof(Barriers) + 1024;
+  const int smemBytes = smemMax;
   if (!attrSet) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);

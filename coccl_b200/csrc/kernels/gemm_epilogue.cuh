@@ -122,4 +122,74 @@ __device__ __forceinline__ void epilogueTmaTileF32(const CUtensorMap* tmC, bool 
   }
 }
 
+// bf16 outputs through the TMA unit: the same 32-row x 128-byte swizzled boxes, here 64 columns wide (two accumulator
+// chunks per box). Bias and GELU are applied in registers; the optional pre-activation Z keeps its direct stores.
+__device__ __forceinline__ void epilogueTmaTileBf16(const GemmArgs& g, const CUtensorMap* tmC, uint32_t tbase, int row0,
+                                                   int colBase, uint8_t* stage, uint32_t& boxCounter) {
+  using namespace sm100;
+  const int lane = threadIdx.x & 31;
+  const int row = row0 + lane;
+  const bool hasBias = g.epi == GEMM_EPI_BIAS || g.epi == GEMM_EPI_BIAS_GELU;
+#pragma unroll 1
+  for (int cp = 0; cp < 256 / 64; ++cp) {
+    const int col0 = colBase + cp * 64;
+    if (col0 >= g.N) continue;  // uniform over the warp
+    uint8_t* box = stage + (boxCounter & 1u) * kEpiBoxBytes;
+    if (lane == 0) bulkWaitGroupRead<1>();
+    __syncwarp();
+    uint4* rowp = reinterpret_cast<uint4*>(box + lane * 128);
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      uint32_t r[32];
+      tmemLd32x32(tbase + (cp * 2 + half) * 32, r);
+      tmemLdWait();
+      const int colh = col0 + half * 32;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = colh + 8 * j;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
+        uint32_t o[4] = {0, 0, 0, 0};
+        if (col < g.N) {  // N is a multiple of 8: a group of 8 columns is inside or outside as a whole
+          if (hasBias) {
+            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g.bias) + col));
+            const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              v[2 * i] += __uint_as_float(w[i] << 16);
+              v[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+          }
+          if (g.epi == GEMM_EPI_BIAS_GELU) {
+            if (g.Z != nullptr && row < g.M) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                o[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.Z) + (long)row * g.ldc + col) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = geluTanh(v[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            o[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        rowp[(half * 4 + j) ^ (lane & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    fenceProxyAsyncShared();
+    __syncwarp();
+    if (lane == 0) {
+      tmaStore2d(tmC, box, col0, row0);
+      bulkCommitGroup();
+    }
+    ++boxCounter;
+  }
+}
+
 }  // namespace coccl

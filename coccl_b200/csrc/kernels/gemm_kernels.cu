@@ -169,14 +169,14 @@ gemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (f32) {
         if (row0 < g.M)
           epilogueTmaTileF32(&tmC, g.epi == GEMM_EPI_F32_ACC, tbase, row0, tn * BN, g.N, epiStage + quad * kEpiStageBytesPerWarp, boxes);
-      } else {
-        epilogueStoreTile(g, tbase, row0 + lane, tn * BN);
+      } else if (row0 < g.M) {
+        epilogueTmaTileBf16(g, &tmC, tbase, row0, tn * BN, epiStage + quad * kEpiStageBytesPerWarp, boxes);
       }
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(&bars->tmemEmpty[acc]);
     }
-    if (f32 && lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
+    if (lane == 0) bulkWaitGroup<0>();  // the boxes must have left shared memory before the CTA ends
   }
 
   tcFenceBefore();
@@ -207,21 +207,23 @@ static EncodeTiledFn encodeTiled() {
   return fn;
 }
 
-// 2-D fp32 tensor map of an output matrix for the epilogue boxes (32 columns x 32 rows, 128-byte swizzle).
-int makeF32OutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld) {
+// 2-D tensor map of an output matrix for the epilogue boxes: 32 rows x 128 bytes (32 fp32 or 64 bf16 columns),
+// 128-byte swizzle.
+int makeOutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld, bool f32) {
   EncodeTiledFn f = encodeTiled();
   if (!f) return -2;
   static thread_local bool ctxBound = false;
   if (!ctxBound) { cudaFree(nullptr); ctxBound = true; }
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * 4) & 15)) return -3;
+  const int es_ = f32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * es_) & 15)) return -3;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  cuuint32_t box[2] = {32, 32};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es_};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / es_), 32};
   cuuint32_t es[2] = {1, 1};
-  CUresult r = f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = f(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    fprintf(stderr, "coccl: cuTensorMapEncodeTiled (fp32 output) failed (%d): base=%p dims={%ld,%ld} ld=%ld\n", (int)r, base, cols, rows, ld);
+    fprintf(stderr, "coccl: cuTensorMapEncodeTiled (output) failed (%d): base=%p dims={%ld,%ld} ld=%ld\n", (int)r, base, cols, rows, ld);
     return -4;
   }
   return 0;
@@ -291,11 +293,9 @@ extern "C" int cocclkGemmBf16Single(const void* A, long lda, int aMN, const void
   if (rc) return rc;
   static int sms = 0;
   static bool attrSet = false;
-  CUtensorMap tc = ta;  // placeholder unless the epilogue writes fp32 through the TMA unit
-  if (epi == GEMM_EPI_F32 || epi == GEMM_EPI_F32_ACC) {
-    rc = makeF32OutputMap(&tc, C, N, M, ldc);
-    if (rc) return rc;
-  }
+  CUtensorMap tc;
+  rc = makeOutputMap(&tc, C, N, M, ldc, epi == GEMM_EPI_F32 || epi == GEMM_EPI_F32_ACC);
+  if (rc) return rc;
   const int smemBytes = kStages * kStageBytes + kEpiStageBytes + (int)sizeof(GemmBarriers) + 1024;
   if (!attrSet) {
     int dev = 0;
