@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: 3-D-parallel GPT training throughput (tokens/s) on N B200s of one node.
 
-Model / config (BASELINE.json, config 5): GPT with 32 layers, hidden 4096, 32 heads, FFN 16384,
+Model / config (the reference's GPT-6.7B end-to-end setting): GPT with 32 layers, hidden 4096, 32 heads, FFN 16384,
 GELU, sequence 2048, vocabulary 50304, micro-batch 2, bf16 compute with fp32 master weights and
 Adam, random-init N(0, 0.02) weights, uniform-random token ids. The 8-GPU configuration is
 TP=2, PP=2, DP=2 with global batch 256; smaller N keep the per-GPU work fixed (weak scaling:
@@ -82,7 +82,7 @@ class ClockSampler(threading.Thread):
 
 def reference_arm(args):
     # The reference is a C++/CUDA fork of NCCL with no Python package and no trainer:
-    # `pip install /root/reference` fails ("Neither 'setup.py' nor 'pyproject.toml' found"), and the
+    # a pip install of its source tree fails ("Neither 'setup.py' nor 'pyproject.toml' found"), and the
     # repository ships no model or training loop that could produce tokens/s.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a C++ NCCL fork without setup.py/pyproject.toml (pip install fails) and "
