@@ -1,7 +1,7 @@
 // Tensor-parallel fusions on sm_100a: one persistent tcgen05 kernel per operation, with the collective
 // inside the kernel.
 //
-//  agGemmKernel  C = gather(A) * B^T. Two (2 ranks) or six extra warps of every CTA copy the local activation shard into the
+//  agGemmKernel  C = gather(A) * B^T. Two spare warps of every CTA copy the local activation shard into the
 //                peers' gather buffers (plain peer stores, 16-row parts, one release flag per part) while the
 //                tensor cores already work on the local shard; the TMA producer waits for the flags of a
 //                remote shard's rows right before it loads them (from LOCAL memory, no multicast). Shards are
@@ -34,7 +34,7 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 256;       // gemmRsKernel: producer, MMA, 4 epilogue warps, 2 spare
-constexpr int kAgThreads = 384;     // agGemmKernel with more than 2 ranks: the same roles + 6 warps that push the local shard
+constexpr int kAgThreads = 384;     // upper bound of the block size of agGemmKernel (push warps = warps beyond the sixth)
 constexpr int kParts = 8;                 // flag granularity of the gather: 16 rows
 constexpr int kPartRows = BM / kParts;
 constexpr int kFlagStride = 4096;         // flags per source rank
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kAgThreads, 1) agGemmKernel(const __grid_const
     }
   } else {
     // ---------------- gather push: this rank's shard -> every peer's gather buffer ----------------
-    // two push warps suffice while the GEMM is the longer part (2 ranks); more ranks mean more bytes per FLOP
+    // two push warps per CTA: six were measured slower at 2 and at 8 ranks (the copy is not limited by issue slots)
     const int commWarps = (int)(blockDim.x >> 5) - 6;
     const int cw = blockIdx.x * commWarps + (warp - 6), W = gridDim.x * commWarps;
     const long items = (long)(N - 1) * tps * kParts;
@@ -521,7 +521,7 @@ extern "C" int cocclkAgGemm(const cocclkTpArgs* args, int emulatedRanks, int max
     if (rc) return rc;
   }
   const long tiles = (long)(args->M / BM) * ((args->N + BN - 1) / BN);
-  return launchTp(agGemmKernel, args->nRanks <= 2 ? kThreads : kAgThreads, P, emulatedRanks, maxCtas, tiles, stream);
+  return launchTp(agGemmKernel, kThreads, P, emulatedRanks, maxCtas, tiles, stream);
 }
 
 extern "C" int cocclkGemmRs(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
