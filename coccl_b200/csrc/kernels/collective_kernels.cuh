@@ -29,7 +29,14 @@
 
 namespace coccl {
 
-enum CollOp : int { kOpReduceScatter = 0, kOpAllGather = 1, kOpAllToAll = 2, kOpAllReduceOneShot = 3, kOpAllReduceTwoShot = 4 };
+enum CollOp : int {
+  kOpReduceScatter = 0, kOpAllGather = 1, kOpAllToAll = 2, kOpAllReduceOneShot = 3, kOpAllReduceTwoShot = 4,
+  // All-gather of DELTAS (the reference's subAdd AllGather, sdp4bit/quantization/sub_quantize.cu:176-262 and
+  // dequantize_add.cu:145-275): `out` holds the result of the previous call on every rank, a rank encodes
+  // in - out[own chunk] and every rank adds the decoded deltas to all chunks of `out`. Every rank performs the same
+  // arithmetic on the same bytes, so the copies of `out` stay identical. The first call must fill `out` exactly.
+  kOpAllGatherDelta = 5
+};
 
 constexpr int kMaxSlices = 4096;  // per source rank and region
 
@@ -67,12 +74,18 @@ __device__ __forceinline__ unsigned int* flagPtr(unsigned int* base, int region,
 template <typename T, class Codec>
 __device__ __forceinline__ void encodeTiles(const T* src, const ChunkLayout& L, const CodecCfg& c, long t0, long t1,
                                             uint8_t* const* dst, int nDst, TileStage<T>& stage, float* sm,
-                                            uint64_t rngBase) {
+                                            uint64_t rngBase, const T* prev = nullptr) {
   for (long t = t0; t < t1; ++t) {
     const long e0 = t * kTileElems;
     const long e = e0 + (long)threadIdx.x * kElemsPerThread;
     float v[32];
     TileIO<T>::load(src, L.count, e0, TileIO<T>::fastTile(src, L.count, e0), stage, v);
+    if (prev != nullptr) {  // delta coding: what is sent is the change since the previous result
+      float pv[32];
+      TileIO<T>::load(prev, L.count, e0, TileIO<T>::fastTile(prev, L.count, e0), stage, pv);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] -= pv[i];
+    }
     const typename Codec::Enc enc = Codec::encode(v, c, true, sm, rngBase + (uint64_t)e);
     for (int d = 0; d < nDst; ++d) Codec::store(enc, dst[d], L, c, e);
   }
@@ -147,7 +160,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
           sFlag[threadIdx.x] = flagPtr(a.flags[p], 0, rank, (int)s);
         }
         __syncthreads();
-        encodeTiles<T, Codec>(in, L, c, t0, t1, sDst, N, stage, sm, ((uint64_t)rank << 40));
+        encodeTiles<T, Codec>(in, L, c, t0, t1, sDst, N, stage, sm, ((uint64_t)rank << 40),
+                              a.op == kOpAllGatherDelta ? out + (long)rank * a.count : nullptr);
         publish(sFlag, N, a.epoch);
       }
     }
@@ -192,7 +206,14 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
           for (int d = 0; d < N; ++d) Codec::store(enc, sDst[d], L, c, e);
         } else {
           Codec::finish(acc);
-          TileIO<T>::store(dstChunk, L.count, e0, TileIO<T>::fastTile(dstChunk, L.count, e0), stage, acc);
+          const bool fast = TileIO<T>::fastTile(dstChunk, L.count, e0);
+          if (a.op == kOpAllGatherDelta) {
+            float pv[32];
+            TileIO<T>::load(dstChunk, L.count, e0, fast, stage, pv);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] += pv[i];
+          }
+          TileIO<T>::store(dstChunk, L.count, e0, fast, stage, acc);
         }
       }
       if (a.op == kOpAllReduceTwoShot) publish(sFlag, N, a.epoch);

@@ -13,9 +13,9 @@ import torch
 from .. import _lib
 from .codec import CodecConfig, DTYPE_CODE
 
-OP_RS, OP_AG, OP_A2A, OP_AR1, OP_AR2 = 0, 1, 2, 3, 4
+OP_RS, OP_AG, OP_A2A, OP_AR1, OP_AR2, OP_AGD = 0, 1, 2, 3, 4, 5
 OP_NAMES = {"reduce_scatter": OP_RS, "all_gather": OP_AG, "all_to_all": OP_A2A, "all_reduce_oneshot": OP_AR1,
-            "all_reduce_twoshot": OP_AR2}
+            "all_reduce_twoshot": OP_AR2, "all_gather_delta": OP_AGD}
 
 
 def slot_bytes(cfg: CodecConfig, count: int, dtype) -> int:
@@ -61,8 +61,13 @@ def emulate_collective(op: str, inputs: list[torch.Tensor], cfg: CodecConfig, *,
     dtype, dev = x0.dtype, x0.device
     numel = x0.numel()
     count = chunk_count(opc, numel, n)
-    out_numel = {OP_RS: count, OP_AG: count * n, OP_A2A: numel, OP_AR1: numel, OP_AR2: numel}[opc]
-    outs = [torch.empty(out_numel, dtype=dtype, device=dev) for _ in range(n)]
+    out_numel = {OP_RS: count, OP_AG: count * n, OP_A2A: numel, OP_AR1: numel, OP_AR2: numel, OP_AGD: count * n}[opc]
+    if opc == OP_AGD:
+        # delta all-gather: the outputs of the previous call are the state the deltas are added to
+        assert state is not None and "outs" in state, "all_gather_delta needs state['outs'] from an exact first gather"
+        outs = state["outs"]
+    else:
+        outs = [torch.empty(out_numel, dtype=dtype, device=dev) for _ in range(n)]
     sb, region_b, total = workspace_bytes(opc, cfg, count, dtype, n)
     if state is None:
         state = {}

@@ -22,7 +22,8 @@ from ..ops import collective as K
 from ..ops.codec import MXFP8, SDP4BIT_G128, CodecConfig, DTYPE_CODE
 from ..utils.trace import nvtx_range
 
-K_NAMES = {0: "reduce_scatter", 1: "all_gather", 2: "all_to_all", 3: "all_reduce_oneshot", 4: "all_reduce_twoshot"}
+K_NAMES = {0: "reduce_scatter", 1: "all_gather", 2: "all_to_all", 3: "all_reduce_oneshot", 4: "all_reduce_twoshot",
+           5: "all_gather_delta"}
 
 
 @dataclass
@@ -44,6 +45,7 @@ class Policy:
         ("default", "all_to_all"): SDP4BIT_G128,
     })
     all_reduce_oneshot_max_bytes: int = 1 << 20
+    dp_param_delta: bool = False    # ZeRO-1 parameter all-gather as 8-bit deltas (subAdd); exact first round
     nvls_all_reduce: bool = False   # uncompressed all-reduce below the threshold through multimem instead of NCCL
     timeout_ms: float = 20000.0
     max_ctas: int = 0
@@ -153,6 +155,7 @@ class Communicator:
         self._tp_epoch = 0
         self._moe: _Arena | None = None
         self._nvls: dict | None = None
+        self._delta_seeded: set = set()
         self._trace: torch.Tensor | None = None
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
@@ -523,6 +526,26 @@ class Communicator:
 
     def moe_status(self) -> int:
         return 0 if self._moe is None else self._moe.status()
+
+    def all_gather_delta(self, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig | None = None):
+        """All-gather that sends the CHANGE of `inp` since the previous call with the same `out` (parameters after an
+        optimizer step move little, so 8 bits of a small delta carry far more precision than 8 bits of the value).
+        The first call for a given `out` is an exact native all-gather that seeds the state, as the reference's subAdd
+        codec does with its raw first round (sdp4bit_quan.cu:286-353); `out` itself is the state afterwards."""
+        if self.size == 1:
+            out.copy_(inp.reshape(out.shape))
+            return out
+        key = (out.data_ptr(), out.numel(), out.dtype)
+        cfg = cfg or CodecConfig("sdp4bit", 8, 2048, False, False)
+        usable = self.cuda and inp.is_cuda and inp.dtype in DTYPE_CODE and inp.is_contiguous() and out.is_contiguous()
+        if not usable or key not in self._delta_seeded:
+            self._native(out.numel() * out.element_size())
+            dist.all_gather_into_tensor(out, inp, group=self.group)
+            if usable:
+                self._delta_seeded.add(key)
+            return out
+        self._fused(K.OP_AGD, inp, out, cfg)
+        return out
 
     def all_reduce_small(self, t: torch.Tensor, op=dist.ReduceOp.SUM):
         if self.size > 1:

@@ -17,10 +17,12 @@ from ..ops import fused
 
 class DistributedOptimizer:
     def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, dp_comm=None, *, lr=1e-4, betas=(0.9, 0.95),
-                 eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=()):
+                 eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=(), delta_param_gather: bool | None = None):
         """dp_comm: communicator of the data-parallel group (None = single replica).
         norm_groups: communicators over which the squared gradient norm must be summed besides DP
-        (tensor- and pipeline-parallel groups)."""
+        (tensor- and pipeline-parallel groups).
+        delta_param_gather: send the updated parameters as 8-bit deltas against what every rank already holds (the
+        reference's `training.dp.all_gather` policy with subAdd, training.toml:36-54); None = follow the policy."""
         self.flat_param, self.flat_grad, self.comm = flat_param, flat_grad, dp_comm
         self.dp = dp_comm.size if dp_comm is not None else 1
         self.rank = dp_comm.rank if dp_comm is not None else 0
@@ -37,6 +39,11 @@ class DistributedOptimizer:
             self.shard, dtype=flat_grad.dtype, device=dev)
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         self.norm_groups = tuple(norm_groups)
+        if delta_param_gather is None:
+            delta_param_gather = bool(dp_comm is not None and getattr(dp_comm.policy, "dp_param_delta", False))
+        self.delta = bool(delta_param_gather) and self.dp > 1 and flat_param.is_cuda
+        # with deltas the optimizer must not overwrite the previous parameters before they are subtracted
+        self._new_shard = torch.empty_like(self.param_shard) if self.delta else self.param_shard
         self.step_count = 0
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self._coef = torch.ones(1, dtype=torch.float32, device=dev)
@@ -54,10 +61,12 @@ class DistributedOptimizer:
         for c in self.norm_groups:
             c.all_reduce_small(self._sumsq)
         fused.clip_coef(self._sumsq, self.clip, grad_scale, self._coef, self.grad_norm)
-        fused.adam_step(self.master, self.m, self.v, g, self.param_shard, lr=self.lr, beta1=self.betas[0],
+        fused.adam_step(self.master, self.m, self.v, g, self._new_shard, lr=self.lr, beta1=self.betas[0],
                         beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count,
                         grad_scale=self._coef)
-        if self.dp > 1:
+        if self.delta:
+            self.comm.all_gather_delta(self._new_shard, self.flat_param)
+        elif self.dp > 1:
             self.comm.all_gather(self.param_shard, self.flat_param, role="dp")
 
     # ---- checkpointing (per-rank shard; see coccl_b200.utils.checkpoint)

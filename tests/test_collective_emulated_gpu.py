@@ -131,3 +131,33 @@ def test_phase_trace_records_ordered_timestamps(cuda):
         assert (rows[:, 0] <= rows[:, 1]).all() and (rows[:, 1] <= rows[:, 2]).all() and (rows[:, 2] <= rows[:, 3]).all()
         s = summarise(state["trace"][r])
         assert s["total_us"] > 0 and s["ctas"] == rows.shape[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_all_gather_delta_tracks_slowly_moving_parameters(cuda, dtype):
+    """Delta all-gather (subAdd): after an exact first gather every call sends 8-bit deltas; the copies stay identical on
+    all ranks and the error does not accumulate (the sender subtracts what the receivers actually hold)."""
+    torch.manual_seed(7)
+    n, count = 4, 3 * 8192 + 1000
+    cfg = C.CodecConfig("sdp4bit", 8, 2048, False, False)
+    params = [torch.randn(count, device=cuda).to(dtype) for _ in range(n)]
+    exact = torch.cat(params)
+    state = {"outs": [exact.clone() for _ in range(n)]}           # seeded by an exact gather
+    plain_err = None
+    for step in range(1, 6):
+        params = [(p.float() + 1e-2 * torch.randn(count, device=cuda)).to(dtype) for p in params]
+        K.emulate_collective("all_gather_delta", params, cfg, state=state, epoch=step)
+        torch.cuda.synchronize()
+        assert K.status_codes(state) == [0] * n
+        exact = torch.cat(params).float()
+        outs = state["outs"]
+        assert all(torch.equal(outs[0], o) for o in outs[1:])      # every rank holds the same bytes
+        err = (outs[0].float() - exact).abs().max().item()
+        # a delta of ~1e-2 quantised to 8 bits (and rounded to the output type): far below the 8-bit error of the value
+        bound = 4 * 3e-2 / 127 + (2.0 ** -8 * 4.5 if dtype == torch.bfloat16 else 0.0)
+        assert err < bound, (step, err, bound)
+        if plain_err is None:
+            plain = K.emulate_collective("all_gather", params, cfg, state={}, epoch=1)[0]
+            plain_err = (plain.float() - exact).abs().max().item()
+    if dtype == torch.float32:
+        assert err < 0.2 * plain_err, (err, plain_err)

@@ -64,7 +64,7 @@ def test_fused_collectives_over_peer_memory():
     run_distributed(_collectives_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
 
 
-def _trainer_worker(rank, world, tp, pp, dp, compress):
+def _trainer_worker(rank, world, tp, pp, dp, compress, delta=False):
     import torch.distributed as dist
     from coccl_b200.models.gpt import GPTConfig
     from coccl_b200.parallel.mesh import Mesh
@@ -72,7 +72,8 @@ def _trainer_worker(rank, world, tp, pp, dp, compress):
     from coccl_b200.train import ParallelConfig, Trainer
     dev = torch.device("cuda", rank)
     cfg = GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)
-    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress, policy=Policy(threshold_bytes=0))
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress,
+                policy=Policy(threshold_bytes=0, dp_param_delta=delta))
     tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=3e-4)
     g = torch.Generator().manual_seed(5 + mesh.dp_rank)
     tok = torch.randint(0, cfg.vocab, (8, cfg.seq_len + 1), generator=g).pin_memory()
@@ -83,6 +84,16 @@ def _trainer_worker(rank, world, tp, pp, dp, compress):
         losses.append(t.item() / (tp * dp))
     assert losses[-1] < losses[0] - 0.2, losses
     assert all(l == l for l in losses)
+    if delta:
+        # every replica holds the same parameters after the delta all-gathers, and they track the fp32 master weights
+        assert tr.opt.delta
+        fp = tr.stage.store.flat_param
+        ref = fp.clone()
+        dist.broadcast(ref, src=0, group=mesh.dp_comm.group)
+        assert torch.equal(fp, ref)
+        lo = tr.opt.rank * tr.opt.shard
+        own = fp[lo:lo + tr.opt.shard].float()
+        assert (own - tr.opt.master).abs().max().item() < 2e-2 * tr.opt.master.abs().max().item() + 1e-3
     for c in (mesh.tp_comm, mesh.dp_comm):
         if c is not None:
             assert c.status() == 0
@@ -96,6 +107,11 @@ def _trainer_worker(rank, world, tp, pp, dp, compress):
 def test_trainer_two_gpus_compressed(layout):
     tp, pp, dp = {"tp2": (2, 1, 1), "dp2": (1, 1, 2), "pp2": (1, 2, 1)}[layout]
     run_distributed(_trainer_worker, 2, "nccl", (tp, pp, dp, True))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_trainer_dp2_delta_parameter_gather():
+    run_distributed(_trainer_worker, 2, "nccl", (1, 1, 2, True, True))
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
