@@ -299,6 +299,8 @@ __global__ void __launch_bounds__(kThreads) moeDispatchKernel(const cocclkMoeArg
 }
 
 // ------------------------------------------------------------------ combine
+// KMAX: compile-time bound of topk (2, 4 or 8): sizes the per-token routing registers and the batch of loads.
+template <int KMAX>
 __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs a) {
   __shared__ SegTable T;
   __shared__ int sCnt[kMaxSeg];
@@ -343,9 +345,26 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
   const __nv_bfloat16* dotWith = reinterpret_cast<const __nv_bfloat16*>(a.dotWith[rank]);
   float* dotOut = a.dotOut[rank];
   for (int t = gw; t < a.tokens; t += GW) {
-    float dots[8];
+    float dots[KMAX];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dots[j] = 0.f;
+    for (int j = 0; j < KMAX; ++j) dots[j] = 0.f;
+    // routing of the token's choices, once per token: a dropped or absent choice reads row 0 with gate 0, so that the
+    // loop below has no branches and the loads of all choices go out together
+    const uint4* rowPtr[KMAX];
+    float gate[KMAX];
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      rowPtr[j] = reinterpret_cast<const uint4*>(myRet);
+      gate[j] = 0.f;
+      if (j < a.topk) {
+        const int en = t * a.topk + j;
+        const int p = pos[en];
+        if (p < cap) {
+          rowPtr[j] = reinterpret_cast<const uint4*>(myRet + ((long)(ids[en] / LE) * cap + p) * H * 2);
+          gate[j] = gates[en];
+        }
+      }
+    }
     for (int it = 0; it < H / 256; ++it) {
       float acc[8];
 #pragma unroll
@@ -360,15 +379,15 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
           dw[2 * i + 1] = __uint_as_float(qw[i] & 0xffff0000u);
         }
       }
+      uint4 rawv[KMAX];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < KMAX; ++j)
+        if (j < a.topk) rawv[j] = __ldcg(rowPtr[j] + it * 32 + lane);
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) {
         if (j >= a.topk) break;
-        const int en = t * a.topk + j;
-        const int p = pos[en];
-        if (p >= cap) continue;
-        const int d = ids[en] / LE;
-        const float g = gates[en];
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(myRet + ((long)d * cap + p) * H * 2) + it * 32 + lane);
+        const float g = gate[j];
+        const uint4 raw = rawv[j];
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -388,7 +407,7 @@ __global__ void __launch_bounds__(kThreads) moeCombineKernel(const cocclkMoeArgs
     }
     if (dotOut != nullptr) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < KMAX; ++j) {
         if (j >= a.topk) break;
         float d = dots[j];
         for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
@@ -450,5 +469,7 @@ extern "C" int cocclkMoeDispatch(const cocclkMoeArgs* args, int emulatedRanks, i
   return launchMoe(moeDispatchKernel, args, emulatedRanks, maxCtas, stream);
 }
 extern "C" int cocclkMoeCombine(const cocclkMoeArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
-  return launchMoe(moeCombineKernel, args, emulatedRanks, maxCtas, stream);
+  if (args->topk <= 2) return launchMoe(moeCombineKernel<2>, args, emulatedRanks, maxCtas, stream);
+  if (args->topk <= 4) return launchMoe(moeCombineKernel<4>, args, emulatedRanks, maxCtas, stream);
+  return launchMoe(moeCombineKernel<8>, args, emulatedRanks, maxCtas, stream);
 }
