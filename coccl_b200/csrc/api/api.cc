@@ -178,6 +178,17 @@ ncclResult_t cocclApiCommUserRank(ncclComm_t comm, int* r) { if (!comm || !r) re
 ncclResult_t cocclApiCommCuDevice(ncclComm_t comm, int* d) { if (!comm || !d) return ncclInvalidArgument; *d = unwrap(comm)->cudaDev; return ncclSuccess; }
 ncclResult_t cocclApiCommGetAsyncError(ncclComm_t comm, ncclResult_t* e) {
   if (!comm || !e) return ncclInvalidArgument;
+  // a fused kernel whose wait on a peer ran out reports here as a remote error (the reference inherits NCCL's
+  // abort flag polling for this, src/device/prims_simple.h:97-132 and src/init.cc:2286)
+  if (state().executor != nullptr) {
+    const unsigned int w = state().executor->asyncStatus(unwrap(comm));
+    if (w != 0) {
+      COCCL_WARN("comm %llu: a fused collective gave up waiting (phase %u, peer %u, slice %u)", (unsigned long long)unwrap(comm)->id,
+                 (w >> 23) & 0xffu, (w >> 15) & 0xffu, w & 0x7fffu);
+      *e = ncclRemoteError;
+      return ncclSuccess;
+    }
+  }
   return ncclTransport().asyncError(unwrap(comm), e);
 }
 const char* cocclApiGetErrorString(ncclResult_t r) { return ncclTransport().errorString(r); }

@@ -5,62 +5,62 @@
 #include <map>
 #include <mutex>
 #include <string.h>
+#include <vector>
 
 #include "kernels/kernels_api.h"
 #include "runtime/log.h"
 #include "runtime/primitives.h"
-#include "symm/symm.h"
+#include "runtime/symm_workspace.h"
 
 namespace coccl {
 namespace {
 
-struct SymmRegion {
-  cocclSymmBuffer* buf = nullptr;
-  void* ptrs[COCCLK_MAX_RANKS] = {};
-  size_t bytes = 0;
+// Host-level all-gather through the communicator's own transport: the blobs travel through two small device
+// buffers and come back with a stream synchronisation (rare path: region set-up and regrowth only).
+class TransportExchange : public HostExchange {
+ public:
+  TransportExchange(Comm* comm, cudaStream_t s) : comm_(comm), stream_(s) {}
+  ~TransportExchange() override {
+    if (dMine_) cudaFree(dMine_);
+    if (dAll_) cudaFree(dAll_);
+  }
+  int rank() const override { return comm_->rank; }
+  int nRanks() const override { return comm_->nRanks; }
+  bool allGather(const void* mine, void* all, size_t bytes) override {
+    const size_t n = (size_t)comm_->nRanks;
+    if (bytes > cap_) {
+      if (dMine_) cudaFree(dMine_);
+      if (dAll_) cudaFree(dAll_);
+      dMine_ = dAll_ = nullptr;
+      cap_ = 0;
+      if (cudaMalloc(&dMine_, bytes) != cudaSuccess || cudaMalloc(&dAll_, bytes * n) != cudaSuccess) return false;
+      cap_ = bytes;
+    }
+    if (cudaMemcpyAsync(dMine_, mine, bytes, cudaMemcpyHostToDevice, stream_) != cudaSuccess) return false;
+    if (comm_->transport->allGather(comm_, dMine_, dAll_, bytes, ncclUint8, stream_) != ncclSuccess) return false;
+    if (cudaMemcpyAsync(all, dAll_, bytes * n, cudaMemcpyDeviceToHost, stream_) != cudaSuccess) return false;
+    return cudaStreamSynchronize(stream_) == cudaSuccess;
+  }
+
+ private:
+  Comm* comm_;
+  cudaStream_t stream_;
+  void* dMine_ = nullptr;
+  void* dAll_ = nullptr;
+  size_t cap_ = 0;
 };
 
 struct FusedState {
-  SymmRegion signals;   // flags + status word
-  SymmRegion workspace; // two parity halves
+  SymmRegion signals;    // flags + status word
+  SymmRegion workspace;  // two parity halves
   size_t half = 0;
   unsigned epoch = 0;
-  bool broken = false;
+  bool broken = false;   // agreed by all ranks: the staged pipeline serves this communicator
+  unsigned int* hostStatus = nullptr;  // pinned copy of the status word, refreshed after every fused launch
 };
 
 std::mutex gMutex;
 std::map<Comm*, FusedState> gStates;
-
-// Allocate a symmetric buffer and map every peer's; handles travel through the comm's own all-gather.
-ncclResult_t openRegion(Comm* comm, size_t bytes, cudaStream_t s, SymmRegion* r) {
-  if (cocclSymmAlloc(bytes, &r->buf) != 0) return ncclUnhandledCudaError;
-  r->bytes = bytes;
-  char mine[COCCL_SYMM_HANDLE_BYTES];
-  if (cocclSymmExport(r->buf, mine) != 0) return ncclUnhandledCudaError;
-  void* dMine = nullptr;
-  void* dAll = nullptr;
-  const size_t n = (size_t)comm->nRanks;
-  ncclResult_t res = ncclSuccess;
-  std::vector<char> all(n * COCCL_SYMM_HANDLE_BYTES);
-  if (cudaMalloc(&dMine, COCCL_SYMM_HANDLE_BYTES) != cudaSuccess || cudaMalloc(&dAll, all.size()) != cudaSuccess) res = ncclUnhandledCudaError;
-  if (res == ncclSuccess && cudaMemcpyAsync(dMine, mine, sizeof(mine), cudaMemcpyHostToDevice, s) != cudaSuccess) res = ncclUnhandledCudaError;
-  if (res == ncclSuccess) res = comm->transport->allGather(comm, dMine, dAll, COCCL_SYMM_HANDLE_BYTES, ncclUint8, s);
-  if (res == ncclSuccess && cudaMemcpyAsync(all.data(), dAll, all.size(), cudaMemcpyDeviceToHost, s) != cudaSuccess) res = ncclUnhandledCudaError;
-  if (res == ncclSuccess && cudaStreamSynchronize(s) != cudaSuccess) res = ncclUnhandledCudaError;
-  if (dMine) cudaFree(dMine);
-  if (dAll) cudaFree(dAll);
-  if (res != ncclSuccess) return res;
-  for (int p = 0; p < comm->nRanks; ++p) {
-    if (p == comm->rank) { r->ptrs[p] = cocclSymmLocalPtr(r->buf); continue; }
-    if (cocclSymmImport(r->buf, p, all.data() + (size_t)p * COCCL_SYMM_HANDLE_BYTES, &r->ptrs[p]) != 0) return ncclUnhandledCudaError;
-  }
-  return ncclSuccess;
-}
-
-void closeRegion(SymmRegion* r) {
-  if (r->buf) cocclSymmFree(r->buf);
-  *r = SymmRegion();
-}
 
 int kernelDtype(ncclDataType_t t) { return t == ncclFloat32 ? 0 : t == ncclFloat16 ? 1 : t == ncclBfloat16 ? 2 : -1; }
 
@@ -71,8 +71,10 @@ void FusedExecutor::releaseComm(Comm* comm) {
   auto it = gStates.find(comm);
   if (it == gStates.end()) return;
   cudaDeviceSynchronize();
-  closeRegion(&it->second.workspace);
-  closeRegion(&it->second.signals);
+  // teardown may run after a peer has gone: unmap and free locally, without a rendezvous
+  it->second.workspace.closeLocal(cudaSymmApi());
+  it->second.signals.closeLocal(cudaSymmApi());
+  if (it->second.hostStatus) cudaFreeHost(it->second.hostStatus);
   gStates.erase(it);
 }
 
@@ -105,28 +107,33 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   const long slot = cocclkSlotBytes(&kc, count);
   const long region = (slot * n + 255) / 256 * 256;
   const size_t need = (size_t)region * (op == 4 ? 2 : 1);
-  if (st.signals.buf == nullptr) {
-    if (openRegion(comm, (size_t)cocclkFlagBytes() + 256, info.stream, &st.signals) != ncclSuccess) {
-      COCCL_WARN("fused path: cannot map peer signal memory on comm %llu; using the staged pipeline", (unsigned long long)comm->id);
+  // Opening and growing the peer-mapped regions is collective and its outcome is agreed by all ranks
+  // (runtime/symm_workspace.h). The decision to grow depends only on the call's sizes, which the collective's
+  // contract makes equal on every rank, so all ranks enter the protocol at the same call.
+  if (!st.signals.open() || st.half < need) {
+    cudaStreamSynchronize(info.stream);  // no kernel of this rank still uses the old mapping
+    TransportExchange x(comm, info.stream);
+    const SymmApi& api = cudaSymmApi();
+    bool ok = true;
+    if (!st.signals.open()) {
+      ok = st.signals.reopen(api, x, (size_t)cocclkFlagBytes() + 256);
+      if (ok && st.hostStatus == nullptr && cudaHostAlloc((void**)&st.hostStatus, 64, cudaHostAllocDefault) == cudaSuccess) *st.hostStatus = 0;
+    }
+    if (ok && st.half < need) {
+      const size_t half = (need + (1u << 20) - 1) / (1u << 20) * (1u << 20);
+      ok = st.workspace.reopen(api, x, 2 * half);
+      st.half = ok ? st.workspace.bytes() / 2 : 0;
+      if (ok) COCCL_INFO(kLogMemory, "fused path: comm %llu workspace 2 x %zu B mapped on %d peers", (unsigned long long)comm->id, st.half, n);
+    }
+    if (!ok) {
+      COCCL_WARN("fused path: peer memory of comm %llu could not be mapped on every rank; all ranks use the staged pipeline", (unsigned long long)comm->id);
       st.broken = true;
-      closeRegion(&st.signals);
+      st.workspace.close(api, x);
+      st.signals.close(api, x);
+      st.half = 0;
       ++stagedCalls;
       return StagedExecutor::execute(rt, call);
     }
-  }
-  if (st.half < need) {
-    // every rank reaches this with the same sizes at the same call; drain before remapping
-    cudaStreamSynchronize(info.stream);
-    closeRegion(&st.workspace);
-    const size_t half = (need + (1u << 20) - 1) / (1u << 20) * (1u << 20);
-    if (openRegion(comm, 2 * half, info.stream, &st.workspace) != ncclSuccess) {
-      st.broken = true;
-      closeRegion(&st.workspace);
-      ++stagedCalls;
-      return StagedExecutor::execute(rt, call);
-    }
-    st.half = half;
-    COCCL_INFO(kLogMemory, "fused path: comm %llu workspace 2 x %zu B mapped on %d peers", (unsigned long long)comm->id, half, n);
   }
   ++st.epoch;
   cocclkCollArgs a;
@@ -143,7 +150,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   if (sliceTiles > 16) sliceTiles = 16;
   while ((tiles + sliceTiles - 1) / sliceTiles > COCCLK_MAX_SLICES) sliceTiles *= 2;
   a.sliceTiles = (int)sliceTiles;
-  a.epoch = st.epoch & 0x7fffffffu;
+  a.epoch = st.epoch;  // full 32 bits: waitFlag compares with a wrapping signed difference
   a.timeoutNs = 20ull * 1000000000ull;
   a.codec = kc;
   a.slotBytes = slot;
@@ -151,14 +158,24 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   a.in[comm->rank] = info.sendbuff;
   a.out[comm->rank] = info.recvbuff;
   for (int p = 0; p < n; ++p) {
-    a.ws[p] = static_cast<uint8_t*>(st.workspace.ptrs[p]) + (size_t)(st.epoch & 1u) * st.half;
-    a.flags[p] = static_cast<unsigned int*>(st.signals.ptrs[p]);
-    a.status[p] = static_cast<char*>(st.signals.ptrs[p]) + cocclkFlagBytes();
+    a.ws[p] = static_cast<uint8_t*>(st.workspace.ptr(p)) + (size_t)(st.epoch & 1u) * st.half;
+    a.flags[p] = static_cast<unsigned int*>(st.signals.ptr(p));
+    a.status[p] = static_cast<char*>(st.signals.ptr(p)) + cocclkFlagBytes();
   }
   const int rc = cocclkFusedCollective(&a, 1, 0, info.stream);
   if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+  // the status word (written by a bounded wait that ran out) follows the kernel to pinned host memory, where
+  // asyncStatus reads it without touching the device
+  if (st.hostStatus) cudaMemcpyAsync(st.hostStatus, a.status[comm->rank], sizeof(unsigned int), cudaMemcpyDeviceToHost, info.stream);
   ++fusedCalls;
   return ncclSuccess;
+}
+
+unsigned int FusedExecutor::asyncStatus(Comm* comm) {
+  std::lock_guard<std::mutex> lock(gMutex);
+  auto it = gStates.find(comm);
+  if (it == gStates.end() || it->second.hostStatus == nullptr) return 0;
+  return *static_cast<volatile unsigned int*>(it->second.hostStatus);
 }
 
 }  // namespace coccl

@@ -41,6 +41,9 @@ class FusedExecutor : public StagedExecutor {
   FusedExecutor(BufferManager* buffers) : StagedExecutor(buffers) {}
   ncclResult_t execute(Runtime* rt, const PreparedCall& call) override;
   void releaseComm(Comm* comm);
+  // Status word of the communicator's last completed fused kernels (0 = fine; otherwise the {phase, peer, slice}
+  // of the first bounded wait that ran out). Reads pinned host memory only.
+  unsigned int asyncStatus(Comm* comm);
   uint64_t fusedCalls = 0, stagedCalls = 0;
 };
 

@@ -57,15 +57,22 @@ extern "C" int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void
 extern "C" void* cocclSymmLocalPtr(const cocclSymmBuffer* buf) { return buf ? buf->local : nullptr; }
 extern "C" size_t cocclSymmBytes(const cocclSymmBuffer* buf) { return buf ? buf->bytes : 0; }
 
-extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
+extern "C" int cocclSymmCloseImports(cocclSymmBuffer* buf) {
   if (!buf) return 0;
   cudaError_t first = cudaSuccess;
-  for (void* p : buf->imported) {
+  for (void*& p : buf->imported) {
     if (p) {
       cudaError_t e = cudaIpcCloseMemHandle(p);
       if (first == cudaSuccess) first = e;
+      p = nullptr;
     }
   }
+  return (int)first;
+}
+
+extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
+  if (!buf) return 0;
+  cudaError_t first = (cudaError_t)cocclSymmCloseImports(buf);
   if (buf->local) {
     cudaError_t e = cudaFree(buf->local);
     if (first == cudaSuccess) first = e;
@@ -77,6 +84,11 @@ extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
 // Small synchronous device->host read (status words).
 extern "C" int cocclHostRead32(const void* dev, unsigned int* out) {
   return (int)cudaMemcpy(out, dev, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+}
+
+// Stream-ordered read of `words` 32-bit words into pinned host memory (status words, polled later without a sync).
+extern "C" int cocclAsyncRead32(void* pinnedHost, const void* dev, int words, cudaStream_t stream) {
+  return (int)cudaMemcpyAsync(pinnedHost, dev, (size_t)words * sizeof(unsigned int), cudaMemcpyDeviceToHost, stream);
 }
 
 // Stream-ordered device-to-device copy between raw addresses (e.g. out of a symmetric workspace, which has no

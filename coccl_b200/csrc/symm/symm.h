@@ -9,9 +9,8 @@
 // thing the fused kernels need. Handle exchange itself is left to the caller
 // (torch.distributed store, NCCL all-gather, a socket): handles are plain bytes.
 //
-// Two backends: "ipc" = cudaMalloc + CUDA IPC handles (64 bytes), and "vmm" =
-// cuMemCreate + POSIX file descriptors passed over a Unix-domain socket
-// (see symm_vmm.cc). Both sit behind the same functions.
+// This interface is the CUDA-IPC backend (cudaMalloc + 64-byte IPC handles). The cuMem VMM backend with
+// POSIX file descriptors and the NVSwitch multicast binding is symm_vmm.h.
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -33,7 +32,11 @@ int cocclSymmExport(const cocclSymmBuffer* buf, void* handle);
 int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void* handle, void** mapped);
 void* cocclSymmLocalPtr(const cocclSymmBuffer* buf);
 size_t cocclSymmBytes(const cocclSymmBuffer* buf);
-// Unmap every imported peer and free the local allocation.
+// Unmap every imported peer; the local allocation stays. CUDA leaves freeing exported memory that a peer still
+// has mapped undefined, so a collective teardown is: every rank closes its imports, all ranks meet, then each
+// frees its own allocation.
+int cocclSymmCloseImports(cocclSymmBuffer* buf);
+// Unmap every imported peer (if still mapped) and free the local allocation.
 int cocclSymmFree(cocclSymmBuffer* buf);
 
 #ifdef __cplusplus

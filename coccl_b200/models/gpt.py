@@ -50,9 +50,10 @@ class GPTConfig:
         return self.n_layer * per_layer + self.vocab * h + self.seq_len * h + 2 * h
 
     def flops_per_token(self) -> float:
-        """Training FLOPs per token (fwd+bwd = 3x fwd), causal attention counted at half."""
+        """Training FLOPs per token (fwd+bwd = 3x fwd). Attention: QK^T and PV are 2*s*h each per token for full
+        attention; a causal mask needs half of it, so 2*s*h per layer in total."""
         h, f, s = self.hidden, self.ffn, self.seq_len
-        per_layer = 2 * (4 * h * h + 2 * h * f) + 2 * 2 * s * h / 2 * 2 / 2 * 2
+        per_layer = 2 * (4 * h * h + 2 * h * f) + 2 * s * h
         return 3.0 * (self.n_layer * per_layer + 2 * h * self.vocab)
 
 
@@ -93,6 +94,9 @@ class ParamStore:
         self.replicated[name] = replicated
 
     def materialise(self, seed=1234, tp_rank=0, grad_dtype=torch.float32):
+        # replicated parameters go last, so that "everything a tensor-parallel rank other than 0 must leave out of
+        # the gradient norm" is one contiguous range of the flat buffers (norm_exclude_ranges)
+        self.specs.sort(key=lambda sp: self.replicated[sp[0]])
         sizes = [math.prod(s) for _, s, _, _ in self.specs]
         # every parameter starts on a 16-byte boundary of both buffers (8 elements)
         offs, total = [], 0
@@ -116,7 +120,23 @@ class ParamStore:
             p = nn.Parameter(view, requires_grad=True)
             p.main_grad = self.flat_grad[off:off + n].view(shape)
             self.params[name] = p
+        self.offsets = {name: (off, n) for (name, _, _, _), off, n in zip(self.specs, offs, sizes)}
         return self
+
+    def norm_exclude_ranges(self, tp_rank: int, drop_wte: bool):
+        """[lo, hi) ranges of the flat gradient that this rank must not count in the global gradient norm because
+        another rank counts the same values: parameters replicated over the tensor-parallel group hold identical
+        gradients on every TP rank once they are summed (counted on TP rank 0 only), and the word embedding shared
+        by the first and last pipeline stage is counted on the first stage only (`drop_wte` on the last)."""
+        out = []
+        if tp_rank != 0:
+            rep = [self.offsets[n] for n in self.offsets if self.replicated[n]]
+            if rep:
+                out.append((min(o for o, _ in rep), max(o + n for o, n in rep)))
+        if drop_wte and "wte" in self.offsets:
+            o, n = self.offsets["wte"]
+            out.append((o, o + n))
+        return out
 
 
 class TransformerLayer(nn.Module):

@@ -59,32 +59,73 @@ class Policy:
 NATIVE = Policy(enabled=False)
 
 
-class _Symm:
-    """A symmetric buffer: local allocation + mapped peers."""
+class PeerLost(RuntimeError):
+    """A bounded wait inside a fused kernel ran out: a peer did not deliver. `where` decodes the status word."""
 
-    def __init__(self, comm: "Communicator", nbytes: int):
+    def __init__(self, family: str, word: int, err: int = 0):
+        self.family, self.word, self.err = family, word, err
+        self.where = {"phase": (word >> 23) & 0xFF, "peer": (word >> 15) & 0xFF, "slice": word & 0x7FFF}
+        super().__init__(f"{family}: a wait on a peer gave up (status 0x{word:08x} = {self.where}, pipeline error 0x{err:08x}); "
+                         "the outputs of that call are not valid")
+
+
+class SymmUnavailable(RuntimeError):
+    """Peer-mapped memory could not be set up on at least one rank of the group (agreed by all ranks)."""
+
+
+class _Symm:
+    """A symmetric buffer: local allocation + mapped peers.
+
+    Opening and replacing one is collective and follows the protocol of csrc/runtime/symm_workspace.h: a rank
+    frees its allocation only after every peer has unmapped it, and a failure on one rank makes every rank raise
+    SymmUnavailable, so that all of them leave the fused path at the same call."""
+
+    def __init__(self, comm: "Communicator", nbytes: int, replaces: "_Symm | None" = None):
         lib = _lib.lib()
         self._alloc = _lib.declare("cocclSymmAlloc", C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)])
         self._export = _lib.declare("cocclSymmExport", C.c_int, [C.c_void_p, C.c_void_p])
         self._import = _lib.declare("cocclSymmImport", C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_void_p)])
         self._local = _lib.declare("cocclSymmLocalPtr", C.c_void_p, [C.c_void_p])
+        self._close = _lib.declare("cocclSymmCloseImports", C.c_int, [C.c_void_p])
         self._free = _lib.declare("cocclSymmFree", C.c_int, [C.c_void_p])
+        self.handle, self.nbytes, self.ptrs = None, nbytes, []
+        if replaces is not None:
+            # nobody's kernels use the old mapping any more, then nobody maps it, then it is freed
+            torch.cuda.synchronize()
+            dist.barrier(group=comm.group)
+            replaces.close_imports()
+            dist.barrier(group=comm.group)
+            replaces.free()
         h = C.c_void_p()
-        _lib.check(self._alloc(nbytes, C.byref(h)), "cocclSymmAlloc")
-        self.handle, self.nbytes = h, nbytes
         buf = C.create_string_buffer(64)
-        _lib.check(self._export(h, buf), "cocclSymmExport")
-        handles = [None] * comm.size
-        dist.all_gather_object(handles, bytes(buf.raw), group=comm.group)
-        self.ptrs = []
-        for p in range(comm.size):
-            if p == comm.rank:
-                self.ptrs.append(self._local(h))
-            else:
+        ok = self._alloc(nbytes, C.byref(h)) == 0 and self._export(h, buf) == 0
+        self.handle = h if h.value else None
+        offers = [None] * comm.size
+        dist.all_gather_object(offers, (ok, bytes(buf.raw)), group=comm.group)
+        ok = all(o[0] for o in offers)
+        if ok:
+            for p in range(comm.size):
+                if p == comm.rank:
+                    self.ptrs.append(self._local(h))
+                    continue
                 m = C.c_void_p()
-                hb = C.create_string_buffer(handles[p], 64)
-                _lib.check(self._import(h, p, hb, C.byref(m)), "cocclSymmImport")
+                hb = C.create_string_buffer(offers[p][1], 64)
+                if self._import(h, p, hb, C.byref(m)) != 0:
+                    ok = False
+                    break
                 self.ptrs.append(m.value)
+        outcome = [None] * comm.size
+        dist.all_gather_object(outcome, ok, group=comm.group)
+        if not all(outcome):
+            self.close_imports()
+            dist.barrier(group=comm.group)
+            self.free()
+            raise SymmUnavailable(f"peer memory of group '{comm.name}' could not be mapped on ranks "
+                                  f"{[i for i, o in enumerate(outcome) if not o]}")
+
+    def close_imports(self):
+        if self.handle is not None:
+            self._close(self.handle)
 
     def free(self):
         if self.handle is not None:
@@ -95,8 +136,8 @@ class _Symm:
 class _Arena:
     """Parity-double-buffered symmetric workspace + flag/status block + epoch counter of one kernel family."""
 
-    def __init__(self, comm: "Communicator"):
-        self.comm = comm
+    def __init__(self, comm: "Communicator", name: str = "moe"):
+        self.comm, self.name = comm, name
         self.flag_bytes = _lib.lib().cocclkFlagBytes()
         self.sig = _Symm(comm, self.flag_bytes + 256)
         self.ws: _Symm | None = None
@@ -105,29 +146,33 @@ class _Arena:
 
     def ensure(self, half_bytes: int):
         if self.ws is None or self.half < half_bytes:
-            if self.ws is not None:
-                torch.cuda.synchronize()
-                dist.barrier(group=self.comm.group)
-                self.ws.free()
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
-            self.ws = _Symm(self.comm, 2 * half)
+            old, self.ws, self.half = self.ws, None, 0
+            self.ws = _Symm(self.comm, 2 * half, replaces=old)
             self.half = half
-            dist.barrier(group=self.comm.group)
 
     def next(self):
         """(epoch, [workspace half of every rank], [flags], [status])"""
         self.epoch += 1
         off = (self.epoch & 1) * self.half
         n = self.comm.size
-        return (self.epoch & 0x7FFFFFFF, [self.ws.ptrs[p] + off for p in range(n)], list(self.sig.ptrs),
+        return (self.epoch & 0xFFFFFFFF, [self.ws.ptrs[p] + off for p in range(n)], list(self.sig.ptrs),
                 [self.sig.ptrs[p] + self.flag_bytes for p in range(n)])
+
+    def status_ptr(self) -> int:
+        return self.sig.ptrs[self.comm.rank] + self.flag_bytes
 
     def status(self) -> int:
         torch.cuda.synchronize()
         w = (C.c_uint * 1)()
         rd = _lib.declare("cocclHostRead32", C.c_int, [C.c_void_p, C.POINTER(C.c_uint)])
-        _lib.check(rd(self.sig.ptrs[self.comm.rank] + self.flag_bytes, w), "cocclHostRead32")
+        _lib.check(rd(self.status_ptr(), w), "cocclHostRead32")
         return int(w[0])
+
+    def close_imports(self):
+        for s in (self.ws, self.sig):
+            if s is not None:
+                s.close_imports()
 
     def free(self):
         for s in (self.ws, self.sig):
@@ -155,8 +200,8 @@ class Communicator:
         self._tp_epoch = 0
         self._moe: _Arena | None = None
         self._nvls: dict | None = None
-        self._delta_seeded: set = set()
         self._trace: torch.Tensor | None = None
+        self._health: dict | None = None
         self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
@@ -168,26 +213,32 @@ class Communicator:
             self._flag_bytes = flag_bytes
             self._sig = _Symm(self, flag_bytes + 256)
         if self._ws is None or self._ws_half < half_bytes:
-            if self._ws is not None:
-                torch.cuda.synchronize()
-                dist.barrier(group=self.group)
-                self._ws.free()
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
-            self._ws = _Symm(self, 2 * half)
+            old, self._ws, self._ws_half = self._ws, None, 0
+            self._ws = _Symm(self, 2 * half, replaces=old)
             self._ws_half = half
-            dist.barrier(group=self.group)
 
-    def _fused(self, opc: int, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig):
+    def _leave_fused_path(self, why: Exception) -> None:
+        import warnings
+        warnings.warn(f"coccl_b200: group '{self.name}' falls back to native collectives on every rank: {why}")
+        self.policy = NATIVE
+
+    def _fused(self, opc: int, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig) -> bool:
+        """Launch the fused kernel; False (nothing launched, on any rank) when peer memory cannot be mapped."""
         n = self.size
         count = K.chunk_count(opc, inp.numel(), n)
         sb, region_b, total = K.workspace_bytes(opc, cfg, count, inp.dtype, n)
-        self._ensure(total)
+        try:
+            self._ensure(total)
+        except SymmUnavailable as e:
+            self._leave_fused_path(e)
+            return False
         self.epoch += 1
         parity = self.epoch & 1
         a = _lib.CollArgs()
         a.op, a.nRanks, a.rankBase, a.dtype, a.count = opc, n, self.rank, DTYPE_CODE[inp.dtype], count
         a.sliceTiles = K.pick_slice_tiles(count, n)
-        a.epoch = self.epoch & 0x7FFFFFFF
+        a.epoch = self.epoch & 0xFFFFFFFF
         a.timeoutNs = int(self.policy.timeout_ms * 1e6)
         a.codec = cfg.to_c(inp.dtype)
         a.slotBytes, a.regionBOffset = sb, region_b
@@ -204,6 +255,7 @@ class Communicator:
         _lib.check(rc, "cocclkFusedCollective")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += inp.numel() * inp.element_size()
+        return True
 
     def enable_trace(self, on: bool = True) -> None:
         """Record per-CTA phase timestamps of every following fused collective (see utils.trace)."""
@@ -252,9 +304,7 @@ class Communicator:
             return out
         nbytes = inp.numel() * inp.element_size()
         cfg = self._route(role, "reduce_scatter", inp, nbytes)
-        if cfg is not None:
-            self._fused(K.OP_RS, inp, out, cfg)
-        else:
+        if cfg is None or not self._fused(K.OP_RS, inp, out, cfg):
             self._native(nbytes)
             with nvtx_range("coccl.native.reduce_scatter"):
                 dist.reduce_scatter_tensor(out, inp, group=self.group)
@@ -266,9 +316,7 @@ class Communicator:
             return out
         nbytes = out.numel() * out.element_size()
         cfg = self._route(role, "all_gather", inp, nbytes)
-        if cfg is not None:
-            self._fused(K.OP_AG, inp, out, cfg)
-        else:
+        if cfg is None or not self._fused(K.OP_AG, inp, out, cfg):
             self._native(nbytes)
             with nvtx_range("coccl.native.all_gather"):
                 dist.all_gather_into_tensor(out, inp, group=self.group)
@@ -315,7 +363,7 @@ class Communicator:
         status = st["flags"].ptrs[self.rank] + _lib.lib().cocclkNvlsFlagBytes()
         with nvtx_range("coccl.nvls.all_reduce"):
             rc = _lib.lib().cocclkNvlsAllReduce(st["mc"], x.numel(), DTYPE_CODE[x.dtype], self.size, self.rank, fl, status,
-                                                st["epoch"] & 0x7FFFFFFF, int(self.policy.timeout_ms * 1e6),
+                                                st["epoch"] & 0xFFFFFFFF, int(self.policy.timeout_ms * 1e6),
                                                 self.policy.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkNvlsAllReduce")
         x.view(-1).copy_(buf)
@@ -329,10 +377,8 @@ class Communicator:
         cfg = self._route(role, "all_reduce", x, nbytes, divisible=(x.numel() % self.size == 0))
         if cfg is None and self.policy.nvls_all_reduce and self.cuda and x.is_cuda and self.all_reduce_nvls(x):
             return x
-        if cfg is not None:
-            op = K.OP_AR1 if nbytes <= self.policy.all_reduce_oneshot_max_bytes else K.OP_AR2
-            self._fused(op, x, x, cfg)
-        else:
+        op = K.OP_AR1 if nbytes <= self.policy.all_reduce_oneshot_max_bytes else K.OP_AR2
+        if cfg is None or not self._fused(op, x, x, cfg):
             self._native(nbytes)
             with nvtx_range("coccl.native.all_reduce"):
                 dist.all_reduce(x, group=self.group)
@@ -344,9 +390,7 @@ class Communicator:
             return out
         nbytes = inp.numel() * inp.element_size()
         cfg = self._route(role, "all_to_all", inp, nbytes, divisible=(inp.numel() % self.size == 0))
-        if cfg is not None:
-            self._fused(K.OP_A2A, inp, out, cfg)
-        else:
+        if cfg is None or not self._fused(K.OP_A2A, inp, out, cfg):
             self._native(nbytes)
             with nvtx_range("coccl.native.all_to_all"):
                 dist.all_to_all_single(out, inp, group=self.group)
@@ -359,21 +403,17 @@ class Communicator:
             self._tp_sig = _Symm(self, self._tp_flag_bytes + 256)
             self._tp_err = torch.zeros(1, dtype=torch.int32, device=self.device)
         if self._tp_ws is None or self._tp_half < half_bytes:
-            if self._tp_ws is not None:
-                torch.cuda.synchronize()
-                dist.barrier(group=self.group)
-                self._tp_ws.free()
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
-            self._tp_ws = _Symm(self, 2 * half)
+            old, self._tp_ws, self._tp_half = self._tp_ws, None, 0
+            self._tp_ws = _Symm(self, 2 * half, replaces=old)
             self._tp_half = half
-            dist.barrier(group=self.group)
 
     def _tp_args(self, M: int, N: int, K: int):
         self._tp_epoch += 1
         parity = self._tp_epoch & 1
         a = _lib.TpArgs()
         a.nRanks, a.rankBase, a.M, a.N, a.K = self.size, self.rank, M, N, K
-        a.epoch = self._tp_epoch & 0x7FFFFFFF
+        a.epoch = self._tp_epoch & 0xFFFFFFFF
         a.timeoutNs = int(self.policy.timeout_ms * 1e6)
         for p in range(self.size):
             a.ws[p] = self._tp_ws.ptrs[p] + parity * self._tp_half
@@ -443,14 +483,33 @@ class Communicator:
         self.stats["compressed_raw_bytes"] += M * N * 2
         return out
 
-    def tp_fusable(self, rows_total: int, n_out_rs: int | None = None) -> bool:
-        """Whether the one-kernel TP fusions accept a problem with `rows_total` gathered rows (and, for gemm_rs,
-        `n_out_rs` output columns)."""
+    def tp_fusable(self, rows_total: int, n_out_rs: int | None = None, width: int | None = None) -> bool:
+        """Whether the one-kernel TP fusions serve a problem with `rows_total` gathered rows (and, for gemm_rs,
+        `n_out_rs` output columns). The fusions quantise the reduce-scattered partial sums to block-scaled FP8, so
+        they apply only where the policy asks for exactly that: an MX-FP8 codec on ('tp', 'reduce_scatter'), a
+        codec on ('tp', 'all_gather'), and a message above the threshold (`width` = columns of the gathered
+        operand; the router's `bytes <= threshold` rule, coccl_runtime.cc:214). Otherwise the caller takes the
+        unfused path, whose collectives are routed one by one."""
         if not (self.cuda and self.policy.enabled and 1 < self.size <= _lib.MAX_RANKS):
+            return False
+        rs = self.policy.codec_for("tp", "reduce_scatter")
+        ag = self.policy.codec_for("tp", "all_gather")
+        if rs is None or ag is None or rs.kind != "mxfp8":
+            return False
+        cols = max(width or 0, n_out_rs or 0)
+        if cols and rows_total * cols * 2 <= self.policy.threshold_bytes:
             return False
         if rows_total % (self.size * 128) != 0:
             return False
-        return n_out_rs is None or n_out_rs % 256 == 0
+        if n_out_rs is not None and n_out_rs % 256 != 0:
+            return False
+        if self._tp_sig is None:
+            try:
+                self._ensure_tp(1 << 20)   # collective: every rank of the group asks this at the same call
+            except SymmUnavailable as e:
+                self._leave_fused_path(e)
+                return False
+        return True
 
     def tp_status(self) -> tuple[int, int]:
         """(status word, pipeline error word) of the tensor-parallel fusions; synchronises the device."""
@@ -527,25 +586,30 @@ class Communicator:
     def moe_status(self) -> int:
         return 0 if self._moe is None else self._moe.status()
 
-    def all_gather_delta(self, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig | None = None):
-        """All-gather that sends the CHANGE of `inp` since the previous call with the same `out` (parameters after an
-        optimizer step move little, so 8 bits of a small delta carry far more precision than 8 bits of the value).
-        The first call for a given `out` is an exact native all-gather that seeds the state, as the reference's subAdd
-        codec does with its raw first round (sdp4bit_quan.cu:286-353); `out` itself is the state afterwards."""
+    def all_gather_delta(self, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig | None = None, state=None):
+        """All-gather that sends the CHANGE of `inp` since the previous call (parameters after an optimizer step move
+        little, so 8 bits of a small delta carry far more precision than 8 bits of the value). `out` itself is the
+        codec state: every rank adds the same decoded deltas to it. The caller owns the state handle: pass None
+        for the first call (an exact native all-gather that seeds `out`, as the reference's subAdd codec does with
+        its raw first round, sdp4bit_quan.cu:286-353) and afterwards the handle that the previous call returned.
+        Between calls `out` must not be written by anyone else (load a checkpoint into it -> pass None again);
+        the handle also pins `out`'s storage, so a recycled address cannot be mistaken for seeded state.
+        Returns the handle (None when the delta path is not usable and the call ran exact)."""
         if self.size == 1:
             out.copy_(inp.reshape(out.shape))
-            return out
-        key = (out.data_ptr(), out.numel(), out.dtype)
+            return None
         cfg = cfg or CodecConfig("sdp4bit", 8, 2048, False, False)
         usable = self.cuda and inp.is_cuda and inp.dtype in DTYPE_CODE and inp.is_contiguous() and out.is_contiguous()
-        if not usable or key not in self._delta_seeded:
+        seeded = (state is not None and state.get("out") is out and state.get("numel") == out.numel()
+                  and state.get("version") == out._version)
+        if not usable or not seeded or not self._fused(K.OP_AGD, inp, out, cfg):
             self._native(out.numel() * out.element_size())
             dist.all_gather_into_tensor(out, inp, group=self.group)
-            if usable:
-                self._delta_seeded.add(key)
-            return out
-        self._fused(K.OP_AGD, inp, out, cfg)
-        return out
+        if not usable or not self.policy.enabled:
+            return None
+        # the kernel and the native call write `out` behind autograd's back; record the version counter after
+        # our own write so that a later in-place write by anyone else is noticed
+        return {"out": out, "numel": out.numel(), "version": out._version}
 
     def all_reduce_small(self, t: torch.Tensor, op=dist.ReduceOp.SUM):
         if self.size > 1:
@@ -559,12 +623,66 @@ class Communicator:
     def global_rank(self, group_rank: int) -> int:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
 
+    # ------------------------------------------------------------------ health
+    def post_status_read(self) -> None:
+        """Queue a copy of every status / error word of this communicator's fused kernels into pinned host memory
+        behind the work already on the current stream. Costs a few 4-byte copies and one event, no synchronisation;
+        `poll_status` looks at the result later (the trainer does both once per step)."""
+        if not self.cuda:
+            return
+        words = []  # (family, device address)
+        if self._sig is not None:
+            words.append(("collective", self._sig.ptrs[self.rank] + self._flag_bytes))
+        if self._tp_sig is not None:
+            words.append(("tensor-parallel fusion", self._tp_sig.ptrs[self.rank] + self._tp_flag_bytes))
+            words.append(("tensor-parallel pipeline", self._tp_err.data_ptr()))
+        if self._moe is not None:
+            words.append(("expert all-to-all", self._moe.status_ptr()))
+        if self._nvls is not None and self._nvls.get("flags") is not None:
+            words.append(("multimem all-reduce", self._nvls["flags"].ptrs[self.rank] + _lib.lib().cocclkNvlsFlagBytes()))
+        if not words:
+            return
+        if self._health is None:
+            self._health = {"host": torch.zeros(16, dtype=torch.int32).pin_memory(), "event": torch.cuda.Event(),
+                            "families": [], "pending": False}
+        rd = _lib.declare("cocclAsyncRead32", C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p])
+        h = self._health
+        for i, (_, addr) in enumerate(words):
+            _lib.check(rd(h["host"].data_ptr() + 4 * i, addr, 1, _lib.cur_stream()), "cocclAsyncRead32")
+        h["families"] = [f for f, _ in words]
+        h["event"].record()
+        h["pending"] = True
+
+    def poll_status(self, wait: bool = False) -> None:
+        """Raise PeerLost if the words copied by the last `post_status_read` show that a wait gave up. Without
+        `wait` a copy that has not finished yet is simply looked at on the next call."""
+        h = self._health
+        if h is None or not h["pending"]:
+            return
+        if wait:
+            h["event"].synchronize()
+        elif not h["event"].query():
+            return
+        h["pending"] = False
+        vals = [int(v) & 0xFFFFFFFF for v in h["host"][:len(h["families"])].tolist()]
+        for fam, v in zip(h["families"], vals):
+            if v != 0:
+                if fam == "tensor-parallel pipeline":
+                    raise PeerLost(fam, 0, v)
+                raise PeerLost(fam, v)
+
     def close(self):
-        if self._ws is not None or self._sig is not None or self._tp_ws is not None or self._moe is not None:
+        arenas = [self._ws, self._sig, self._tp_ws, self._tp_sig, self._moe, self._nvls["flags"] if self._nvls else None]
+        if any(x is not None for x in arenas):
             torch.cuda.synchronize()
             if self.size > 1:
                 dist.barrier(group=self.group)
-        for s in (self._ws, self._sig, self._tp_ws, self._tp_sig, self._moe, self._nvls["flags"] if self._nvls else None):
-            if s is not None:
-                s.free()
-        self._ws = self._sig = None
+            for x in arenas:
+                if x is not None:
+                    x.close_imports()
+            if self.size > 1:
+                dist.barrier(group=self.group)
+        for x in arenas:
+            if x is not None:
+                x.free()
+        self._ws = self._sig = self._tp_ws = self._tp_sig = self._moe = None

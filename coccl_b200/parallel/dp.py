@@ -17,10 +17,14 @@ from ..ops import fused
 
 class DistributedOptimizer:
     def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, dp_comm=None, *, lr=1e-4, betas=(0.9, 0.95),
-                 eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=(), delta_param_gather: bool | None = None):
+                 eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=(), delta_param_gather: bool | None = None,
+                 norm_exclude=()):
         """dp_comm: communicator of the data-parallel group (None = single replica).
         norm_groups: communicators over which the squared gradient norm must be summed besides DP
         (tensor- and pipeline-parallel groups).
+        norm_exclude: [lo, hi) ranges of the flat buffers whose gradients another rank of `norm_groups` already
+        counts (ParamStore.norm_exclude_ranges); they are left out of this rank's sum of squares, so the clip
+        coefficient equals the one of a run without tensor / pipeline parallelism.
         delta_param_gather: send the updated parameters as 8-bit deltas against what every rank already holds (the
         reference's `training.dp.all_gather` policy with subAdd, training.toml:36-54); None = follow the policy."""
         self.flat_param, self.flat_grad, self.comm = flat_param, flat_grad, dp_comm
@@ -39,11 +43,16 @@ class DistributedOptimizer:
             self.shard, dtype=flat_grad.dtype, device=dev)
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         self.norm_groups = tuple(norm_groups)
+        # the excluded ranges, cut to this rank's shard and expressed in shard coordinates
+        self._excl = [(max(a, lo) - lo, min(b, lo + self.shard) - lo) for a, b in norm_exclude
+                      if max(a, lo) < min(b, lo + self.shard)]
+        self._sumsq_excl = torch.zeros(1, dtype=torch.float32, device=dev)
         if delta_param_gather is None:
             delta_param_gather = bool(dp_comm is not None and getattr(dp_comm.policy, "dp_param_delta", False))
         self.delta = bool(delta_param_gather) and self.dp > 1 and flat_param.is_cuda
         # with deltas the optimizer must not overwrite the previous parameters before they are subtracted
         self._new_shard = torch.empty_like(self.param_shard) if self.delta else self.param_shard
+        self._delta_state = None   # handle of the seeded delta all-gather (see Communicator.all_gather_delta)
         self.step_count = 0
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self._coef = torch.ones(1, dtype=torch.float32, device=dev)
@@ -56,6 +65,9 @@ class DistributedOptimizer:
             self.comm.reduce_scatter(self.flat_grad, self.grad_shard, role="dp")
         g = self.grad_shard
         fused.sum_squares(g, self._sumsq)
+        for a, b in self._excl:
+            fused.sum_squares(g[a:b], self._sumsq_excl)
+            self._sumsq -= self._sumsq_excl
         if self.dp > 1:
             self.comm.all_reduce_small(self._sumsq)
         for c in self.norm_groups:
@@ -65,7 +77,7 @@ class DistributedOptimizer:
                         beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count,
                         grad_scale=self._coef)
         if self.delta:
-            self.comm.all_gather_delta(self._new_shard, self.flat_param)
+            self._delta_state = self.comm.all_gather_delta(self._new_shard, self.flat_param, state=self._delta_state)
         elif self.dp > 1:
             self.comm.all_gather(self.param_shard, self.flat_param, role="dp")
 
@@ -79,5 +91,6 @@ class DistributedOptimizer:
         self.v.copy_(sd["v"])
         self.step_count = int(sd["step"])
         self.param_shard.copy_(self.master)
+        self._delta_state = None   # the replicas no longer match what the deltas were taken against: re-seed exactly
         if self.dp > 1:
             self.comm.all_gather(self.param_shard, self.flat_param, role="dp")

@@ -202,7 +202,7 @@ class TPContext:
 
     def can_fuse(self, x_shard, n_out_rs=None) -> bool:
         return (self.fuse_gemm and self.sequence_parallel and x_shard.is_cuda and x_shard.dim() == 2 and
-                self.comm.tp_fusable(x_shard.shape[0] * self.size, n_out_rs))
+                self.comm.tp_fusable(x_shard.shape[0] * self.size, n_out_rs, x_shard.shape[1]))
 
     def gather_linear(self, x_shard, w, bias=None, gelu=False):
         """act(gather_tokens(x_shard) @ w.T + bias) for a column-parallel weight shard."""
@@ -213,7 +213,7 @@ class TPContext:
     def linear_scatter(self, x_full, w, bias=None):
         """scatter_sum_tokens(x_full @ w.T) + bias for a row-parallel weight shard."""
         if self.size > 1 and self.fuse_gemm and self.sequence_parallel and x_full.is_cuda and x_full.dim() == 2 and \
-                self.comm.tp_fusable(x_full.shape[0], w.shape[0]):
+                self.comm.tp_fusable(x_full.shape[0], w.shape[0], x_full.shape[1]):
             return _LinearScatter.apply(x_full, w, bias, self.comm)
         o = fused.linear(x_full, w, bias if self.rank == 0 else None)
         return self.scatter_sum_tokens(o)

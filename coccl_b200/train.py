@@ -47,7 +47,10 @@ class Trainer:
                 norm_groups.append(g.pp_comm)
         self.opt = DistributedOptimizer(self.stage.store.flat_param, self.stage.store.flat_grad,
                                         g.dp_comm if (g is not None and dp > 1) else None, lr=lr,
-                                        weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups)
+                                        weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups,
+                                        norm_exclude=self.stage.store.norm_exclude_ranges(
+                                            g.tp_rank if g is not None else 0,
+                                            drop_wte=(pp > 1 and pp_rank == pp - 1)))
         self.schedule = None
         if pp > 1:
             from .parallel.pp import PipelineSchedule
@@ -66,6 +69,9 @@ class Trainer:
                 self._dev_tokens = torch.empty(tokens.shape, dtype=tokens.dtype, device=self.device)
             self._dev_tokens.copy_(tokens, non_blocking=True)
             tokens = self._dev_tokens
+        # health: the status words copied at the end of the previous step (no synchronisation); a wait that gave
+        # up inside a fused kernel means that step's gradients or parameters are not valid
+        self.check_health(wait=False)
         self.stage.zero_grad_buffer()
         self._loss_acc.zero_()
         # loss is summed over tokens of this rank's micro-batches and scaled so that the sum over
@@ -83,4 +89,20 @@ class Trainer:
         if self.groups is not None:
             self.groups.sync_shared_grads(self.stage)
         self.opt.step(grad_scale=1.0)
+        for c in self._comms():
+            c.post_status_read()
         return self._loss_acc * self.parallel.dp  # this rank's mean loss
+
+    def _comms(self):
+        g = self.groups
+        return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm) if g is not None else ()) if c is not None]
+
+    def check_health(self, wait: bool = True) -> None:
+        """Raise coccl_b200.parallel.comm.PeerLost if a bounded wait inside a fused collective, a tensor-parallel
+        fusion or the expert exchange gave up during an earlier step, and RuntimeError for a GEMM pipeline error.
+        `wait=True` first waits for the copies of the status words queued by the last step."""
+        for c in self._comms():
+            c.poll_status(wait=wait)
+        if wait:
+            from .ops import gemm as G
+            G.check_errors()

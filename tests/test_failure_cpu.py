@@ -130,3 +130,54 @@ def test_plugin_load_failure_degrades_to_an_error_not_a_crash(tmp_path):
                    f'library_path = "{lib / "plugins"}"\n[normal.all_reduce.default]\ncompressor = "nosuchcodec"\n')
     r = subprocess.run([str(lib / "coccl-config-check"), str(bad)], capture_output=True, text=True)
     assert r.returncode == 1 and "nosuchcodec" in r.stderr
+
+
+def test_status_word_raises_peer_lost_with_decoded_fields():
+    """poll_status turns a non-zero status word (as a bounded wait writes it: 0x80000000 | phase << 23 | peer << 15 |
+    slice) into PeerLost; a pending copy whose event has not completed is left for the next poll."""
+    import torch
+    from coccl_b200.parallel.comm import Communicator, PeerLost
+
+    class Ev:
+        def __init__(self, done): self.done = done
+        def query(self): return self.done
+        def synchronize(self): self.done = True
+
+    c = Communicator(None, None, None, "dp")
+    word = 0x80000000 | (2 << 23) | (5 << 15) | 77
+    host = torch.zeros(16, dtype=torch.int32)
+    host[1] = word - (1 << 32)
+    c._health = {"host": host, "event": Ev(False), "families": ["collective", "tensor-parallel fusion"], "pending": True}
+    c.poll_status(wait=False)            # copy still in flight: nothing raised, still pending
+    assert c._health["pending"]
+    try:
+        c.poll_status(wait=True)
+    except PeerLost as e:
+        assert e.family == "tensor-parallel fusion" and e.where == {"phase": 2, "peer": 5, "slice": 77}
+    else:
+        raise AssertionError("PeerLost not raised")
+    assert not c._health["pending"]
+    c.poll_status(wait=True)             # consumed: a second poll is quiet
+
+
+def test_tp_fusion_follows_the_policy():
+    """The one-kernel TP fusions quantise to FP8: they are taken only when the policy configures MX-FP8 for the TP
+    reduce-scatter and a codec for the TP all-gather, and only above the threshold."""
+    from coccl_b200.ops.codec import MXFP8, SDP4BIT_G128
+    from coccl_b200.parallel.comm import Communicator, Policy
+
+    def fusable(policy, rows=4096, n=1024, width=1024):
+        c = Communicator(None, None, policy, "tp")
+        c.cuda, c.size, c._tp_sig = True, 2, object()   # pretend: CUDA group of two with its signal region open
+        return c.tp_fusable(rows, n, width)
+
+    assert fusable(Policy(threshold_bytes=0))
+    p = Policy(threshold_bytes=0); p.codecs[("tp", "reduce_scatter")] = None
+    assert not fusable(p)
+    p = Policy(threshold_bytes=0); p.codecs[("tp", "all_gather")] = None
+    assert not fusable(p)
+    p = Policy(threshold_bytes=0); p.codecs[("tp", "reduce_scatter")] = SDP4BIT_G128
+    assert not fusable(p)
+    assert not fusable(Policy(threshold_bytes=4096 * 1024 * 2))       # bytes <= threshold stays native
+    assert fusable(Policy(threshold_bytes=4096 * 1024 * 2 - 1))
+    assert not fusable(Policy(enabled=False))

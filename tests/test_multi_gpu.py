@@ -250,3 +250,36 @@ def _nvls_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_nvls_all_reduce_or_native_fallback():
     run_distributed(_nvls_worker, min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, "nccl")
+
+
+def _lost_peer_worker(rank, world):
+    """Rank 1 never launches its side of an all-reduce: rank 0's bounded waits run out (50 ms), the kernel returns,
+    and the status word copied after the call makes poll_status raise PeerLost with the phase and peer. Nothing
+    traps or hangs; rank 1 has no kernel in flight."""
+    import torch.distributed as dist
+    from coccl_b200.parallel.comm import Communicator, PeerLost, Policy
+    dev = torch.device("cuda", rank)
+    comm = Communicator(None, dev, Policy(threshold_bytes=0, timeout_ms=50.0), "default")
+    x = torch.randn(world * 65536, device=dev)
+    comm.all_reduce(x.clone())          # both ranks: maps the peer memory, epoch 1
+    comm.post_status_read()
+    comm.poll_status(wait=True)         # healthy
+    dist.barrier()
+    raised = False
+    if rank == 0:
+        comm.all_reduce(x.clone())      # epoch 2 on rank 0 only
+        comm.post_status_read()
+        try:
+            comm.poll_status(wait=True)
+        except PeerLost as e:
+            raised = True
+            assert e.family == "collective" and e.where["phase"] in (2, 3) and e.where["peer"] < world, e.where
+        assert raised
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_lost_peer_raises_on_the_host():
+    run_distributed(_lost_peer_worker, 2, "nccl")

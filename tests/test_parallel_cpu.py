@@ -22,7 +22,11 @@ def _reference_losses(steps=3, n_seq=8):
     cfg = _cfg()
     tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2)
     tok = _data(cfg, n_seq)
-    return tr, [tr.train_step(tok).item() for _ in range(steps)]
+    losses, norms = [], []
+    for _ in range(steps):
+        losses.append(tr.train_step(tok).item())
+        norms.append(tr.opt.grad_norm.item())
+    return tr, list(zip(losses, norms))
 
 
 def _worker(rank, world, tp, pp, dp, ref_losses, ref_params):
@@ -40,8 +44,12 @@ def _worker(rank, world, tp, pp, dp, ref_losses, ref_params):
     tok = _data(cfg, 8)
     per = 8 // dp
     mine = tok[mesh.dp_rank * per:(mesh.dp_rank + 1) * per]
-    for step, ref in enumerate(ref_losses):
+    for step, (ref, ref_norm) in enumerate(ref_losses):
         loss = tr.train_step(mine)
+        # the global gradient norm counts every parameter once, whatever the layout: replicated parameters on one
+        # tensor-parallel rank only, the shared embedding on one pipeline stage only
+        norm = tr.opt.grad_norm.item()
+        assert abs(norm - ref_norm) < 2e-3 * ref_norm + 1e-6, (step, norm, ref_norm)
         # mean over DP ranks of the per-rank mean == global mean; only the last stage holds the loss
         t = loss.clone()
         dist.all_reduce(t)
