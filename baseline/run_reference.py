@@ -19,6 +19,15 @@ Output: one JSON line per (op, codec, dtype, size) on stdout and, with --out, on
    "ms", "algbw_gbs", "busbw_gbs", "timing": "host wall clock / iterations, max over ranks (-a 3)"}
 A binary that exits non-zero or runs into its time limit is recorded as {"unavailable": reason} for that case
 and is not started again.
+
+Observed on 2 x B200 (driver 580, CUDA 12.9; log kept in profiles/reference_collectives_2gpu.md): the reference's
+NCCL 2.21.5 core predates this architecture and its own collective kernels do not run here. Native
+`all_reduce_perf` and `reduce_scatter_perf` stop with "an illegal memory access was encountered", native
+`all_gather_perf` and the compressed reduce-scatter / all-to-all / all-reduce programs never finish, the compressed
+all-gather faults like the native one. Only the send/receive based `alltoall_p2p_perf` completes. Code that
+faulted or hung a GPU is not started again: CLOSED below turns those cases into `unavailable` lines without
+launching anything, and the compressed programs that were not reached before the call ended are closed with
+them because they drive the same NCCL kernels.
 """
 from __future__ import annotations
 
@@ -44,6 +53,26 @@ COMP_BIN = {"all_reduce": "all_reduce_comp_twoshot_perf", "reduce_scatter": "red
 TOML_OP = {"all_reduce": "all_reduce", "reduce_scatter": "reduce_scatter", "all_gather": "all_gather",
            "all_to_all": "all_to_all"}
 DTYPE_FLAG = {"fp32": "float", "bf16": "bfloat16", "fp16": "half"}
+
+_ILLEGAL = "reference NCCL 2.21.5 kernel faults on B200: 'an illegal memory access was encountered' (common.cu:304)"
+_HANG = "reference program did not finish within 120 s on B200 (1 MiB - 64 MiB, 2 GPUs)"
+_SAME = "not started: it drives the same reference NCCL kernels and runtime that faulted or hung on B200"
+# (codec or "*" for every compressed codec, op) -> why the case is closed on B200
+CLOSED = {
+    ("native", "all_reduce"): _ILLEGAL, ("native", "reduce_scatter"): _ILLEGAL, ("native", "all_gather"): _HANG,
+    ("sdp4bit", "all_reduce"): "reference all_reduce_comp_twoshot_perf exited 2 before its first table row on B200",
+    ("sdp4bit", "reduce_scatter"): _HANG, ("sdp4bit", "all_gather"): _ILLEGAL, ("sdp4bit", "all_to_all"): _HANG,
+    ("zfp", "all_reduce"): _HANG,
+    ("*", "all_reduce"): _SAME, ("*", "reduce_scatter"): _SAME, ("*", "all_gather"): _SAME, ("*", "all_to_all"): _SAME,
+}
+
+
+def closed_reason(codec: str, op: str):
+    if (codec, op) in CLOSED:
+        return CLOSED[(codec, op)]
+    if codec != "native" and ("*", op) in CLOSED:
+        return CLOSED[("*", op)]
+    return None
 
 
 def codec_options(codec: str, op: str, stochastic_note: list) -> dict:
@@ -148,7 +177,9 @@ def main() -> int:
             binary = (NATIVE_BIN if codec == "native" else COMP_BIN)[op]
             for dt in a.dtypes.split(","):
                 key = (codec, op)
-                if time.time() - t_start > a.budget_s:
+                if closed_reason(codec, op) is not None:
+                    reason, res, tail = closed_reason(codec, op), None, ""
+                elif time.time() - t_start > a.budget_s:
                     reason = "not run: time budget of this call used up"
                     res, tail = None, ""
                 elif key in dead:

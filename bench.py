@@ -81,12 +81,17 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    # The reference is a C++/CUDA fork of NCCL with no Python package and no trainer:
-    # a pip install of its source tree fails ("Neither 'setup.py' nor 'pyproject.toml' found"), and the
-    # repository ships no model or training loop that could produce tokens/s.
+    # Two independent reasons, both recorded in DESIGN.md:
+    #  * the reference is a C++/CUDA fork of NCCL with no Python package and no trainer: a pip install of its source
+    #    tree fails ("Neither 'setup.py' nor 'pyproject.toml' found") and its Megatron submodule is empty, so no
+    #    stock code path of it produces GPT tokens/s;
+    #  * built unmodified for sm_100 (baseline/build_reference.py), its NCCL 2.21.5 collective kernels fault
+    #    ("an illegal memory access was encountered") or never finish on B200 (profiles/reference_collectives_2gpu.md),
+    #    so even a trainer preloading it could not run. Code that faulted or hung a GPU is not started again.
     print(json.dumps({"impl": "reference", "unavailable":
-                      "reference is a C++ NCCL fork without setup.py/pyproject.toml (pip install fails) and "
-                      "ships no trainer (its Megatron submodule is empty), so GPT tokens/s cannot be run from it"}))
+                      "reference is a C++ NCCL 2.21.5 fork without setup.py/pyproject.toml (pip install fails) and ships "
+                      "no trainer (empty Megatron submodule), so GPT tokens/s cannot be run from it; built for sm_100 its "
+                      "own all-reduce / reduce-scatter / all-gather kernels fault or hang on B200 and are not run again"}))
     return 0
 
 

@@ -22,7 +22,8 @@ MAX_SLICES = 4096
 class Codec(C.Structure):
     """Mirror of cocclkCodec (csrc/kernels/kernels_api.h)."""
     _fields_ = [("kind", c_int), ("bits", c_int), ("group", c_int), ("asym", c_int), ("hadamard", c_int),
-                ("stochastic", c_int), ("paramBytes", c_int), ("seed", C.c_uint32)]
+                ("stochastic", c_int), ("paramBytes", c_int), ("seed", C.c_uint32), ("aux", c_int),
+                ("f0", c_float), ("f1", c_float), ("f2", c_float)]
 
 
 class CollArgs(C.Structure):

@@ -9,8 +9,9 @@ by baseline/build_reference.py, load as they are. Inputs are seeded and identica
   * 64 Mi values ~N(0,1e-2) in fp32 and bf16, eight chunks (the collective sweep's data).
 
 Per case: encoded bytes, max and RMS error of decode(encode(x)) against x, RMS relative to the RMS of x, and the
-time of one compress+decompress round trip (host wall clock around `rounds` in-stream round trips between two
-device synchronisations, minus the same call with one round, divided by rounds-1: allocation and set-up cancel).
+time of one compress+decompress round trip (host wall clock around n in-stream round trips between two device
+synchronisations, minus the same call with one round, divided by n-1: allocation and set-up cancel; n is chosen
+so that the measured call runs about 50 ms).
 
     python -m coccl_b200.bench_codec_parity [--reference-plugins baseline/_ref/build/obj/coccl-extend/compressor_plugin/libcompress]
 """
@@ -68,11 +69,16 @@ def measure(plugin_dir, spec, x, chunks, rounds):
     rc, y, enc, t1 = roundtrip(plugin_dir, name, options, x, chunks, 1)
     if rc != 0:
         return {"error": f"round trip returned {rc}"}
-    _, _, _, t1 = roundtrip(plugin_dir, name, options, x, chunks, 1)
-    _, _, _, tr = roundtrip(plugin_dir, name, options, x, chunks, rounds)
+    # a first estimate sizes the measured run to about 50 ms of round trips, so that the allocation and plugin
+    # set-up inside the harness call (cancelled by the subtraction) do not drown a microsecond-scale kernel pair
+    t1 = min(roundtrip(plugin_dir, name, options, x, chunks, 1)[3] for _ in range(3))
+    tr = roundtrip(plugin_dir, name, options, x, chunks, rounds)[3]
+    est = max((tr - t1) / (rounds - 1), 2e-6)
+    n = int(min(max(0.05 / est, rounds), 2000))
+    tn = min(roundtrip(plugin_dir, name, options, x, chunks, n)[3] for _ in range(2))
     d = (y.float() - x.float())
     rms_x = x.float().pow(2).mean().sqrt().item()
-    per = max((tr - t1) / (rounds - 1), 1e-9)
+    per = max((tn - t1) / (n - 1), 1e-9)
     raw = x.numel() * x.element_size()
     return {"encoded_bytes": int(enc), "ratio": raw / max(enc, 1), "max_err": d.abs().max().item(),
             "rms_err": d.pow(2).mean().sqrt().item(), "rel_rms": d.pow(2).mean().sqrt().item() / rms_x,

@@ -22,10 +22,11 @@ import os
 import torch
 import torch.distributed as dist
 
-from .ops.codec import MXFP8, SDP4BIT_G128
+from .ops.codec import MXFP8, SDP4BIT_G128, SDP4BIT_G128_SR, TACO_G128, ZFP_RATE8
 from .parallel.comm import NATIVE, Communicator, Policy
 
-CODECS = {"sdp4bit": SDP4BIT_G128, "mxfp8": MXFP8}
+# sdp4bit rounds to nearest, sdp4bit_sr stochastically (the reference's SDP4Bit has only the stochastic mode)
+CODECS = {"sdp4bit": SDP4BIT_G128, "sdp4bit_sr": SDP4BIT_G128_SR, "mxfp8": MXFP8, "taco": TACO_G128, "zfp8": ZFP_RATE8}
 OPS = ("all_reduce", "reduce_scatter", "all_gather", "all_to_all")
 
 
@@ -84,6 +85,25 @@ def _time(comm: Communicator, op: str, inp, out, iters: int, warmup: int, flush)
     return float(ts.median().item())
 
 
+def _reference(a) -> None:
+    """The stock binaries of the reference, built by baseline/build_reference.py, with the same sizes, dtypes and
+    bandwidth convention. Cases whose programs faulted or hung on this hardware print an `unavailable` line."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    runner = Path(__file__).resolve().parent.parent / "baseline" / "run_reference.py"
+    if not runner.exists():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/run_reference.py is not in this checkout"}))
+        return
+    def size(mib):
+        return f"{int(mib * 1024)}K" if mib < 1 else (f"{int(mib)}M" if mib < 1024 else f"{int(mib // 1024)}G")
+    cmd = [sys.executable, str(runner), "--gpus", str(a.gpus), "--min", size(a.min_mib), "--max", size(a.max_mib),
+           "--ops", a.ops, "--dtypes", a.dtypes, "--warmup", str(max(a.warmup, 5)), "--iters", str(max(a.iters, 20))]
+    if a.out:
+        cmd += ["--out", a.out]
+    subprocess.run(cmd, check=False)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-mib", type=float, default=1)
@@ -94,7 +114,13 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default="")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: run the reference's own stock *_perf binaries (baseline/run_reference.py), "
+                         "nothing of this library; launch WITHOUT torchrun, with --gpus N")
+    ap.add_argument("--gpus", type=int, default=2, help="--impl reference only: ranks of the single-process run")
     a = ap.parse_args()
+    if a.impl == "reference":
+        return _reference(a)
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))

@@ -46,7 +46,7 @@ def main():
     ap.add_argument("--layout", default="tn", choices=["tn", "nn", "nt"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--codec", default="sdp4bit", choices=["sdp4bit", "sdp4bit_sr", "mxfp8", "sdp8"])
+    ap.add_argument("--codec", default="sdp4bit", choices=["sdp4bit", "sdp4bit_sr", "mxfp8", "sdp8", "taco", "zfp4", "zfp8", "zfp16"])
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--mib", type=int, default=256)
     ap.add_argument("--op", default="reduce_scatter")
@@ -57,7 +57,9 @@ def main():
     dev = torch.device("cuda")
     dt = torch.float32 if a.dtype == "fp32" else torch.bfloat16
     cfgs = {"sdp4bit": C.SDP4BIT_G128, "sdp4bit_sr": C.CodecConfig("sdp4bit", 4, 128, False, True, True),
-            "mxfp8": C.MXFP8, "sdp8": C.CodecConfig("sdp4bit", 8, 2048, False, False)}
+            "mxfp8": C.MXFP8, "sdp8": C.CodecConfig("sdp4bit", 8, 2048, False, False), "taco": C.TACO_G128,
+            "zfp4": C.CodecConfig("zfp", 4, 4, False, False), "zfp8": C.ZFP_RATE8,
+            "zfp16": C.CodecConfig("zfp", 16, 4, False, False)}
     out = {"what": a.what}
     if a.what == "gemm":
         G.set_variant(a.variant)

@@ -15,7 +15,7 @@ struct Fp8Config {
 };
 
 int dtypeCode(ncclDataType_t t) { return t == ncclFloat32 ? 0 : t == ncclFloat16 ? 1 : t == ncclBfloat16 ? 2 : -1; }
-cocclkCodec codec() { return cocclkCodec{1, 8, 32, 0, 0, 0, 1, 0}; }
+cocclkCodec codec() { return cocclkCodec{1, 8, 32, 0, 0, 0, 1, 0, 0, 0.f, 0.f, 0.f}; }
 Status rcToStatus(int rc) { return rc == 0 ? ncclSuccess : (rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError); }
 
 struct Fp8Block {

@@ -47,7 +47,7 @@ int dtypeCode(ncclDataType_t t) {
 }
 
 cocclkCodec toCodec(const Sdp4Config& c, ncclDataType_t dt) {
-  cocclkCodec k;
+  cocclkCodec k = {};
   k.kind = 0;
   k.bits = c.quantBits;
   k.group = c.hadamard && c.groupCount > 128 ? 128 : c.groupCount;

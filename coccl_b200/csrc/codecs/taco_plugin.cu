@@ -16,6 +16,7 @@
 // kernels/tile_io.cuh); the first five Hadamard stages are register butterflies, the remaining log2(G/32)
 // stages and the group statistics are warp shuffles over the G/32 lanes of the group.
 #include "compressor_plugin/coccl_compressor_plugin.h"
+#include "kernels/kernels_api.h"
 #include "kernels/tile_io.cuh"
 #include <cuda_fp8.h>
 
@@ -268,7 +269,60 @@ struct Taco {
     if (cudaGetLastError() != cudaSuccess) return ncclUnhandledCudaError;
     return out.commitPlanned();
   }
+
+  static cocclkCodec tileCodec(const Config& c) {
+    cocclkCodec k = {};
+    k.kind = 3; k.bits = 8; k.group = c.groupSize; k.paramBytes = 8;
+    k.aux = (c.e5m2 ? 1 : 0) | (c.saturate ? 2 : 0);
+    k.f0 = c.targetRange; k.f1 = c.lambda;
+    k.f2 = c.fp8MaxValue > 0.f ? c.fp8MaxValue : (c.e5m2 ? 57344.f : 448.f);
+    return k;
+  }
+
+  // Fused reductions (the reference's TACO offers compress / decompress only, taco/taco.cu:297-345, and leaves
+  // reductions to the runtime's decompress-to-scratch + reduce). Copies from different ranks carry different
+  // adaptive scales, but code * qs / ada is H_G(x) / sqrt(G) for every one of them, so they add up before the
+  // inverse transform (kernels/codecs.cuh TacoCodec).
+  static Status decompressReduce(const coccl::Input& in, coccl::Output& out, coccl::Context& ctx) {
+    const size_t reduce = ctx.reduceChunks();
+    if (coccl::isPassthrough(in)) return ncclInvalidUsage;
+    if (!supported(out.datatype()) || out.chunks() == 0 || out.elements() % out.chunks() != 0 || reduce == 0 ||
+        in.chunks() != out.chunks() * reduce)
+      return ncclInvalidArgument;
+    const Config& c = ctx.config<Config>();
+    const long count = (long)(out.elements() / out.chunks());
+    const long stride = tacoLayout(count, c.groupSize).totalBytes;
+    if ((size_t)stride * in.chunks() > in.bytes()) return ncclInvalidArgument;
+    cocclkCodec k = tileCodec(c);
+    const int rc = cocclkDecodeReduce(in.data(), out.data(), count, (long)out.chunks(), (long)reduce, count, stride,
+                                      out.datatype() == ncclFloat32 ? 0 : 2, &k, ctx.stream());
+    if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+    return out.commitPlanned();
+  }
+
+  static Status decompressReduceCompress(const coccl::Input& in, coccl::Output& out, coccl::Context& ctx) {
+    const size_t reduce = ctx.reduceChunks();
+    if (coccl::isPassthrough(in)) return ncclInvalidUsage;
+    if (reduce == 0 || in.chunks() % reduce != 0 || !supported(ctx.originalDatatype())) return ncclInvalidArgument;
+    const Config& c = ctx.config<Config>();
+    const size_t outChunks = in.chunks() / reduce;
+    const long count = (long)(ctx.originalElements() / outChunks);
+    const long stride = tacoLayout(count, c.groupSize).totalBytes;
+    if ((size_t)stride * in.chunks() > in.bytes() || (size_t)stride * outChunks > out.capacityBytes()) return ncclInvalidArgument;
+    cocclkCodec k = tileCodec(c);
+    const int rc = cocclkDecodeReduceEncode(in.data(), out.data(), count, (long)outChunks, (long)reduce, stride, stride, &k, ctx.stream());
+    if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+    return out.commitBytes((size_t)stride * outChunks, outChunks);
+  }
 };
 }  // namespace
 
 COCCL_REGISTER_COMPRESSOR("taco", Taco)
+
+// The library's fused collectives carry this codec as a tile codec (kernels/codecs.cuh TacoCodec, same numerics and
+// chunk layout): report the configuration so that the executor can take the one-kernel path.
+extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecQuery(const void* config, int ncclDatatype, void* out) {
+  if (config == nullptr || out == nullptr || !Taco::supported((ncclDataType_t)ncclDatatype)) return 0;
+  *static_cast<cocclkCodec*>(out) = Taco::tileCodec(*static_cast<const TacoConfig*>(config));
+  return 1;
+}

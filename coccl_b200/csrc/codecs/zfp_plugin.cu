@@ -12,6 +12,7 @@
 // its block.
 #include "compressor_plugin/coccl_compressor_plugin.h"
 #include "kernels/common.cuh"
+#include "kernels/kernels_api.h"
 #include "oracle/zfp1d.h"
 
 namespace {
@@ -134,6 +135,17 @@ bool dispatch(ncclDataType_t t, F&& f) {
   return false;
 }
 
+// Rates whose blocks fit a 64-bit register run on the library's tile kernels (kernels/codecs.cuh ZfpCodec): a
+// thread codes eight blocks and writes whole words of the same stream. They also give this codec a fused
+// decompress-reduce. Other rates use the generic kernels above.
+inline bool tileRate(int rate) { return rate == 4 || rate == 8 || rate == 16; }
+inline cocclkCodec tileCodec(int rate) {
+  cocclkCodec k = {};
+  k.kind = 4; k.bits = rate; k.group = 4; k.paramBytes = 0;
+  return k;
+}
+inline int tileDtype(ncclDataType_t t) { return t == ncclFloat32 ? 0 : t == ncclFloat16 ? 1 : t == ncclBfloat16 ? 2 : -1; }
+
 struct Zfp {
   using Config = ZfpConfig;
 
@@ -156,8 +168,17 @@ struct Zfp {
     a.rawPitch = a.count; a.maxbits = maxBits(ctx.config<Config>().rate);
     a.encStride = zfpChunkBytes(a.count, a.maxbits);
     const size_t total = (size_t)a.encStride * in.chunks();
-    if (coccl::shouldPassthrough(in, total)) return out.passthrough(in, ctx.stream());
+    // a stream as large as the input gains nothing: pass the bytes through (the reference reaches the same through
+    // the header slack in its size bound, zfp_plugin.cc:121-137)
+    if (coccl::shouldPassthrough(in, total) || total == in.bytes()) return out.passthrough(in, ctx.stream());
     if (total > out.capacityBytes()) return ncclInvalidArgument;
+    const int rate = ctx.config<Config>().rate;
+    if (tileRate(rate)) {
+      cocclkCodec k = tileCodec(rate);
+      const int rc = cocclkEncode(in.data(), out.data(), a.count, a.chunks, a.count, a.encStride, tileDtype(in.datatype()), &k, ctx.stream());
+      if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+      return out.commitBytes(total, in.chunks());
+    }
     const long items = ((a.count + 3) / 4 + 31) / 32 * a.chunks;
     dispatch(in.datatype(), [&](auto t) {
       using T = decltype(t);
@@ -182,6 +203,13 @@ struct Zfp {
     a.rawPitch = a.count; a.maxbits = maxBits(ctx.config<Config>().rate);
     a.encStride = zfpChunkBytes(a.count, a.maxbits);
     if ((size_t)a.encStride * out.chunks() > in.bytes()) return ncclInvalidArgument;
+    const int rate = ctx.config<Config>().rate;
+    if (tileRate(rate)) {
+      cocclkCodec k = tileCodec(rate);
+      const int rc = cocclkDecodeReduce(in.data(), out.data(), a.count, a.chunks, 1, a.count, a.encStride, tileDtype(out.datatype()), &k, ctx.stream());
+      if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+      return out.commitPlanned();
+    }
     const long items = ((a.count + 3) / 4 + 31) / 32 * a.chunks;
     dispatch(out.datatype(), [&](auto t) {
       using T = decltype(t);
@@ -190,7 +218,36 @@ struct Zfp {
     if (cudaGetLastError() != cudaSuccess) return ncclUnhandledCudaError;
     return out.commitPlanned();
   }
+
+  // Sum of `reduceChunks` decoded copies per output chunk in one pass (tile rates only; other rates leave the
+  // reduction to the runtime's generic decompress + reduce).
+  static Status decompressReduce(const coccl::Input& in, coccl::Output& out, coccl::Context& ctx) {
+    const int rate = ctx.config<Config>().rate;
+    const size_t reduce = ctx.reduceChunks();
+    if (!tileRate(rate) || coccl::isPassthrough(in)) return ncclInvalidUsage;
+    if (!supported(out.datatype()) || out.chunks() == 0 || out.elements() % out.chunks() != 0 || reduce == 0 ||
+        in.chunks() != out.chunks() * reduce)
+      return ncclInvalidArgument;
+    const long count = (long)(out.elements() / out.chunks());
+    const long stride = zfpChunkBytes(count, maxBits(rate));
+    if ((size_t)stride * in.chunks() > in.bytes()) return ncclInvalidArgument;
+    cocclkCodec k = tileCodec(rate);
+    const int rc = cocclkDecodeReduce(in.data(), out.data(), count, (long)out.chunks(), (long)reduce, count, stride,
+                                      tileDtype(out.datatype()), &k, ctx.stream());
+    if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
+    return out.commitPlanned();
+  }
 };
 }  // namespace
 
 COCCL_REGISTER_COMPRESSOR("zfp", Zfp)
+
+// Rates 4, 8 and 16 are tile codecs of the library's fused collectives (kernels/codecs.cuh ZfpCodec: a run of 32
+// values is exactly `rate` words of the same stream); other rates stay on this plugin's kernels and the staged path.
+extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecQuery(const void* config, int ncclDatatype, void* out) {
+  if (config == nullptr || out == nullptr || !Zfp::supported((ncclDataType_t)ncclDatatype)) return 0;
+  const int rate = static_cast<const ZfpConfig*>(config)->rate;
+  if (!tileRate(rate)) return 0;
+  *static_cast<cocclkCodec*>(out) = tileCodec(rate);
+  return 1;
+}

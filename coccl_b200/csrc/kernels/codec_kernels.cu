@@ -12,6 +12,7 @@ static inline CodecCfg toCfg(const cocclkCodec* c) {
   CodecCfg r;
   r.kind = c->kind; r.bits = c->bits; r.group = c->group; r.asym = c->asym; r.hadamard = c->hadamard;
   r.stochastic = c->stochastic; r.paramBytes = c->paramBytes; r.seed = c->seed;
+  r.aux = c->aux; r.f0 = c->f0; r.f1 = c->f1; r.f2 = c->f2;
   return r;
 }
 

@@ -33,11 +33,12 @@
 // tests/coccl-tests/src/coccl_fixed_compressor_test.cc:97-105).
 #pragma once
 #include "common.cuh"
+#include "oracle/zfp1d.h"
 #include <cuda_fp8.h>
 
 namespace coccl {
 
-enum CodecKind : int { kCodecSdp4bit = 0, kCodecMxfp8 = 1, kCodecRaw = 2 };
+enum CodecKind : int { kCodecSdp4bit = 0, kCodecMxfp8 = 1, kCodecRaw = 2, kCodecTaco = 3, kCodecZfp = 4 };
 
 struct CodecCfg {
   int kind;        // CodecKind
@@ -46,9 +47,12 @@ struct CodecCfg {
   int asym;        // sdp4bit: 1 = asymmetric
   int hadamard;    // sdp4bit: 1 = H32 rotation
   int stochastic;  // 1 = stochastic rounding, 0 = round to nearest even
-  int paramBytes;  // bytes of parameters per group (4 | 8 sdp4bit, 1 mxfp8)
+  int paramBytes;  // bytes of parameters per group (4 | 8 sdp4bit, 1 mxfp8, 8 taco, 0 zfp)
   uint32_t seed;
+  int aux;         // taco: bit 0 = E5M2 payload, bit 1 = saturating conversion
+  float f0, f1, f2;  // taco: targetRange, lambda, fp8 maximum
 };
+// taco: bits = 8, group = 32..512. zfp: bits = rate (bits per value), group = 4 (one block).
 
 struct ChunkLayout {
   long count;         // elements in the chunk
@@ -125,6 +129,7 @@ struct SdpCodec {
   static constexpr int kPerWord = 32 / BITS;   // elements per payload word
   static constexpr int kParams = SMALLG ? 4 : 1;
   static constexpr bool kRotated = HAD;
+  static constexpr int kMinBlocks = 3;  // resident CTAs per SM the fused kernels are compiled for
   static constexpr uint32_t kSignBits = BITS == 4 ? 0x88888888u : 0x80808080u;
   static constexpr uint32_t kPackFix = kSignBits - kRoundMagicBits * (BITS == 4 ? 0x11111111u : 0x01010101u);
 
@@ -332,8 +337,8 @@ struct SdpCodec {
 
   // Leave the rotated domain (after any reduction: the transform is linear). The 1/32 of the inverse
   // transform was applied by fetch (kFinishScale).
-  static constexpr float kFinishScale = HAD ? 1.f / 32.f : 1.f;
-  static __device__ __forceinline__ void finish(float (&v)[32]) {
+  static __device__ __forceinline__ float finishScale(const CodecCfg&) { return HAD ? 1.f / 32.f : 1.f; }
+  static __device__ __forceinline__ void finish(float (&v)[32], const CodecCfg&) {
     if (HAD) hadamard32(v);
   }
 };
@@ -344,6 +349,7 @@ struct MxFp8Codec {
   static constexpr int kBits = 8;
   static constexpr int kWords = 8;
   static constexpr bool kRotated = false;
+  static constexpr int kMinBlocks = 3;
 
   struct Enc {
     uint32_t w[8];
@@ -432,8 +438,249 @@ struct MxFp8Codec {
     }
   }
 
-  static constexpr float kFinishScale = 1.f;
-  static __device__ __forceinline__ void finish(float (&)[32]) {}
+  static __device__ __forceinline__ float finishScale(const CodecCfg&) { return 1.f; }
+  static __device__ __forceinline__ void finish(float (&)[32], const CodecCfg&) {}
+};
+
+// ------------------------------------------------------------------ TACO
+// Adaptive FP8 with a Walsh-Hadamard transform over the whole group (reference numerics: taco/taco.cu:118-218):
+//   ada = clamp(fp8max * rsqrt(mean(x^2) + lambda), 1e-3, 1e3);  y = H_G(x * ada) / sqrt(G);
+//   qs = clamp(max|y| / targetRange, 1e-12, 1e6);  code = fp8(clamp(y / qs, +-448));  x^ = H_G(code * qs) / sqrt(G) / ada
+// Chunk layout as the reference's: [one fp8 byte per value of every (padded) group][groups x f32 qs][groups x f32 ada].
+// A group is G/32 consecutive runs, i.e. G/32 adjacent lanes of one warp: the first five butterfly stages are
+// register work, the rest and the group statistics are warp shuffles, so every lane of the warp must call
+// encode() and finish() together. "Rotated domain" here is y / ada = H_G(x) / sqrt(G): independent of the
+// sender's ada, so copies from different ranks add up there and one inverse transform serves the sum; the
+// transform is orthonormal, so mean(x^2) for a re-encode is available without leaving the domain.
+struct TacoCodec {
+  static constexpr int kBits = 8;
+  static constexpr int kWords = 8;
+  static constexpr bool kRotated = true;
+  static constexpr int kMinBlocks = 2;  // the lane butterflies keep two copies of a run live: 128 registers, no spills
+
+  struct Enc {
+    uint32_t w[8];
+    float qs, ada;
+  };
+
+  static __device__ __forceinline__ void lanes(float (&v)[32], int lpg) {
+    const int lane = threadIdx.x & 31;
+    for (int s = 1; s < lpg; s <<= 1) {
+      const bool upper = (lane & s) != 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[i], s);
+        v[i] = upper ? o - v[i] : v[i] + o;
+      }
+    }
+  }
+
+  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& c, bool rotate, float* /*sm*/,
+                                               uint64_t /*rngElem*/) {
+    const int lpg = c.group >> 5;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) ss = fmaf(v[i], v[i], ss);
+    for (int o = 1; o < lpg; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    Enc e;
+    e.ada = fminf(fmaxf(c.f2 * rsqrtf(ss / (float)c.group + c.f1), 1e-3f), 1e3f);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= e.ada;
+    if (rotate) {
+      hadamard32(v);
+      lanes(v, lpg);
+      const float rsG = rsqrtf((float)c.group);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= rsG;
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(v[i]));
+    for (int o = 1; o < lpg; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    e.qs = fminf(fmaxf(m / c.f0, 1e-12f), 1e6f);
+    const float inv = 1.f / e.qs;
+    const __nv_fp8_interpretation_t fmt = (c.aux & 1) ? __NV_E5M2 : __NV_E4M3;
+    const __nv_saturation_t sat = (c.aux & 2) ? __NV_SATFINITE : __NV_NOSAT;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float q[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = fminf(fmaxf(v[4 * k + i] * inv, -448.f), 448.f);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), sat, fmt);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), sat, fmt);
+      e.w[k] = lo | (hi << 16);
+    }
+    return e;
+  }
+
+  static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c,
+                                               long elem) {
+    if (elem >= L.payloadBytes) return;  // runs of the padded last group are part of the stream
+    uint8_t* pw = chunk + elem;
+    if (aligned16(pw)) {
+      reinterpret_cast<uint4*>(pw)[0] = make_uint4(e.w[0], e.w[1], e.w[2], e.w[3]);
+      reinterpret_cast<uint4*>(pw)[1] = make_uint4(e.w[4], e.w[5], e.w[6], e.w[7]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) reinterpret_cast<uint32_t*>(pw)[k] = e.w[k];
+    }
+    if ((elem & (c.group - 1)) == 0) {
+      float* ps = reinterpret_cast<float*>(chunk + L.payloadBytes);
+      const long g = elem / c.group;
+      ps[g] = e.qs;
+      ps[L.groups + g] = e.ada;
+    }
+  }
+
+  struct Raw {
+    uint32_t w[8];
+    float scale;  // qs / ada (* mul)
+    int e5m2;
+    bool valid;
+  };
+  static constexpr int kBatch = 2;
+
+  static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c, long elem,
+                                              float mul) {
+    Raw r;
+    r.valid = elem < L.payloadBytes;
+    r.e5m2 = c.aux & 1;
+    if (!r.valid) return r;
+    const uint8_t* pw = chunk + elem;
+    if (aligned16(pw)) {
+      const uint4 a = __ldcg(reinterpret_cast<const uint4*>(pw)), b = __ldcg(reinterpret_cast<const uint4*>(pw) + 1);
+      r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r.w[k] = __ldcg(reinterpret_cast<const uint32_t*>(pw) + k);
+    }
+    const float* ps = reinterpret_cast<const float*>(chunk + L.payloadBytes);
+    const long g = elem / c.group;
+    r.scale = __ldcg(ps + g) / __ldcg(ps + L.groups + g) * mul;
+    return r;
+  }
+
+  static __device__ __forceinline__ void accumulate(const Raw& r, float (&acc)[32]) {
+    if (!r.valid) return;
+    const __nv_fp8_interpretation_t fmt = r.e5m2 ? __NV_E5M2 : __NV_E4M3;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(r.w[k] >> (16 * h)), fmt);
+        const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+        acc[4 * k + 2 * h] = fmaf(f.x, r.scale, acc[4 * k + 2 * h]);
+        acc[4 * k + 2 * h + 1] = fmaf(f.y, r.scale, acc[4 * k + 2 * h + 1]);
+      }
+    }
+  }
+
+  static __device__ __forceinline__ float finishScale(const CodecCfg& c) { return rsqrtf((float)c.group); }
+  static __device__ __forceinline__ void finish(float (&v)[32], const CodecCfg& c) {
+    hadamard32(v);
+    lanes(v, c.group >> 5);
+  }
+};
+
+// ------------------------------------------------------------------ ZFP fixed rate, 1-D
+// A run of 32 values is eight ZFP blocks of four; at RATE bits per value a block takes 4 * RATE bits
+// (zfp/src/zfp.c:773-803) and the run exactly RATE 32-bit words, so a thread writes whole words of the stream and
+// nothing is assembled across threads (the reference's encoder ORs blocks into a zeroed stream with atomics,
+// zfp/src/cuda_zfp/encode.cuh:224-231). Block i of a chunk sits at bit i * 4 * RATE, as in the reference stream;
+// the block coder is oracle/zfp1d.h, shared with the CPU oracle. Lossy re-encoding (two-shot all-reduce) simply
+// encodes the decoded sum again: there is no separate domain.
+template <int RATE>
+struct ZfpCodec {
+  static_assert(RATE == 4 || RATE == 8 || RATE == 16, "fused rates: 4, 8, 16 bits per value");
+  static constexpr int kBits = RATE;
+  static constexpr int kWords = RATE;
+  static constexpr bool kRotated = false;
+  static constexpr int kMinBlocks = 2;
+  static constexpr int kMaxBits = 4 * RATE;
+
+  struct Enc { uint32_t w[RATE]; };
+
+  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& /*c*/, bool /*rotate*/, float* /*sm*/,
+                                               uint64_t /*rngElem*/) {
+    Enc e;
+    if (RATE == 4) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = (uint32_t)zfp1d::encodeBlock64(&v[8 * k], kMaxBits);
+        const uint32_t hi = (uint32_t)zfp1d::encodeBlock64(&v[8 * k + 4], kMaxBits);
+        e.w[k] = lo | (hi << 16);
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        const uint64_t s = zfp1d::encodeBlock64(&v[4 * b], kMaxBits);
+        if (RATE == 8) e.w[b] = (uint32_t)s;
+        else { e.w[(2 * b) % RATE] = (uint32_t)s; e.w[(2 * b + 1) % RATE] = (uint32_t)(s >> 32); }
+      }
+    }
+    return e;
+  }
+
+  static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/,
+                                               long elem) {
+    const long off = (elem >> 5) * (4 * RATE);
+    if (off >= L.totalBytes) return;
+    uint8_t* pw = chunk + off;
+    if (off + 4 * RATE <= L.totalBytes && aligned16(pw)) {
+#pragma unroll
+      for (int q = 0; q < RATE / 4; ++q)
+        reinterpret_cast<uint4*>(pw)[q] = make_uint4(e.w[4 * q], e.w[4 * q + 1], e.w[4 * q + 2], e.w[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < RATE; ++k)
+        if (off + 4 * k + 4 <= L.totalBytes) reinterpret_cast<uint32_t*>(pw)[k] = e.w[k];
+    }
+  }
+
+  struct Raw {
+    uint32_t w[RATE];
+    bool valid;
+  };
+  static constexpr int kBatch = 1;
+
+  static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/, long elem,
+                                              float /*mul*/) {
+    Raw r;
+    const long off = (elem >> 5) * (4 * RATE);
+    r.valid = off < L.totalBytes;
+    if (!r.valid) return r;
+    const uint8_t* pw = chunk + off;
+    if (off + 4 * RATE <= L.totalBytes && aligned16(pw)) {
+#pragma unroll
+      for (int q = 0; q < RATE / 4; ++q) {
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(pw) + q);
+        r.w[4 * q] = t.x; r.w[4 * q + 1] = t.y; r.w[4 * q + 2] = t.z; r.w[4 * q + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < RATE; ++k)
+        r.w[k] = (off + 4 * k + 4 <= L.totalBytes) ? __ldcg(reinterpret_cast<const uint32_t*>(pw) + k) : 0u;
+    }
+    return r;
+  }
+
+  static __device__ __forceinline__ void accumulate(const Raw& r, float (&acc)[32]) {
+    if (!r.valid) return;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      uint64_t s;
+      if (RATE == 4) s = (r.w[b >> 1] >> (16 * (b & 1))) & 0xffffu;
+      else if (RATE == 8) s = r.w[b % RATE];
+      else s = (uint64_t)r.w[(2 * b) % RATE] | ((uint64_t)r.w[(2 * b + 1) % RATE] << 32);
+      float x[4];
+      zfp1d::decodeBlock64(s, kMaxBits, x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[4 * b + i] += x[i];
+    }
+  }
+
+  static __device__ __forceinline__ float finishScale(const CodecCfg&) { return 1.f; }
+  static __device__ __forceinline__ void finish(float (&)[32], const CodecCfg&) {}
 };
 
 // acc += mul * sum over n encoded copies of the run at `elem`, copy i at base + i * stride. The loads of
@@ -458,6 +705,13 @@ __device__ __forceinline__ void decodeSum(const uint8_t* base, long stride, int 
 template <class F>
 inline bool dispatchCodec(const CodecCfg& c, F&& f) {
   if (c.kind == kCodecMxfp8) { f(MxFp8Codec{}); return true; }
+  if (c.kind == kCodecTaco) { f(TacoCodec{}); return true; }
+  if (c.kind == kCodecZfp) {
+    if (c.bits == 4) { f(ZfpCodec<4>{}); return true; }
+    if (c.bits == 8) { f(ZfpCodec<8>{}); return true; }
+    if (c.bits == 16) { f(ZfpCodec<16>{}); return true; }
+    return false;
+  }
   if (c.kind != kCodecSdp4bit) return false;
   const bool small = c.group < 32;
 #define COCCL_SDP_CASE(B, A, H, S) \
@@ -480,6 +734,9 @@ inline bool dispatchCodec(const CodecCfg& c, F&& f) {
 
 inline bool tileCodecSupported(const CodecCfg& c) {
   if (c.kind == kCodecMxfp8) return c.group == 32;
+  if (c.kind == kCodecTaco)
+    return c.bits == 8 && c.paramBytes == 8 && (c.group == 32 || c.group == 64 || c.group == 128 || c.group == 256 || c.group == 512);
+  if (c.kind == kCodecZfp) return c.group == 4 && c.paramBytes == 0 && (c.bits == 4 || c.bits == 8 || c.bits == 16);
   if (c.kind != kCodecSdp4bit) return false;
   if (c.group < 8 || c.group > 2048 || (c.group & (c.group - 1))) return false;
   if (c.hadamard && c.group < 32) return false;

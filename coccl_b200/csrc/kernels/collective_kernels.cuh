@@ -113,7 +113,7 @@ __device__ __forceinline__ bool waitAll(unsigned int* const* flagAddrs, int n, u
 }
 
 template <typename T, class Codec>
-__global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const CollArgs a) {
+__global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollectiveKernel(const CollArgs a) {
   __shared__ TileStage<T> stage;
   __shared__ float sm[8];
   __shared__ uint8_t* sDst[kMaxRanks];
@@ -199,13 +199,13 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = 0.f;
         decodeSum<Codec>(myWs + (long)q0 * a.slotBytes, a.slotBytes, nq, L, c, e,
-                         a.op == kOpAllReduceTwoShot ? 1.f : Codec::kFinishScale, acc);
+                         a.op == kOpAllReduceTwoShot ? 1.f : Codec::finishScale(c), acc);
         if (a.op == kOpAllReduceTwoShot) {
           // stay in the rotated domain: the sum of rotated values is the rotation of the sum
           const typename Codec::Enc enc = Codec::encode(acc, c, false, sm, ((uint64_t)(0x80 + rank) << 40) + (uint64_t)e);
           for (int d = 0; d < N; ++d) Codec::store(enc, sDst[d], L, c, e);
         } else {
-          Codec::finish(acc);
+          Codec::finish(acc, c);
           const bool fast = TileIO<T>::fastTile(dstChunk, L.count, e0);
           if (a.op == kOpAllGatherDelta) {
             float pv[32];
@@ -240,8 +240,8 @@ __global__ void __launch_bounds__(kTileThreads, 3) fusedCollectiveKernel(const C
         float acc[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-        decodeSum<Codec>(myWs + a.regionBOffset + (long)q * a.slotBytes, 0, 1, L, c, e, Codec::kFinishScale, acc);
-        Codec::finish(acc);
+        decodeSum<Codec>(myWs + a.regionBOffset + (long)q * a.slotBytes, 0, 1, L, c, e, Codec::finishScale(c), acc);
+        Codec::finish(acc, c);
         TileIO<T>::store(dstChunk, L.count, e0, TileIO<T>::fastTile(dstChunk, L.count, e0), stage, acc);
       }
     }
@@ -299,8 +299,8 @@ __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecAr
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e,
-                     Codec::kFinishScale, acc);
-    Codec::finish(acc);
+                     Codec::finishScale(a.codec), acc);
+    Codec::finish(acc, a.codec);
     TileIO<T>::store(dst, L.count, e0, TileIO<T>::fastTile(dst, L.count, e0), stage, acc);
   }
 }
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecAr
 // decode + reduce + re-encode without leaving registers
 // (reference kernel: sdp4bit/quantization/dequant_reduce_quant.cu:14-179).
 template <class Codec>
-__global__ void __launch_bounds__(kTileThreads, 3) decodeReduceEncodeKernel(const CodecArgs a) {
+__global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) decodeReduceEncodeKernel(const CodecArgs a) {
   __shared__ float sm[8];
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;

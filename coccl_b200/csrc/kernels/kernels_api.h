@@ -10,14 +10,16 @@ extern "C" {
 
 // Mirrors coccl::CodecCfg (kernels/codecs.cuh).
 typedef struct cocclkCodec {
-  int kind;        // 0 sdp4bit, 1 mxfp8
-  int bits;
-  int group;
+  int kind;        // 0 sdp4bit, 1 mxfp8, 3 taco, 4 zfp
+  int bits;        // zfp: the rate (4, 8 or 16 bits per value on the tile path)
+  int group;       // zfp: 4
   int asym;
   int hadamard;
   int stochastic;
-  int paramBytes;
+  int paramBytes;  // taco: 8; zfp: 0
   uint32_t seed;
+  int aux;         // taco: bit 0 = E5M2, bit 1 = saturate
+  float f0, f1, f2;  // taco: targetRange, lambda, fp8 maximum
 } cocclkCodec;
 
 // dtype: 0 fp32, 1 fp16, 2 bf16. All return a cudaError_t value (0 = ok) or

@@ -171,5 +171,92 @@ COCCL_HD void decodeBlock(BitWindow& s, int maxbits, float* x) {
   s.pos = start + maxbits;
 }
 
+
+// ------------------------------------------------------------------ blocks of at most 64 bits
+// The same coder with the block's bit stream held in ONE 64-bit register (maxbits <= 64, i.e. rate <= 16): no
+// indexed window, so on the GPU nothing spills to local memory. Bit i of the result is bit i of the block's
+// stream; the results are bit-identical to encodeBlock / decodeBlock.
+COCCL_HD uint64_t encodeBlock64(const float* x, int maxbits) {
+  const int emax = blockExponent(x);
+  if (emax == -kEbias) return 0;
+  uint64_t acc = (uint64_t)(2 * (emax + kEbias) + 1);
+  int pos = 9;
+  int32_t q[kBlock];
+  const float scale = ldexpf(1.f, 30 - emax);
+  for (int i = 0; i < kBlock; ++i) q[i] = (int32_t)(x[i] * scale);
+  forwardLift(q);
+  uint32_t u0 = toNegabinary(q[0]), u1 = toNegabinary(q[1]), u2 = toNegabinary(q[2]), u3 = toNegabinary(q[3]);
+  int bits = maxbits - 9;
+  int n = 0;
+  for (int k = 32; bits && k-- > 0;) {
+    uint32_t plane = ((u0 >> k) & 1u) | (((u1 >> k) & 1u) << 1) | (((u2 >> k) & 1u) << 2) | (((u3 >> k) & 1u) << 3);
+    const int m = n < bits ? n : bits;
+    bits -= m;
+    acc |= (uint64_t)(plane & ((1u << m) - 1u)) << pos;
+    pos += m;
+    plane >>= m;
+    while (n < kBlock && bits) {
+      --bits;
+      const uint32_t any = plane != 0;
+      acc |= (uint64_t)any << pos;
+      ++pos;
+      if (!any) break;
+      while (n < kBlock - 1 && bits) {
+        --bits;
+        const uint32_t bit = plane & 1u;
+        acc |= (uint64_t)bit << pos;
+        ++pos;
+        if (bit) break;
+        plane >>= 1;
+        ++n;
+      }
+      plane >>= 1;
+      ++n;
+    }
+  }
+  return acc;
+}
+
+COCCL_HD void decodeBlock64(uint64_t s, int maxbits, float* x) {
+  if ((s & 1u) == 0) {
+    for (int i = 0; i < kBlock; ++i) x[i] = 0.f;
+    return;
+  }
+  const int emax = (int)((s >> 1) & 0xffu) - kEbias;
+  int pos = 9;
+  uint32_t u0 = 0, u1 = 0, u2 = 0, u3 = 0;
+  int bits = maxbits - 9;
+  int n = 0;
+  for (int k = 32; bits && k-- > 0;) {
+    const int m = n < bits ? n : bits;
+    bits -= m;
+    uint32_t plane = (uint32_t)(s >> pos) & ((1u << m) - 1u);
+    pos += m;
+    while (n < kBlock && bits) {
+      --bits;
+      const uint32_t any = (uint32_t)(s >> pos) & 1u;
+      ++pos;
+      if (!any) break;
+      while (n < kBlock - 1 && bits) {
+        --bits;
+        const uint32_t bit = (uint32_t)(s >> pos) & 1u;
+        ++pos;
+        if (bit) break;
+        ++n;
+      }
+      plane |= 1u << n;
+      ++n;
+    }
+    u0 |= (plane & 1u) << k;
+    u1 |= ((plane >> 1) & 1u) << k;
+    u2 |= ((plane >> 2) & 1u) << k;
+    u3 |= ((plane >> 3) & 1u) << k;
+  }
+  int32_t q[kBlock] = {fromNegabinary(u0), fromNegabinary(u1), fromNegabinary(u2), fromNegabinary(u3)};
+  inverseLift(q);
+  const float scale = ldexpf(1.f, emax - 30);
+  for (int i = 0; i < kBlock; ++i) x[i] = (float)q[i] * scale;
+}
+
 }  // namespace zfp1d
 }  // namespace coccl

@@ -16,22 +16,32 @@ import torch
 from .. import _lib
 
 DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
-KIND_SDP4BIT, KIND_MXFP8 = 0, 1
+KIND_SDP4BIT, KIND_MXFP8, KIND_TACO, KIND_ZFP = 0, 1, 3, 4
 
 
 @dataclass(frozen=True)
 class CodecConfig:
-    kind: str = "sdp4bit"          # "sdp4bit" | "mxfp8"
-    bits: int = 4                  # sdp4bit: 4 | 8
-    group: int = 128               # elements per quantisation group (mxfp8: 32)
+    kind: str = "sdp4bit"          # "sdp4bit" | "mxfp8" | "taco" | "zfp"
+    bits: int = 4                  # sdp4bit: 4 | 8; zfp: the rate in bits per value (4 | 8 | 16); taco: 8
+    group: int = 128               # elements per quantisation group (mxfp8: 32; zfp: 4, one block; taco: 32..512)
     asym: bool = False
     hadamard: bool = True
     stochastic: bool = False
     seed: int = 0
+    # taco only (reference options fp8Format, saturate, targetRange, lambda, fp8MaxValue; taco/taco.cu:16-33)
+    e5m2: bool = False
+    saturate: bool = True
+    target_range: float = 448.0
+    lam: float = 1e-6
+    fp8_max: float = 0.0
 
     def param_bytes(self, dtype: torch.dtype) -> int:
         if self.kind == "mxfp8":
             return 1
+        if self.kind == "taco":
+            return 8
+        if self.kind == "zfp":
+            return 0
         # fp32 symmetric stores one float per group; asymmetric and all 16-bit inputs store two
         # (sdp4bit_quan.cu:63-109)
         return 4 if (dtype == torch.float32 and not self.asym) else 8
@@ -39,19 +49,28 @@ class CodecConfig:
     def to_c(self, dtype: torch.dtype) -> _lib.Codec:
         if self.kind == "mxfp8":
             return _lib.Codec(KIND_MXFP8, 8, 32, 0, 0, 0, 1, self.seed & 0xFFFFFFFF)
+        if self.kind == "taco":
+            fmax = self.fp8_max if self.fp8_max > 0 else (57344.0 if self.e5m2 else 448.0)
+            return _lib.Codec(KIND_TACO, 8, self.group, 0, 0, 0, 8, 0, int(self.e5m2) | (int(self.saturate) << 1),
+                              self.target_range, self.lam, fmax)
+        if self.kind == "zfp":
+            return _lib.Codec(KIND_ZFP, self.bits, 4, 0, 0, 0, 0, 0)
         return _lib.Codec(KIND_SDP4BIT, self.bits, self.group, int(self.asym), int(self.hadamard),
                           int(self.stochastic), self.param_bytes(dtype), self.seed & 0xFFFFFFFF)
 
     def encoded_chunk_bytes(self, count: int, dtype: torch.dtype) -> int:
-        g = 32 if self.kind == "mxfp8" else self.group
-        bits = 8 if self.kind == "mxfp8" else self.bits
+        g = {"mxfp8": 32, "zfp": 4}.get(self.kind, self.group)
+        bits = 8 if self.kind in ("mxfp8", "taco") else self.bits
         groups = -(-count // g)
         total = groups * g * bits // 8 + groups * self.param_bytes(dtype)
         return -(-total // 4) * 4
 
 
 SDP4BIT_G128 = CodecConfig("sdp4bit", 4, 128, False, True)
+SDP4BIT_G128_SR = CodecConfig("sdp4bit", 4, 128, False, True, True)   # stochastic rounding, the reference's only mode
 MXFP8 = CodecConfig("mxfp8", 8, 32, False, False)
+TACO_G128 = CodecConfig("taco", 8, 128, False, False)
+ZFP_RATE8 = CodecConfig("zfp", 8, 4, False, False)
 
 
 def encode(x: torch.Tensor, cfg: CodecConfig, chunks: int = 1) -> torch.Tensor:
@@ -129,10 +148,29 @@ def _rng_unit(seed: int, elem: torch.Tensor) -> torch.Tensor:
     return (byte.to(torch.float32) + 0.5) / 256.0
 
 
+def _zfp_oracle_roundtrip(xf: torch.Tensor, rate: int) -> torch.Tensor:
+    """ZFP fixed-rate round trip of every row of xf through the CPU coder of csrc/oracle (bit-serial: no PyTorch
+    restatement exists that would be more than a transliteration of it)."""
+    import ctypes as C
+    cb = _lib.declare("cocclOracleZfpChunkBytes", C.c_long, [C.c_long, C.c_int])
+    en = _lib.declare("cocclOracleZfpEncode", C.c_int, [C.c_void_p, C.c_long, C.c_int, C.c_void_p])
+    de = _lib.declare("cocclOracleZfpDecode", C.c_int, [C.c_void_p, C.c_long, C.c_int, C.c_void_p])
+    xc = xf.detach().cpu().contiguous()
+    out = torch.empty_like(xc)
+    count = xc.shape[1]
+    buf = torch.zeros(cb(count, rate), dtype=torch.uint8)
+    for ch in range(xc.shape[0]):
+        assert en(xc[ch].data_ptr(), count, rate, buf.data_ptr()) == 0
+        assert de(buf.data_ptr(), count, rate, out[ch].data_ptr()) == 0
+    return out
+
+
 def reference_roundtrip(x: torch.Tensor, cfg: CodecConfig, chunks: int = 1, rng_base: int = 0) -> torch.Tensor:
     """encode->decode of every chunk in fp32 PyTorch (CPU or GPU); returns fp32 of x's shape."""
     count = x.numel() // chunks
     xf = x.detach().reshape(chunks, count).to(torch.float32)
+    if cfg.kind == "zfp":
+        return _zfp_oracle_roundtrip(xf, cfg.bits).reshape(x.shape).to(x.device)
     g = 32 if cfg.kind == "mxfp8" else cfg.group
     pad = (-count) % g
     if pad:
@@ -152,6 +190,19 @@ def reference_roundtrip(x: torch.Tensor, cfg: CodecConfig, chunks: int = 1, rng_
         del e
         q = (blk / scale).to(torch.float8_e4m3fn).to(torch.float32)
         out = (q * scale).reshape(chunks, n)
+        return out[:, :count].reshape(x.shape)
+    if cfg.kind == "taco":
+        # taco/taco.cu:118-218: adaptive scale, Hadamard over the whole group, FP8 with a group scale
+        grp = xf.reshape(chunks, n // g, g)
+        h = torch.ones(1, 1, device=x.device)
+        while h.shape[0] < g:
+            h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+        fmax = cfg.fp8_max if cfg.fp8_max > 0 else (57344.0 if cfg.e5m2 else 448.0)
+        ada = (fmax * torch.rsqrt((grp * grp).mean(-1, keepdim=True) + cfg.lam)).clamp(1e-3, 1e3)
+        y = (grp * ada) @ h / g ** 0.5
+        qs = (y.abs().amax(-1, keepdim=True) / cfg.target_range).clamp(1e-12, 1e6)
+        code = (y / qs).clamp(-448, 448).to(torch.float8_e5m2 if cfg.e5m2 else torch.float8_e4m3fn).float()
+        out = ((code * qs) @ h / g ** 0.5 / ada).reshape(chunks, n)
         return out[:, :count].reshape(x.shape)
     v = xf
     if cfg.hadamard:

@@ -84,3 +84,60 @@ def test_stochastic_rounding_is_unbiased_and_reproducible(cuda):
     assert abs(a[mask].mean().item() - 0.3) < 2e-3
     ref = C.reference_roundtrip(x, cfg)
     assert ((a - ref).abs() > 1e-6).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("rate", [4, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("count,chunks", [(4096, 2), (1002, 3), (8192 * 2 + 36, 1)])
+def test_zfp_tile_codec_is_bit_identical_to_the_cpu_coder(cuda, rate, dtype, count, chunks):
+    """The tile codec writes the same stream as the CPU coder of csrc/oracle (block i at bit i * 4 * rate), and
+    decodes to the same values; sums of several encoded copies equal the sum of the oracle's decodes."""
+    import ctypes as CT
+    from coccl_b200 import _lib
+    cfg = C.CodecConfig("zfp", rate, 4, False, False)
+    torch.manual_seed(11)
+    x = (torch.randn(chunks * count, device=cuda) * 0.01).to(dtype)
+    enc = C.encode(x, cfg, chunks)
+    en = _lib.declare("cocclOracleZfpEncode", CT.c_int, [CT.c_void_p, CT.c_long, CT.c_int, CT.c_void_p])
+    cb = _lib.declare("cocclOracleZfpChunkBytes", CT.c_long, [CT.c_long, CT.c_int])
+    xc = x.float().cpu().reshape(chunks, count).contiguous()
+    want = torch.zeros(cb(count, rate), dtype=torch.uint8)
+    for ch in range(chunks):
+        want.zero_()
+        assert en(xc[ch].data_ptr(), count, rate, want.data_ptr()) == 0
+        got = enc[ch].cpu()
+        nbytes = (-(-count // 4) * 4 * rate + 7) // 8       # bits of the whole blocks, in bytes
+        assert torch.equal(got[:nbytes], want[:nbytes]), (ch, (got[:nbytes] != want[:nbytes]).nonzero()[:4])
+    ref = C.reference_roundtrip(x, cfg, chunks)
+    y = C.decode(enc, cfg, count, dtype, chunks).reshape(-1)
+    if dtype == torch.float32:
+        assert torch.equal(y.cpu(), ref.cpu())
+    else:
+        assert ((y.float().cpu() - ref.cpu()).abs() <= ref.cpu().abs() * 2.0 ** -7 + 1e-12).all()
+    if chunks > 1 and dtype == torch.float32:
+        s = C.decode_reduce(enc, cfg, count, dtype, 1, chunks).reshape(-1)
+        assert torch.allclose(s.cpu(), ref.cpu().reshape(chunks, count).sum(0), atol=1e-6)
+
+
+@pytest.mark.parametrize("group", [32, 128, 512])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("count,chunks", [(4096, 2), (1000, 3), (8192 * 2 + 200, 1)])
+def test_taco_tile_codec_matches_oracle(cuda, group, dtype, count, chunks):
+    cfg = C.CodecConfig("taco", 8, group, False, False)
+    torch.manual_seed(12)
+    x = (torch.randn(chunks * count, device=cuda) * 0.05).to(dtype)
+    enc = C.encode(x, cfg, chunks)
+    assert enc.shape[1] == -(-count // group) * (group + 8)
+    y = C.decode(enc, cfg, count, dtype, chunks).reshape(-1).float()
+    ref = C.reference_roundtrip(x, cfg, chunks).reshape(-1).to(dtype).float()
+    scale = ref.abs().max().item()
+    assert ((y - ref).abs() > 2e-2 * scale).float().mean().item() < 5e-3   # a flipped FP8 rounding is spread over the group
+    assert ((y - x.float()).norm() / x.float().norm()).item() < 0.05
+    if chunks > 1:
+        # copies with different adaptive scales add up in the rotated domain; one inverse transform serves the sum
+        s = C.decode_reduce(enc, cfg, count, dtype, 1, chunks).reshape(-1).float()
+        want = C.reference_roundtrip(x, cfg, chunks).reshape(chunks, count).sum(0)
+        assert ((s - want).norm() / want.norm()).item() < 0.02
+        drc = C.decode_reduce_encode(enc, cfg, count, dtype, 1, chunks)
+        s2 = C.decode(drc, cfg, count, dtype, 1).reshape(-1).float()
+        assert ((s2 - want).norm() / want.norm()).item() < 0.06
