@@ -3,6 +3,8 @@
     python -m coccl_b200.bench_kernels gemm --m 4096 --n 4096 --k 4096 [--iters 20]
     python -m coccl_b200.bench_kernels codec --codec sdp4bit --dtype fp32 --mib 1024
     python -m coccl_b200.bench_kernels collective --op reduce_scatter --ranks 8 --mib 256   (ranks emulated on one GPU)
+    python -m coccl_b200.bench_kernels tp --ranks 2 --m 4096 --k 4096 --n 2048 [--tp-variant 1cta]   (emulated ranks)
+    python -m coccl_b200.bench_kernels moe --ranks 4 --tokens 4096 --hidden 4096 --experts 32     (emulated ranks)
 
 Also the small, self-ending workloads used for ncu captures (see profiles/).
 """
@@ -39,7 +41,12 @@ def timed(fn, iters=20, warmup=5, flush_mib=256):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "codec", "collective"])
+    ap.add_argument("what", choices=["gemm", "codec", "collective", "tp", "moe"])
+    ap.add_argument("--tp-variant", default="auto", choices=["auto", "1cta", "2cta"])
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -88,6 +95,54 @@ def main():
                    encode_ms=t_enc, encode_gbs_traffic=(raw + enc.numel()) / t_enc / 1e6,
                    decode_ms=t_dec, decode_gbs_traffic=(raw + enc.numel()) / t_dec / 1e6,
                    decode_reduce8_ms=t_red, decode_reduce8_gbs_traffic=(raw / 8 + enc.numel()) / t_red / 1e6)
+    elif a.what == "tp":
+        # all-gather -> GEMM then GEMM -> FP8 reduce-scatter with every rank emulated on this GPU in one launch each
+        # (each rank owns 1/ranks of the SMs, "peer" memory is local): per rank X shard [m, k], W_up [n, k], W_down [k, n]
+        from .ops import tp_fused as T
+        T.set_variant(a.tp_variant)
+        n = a.ranks
+        xs = [torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+        ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n)]
+        w2 = [torch.randn(a.k, a.n, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n)]
+        s1, s2, ep = {}, {}, [1]   # epochs must increase per workspace: the flags carry them
+        ys, s1 = T.emulate_ag_gemm(xs, ws, state=s1, epoch=1, max_ctas=148 // n)
+        torch.cuda.synchronize()
+
+        def ag():
+            ep[0] += 1
+            T.emulate_ag_gemm(xs, ws, state=s1, epoch=ep[0], max_ctas=148 // n)
+
+        def rs():
+            ep[0] += 1
+            T.emulate_gemm_rs(ys, w2, state=s2, epoch=ep[0], max_ctas=148 // n)
+        t_ag = timed(ag, a.iters, a.warmup)
+        var_ag = T.last_variant()
+        t_rs = timed(rs, a.iters, a.warmup)
+        T.check_state(s1)
+        T.check_state(s2)
+        fl = 2.0 * n * (a.m * n) * a.n * a.k
+        out.update(ranks=n, m=a.m, n=a.n, k=a.k, variant=var_ag, ag_gemm_ms=t_ag, ag_gemm_tflops_all_ranks=fl / t_ag / 1e9,
+                   gemm_rs_ms=t_rs, gemm_rs_tflops_all_ranks=fl / t_rs / 1e9,
+                   note="all ranks emulated on one GPU: TFLOP/s over the whole device, no NVLink involved")
+    elif a.what == "moe":
+        from .ops import moe as M
+        n = a.ranks
+        xs = [torch.randn(a.tokens, a.hidden, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+        ids, gates = [], []
+        for r in range(n):
+            top = torch.rand(a.tokens, a.experts, device=dev).topk(a.topk, dim=1)
+            ids.append(top.indices.to(torch.int32).contiguous())
+            gates.append(torch.softmax(top.values, dim=1).float().contiguous())
+        state = {}
+        recvs, hs, state = M.emulate_dispatch(xs, ids, a.experts, state=state)
+        torch.cuda.synchronize()
+        t_d = timed(lambda: M.emulate_dispatch(xs, ids, a.experts, state=state), a.iters, a.warmup)
+        t_c = timed(lambda: M.emulate_combine(recvs, gates, hs, state=state), a.iters, a.warmup)
+        M.check_state(state)
+        rows = n * a.tokens * a.topk
+        out.update(ranks=n, tokens=a.tokens, hidden=a.hidden, experts=a.experts, topk=a.topk, dispatch_ms=t_d,
+                   combine_ms=t_c, dispatch_rows_gbs=rows * a.hidden * 2 / t_d / 1e6, combine_rows_gbs=rows * a.hidden * 2 / t_c / 1e6,
+                   note="all ranks emulated on one GPU; GB/s = bf16 bytes of the routed rows over the time")
     else:
         cfg = cfgs[a.codec]
         n = a.ranks

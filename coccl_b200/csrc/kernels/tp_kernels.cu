@@ -22,6 +22,7 @@
 #include "tp_api.h"
 
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace coccl {
@@ -502,9 +503,53 @@ static int checkCommon(const cocclkTpArgs* a, int emulatedRanks) {
   return 0;
 }
 
+// CTA-pair kernels (tp2_kernels.cu): taken whenever the shape allows it (rows per rank a multiple of 256).
+extern "C" int cocclkTpPairUsable(const cocclkTpArgs* a, int isRs);
+extern "C" int cocclkAgGemmPair(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream);
+extern "C" int cocclkGemmRsPair(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream);
+
+// 0 = pair kernels where the shape allows, 1 = always the single-CTA kernels, 2 = pair kernels or an error.
+// The initial value comes from COCCL_TP_VARIANT ("1cta" / "2cta").
+static int gTpVariant = -1;
+extern "C" void cocclkTpSetVariant(int v) { gTpVariant = v; }
+extern "C" int cocclkTpGetVariant() {
+  if (gTpVariant < 0) {
+    const char* e = getenv("COCCL_TP_VARIANT");
+    gTpVariant = (e && !strcmp(e, "1cta")) ? 1 : (e && !strcmp(e, "2cta")) ? 2 : 0;
+  }
+  return gTpVariant;
+}
+// which kernel served the last call of this process: 1 = single CTA, 2 = pair
+static int gTpLast = 0;
+extern "C" int cocclkTpLastVariant() { return gTpLast; }
+
+// Returns 1 when the pair kernel was launched (rc holds its result), 0 when the caller should use the single-CTA one.
+static int tryPair(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream, int isRs, int* rc) {
+  const int v = cocclkTpGetVariant();
+  if (v == 1) return 0;
+  if (!cocclkTpPairUsable(args, isRs)) {
+    if (v == 2) { *rc = -1; return 1; }
+    return 0;
+  }
+  *rc = isRs ? cocclkGemmRsPair(args, emulatedRanks, maxCtas, stream) : cocclkAgGemmPair(args, emulatedRanks, maxCtas, stream);
+  if (*rc != 0 && emulatedRanks > 1 && v != 2) {
+    // a cooperative launch of clusters is refused on some configurations: the emulation then runs on the single-CTA
+    // kernels (a refused launch has not started anything)
+    (void)cudaGetLastError();
+    return 0;
+  }
+  gTpLast = 2;
+  return 1;
+}
+
 extern "C" int cocclkAgGemm(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
   if (checkCommon(args, emulatedRanks)) return -1;
   if ((args->epi == GEMM_EPI_BIAS || args->epi == GEMM_EPI_BIAS_GELU) == false && args->epi != GEMM_EPI_NONE) return -1;
+  {
+    int rc = 0;
+    if (tryPair(args, emulatedRanks, maxCtas, stream, 0, &rc)) return rc;
+    gTpLast = 1;
+  }
   const int N = args->nRanks, rowsPerShard = args->M / N;
   if ((long)(rowsPerShard / BM) * kParts > kFlagStride) return -1;
   Params P;
@@ -527,6 +572,11 @@ extern "C" int cocclkAgGemm(const cocclkTpArgs* args, int emulatedRanks, int max
 extern "C" int cocclkGemmRs(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
   if (checkCommon(args, emulatedRanks)) return -1;
   if (args->N % BN != 0) return -1;
+  {
+    int rc = 0;
+    if (tryPair(args, emulatedRanks, maxCtas, stream, 1, &rc)) return rc;
+    gTpLast = 1;
+  }
   const int N = args->nRanks, rowsPerRank = args->M / N;
   if ((long)(rowsPerRank / BM) * (args->N / BN) * 4 > kFlagStride) return -1;
   Params P;

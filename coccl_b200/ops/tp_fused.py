@@ -14,6 +14,18 @@ from .gemm import EPI_BIAS, EPI_BIAS_GELU, EPI_NONE
 STATUS_BYTES = 256
 
 
+def set_variant(name: str) -> None:
+    """'auto' (CTA-pair kernels where rows per rank are a multiple of 256), '1cta' or '2cta' (pair kernels or an error)."""
+    import ctypes as C
+    _lib.declare("cocclkTpSetVariant", None, [C.c_int])({"auto": 0, "1cta": 1, "2cta": 2}[name])
+
+
+def last_variant() -> str:
+    """Which kernel family served the last fusion call of this process."""
+    import ctypes as C
+    return {0: "none", 1: "1cta", 2: "2cta"}[_lib.declare("cocclkTpLastVariant", C.c_int, [])()]
+
+
 def ag_ws_bytes(M: int, K: int) -> int:
     return _lib.lib().cocclkAgGemmWorkspaceBytes(M, K)
 

@@ -8,9 +8,17 @@ from coccl_b200.ops import tp_fused as T
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["1cta", "2cta"])
+def variant(request):
+    """Both kernel families: single-CTA tiles, and CTA pairs (cta_group::2) where rows per rank are a multiple of 256."""
+    T.set_variant("auto" if request.param == "2cta" else "1cta")
+    yield request.param
+    T.set_variant("auto")
+
+
 @pytest.mark.parametrize("n,m,N,K,bias,gelu", [(2, 128, 256, 64, False, False), (2, 256, 520, 192, True, False),
                                                (4, 256, 512, 256, True, True), (2, 1024, 1024, 1024, False, False)])
-def test_ag_gemm_emulated(cuda, n, m, N, K, bias, gelu):
+def test_ag_gemm_emulated(cuda, variant, n, m, N, K, bias, gelu):
     torch.manual_seed(0)
     xs = [torch.randn(m, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
     ws = [torch.randn(N, K, device=cuda, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
@@ -20,6 +28,7 @@ def test_ag_gemm_emulated(cuda, n, m, N, K, bias, gelu):
         outs, state = T.emulate_ag_gemm(xs, ws, bias=bs, gelu=gelu, state=state, epoch=epoch, max_ctas=148 // n)
         torch.cuda.synchronize()
         T.check_state(state)
+        assert T.last_variant() == ("2cta" if variant == "2cta" and m % 256 == 0 else "1cta")
         xf = torch.cat(xs).float()
         for r in range(n):
             ref = xf @ ws[r].float().t()
@@ -32,8 +41,8 @@ def test_ag_gemm_emulated(cuda, n, m, N, K, bias, gelu):
         xs = [x * 0.5 for x in xs]
 
 
-@pytest.mark.parametrize("n,M,N,K", [(2, 256, 256, 64), (2, 512, 512, 320), (4, 1024, 768, 256), (2, 2048, 1024, 1024)])
-def test_gemm_rs_emulated(cuda, n, M, N, K):
+@pytest.mark.parametrize("n,M,N,K", [(2, 256, 256, 64), (2, 512, 512, 320), (4, 1024, 768, 256), (2, 2048, 1024, 1024), (4, 2048, 512, 2048)])
+def test_gemm_rs_emulated(cuda, variant, n, M, N, K):
     torch.manual_seed(1)
     As = [torch.randn(M, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)]
     Ws = [torch.randn(N, K, device=cuda, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
@@ -42,14 +51,17 @@ def test_gemm_rs_emulated(cuda, n, M, N, K):
         outs, state = T.emulate_gemm_rs(As, Ws, state=state, epoch=epoch, max_ctas=148 // n)
         torch.cuda.synchronize()
         T.check_state(state)
+        pair = variant == "2cta" and (M // n) % 256 == 0
+        assert T.last_variant() == ("2cta" if pair else "1cta")
         parts = [As[q].float() @ Ws[q].float().t() for q in range(n)]
         exact = sum(parts)
         # oracle of the transport: every partial product goes through the MX-FP8 codec (32 columns per block)
-        quant = sum(C.reference_roundtrip(p.contiguous(), C.MXFP8, 1) for p in parts)
+        qparts = [C.reference_roundtrip(p.contiguous(), C.MXFP8, 1) for p in parts]
         rows = M // n
         for r in range(n):
             got = outs[r].float()
-            ref_q = quant[r * rows:(r + 1) * rows]
+            # the pair kernel adds a rank's own partial product straight from the accumulator, unquantised
+            ref_q = sum((parts[q] if (pair and q == r) else qparts[q])[r * rows:(r + 1) * rows] for q in range(n))
             ref = exact[r * rows:(r + 1) * rows]
             # the kernel's fp32 sums differ from torch's in the last bits, which can flip an E4M3 rounding
             # decision: almost every element matches the oracle, a flipped one is off by one step (<= |x|/8)
