@@ -95,6 +95,34 @@ def reference_arm(args):
     return 0
 
 
+def _profile_one_step(trainer, batch, path):
+    """One extra training step under torch.profiler (CUDA activities only). Writes, for this rank, the device time of
+    every kernel summed over the step, its share, and the step's wall time, so that launch gaps show as the difference."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        trainer.train_step(batch)
+        torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    if path is None:
+        return
+    rows, tot = [], 0.0
+    for e in prof.key_averages():
+        t = getattr(e, "device_time_total", None)
+        if t is None:
+            t = e.cuda_time_total
+        if t > 0:
+            rows.append((t, e.count, e.key))
+            tot += t
+    rows.sort(reverse=True)
+    with open(path, "w") as f:
+        f.write(f"step wall time under the profiler {wall_ms:.1f} ms; device time summed over kernels {tot / 1e3:.1f} ms\n")
+        for t, c, k in rows[:60]:
+            f.write(f"{t / tot * 100:6.2f}% {t / 1e3:10.3f} ms  x{c:6d}  {k[:140]}\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -105,6 +133,9 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--parallelism", default=None, help="override as tp,pp,dp")
     ap.add_argument("--no-compress", action="store_true", help="route collectives through NCCL only")
+    ap.add_argument("--profile-step", default="", metavar="FILE",
+                    help="after the timed regions, run ONE more step under torch.profiler and write rank 0's per-kernel "
+                         "device-time table (shares; never a bench value) to FILE")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -181,6 +212,10 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
+
+    if args.profile_step:
+        _profile_one_step(trainer, dev_batches[0], args.profile_step if rank == 0 else None)
+        barrier()
 
     # the loss lives on the last pipeline stage: take the maximum over ranks (it is positive)
     t = torch.tensor([ms, e2e_s * 1e3, last if last is not None else 0.0], dtype=torch.float64, device=dev)

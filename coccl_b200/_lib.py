@@ -41,7 +41,8 @@ class TpArgs(C.Structure):
                 ("bMN", c_int), ("epoch", c_uint), ("timeoutNs", c_ulonglong),
                 ("a", c_void_p * MAX_RANKS), ("b", c_void_p * MAX_RANKS), ("c", c_void_p * MAX_RANKS),
                 ("bias", c_void_p * MAX_RANKS), ("z", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
-                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS)]
+                ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS),
+                ("gathered", c_void_p * MAX_RANKS)]
 
 
 class MoeArgs(C.Structure):
@@ -79,6 +80,7 @@ _PROTOS = {
     "cocclkGemmRsWorkspaceBytes": (c_long, [c_int, c_int, c_int]),
     "cocclkAgGemm": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
     "cocclkGemmRs": (c_int, [C.POINTER(TpArgs), c_int, c_int, c_void_p]),
+    "cocclkTpLastVariant": (c_int, []),
     # moe_api.h
     "cocclkMoeWorkspaceBytes": (c_long, [c_int, c_int, c_int, c_int]),
     "cocclkMoeLayout": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -93,6 +95,9 @@ _PROTOS = {
     "cocclkGeluFwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
     "cocclkGeluBwd": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_void_p]),
     "cocclkCrossEntropy": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_long, c_float, c_void_p]),
+    "cocclkCrossEntropyStats": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_long, c_long, c_void_p]),
+    "cocclkCrossEntropyFinish": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_long, c_long,
+                                         c_float, c_void_p]),
     "cocclkAdam": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_float, c_float, c_float,
                            c_float, c_float, c_int, c_void_p, c_void_p]),
     "cocclkSumSqBlocks": (c_int, [c_long]),

@@ -245,3 +245,12 @@ extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecQuery(const void* config, int 
   *static_cast<cocclkCodec*>(out) = toCodec(*c, (ncclDataType_t)ncclDatatype);
   return 1;
 }
+
+// The stateful delta configuration (subAdd) maps onto the fused all-gather of deltas (kernels/collective_kernels.cuh,
+// kOpAllGatherDelta): same tile codec, the output buffer is the state.
+extern "C" COCCL_PLUGIN_EXPORT int cocclFusedCodecDeltaQuery(const void* config, int ncclDatatype, void* out) {
+  const Sdp4Config* c = static_cast<const Sdp4Config*>(config);
+  if (c == nullptr || out == nullptr || !c->subAdd || dtypeCode((ncclDataType_t)ncclDatatype) < 0) return 0;
+  *static_cast<cocclkCodec*>(out) = toCodec(*c, (ncclDataType_t)ncclDatatype);
+  return 1;
+}

@@ -217,6 +217,7 @@ bool CompressorRuntime::loadPlugin(const std::string& name, const std::string& d
   p->handle = h;
   p->descriptor = d;
   p->fusedQuery = reinterpret_cast<int (*)(const void*, int, void*)>(dlsym(h, "cocclFusedCodecQuery"));
+  p->deltaQuery = reinterpret_cast<int (*)(const void*, int, void*)>(dlsym(h, "cocclFusedCodecDeltaQuery"));
   plugins_.push_back(std::move(p));
   COCCL_INFO(kLogInit, "loaded compressor %s (capabilities 0x%llx) from %s", name.c_str(),
              (unsigned long long)d->capabilities, path.c_str());

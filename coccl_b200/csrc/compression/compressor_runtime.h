@@ -38,6 +38,10 @@ struct LoadedPlugin {
   // describe a parsed configuration as a kernel codec, which unlocks the fused collectives for it.
   // Returns 1 and fills `out` (a cocclkCodec) when the configuration can run fused for `ncclDatatype`.
   int (*fusedQuery)(const void* config, int ncclDatatype, void* out) = nullptr;
+  // Optional export `cocclFusedCodecDeltaQuery`: the same for a STATEFUL configuration that sends the change against
+  // the previous result (sdp4bit subAdd). The fused all-gather has a delta form whose state is the output buffer
+  // itself; `out` receives the tile codec of the deltas.
+  int (*deltaQuery)(const void* config, int ncclDatatype, void* out) = nullptr;
 };
 
 // Everything the pipeline needs to run one codec for one policy scope.

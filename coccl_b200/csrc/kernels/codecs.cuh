@@ -130,6 +130,8 @@ struct SdpCodec {
   static constexpr int kParams = SMALLG ? 4 : 1;
   static constexpr bool kRotated = HAD;
   static constexpr int kMinBlocks = 3;  // resident CTAs per SM the fused kernels are compiled for
+  static constexpr int kSmemFloats = 8; // shared scratch every kernel passes as `sm` (group reductions wider than a warp)
+  static __device__ __forceinline__ void initShared(float*) {}
   static constexpr uint32_t kSignBits = BITS == 4 ? 0x88888888u : 0x80808080u;
   static constexpr uint32_t kPackFix = kSignBits - kRoundMagicBits * (BITS == 4 ? 0x11111111u : 0x01010101u);
 
@@ -280,7 +282,7 @@ struct SdpCodec {
   // `mul` scales the dequantised values (a power of two: exact); decoders that leave the rotated domain
   // right afterwards pass 1/32 here instead of multiplying all 32 outputs.
   static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c, long elem,
-                                              float mul) {
+                                              float mul, const float* /*sm*/ = nullptr) {
     Raw r;
     const int gs = 31 - __clz(c.group);
     const long padded = L.groups << gs;
@@ -350,6 +352,8 @@ struct MxFp8Codec {
   static constexpr int kWords = 8;
   static constexpr bool kRotated = false;
   static constexpr int kMinBlocks = 3;
+  static constexpr int kSmemFloats = 8;
+  static __device__ __forceinline__ void initShared(float*) {}
 
   struct Enc {
     uint32_t w[8];
@@ -406,7 +410,7 @@ struct MxFp8Codec {
   static constexpr int kBatch = 2;
 
   static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/, long elem,
-                                              float /*mul*/) {
+                                              float /*mul*/, const float* /*sm*/ = nullptr) {
     Raw r;
     r.valid = elem < L.groups * 32;
     if (!r.valid) return r;
@@ -457,6 +461,8 @@ struct TacoCodec {
   static constexpr int kWords = 8;
   static constexpr bool kRotated = true;
   static constexpr int kMinBlocks = 2;  // the lane butterflies keep two copies of a run live: 128 registers, no spills
+  static constexpr int kSmemFloats = 8;
+  static __device__ __forceinline__ void initShared(float*) {}
 
   struct Enc {
     uint32_t w[8];
@@ -541,7 +547,7 @@ struct TacoCodec {
   static constexpr int kBatch = 2;
 
   static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c, long elem,
-                                              float mul) {
+                                              float mul, const float* /*sm*/ = nullptr) {
     Raw r;
     r.valid = elem < L.payloadBytes;
     r.e5m2 = c.aux & 1;
@@ -597,23 +603,38 @@ struct ZfpCodec {
   static constexpr bool kRotated = false;
   static constexpr int kMinBlocks = 2;
   static constexpr int kMaxBits = 4 * RATE;
+  // the plane tables of oracle/zfp1d.h live in the kernel's shared scratch, behind its first 8 floats
+  static constexpr int kSmemFloats = 8 + (zfp1d::kPlaneEncEntries + zfp1d::kPlaneDecEntries) / 2;
+  static __device__ __forceinline__ uint16_t* encTab(float* sm) { return reinterpret_cast<uint16_t*>(sm + 8); }
+  static __device__ __forceinline__ const uint16_t* decTab(const float* sm) {
+    return reinterpret_cast<const uint16_t*>(sm + 8) + zfp1d::kPlaneEncEntries;
+  }
+  // Every thread of the CTA calls this once, followed by a __syncthreads(), before any encode or fetch.
+  static __device__ __forceinline__ void initShared(float* sm) {
+    uint16_t* t = encTab(sm);
+    for (int i = threadIdx.x; i < zfp1d::kPlaneEncEntries + zfp1d::kPlaneDecEntries; i += blockDim.x) {
+      if (i < zfp1d::kPlaneEncEntries) t[i] = zfp1d::planeCode(i >> 4, (uint32_t)(i & 15));
+      else t[i] = zfp1d::planeDecode((i - zfp1d::kPlaneEncEntries) >> 7, (uint32_t)((i - zfp1d::kPlaneEncEntries) & 127));
+    }
+  }
 
   struct Enc { uint32_t w[RATE]; };
 
-  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& /*c*/, bool /*rotate*/, float* /*sm*/,
+  static __device__ __forceinline__ Enc encode(float (&v)[32], const CodecCfg& /*c*/, bool /*rotate*/, float* sm,
                                                uint64_t /*rngElem*/) {
     Enc e;
+    const uint16_t* tab = encTab(sm);
     if (RATE == 4) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t lo = (uint32_t)zfp1d::encodeBlock64(&v[8 * k], kMaxBits);
-        const uint32_t hi = (uint32_t)zfp1d::encodeBlock64(&v[8 * k + 4], kMaxBits);
+        const uint32_t lo = (uint32_t)zfp1d::encodeBlock64T(&v[8 * k], kMaxBits, tab);
+        const uint32_t hi = (uint32_t)zfp1d::encodeBlock64T(&v[8 * k + 4], kMaxBits, tab);
         e.w[k] = lo | (hi << 16);
       }
     } else {
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
-        const uint64_t s = zfp1d::encodeBlock64(&v[4 * b], kMaxBits);
+        const uint64_t s = zfp1d::encodeBlock64T(&v[4 * b], kMaxBits, tab);
         if (RATE == 8) e.w[b] = (uint32_t)s;
         else { e.w[(2 * b) % RATE] = (uint32_t)s; e.w[(2 * b + 1) % RATE] = (uint32_t)(s >> 32); }
       }
@@ -639,13 +660,15 @@ struct ZfpCodec {
 
   struct Raw {
     uint32_t w[RATE];
+    const uint16_t* tab;
     bool valid;
   };
   static constexpr int kBatch = 1;
 
   static __device__ __forceinline__ Raw fetch(const uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/, long elem,
-                                              float /*mul*/) {
+                                              float /*mul*/, const float* sm) {
     Raw r;
+    r.tab = decTab(sm);
     const long off = (elem >> 5) * (4 * RATE);
     r.valid = off < L.totalBytes;
     if (!r.valid) return r;
@@ -673,7 +696,7 @@ struct ZfpCodec {
       else if (RATE == 8) s = r.w[b % RATE];
       else s = (uint64_t)r.w[(2 * b) % RATE] | ((uint64_t)r.w[(2 * b + 1) % RATE] << 32);
       float x[4];
-      zfp1d::decodeBlock64(s, kMaxBits, x);
+      zfp1d::decodeBlock64T(s, kMaxBits, r.tab, x);
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[4 * b + i] += x[i];
     }
@@ -685,14 +708,15 @@ struct ZfpCodec {
 
 // acc += mul * sum over n encoded copies of the run at `elem`, copy i at base + i * stride. The loads of
 // Codec::kBatch copies are issued before any of them is unpacked.
+// `sm`: the kernel's shared scratch (Codec::kSmemFloats floats, Codec::initShared called).
 template <class Codec>
 __device__ __forceinline__ void decodeSum(const uint8_t* base, long stride, int n, const ChunkLayout& L,
-                                          const CodecCfg& c, long elem, float mul, float (&acc)[32]) {
+                                          const CodecCfg& c, long elem, float mul, float (&acc)[32], const float* sm) {
   for (int q = 0; q < n; q += Codec::kBatch) {
     typename Codec::Raw r[Codec::kBatch];
 #pragma unroll
     for (int j = 0; j < Codec::kBatch; ++j) {
-      if (q + j < n) r[j] = Codec::fetch(base + (long)(q + j) * stride, L, c, elem, mul);
+      if (q + j < n) r[j] = Codec::fetch(base + (long)(q + j) * stride, L, c, elem, mul, sm);
       else r[j].valid = false;
     }
 #pragma unroll

@@ -115,9 +115,11 @@ __device__ __forceinline__ bool waitAll(unsigned int* const* flagAddrs, int n, u
 template <typename T, class Codec>
 __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollectiveKernel(const CollArgs a) {
   __shared__ TileStage<T> stage;
-  __shared__ float sm[8];
+  __shared__ float sm[Codec::kSmemFloats];
   __shared__ uint8_t* sDst[kMaxRanks];
   __shared__ unsigned int* sFlag[kMaxRanks];
+  Codec::initShared(sm);
+  __syncthreads();
 
   const int N = a.nRanks;
   const int rank = a.rankBase + blockIdx.y;
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollecti
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = 0.f;
         decodeSum<Codec>(myWs + (long)q0 * a.slotBytes, a.slotBytes, nq, L, c, e,
-                         a.op == kOpAllReduceTwoShot ? 1.f : Codec::finishScale(c), acc);
+                         a.op == kOpAllReduceTwoShot ? 1.f : Codec::finishScale(c), acc, sm);
         if (a.op == kOpAllReduceTwoShot) {
           // stay in the rotated domain: the sum of rotated values is the rotation of the sum
           const typename Codec::Enc enc = Codec::encode(acc, c, false, sm, ((uint64_t)(0x80 + rank) << 40) + (uint64_t)e);
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollecti
         float acc[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-        decodeSum<Codec>(myWs + a.regionBOffset + (long)q * a.slotBytes, 0, 1, L, c, e, Codec::finishScale(c), acc);
+        decodeSum<Codec>(myWs + a.regionBOffset + (long)q * a.slotBytes, 0, 1, L, c, e, Codec::finishScale(c), acc, sm);
         Codec::finish(acc, c);
         TileIO<T>::store(dstChunk, L.count, e0, TileIO<T>::fastTile(dstChunk, L.count, e0), stage, acc);
       }
@@ -269,8 +271,10 @@ struct CodecArgs {
 template <typename T, class Codec>
 __global__ void __launch_bounds__(kTileThreads) encodeKernel(const CodecArgs a) {
   __shared__ TileStage<T> stage;
-  __shared__ float sm[8];
+  __shared__ float sm[Codec::kSmemFloats];
   __shared__ uint8_t* sDst[1];
+  Codec::initShared(sm);
+  __syncthreads();
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
   for (long it = blockIdx.x; it < tiles * a.chunks; it += gridDim.x) {
@@ -287,6 +291,9 @@ __global__ void __launch_bounds__(kTileThreads) encodeKernel(const CodecArgs a) 
 template <typename T, class Codec>
 __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecArgs a) {
   __shared__ TileStage<T> stage;
+  __shared__ float sm[Codec::kSmemFloats];
+  Codec::initShared(sm);
+  __syncthreads();
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
   const uint8_t* enc = reinterpret_cast<const uint8_t*>(a.in);
@@ -299,7 +306,7 @@ __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecAr
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e,
-                     Codec::finishScale(a.codec), acc);
+                     Codec::finishScale(a.codec), acc, sm);
     Codec::finish(acc, a.codec);
     TileIO<T>::store(dst, L.count, e0, TileIO<T>::fastTile(dst, L.count, e0), stage, acc);
   }
@@ -309,7 +316,9 @@ __global__ void __launch_bounds__(kTileThreads) decodeReduceKernel(const CodecAr
 // (reference kernel: sdp4bit/quantization/dequant_reduce_quant.cu:14-179).
 template <class Codec>
 __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) decodeReduceEncodeKernel(const CodecArgs a) {
-  __shared__ float sm[8];
+  __shared__ float sm[Codec::kSmemFloats];
+  Codec::initShared(sm);
+  __syncthreads();
   const ChunkLayout L = makeChunkLayout(a.codec, a.count, 4);
   const long tiles = (a.count + kTileElems - 1) / kTileElems;
   const uint8_t* enc = reinterpret_cast<const uint8_t*>(a.in);
@@ -319,7 +328,7 @@ __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) decodeReduceE
     float acc[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e, 1.f, acc);
+    decodeSum<Codec>(enc + ch * a.encStrideIn, a.chunks * a.encStrideIn, (int)a.reduce, L, a.codec, e, 1.f, acc, sm);
     const typename Codec::Enc o = Codec::encode(acc, a.codec, false, sm, ((uint64_t)(0x40 + ch) << 40) + (uint64_t)e);
     Codec::store(o, reinterpret_cast<uint8_t*>(a.out) + ch * a.encStrideOut, L, a.codec, e);
   }

@@ -180,6 +180,44 @@ __device__ __forceinline__ void mmaRole(const Pipe& p, int firstTile, int numTil
 // ---------------------------------------------------------------------------------------------
 // all-gather -> GEMM
 // ---------------------------------------------------------------------------------------------
+// Tile t -> (ring step, 256-row tile inside the shard, column tile). Inside a shard the column tile runs fastest:
+// the clusters that work at the same time then share a few row tiles, so a remote shard is needed in the order in
+// which it arrives instead of all at once.
+__device__ __forceinline__ void agTile(int t, int tilesPerShard, int tps, int numN, int& step, int& tmL, int& tn) {
+  step = t / tilesPerShard;
+  const int r = t - step * tilesPerShard;
+  tmL = r / numN;
+  tn = r - tmL * numN;
+  (void)tps;
+}
+
+// One warp copies a piece of 16 rows x pcv 16-byte vectors (row pitch rowVecs) with eight loads in flight per lane.
+// CG: the source was written by a peer during this launch, so the loads must not come from L1.
+template <bool CG>
+__device__ __forceinline__ void copyPiece(const uint4* src, uint4* dst, long base, long rowVecs, int pcv, int lane) {
+  if ((pcv & 31) == 0) {
+    for (int c0 = 0; c0 < pcv; c0 += 32) {
+#pragma unroll 1
+      for (int r0 = 0; r0 < kPartRows; r0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4* q = src + base + (long)(r0 + u) * rowVecs + c0 + lane;
+          v[u] = CG ? __ldcg(q) : __ldg(q);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[base + (long)(r0 + u) * rowVecs + c0 + lane] = v[u];
+      }
+    }
+  } else {
+    for (int r0 = 0; r0 < kPartRows; ++r0)
+      for (int c = lane; c < pcv; c += 32) {
+        const uint4* q = src + base + (long)r0 * rowVecs + c;
+        dst[base + (long)r0 * rowVecs + c] = CG ? __ldcg(q) : __ldg(q);
+      }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_constant__ Params P) {
   extern __shared__ uint8_t smemRaw[];
   const cocclkTpArgs& a = P.a;
@@ -203,28 +241,32 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
   StatusWord* st = reinterpret_cast<StatusWord*>(a.status[rank]);
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = clusterId; t < numTiles && ok; t += numClusters) {
-        const int step = t / tilesPerShard, r = t - step * tilesPerShard;
-        const int tmL = r % tps, tn = r / tps;
-        const int shard = (rank + step) % N;
-        const int rowInShard = tmL * 2 * BM + (int)p.cta * BM;
-        if (step > 0) {
-          // this CTA's 128 rows of a remote shard: every piece of their eight 16-row parts must have landed
-          const unsigned int* f = a.flags[rank] + (long)shard * kFlagStride + (long)(rowInShard / kPartRows) * pieces;
-          const int nFlags = (BM / kPartRows) * pieces;
-          for (int i = 0; i < nFlags && ok; ++i) {
-            if (*p.abortFlag || !waitFlag(f + i, a.epoch, a.timeoutNs)) {
-              reportTimeout(st, 4, shard, tmL);
-              raiseAbort(p);
-              ok = false;
-            }
+    // The whole warp walks the tiles: the flags of a remote tile are polled by all lanes at once (one acquire load
+    // over the fabric takes about a microsecond; 32 of them in sequence would cost as much as the tile's main loop),
+    // the copies are issued by lane 0.
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = clusterId; t < numTiles && ok; t += numClusters) {
+      int step, tmL, tn;
+      agTile(t, tilesPerShard, tps, numN, step, tmL, tn);
+      const int shard = (rank + step) % N;
+      const int rowInShard = tmL * 2 * BM + (int)p.cta * BM;
+      if (step > 0) {
+        // this CTA's 128 rows of a remote shard: every piece of their eight 16-row parts must have landed
+        const unsigned int* f = a.flags[rank] + (long)shard * kFlagStride + (long)(rowInShard / kPartRows) * pieces;
+        const int nFlags = (BM / kPartRows) * pieces;
+        bool got = true;
+        for (int i = lane; i < nFlags; i += 32) {
+          if (*p.abortFlag || !waitFlag(f + i, a.epoch, a.timeoutNs)) {
+            reportTimeout(st, 4, shard, tmL);
+            got = false;
           }
-          if (!ok) break;
-          fenceProxyAsyncGlobal();  // peer stores (generic proxy) -> TMA reads (async proxy)
         }
+        ok = __all_sync(0xffffffffu, got) != 0;
+        if (!ok) { if (lane == 0) raiseAbort(p); break; }
+      }
+      if (lane == 0) {
+        if (step > 0) fenceProxyAsyncGlobal();  // peer stores (generic proxy) -> TMA reads (async proxy)
         const CUtensorMap* tmA = step == 0 ? tmLocal : tmGather;
         const int arow = step == 0 ? rowInShard : shard * rowsPerShard + rowInShard;
         const int n0 = tn * BN + (int)p.cta * BNH;
@@ -236,8 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
           loadStage(p, s, tmA, tmB, kb, arow, n0, a.bMN != 0);
         }
       }
-      if (!ok) drainWait();
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
+    if (!ok && lane == 0) drainWait();
+    __syncwarp();
   } else if (warp == 1) {
     if (p.cta == 0 && lane == 0) mmaRole<kAgStages>(p, clusterId, numTiles, numClusters, kBlocks, a.bMN != 0);
   } else if (warp < 6) {
@@ -247,8 +291,8 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
     const int quad = warp & 3;
     uint32_t tileIdx = 0;
     for (int t = clusterId; t < numTiles; t += numClusters, ++tileIdx) {
-      const int step = t / tilesPerShard, r = t - step * tilesPerShard;
-      const int tmL = r % tps, tn = r / tps;
+      int step, tmL, tn;
+      agTile(t, tilesPerShard, tps, numN, step, tmL, tn);
       const int shard = (rank + step) % N;
       const int acc = tileIdx & 1;
       const uint32_t accPhase = (tileIdx >> 1) & 1;
@@ -268,7 +312,6 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
     const int cw = blockIdx.x * 2 + (warp - 6), W = gridDim.x * 2;
     const int pieceCols = a.K / pieces;
     const int pcv = pieceCols / 8;                     // 16-byte vectors per row of a piece
-    const int vecs = kPartRows * pcv;
     const long rowVecs = a.K / 8;
     const long items = (long)(rowsPerShard / kPartRows) * pieces;
     const uint4* src0 = reinterpret_cast<const uint4*>(a.a[rank]);
@@ -280,27 +323,37 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
         const long part = itx / pieces;
         const int piece = (int)(itx - part * pieces);
         const long base = part * kPartRows * rowVecs + (long)piece * pcv;
-        int j = lane;
-        for (; j + 7 * 32 < vecs; j += 8 * 32) {
-          uint4 v[8];
-          long off[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int idx = j + u * 32;
-            off[u] = base + (long)(idx / pcv) * rowVecs + (idx % pcv);
-            v[u] = __ldg(src0 + off[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) dst0[off[u]] = v[u];
-        }
-        for (; j < vecs; j += 32) {
-          const long off = base + (long)(j / pcv) * rowVecs + (j % pcv);
-          dst0[off] = __ldg(src0 + off);
-        }
+        copyPiece<false>(src0, dst0, base, rowVecs, pcv, lane);
         __syncwarp();
         if (lane == 0) {
           __threadfence_system();
           stReleaseSys(pf + itx, a.epoch);
+        }
+      }
+    }
+    // ---------------- optional copy-out of the whole gathered operand (kept for the weight gradient) ----------------
+    // own shard from the input, remote shards from the gather buffer as their pieces arrive (ring order again)
+    uint4* keep = reinterpret_cast<uint4*>(a.gathered[rank]);
+    if (keep != nullptr) {
+      const uint4* wsLocal = reinterpret_cast<const uint4*>(a.ws[rank]);
+      bool alive = true;
+      for (int step = 0; step < N && alive; ++step) {
+        const int shard = (rank + step) % N;
+        const uint4* from = step == 0 ? src0 : wsLocal + (long)shard * rowsPerShard * rowVecs;
+        uint4* to = keep + (long)shard * rowsPerShard * rowVecs;
+        const unsigned int* f = a.flags[rank] + (long)shard * kFlagStride;
+        for (long itx = cw; itx < items && alive; itx += W) {
+          if (step > 0) {
+            bool got = true;
+            if (lane == 0) got = !*p.abortFlag && waitFlag(f + itx, a.epoch, a.timeoutNs);
+            alive = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;  // the producer reports the missing piece
+            if (!alive) break;
+          }
+          const long part = itx / pieces;
+          const int piece = (int)(itx - part * pieces);
+          const long base = part * kPartRows * rowVecs + (long)piece * pcv;
+          if (step == 0) copyPiece<false>(from, to, base, rowVecs, pcv, lane);
+          else copyPiece<true>(from, to, base, rowVecs, pcv, lane);
         }
       }
     }
@@ -366,6 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmRsPairKernel(const __grid_con
     uint8_t* stage = p.epiStage + quad * (32 * kStageRowBytes);
     CodecCfg dummy{};
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.c[rank]);
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias[rank]);
     const uint8_t* myWs = reinterpret_cast<const uint8_t*>(a.ws[rank]);
     uint32_t tileIdx = 0;
     for (int t = clusterId; t < numTiles; t += numClusters, ++tileIdx) {
@@ -461,6 +515,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemmRsPairKernel(const __grid_con
             }
 #pragma unroll
             for (int u = 0; u < 2; ++u) MxFp8Codec::accumulate(raw[u], v);
+          }
+          if (bias != nullptr) {  // added once, to the reduced sum
+            const uint4* bp = reinterpret_cast<const uint4*>(bias + tn * BN + c * 32);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint4 bw = __ldg(bp + k);
+              const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                v[8 * k + 2 * i] += __uint_as_float(w[i] << 16);
+                v[8 * k + 2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+              }
+            }
           }
           uint4* op = reinterpret_cast<uint4*>(out + (long)row * a.N + tn * BN + c * 32);
 #pragma unroll

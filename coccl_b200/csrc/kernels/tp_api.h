@@ -27,13 +27,21 @@ typedef struct {
   const void* a[COCCLK_TP_MAX_RANKS];     // ag_gemm: own shard [M/nRanks, K] bf16; gemm_rs: A [M, K] bf16
   const void* b[COCCLK_TP_MAX_RANKS];     // bf16 weights, layout per bMN
   void* c[COCCLK_TP_MAX_RANKS];           // ag_gemm: [M, N] bf16; gemm_rs: [M/nRanks, N] bf16
-  const void* bias[COCCLK_TP_MAX_RANKS];  // ag_gemm, optional
+  const void* bias[COCCLK_TP_MAX_RANKS];  // optional bf16 [N]: ag_gemm adds it in the epilogue; gemm_rs (CTA-pair kernel only)
+                                          // adds it once, to the reduced rows
   void* z[COCCLK_TP_MAX_RANKS];           // ag_gemm with GELU: optional pre-activation output
   void* ws[COCCLK_TP_MAX_RANKS];          // ag_gemm: gather buffer [M, K] bf16; gemm_rs: nRanks receive slots
   unsigned int* flags[COCCLK_TP_MAX_RANKS];  // cocclkFlagBytes() bytes each
   void* status[COCCLK_TP_MAX_RANKS];         // StatusWord
   unsigned int* err[COCCLK_TP_MAX_RANKS];    // optional: GEMM pipeline error word
+  void* gathered[COCCLK_TP_MAX_RANKS];       // ag_gemm (CTA-pair kernel only), optional: [M, K] bf16 that receives the whole
+                                             // gathered operand (the backward pass needs it for the weight gradient);
+                                             // the kernel's push warps copy it out of the gather buffer as shards arrive
 } cocclkTpArgs;
+
+// Which kernel family served the last fusion call of this process: 1 = single-CTA tiles, 2 = CTA pairs. The single-CTA
+// kernels ignore `gathered` and gemm_rs's `bias`; a caller that passed them applies them itself in that case.
+int cocclkTpLastVariant(void);
 
 // Bytes of ws[] per rank.
 long cocclkAgGemmWorkspaceBytes(int M, int K);

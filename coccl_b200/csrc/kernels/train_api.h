@@ -27,6 +27,14 @@ int cocclkGeluBwd(const void* dy, const void* z, void* dz, long n, cudaStream_t 
 // loss[m] = CE(logits[m], targets[m]); logits are overwritten by their gradient times gscale.
 int cocclkCrossEntropy(void* logits, const long* targets, float* loss, int M, int V, long ld, float gscale,
                        cudaStream_t s);
+// Vocabulary-parallel cross-entropy (the vocabulary is sharded over tensor-parallel ranks; this rank holds columns
+// [vocabOffset, vocabOffset + V)). Stats writes 4 floats per row {local max, sum exp(logit - max), target logit or 0,
+// target-in-shard flag}; the caller all-gathers them over the group into statsAll [tp][M][4]; Finish writes
+// loss[m] (the same value on every rank) and overwrites the logits with (softmax - onehot) * gscale.
+int cocclkCrossEntropyStats(const void* logits, const long* targets, float* stats, int M, int V, long ld, long vocabOffset,
+                            cudaStream_t s);
+int cocclkCrossEntropyFinish(void* logits, const long* targets, const float* statsAll, int tp, float* loss, int M, int V,
+                             long ld, long vocabOffset, float gscale, cudaStream_t s);
 // AdamW over a flat shard. grad is fp32 or bf16; param (optional) receives the bf16 copy.
 int cocclkAdam(float* master, float* m, float* v, const void* grad, int gradIsBf16, void* param, long n, float lr,
                float b1, float b2, float eps, float wd, int step, const float* gradScale, cudaStream_t s);

@@ -183,27 +183,56 @@ __global__ void colReduceKernel(const float* partial, float* out, int rows, long
   const long c = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float s = 0.f;
+#pragma unroll 8
   for (int r = 0; r < rows; ++r) s += partial[(long)r * stride + c];
   out[c] = accumulate ? out[c] + s : s;
 }
 
 // ---------------------------------------------------------------- column sum of a bf16 matrix
 // partial[blockIdx.y][n] = sum over this block's rows of x[m][n]
+// A CTA owns 256 columns (32 lanes x 8) and `rowsPerBlock` rows; its 8 warps take every 8th row, four rows in
+// flight per thread, and fold their sums through shared memory. A warp reads 512 contiguous bytes of one row.
 __global__ void __launch_bounds__(256) colSumPartialKernel(const bf16* x, float* partial, int M, int N, int rowsPerBlock) {
-  const int vi = blockIdx.x * blockDim.x + threadIdx.x;  // vector of 8 columns
-  if (vi * 8 >= N) return;
+  __shared__ float red[8][32][9];
+  const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + lane) * 8;
   const int r0 = blockIdx.y * rowsPerBlock;
   const int r1 = min(M, r0 + rowsPerBlock);
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  for (int r = r0; r < r1; ++r) {
-    float v[8];
-    Vec8<bf16>::load(x + (long)r * N + vi * 8, 8, true, v);
+  if (col < N) {
+    const bf16* base = x + col;
+    int r = r0 + wy;
+    for (; r + 24 < r1; r += 32) {
+      float v[4][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] += v[j];
+      for (int u = 0; u < 4; ++u) Vec8<bf16>::load(base + (long)(r + 8 * u) * N, 8, true, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[u][j];
+    }
+    for (; r < r1; r += 8) {
+      float v[8];
+      Vec8<bf16>::load(base + (long)r * N, 8, true, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
   }
-  Vec8<float>::store(partial + (long)blockIdx.y * N + vi * 8, 8, true, acc);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[wy][lane][j] = acc[j];
+  __syncthreads();
+  if (wy == 0 && col < N) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[w][lane][j];   // fixed order: the result does not depend on scheduling
+      acc[j] = s;
+    }
+    Vec8<float>::store(partial + (long)blockIdx.y * N + col, 8, true, acc);
+  }
 }
 
 // ---------------------------------------------------------------- GELU (tanh form)
@@ -299,6 +328,85 @@ __global__ void __launch_bounds__(kCeThreads) crossEntropyKernel(bf16* logits, c
           const float p = v[i][j] * inv;
           const bool hit = (long)(vi * 8 + j) == tgt;
           if (hit) loss[row] = -__logf(fmaxf(p, 1e-37f));
+          o[j] = ignore ? 0.f : (p - (hit ? 1.f : 0.f)) * gscale;
+        }
+        Vec8<bf16>::store(lr + vi * 8, 8, true, o);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- vocabulary-parallel cross-entropy
+// The vocabulary is sharded over the tensor-parallel ranks: a rank holds columns [vocabOffset, vocabOffset + V) of
+// every logit row. Pass 1 leaves per row {local max, sum of exp(logit - local max), target logit if the target lies
+// in this shard, else 0}; the ranks exchange these 16 bytes per row (an all-gather of a few hundred KB, issued by the
+// caller), and pass 2 combines them (global max, rescaled sums), writes the loss and overwrites the logits with
+// (softmax - onehot) * gscale. Rows with target < 0 get loss 0 and a zero gradient.
+__global__ void __launch_bounds__(kCeThreads) ceStatsKernel(const bf16* logits, const long* targets, float4* stats,
+                                                            int M, int V, long ld, long vocabOffset) {
+  __shared__ float sm[32];
+  const int nvec = V / 8;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const bf16* lr = logits + (long)row * ld;
+    const long tgt = targets[row] - vocabOffset;
+    float v[kCeMaxVec][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kCeMaxVec; ++i) {
+      const int vi = threadIdx.x + i * kCeThreads;
+      if (vi < nvec) {
+        Vec8<bf16>::load(lr + vi * 8, 8, true, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[i][j]);
+      }
+    }
+    mx = blockMax(mx, sm);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCeMaxVec; ++i) {
+      const int vi = threadIdx.x + i * kCeThreads;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += __expf(v[i][j] - mx);
+      }
+    }
+    s = blockSum(s, sm);
+    if (threadIdx.x == 0) {
+      const bool inside = tgt >= 0 && tgt < V;
+      stats[row] = make_float4(mx, s, inside ? __bfloat162float(lr[tgt]) : 0.f, inside ? 1.f : 0.f);
+    }
+  }
+}
+
+// statsAll: [tp][M] entries of pass 1 from every rank (this rank's included).
+__global__ void __launch_bounds__(kCeThreads) ceFinishKernel(bf16* logits, const long* targets, const float4* statsAll, int tp,
+                                                             float* loss, int M, int V, long ld, long vocabOffset, float gscale) {
+  const int nvec = V / 8;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    bf16* lr = logits + (long)row * ld;
+    const long tgtGlobal = targets[row];
+    const long tgt = tgtGlobal - vocabOffset;
+    float gm = -INFINITY;
+    for (int r = 0; r < tp; ++r) gm = fmaxf(gm, statsAll[(long)r * M + row].x);
+    float S = 0.f, tl = 0.f;
+    for (int r = 0; r < tp; ++r) {
+      const float4 st = statsAll[(long)r * M + row];
+      S += st.y * __expf(st.x - gm);
+      tl += st.z;
+    }
+    const bool ignore = tgtGlobal < 0;
+    if (threadIdx.x == 0) loss[row] = ignore ? 0.f : (__logf(S) + gm - tl);
+    const float inv = 1.f / S;
+#pragma unroll
+    for (int i = 0; i < kCeMaxVec; ++i) {
+      const int vi = threadIdx.x + i * kCeThreads;
+      if (vi < nvec) {
+        float v[8], o[8];
+        Vec8<bf16>::load(lr + vi * 8, 8, true, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float p = __expf(v[j] - gm) * inv;
+          const bool hit = (long)(vi * 8 + j) == tgt;
           o[j] = ignore ? 0.f : (p - (hit ? 1.f : 0.f)) * gscale;
         }
         Vec8<bf16>::store(lr + vi * 8, 8, true, o);
@@ -433,7 +541,7 @@ extern "C" int cocclkColSum(const void* x, float* out, int accumulate, float* sc
   if (N % 8 || M <= 0) return -1;
   const int by = cocclkColSumBlocks(M);
   const int rowsPer = (M + by - 1) / by;
-  dim3 grid((N / 8 + 255) / 256, by);
+  dim3 grid((N / 8 + 31) / 32, by);
   colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
   colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
   cocclkCountLaunches(2);
@@ -458,6 +566,24 @@ extern "C" int cocclkCrossEntropy(void* logits, const long* targets, float* loss
   if (V % 8 || V > kCeThreads * kCeMaxVec * 8 || ld % 8 || M <= 0) return -1;
   const int grid = M < 148 * 2 ? M : 148 * 2;
   crossEntropyKernel<<<grid, kCeThreads, 0, s>>>((bf16*)logits, targets, loss, M, V, ld, gscale);
+  cocclkCountLaunches(1);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int cocclkCrossEntropyStats(const void* logits, const long* targets, float* stats, int M, int V, long ld,
+                                       long vocabOffset, cudaStream_t s) {
+  if (V % 8 || V > kCeThreads * kCeMaxVec * 8 || ld % 8 || M <= 0) return -1;
+  const int grid = M < 148 * 2 ? M : 148 * 2;
+  ceStatsKernel<<<grid, kCeThreads, 0, s>>>((const bf16*)logits, targets, reinterpret_cast<float4*>(stats), M, V, ld, vocabOffset);
+  cocclkCountLaunches(1);
+  return (int)cudaGetLastError();
+}
+extern "C" int cocclkCrossEntropyFinish(void* logits, const long* targets, const float* statsAll, int tp, float* loss, int M,
+                                        int V, long ld, long vocabOffset, float gscale, cudaStream_t s) {
+  if (V % 8 || V > kCeThreads * kCeMaxVec * 8 || ld % 8 || M <= 0 || tp < 1) return -1;
+  const int grid = M < 148 * 2 ? M : 148 * 2;
+  ceFinishKernel<<<grid, kCeThreads, 0, s>>>((bf16*)logits, targets, reinterpret_cast<const float4*>(statsAll), tp, loss, M, V, ld,
+                                             vocabOffset, gscale);
   cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
@@ -554,7 +680,7 @@ extern "C" int cocclkColSumNoAlloc(const void* x, float* out, int accumulate, in
   }
   const int by = cocclkColSumBlocks(M);  // <= kNoAllocRows
   const int rowsPer = (M + by - 1) / by;
-  dim3 grid((N / 8 + 255) / 256, by);
+  dim3 grid((N / 8 + 31) / 32, by);
   colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
   colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
   cocclkCountLaunches(2);

@@ -258,5 +258,122 @@ COCCL_HD void decodeBlock64(uint64_t s, int maxbits, float* x) {
   for (int i = 0; i < kBlock; ++i) x[i] = (float)q[i] * scale;
 }
 
+// ------------------------------------------------------------------ table-driven planes
+// One bit plane of a block is the four bits x of the values at that plane plus the number n of values already
+// known to be significant; what the coder emits for it (the n known bits verbatim, then the group test of the
+// rest) depends on (n, x) only, is at most 7 bits long, and the codes of one n form a prefix code. The stream
+// of a block is the concatenation of its plane codes cut off at the block's budget, so the encoder is one table
+// look-up per plane, and the decoder one look-up on the next 7 stream bits per plane, until the budget ends; only
+// a plane that the budget cuts in two is decoded bit by bit, because the serial rules give a truncated code its
+// own meaning. Results are bit-identical to encodeBlock / decodeBlock.
+constexpr int kPlaneEncEntries = 5 * 16;    // [n][x]
+constexpr int kPlaneDecEntries = 5 * 128;   // [n][next 7 bits]
+
+// bits 0-7: code, LSB first; bits 8-11: length; bits 12-14: n after the plane
+COCCL_HD uint16_t planeCode(int n, uint32_t x) {
+  uint32_t code = x & ((1u << n) - 1u);
+  int len = n;
+  uint32_t r = x >> n;
+  while (n < kBlock) {
+    const uint32_t any = r != 0;
+    code |= any << len;
+    ++len;
+    if (!any) break;
+    while (n < kBlock - 1) {
+      const uint32_t bit = r & 1u;
+      code |= bit << len;
+      ++len;
+      if (bit) break;
+      r >>= 1;
+      ++n;
+    }
+    r >>= 1;
+    ++n;
+  }
+  return (uint16_t)(code | ((uint32_t)len << 8) | ((uint32_t)n << 12));
+}
+// bits 0-3: plane; bits 4-7: code length; bits 8-10: n after the plane
+COCCL_HD uint16_t planeDecode(int n, uint32_t peek) {
+  for (uint32_t x = 0; x < 16; ++x) {
+    const uint16_t e = planeCode(n, x);
+    const uint32_t len = (e >> 8) & 15u;
+    if ((peek & ((1u << len) - 1u)) == (uint32_t)(e & 0xffu)) return (uint16_t)(x | (len << 4) | ((uint32_t)(e >> 12) << 8));
+  }
+  return (uint16_t)(1u << 4);  // not reached: the codes of one n cover every bit pattern
+}
+
+COCCL_HD uint64_t encodeBlock64T(const float* x, int maxbits, const uint16_t* encTab) {
+  const int emax = blockExponent(x);
+  if (emax == -kEbias) return 0;
+  uint64_t acc = (uint64_t)(2 * (emax + kEbias) + 1);
+  int pos = 9;
+  int32_t q[kBlock];
+  const float scale = ldexpf(1.f, 30 - emax);
+  for (int i = 0; i < kBlock; ++i) q[i] = (int32_t)(x[i] * scale);
+  forwardLift(q);
+  const uint32_t u0 = toNegabinary(q[0]), u1 = toNegabinary(q[1]), u2 = toNegabinary(q[2]), u3 = toNegabinary(q[3]);
+  uint32_t n = 0;
+  for (int k = 31; k >= 0 && pos < maxbits; --k) {
+    const uint32_t plane = ((u0 >> k) & 1u) | (((u1 >> k) & 1u) << 1) | (((u2 >> k) & 1u) << 2) | (((u3 >> k) & 1u) << 3);
+    const uint32_t e = encTab[n * 16u + plane];
+    acc |= (uint64_t)(e & 0xffu) << pos;
+    pos += (int)((e >> 8) & 15u);
+    n = e >> 12;
+  }
+  return maxbits >= 64 ? acc : (acc & ((1ull << maxbits) - 1ull));
+}
+
+// `s` must be zero above bit maxbits - 1.
+COCCL_HD void decodeBlock64T(uint64_t s, int maxbits, const uint16_t* decTab, float* x) {
+  if ((s & 1u) == 0) {
+    for (int i = 0; i < kBlock; ++i) x[i] = 0.f;
+    return;
+  }
+  const int emax = (int)((s >> 1) & 0xffu) - kEbias;
+  int pos = 9;
+  uint32_t u0 = 0, u1 = 0, u2 = 0, u3 = 0;
+  uint32_t n = 0;
+  for (int k = 31; k >= 0 && pos < maxbits; --k) {
+    const uint32_t e = decTab[n * 128u + ((uint32_t)(s >> pos) & 0x7fu)];
+    const int len = (int)((e >> 4) & 15u);
+    uint32_t plane;
+    if (pos + len <= maxbits) {
+      plane = e & 15u;
+      n = (e >> 8) & 7u;
+      pos += len;
+    } else {
+      int bits = maxbits - pos;
+      const int m = (int)n < bits ? (int)n : bits;
+      bits -= m;
+      plane = (uint32_t)(s >> pos) & ((1u << m) - 1u);
+      pos += m;
+      while (n < (uint32_t)kBlock && bits) {
+        --bits;
+        const uint32_t any = (uint32_t)(s >> pos) & 1u;
+        ++pos;
+        if (!any) break;
+        while (n < (uint32_t)kBlock - 1 && bits) {
+          --bits;
+          const uint32_t bit = (uint32_t)(s >> pos) & 1u;
+          ++pos;
+          if (bit) break;
+          ++n;
+        }
+        plane |= 1u << n;
+        ++n;
+      }
+      pos = maxbits;
+    }
+    u0 |= (plane & 1u) << k;
+    u1 |= ((plane >> 1) & 1u) << k;
+    u2 |= ((plane >> 2) & 1u) << k;
+    u3 |= ((plane >> 3) & 1u) << k;
+  }
+  int32_t q[kBlock] = {fromNegabinary(u0), fromNegabinary(u1), fromNegabinary(u2), fromNegabinary(u3)};
+  inverseLift(q);
+  const float scale = ldexpf(1.f, emax - 30);
+  for (int i = 0; i < kBlock; ++i) x[i] = (float)q[i] * scale;
+}
+
 }  // namespace zfp1d
 }  // namespace coccl

@@ -26,6 +26,14 @@ float sample(unsigned& st, int kind) {
 
 TEST(zfp_register_coder_matches_window_coder) {
   unsigned st = 12345u;
+  static uint16_t encTab[kPlaneEncEntries], decTab[kPlaneDecEntries];
+  for (int n = 0; n < 5; ++n) {
+    for (uint32_t x = 0; x < 16; ++x) {
+      encTab[n * 16 + x] = planeCode(n, x);
+      EXPECT(((encTab[n * 16 + x] >> 8) & 15) <= 7);   // a plane code fits the decoder's 7-bit look-ahead
+    }
+    for (uint32_t pk = 0; pk < 128; ++pk) decTab[n * 128 + pk] = planeDecode(n, pk);
+  }
   const int rates[] = {4, 8, 16};
   long checked = 0;
   for (int rate : rates) {
@@ -44,6 +52,7 @@ TEST(zfp_register_coder_matches_window_coder) {
         const uint64_t mask = mb == 64 ? ~0ull : ((1ull << mb) - 1ull);
         EXPECT((ref & mask) == (got & mask));
         EXPECT((got & ~mask) == 0);
+        EXPECT(encodeBlock64T(x, mb, encTab) == got);   // table-driven planes: the same stream
         float a[4], b[4];
         BitWindow r;
         memset(&r, 0, sizeof(r));
@@ -53,6 +62,9 @@ TEST(zfp_register_coder_matches_window_coder) {
         decodeBlock(r, mb, a);
         decodeBlock64(got, mb, b);
         for (int i = 0; i < 4; ++i) EXPECT(a[i] == b[i]);
+        float c[4];
+        decodeBlock64T(got, mb, decTab, c);
+        for (int i = 0; i < 4; ++i) EXPECT(a[i] == c[i]);
         ++checked;
       }
     }

@@ -446,10 +446,13 @@ class Communicator:
         if save_preact and gelu and bias is not None:
             z = torch.empty_like(out)
             a.z[self.rank] = z.data_ptr()
+        if gathered is not None:
+            assert gathered.is_contiguous() and gathered.shape == (M, K) and gathered.dtype == torch.bfloat16
+            a.gathered[self.rank] = gathered.data_ptr()   # the CTA-pair kernel copies the operand out itself
         with nvtx_range("coccl.fused.ag_gemm"):
             _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
         self.stats["compressed_calls"] += 1
-        if gathered is not None:
+        if gathered is not None and _lib.lib().cocclkTpLastVariant() != 2:
             # the peers' shards are in this call's half of the workspace, the own shard never left x_local
             cp = _lib.declare("cocclDeviceCopy", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p])
             row = K * 2
@@ -462,10 +465,11 @@ class Communicator:
             gathered[r * m:(r + 1) * m].copy_(x_local)
         return (out, z) if save_preact else out
 
-    def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, b_mn: bool = False) -> torch.Tensor:
+    def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, b_mn: bool = False,
+                bias: torch.Tensor | None = None) -> torch.Tensor:
         """reduce_scatter over ranks of (a_mat @ w.T) along the rows, in ONE kernel: the partial products leave
         the GEMM epilogue as block-scaled FP8 straight into the destination ranks' memory. a_mat [M, K]; w [N, K],
-        or [K, N] with b_mn=True (then the product is a_mat @ w)."""
+        or [K, N] with b_mn=True (then the product is a_mat @ w). bias [N] bf16 is added once to the reduced rows."""
         from ..ops import tp_fused as T
         M, K = a_mat.shape
         N = w.shape[1] if b_mn else w.shape[0]
@@ -477,8 +481,13 @@ class Communicator:
         a.epi = T.EPI_NONE
         a.bMN = int(b_mn)
         a.a[self.rank], a.b[self.rank], a.c[self.rank] = a_mat.data_ptr(), w.data_ptr(), out.data_ptr()
+        if bias is not None:
+            assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
+            a.bias[self.rank] = bias.data_ptr()
         with nvtx_range("coccl.fused.gemm_rs"):
             _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
+        if bias is not None and _lib.lib().cocclkTpLastVariant() != 2:
+            out += bias   # the single-CTA kernel's reducer has no bias operand
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += M * N * 2
         return out

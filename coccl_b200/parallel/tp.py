@@ -87,6 +87,8 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, targets, scale, comm):
+        if logits.is_cuda and logits.dtype == torch.bfloat16:
+            return _VocabParallelCE._forward_cuda(ctx, logits, targets, scale, comm)
         vs = logits.shape[-1]
         lo = comm.rank * vs
         lf = logits.float()
@@ -110,9 +112,35 @@ class _VocabParallelCE(torch.autograd.Function):
         return loss.sum() * scale
 
     @staticmethod
+    def _forward_cuda(ctx, logits, targets, scale, comm):
+        """Two kernels and one small all-gather: per-row {max, sum-exp, target logit} of this vocabulary shard, the
+        exchange of those 16 bytes per row, then loss and in-place gradient (csrc/kernels/train_kernels.cu)."""
+        from .. import _lib
+        V = logits.shape[-1]
+        lg = logits.reshape(-1, V)
+        assert lg.stride(1) == 1
+        tg = targets.reshape(-1).contiguous()
+        M = lg.shape[0]
+        dev = lg.device
+        lib = _lib.lib()
+        stats = torch.empty(M, 4, dtype=torch.float32, device=dev)
+        _lib.check(lib.cocclkCrossEntropyStats(lg.data_ptr(), tg.data_ptr(), stats.data_ptr(), M, V, lg.stride(0),
+                                               comm.rank * V, _lib.cur_stream()), "cocclkCrossEntropyStats")
+        allstats = torch.empty(comm.size, M, 4, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(allstats, stats, group=comm.group)
+        loss = torch.empty(M, dtype=torch.float32, device=dev)
+        _lib.check(lib.cocclkCrossEntropyFinish(lg.data_ptr(), tg.data_ptr(), allstats.data_ptr(), comm.size, loss.data_ptr(),
+                                                M, V, lg.stride(0), comm.rank * V, float(scale), _lib.cur_stream()),
+                   "cocclkCrossEntropyFinish")
+        ctx.save_for_backward(lg)   # overwritten in place with (softmax - onehot) * scale
+        ctx.shape = logits.shape
+        return loss.sum() * scale
+
+    @staticmethod
     def backward(ctx, dloss):
         (g,) = ctx.saved_tensors
-        return g, None, None, None
+        shape = getattr(ctx, "shape", None)
+        return (g.reshape(shape) if shape is not None else g), None, None, None
 
 
 def _gelu_bwd(dy2, z):
@@ -171,9 +199,9 @@ class _LinearScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, comm):
         x2 = x.contiguous()
-        o = comm.gemm_rs(x2, w)
-        if bias is not None:
-            o += bias  # every rank adds it to its own rows; its gradient is summed over the group with the other replicated ones
+        # the bias is added once, to this rank's reduced rows (inside the kernel's epilogue); its gradient is summed
+        # over the group with the other replicated parameters
+        o = comm.gemm_rs(x2, w, bias=bias)
         ctx.save_for_backward(x2, w, bias)
         ctx.comm = comm
         return o

@@ -144,6 +144,11 @@ def _tp_fused_worker(rank, world):
         parts = [torch.empty_like(q) for _ in range(world)]
         dist.all_gather(parts, q)
         rows = m  # M / world
+        # the CTA-pair kernel (rows per rank a multiple of 256) adds a rank's own partial product straight from the
+        # accumulator; only what crosses the link is quantised
+        from coccl_b200.ops import tp_fused as T
+        if T.last_variant() == "2cta":
+            parts[rank] = part
         refq = sum(parts)[rank * rows:(rank + 1) * rows]
         d = (out.float() - refq).abs()
         scale = refq.abs().max().item()

@@ -114,3 +114,58 @@ def test_gpt_step_matches_cpu_reference(cuda):
     a, b = gpu.store.flat_grad.cpu(), cpu.store.flat_grad
     rel = (a - b).norm() / b.norm()
     assert rel < 5e-2, rel.item()
+
+
+@pytest.mark.parametrize("tp,M,V", [(2, 300, 1024), (4, 64, 25152)])
+def test_vocab_parallel_cross_entropy_kernels(cuda, tp, M, V):
+    """Two-pass cross-entropy over a vocabulary split into `tp` shards (all shards on this GPU): the combined loss and
+    the in-place gradients equal the fp32 reference over the whole vocabulary."""
+    import ctypes as C
+    from coccl_b200 import _lib
+    torch.manual_seed(21)
+    full = (torch.randn(M, tp * V, device=cuda) * 3).to(torch.bfloat16)
+    tgt = torch.randint(0, tp * V, (M,), device=cuda)
+    tgt[::7] = -1   # ignored rows
+    scale = 0.37
+    shards = [full[:, r * V:(r + 1) * V].contiguous() for r in range(tp)]
+    lib = _lib.lib()
+    stats = torch.empty(tp, M, 4, dtype=torch.float32, device=cuda)
+    for r in range(tp):
+        _lib.check(lib.cocclkCrossEntropyStats(shards[r].data_ptr(), tgt.data_ptr(), stats[r].data_ptr(), M, V, V, r * V,
+                                               _lib.cur_stream()), "stats")
+    losses = []
+    for r in range(tp):
+        loss = torch.empty(M, dtype=torch.float32, device=cuda)
+        _lib.check(lib.cocclkCrossEntropyFinish(shards[r].data_ptr(), tgt.data_ptr(), stats.data_ptr(), tp, loss.data_ptr(), M, V, V,
+                                                r * V, scale, _lib.cur_stream()), "finish")
+        losses.append(loss)
+    lf = full.float()
+    valid = tgt >= 0
+    ref_loss = torch.where(valid, torch.logsumexp(lf, -1) - lf.gather(1, tgt.clamp(min=0)[:, None])[:, 0], torch.zeros(M, device=cuda))
+    p = torch.softmax(lf, -1)
+    p[torch.arange(M, device=cuda), tgt.clamp(min=0)] -= 1.0
+    ref_grad = p * valid[:, None] * scale
+    for r in range(tp):
+        assert torch.allclose(losses[r], ref_loss, atol=2e-3, rtol=2e-3)
+        assert torch.equal(losses[r], losses[0])   # every rank computes the same loss
+        got = shards[r].float()
+        want = ref_grad[:, r * V:(r + 1) * V]
+        assert (got - want).abs().max().item() <= 4e-3 * scale + 1e-6
+
+
+@pytest.mark.parametrize("M,N", [(4096, 4096), (100, 264), (2048, 6144), (33, 8)])
+def test_column_sum(cuda, M, N):
+    """Bias-gradient column sum (two kernels, fixed summation order) against fp32 torch, overwrite and accumulate."""
+    import ctypes as C
+    from coccl_b200 import _lib
+    torch.manual_seed(22)
+    x = torch.randn(M, N, device=cuda).to(torch.bfloat16)
+    lib = _lib.lib()
+    sc = torch.empty(lib.cocclkColSumBlocks(M) * N, dtype=torch.float32, device=cuda)
+    out = torch.full((N,), 5.0, device=cuda)
+    _lib.check(lib.cocclkColSum(x.data_ptr(), out.data_ptr(), 0, sc.data_ptr(), M, N, _lib.cur_stream()), "colsum")
+    ref = x.float().sum(0)
+    assert torch.allclose(out, ref, atol=1e-3 * M ** 0.5, rtol=1e-5)
+    first = out.clone()
+    _lib.check(lib.cocclkColSum(x.data_ptr(), out.data_ptr(), 1, sc.data_ptr(), M, N, _lib.cur_stream()), "colsum")
+    assert torch.allclose(out, 2 * first, atol=1e-5, rtol=1e-6)   # same partial sums in the same order, added once more
