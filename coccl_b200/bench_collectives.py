@@ -22,18 +22,21 @@ import os
 import torch
 import torch.distributed as dist
 
-from .ops.codec import MXFP8, SDP4BIT_G128, SDP4BIT_G128_SR, TACO_G128, ZFP_RATE8
 from .parallel.comm import NATIVE, Communicator, Policy
 
-# sdp4bit rounds to nearest, sdp4bit_sr stochastically (the reference's SDP4Bit has only the stochastic mode)
-CODECS = {"sdp4bit": SDP4BIT_G128, "sdp4bit_sr": SDP4BIT_G128_SR, "mxfp8": MXFP8, "taco": TACO_G128, "zfp8": ZFP_RATE8}
+# name -> (compressor plugin, its options): what a user would write in the policy file. sdp4bit rounds to nearest,
+# sdp4bit_sr stochastically (the reference's SDP4Bit has only the stochastic mode).
+_SDP = {"groupCount": 128, "quantBits": 4, "quantType": "Symmetric", "hadamard": True}
+CODECS = {"sdp4bit": ("sdp4bit", dict(_SDP, rounding="nearest")), "sdp4bit_sr": ("sdp4bit", dict(_SDP, rounding="stochastic")),
+          "mxfp8": ("fp8block", {}), "taco": ("taco", {"fp8Format": "E4M3", "groupSize": 128}), "zfp8": ("zfp", {"rate": 8})}
 OPS = ("all_reduce", "reduce_scatter", "all_gather", "all_to_all")
 
 
-def _policy(codec) -> Policy:
-    p = Policy(threshold_bytes=0, all_reduce_oneshot_max_bytes=1 << 20)
-    p.codecs = {("default", op): codec for op in OPS}
-    return p
+def _policy(codec, threshold: int, autotune: bool) -> Policy:
+    """A normal-mode policy file with this codec on every collective; the all-reduce algorithm is left to the selector,
+    which (with autotune) is fed one-shot / two-shot timings of this group at the first call."""
+    name, options = codec
+    return Policy.normal(name, options, threshold_bytes=threshold, autotune=autotune)
 
 
 def _buffers(op: str, total_bytes: int, dtype, n: int, dev):
@@ -114,6 +117,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default="")
+    ap.add_argument("--threshold", type=int, default=0, help="compression_threshold_bytes of the policy (0: every size compressed)")
+    ap.add_argument("--no-autotune", action="store_true", help="selector heuristics instead of measured one-/two-shot times")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
                     help="reference: run the reference's own stock *_perf binaries (baseline/run_reference.py), "
                          "nothing of this library; launch WITHOUT torchrun, with --gpus N")
@@ -131,7 +136,7 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     comms = {"native": Communicator(None, dev, NATIVE, "native")}
     for c in a.codecs.split(","):
-        comms[c] = Communicator(None, dev, _policy(CODECS[c]), c)
+        comms[c] = Communicator(None, dev, _policy(CODECS[c], a.threshold, not a.no_autotune), c)
     dts = {"fp32": torch.float32, "bf16": torch.bfloat16}
     rows = []
     size = a.min_mib
@@ -164,6 +169,7 @@ def main():
     if rank == 0 and a.out:
         with open(a.out, "w") as f:
             json.dump({"n_gpus": world, "timing": "cuda events, max over ranks, median of %d, L2 flushed" % a.iters,
+                       "routing": {name: c.routing_summary() for name, c in comms.items()},
                        "rows": rows}, f, indent=1)
     for c in comms.values():
         c.close()

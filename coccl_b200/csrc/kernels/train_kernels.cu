@@ -178,14 +178,31 @@ __global__ void __launch_bounds__(kLnThreads) lnBwdKernel(const bf16* dy, const 
   }
 }
 
-// out[c] (+)= sum_r partial[r][c]; `cols` columns, `rows` partial rows
-__global__ void colReduceKernel(const float* partial, float* out, int rows, long cols, long stride, int accumulate) {
-  const long c = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// out[c] (+)= sum_r partial[r][c]; `cols` columns, `rows` partial rows. A CTA owns 32 columns; its 8 warps take every
+// 8th row (a warp reads 128 contiguous bytes of a row) and fold their sums through shared memory in a fixed order.
+constexpr int kColReduceCols = 32;
+__global__ void __launch_bounds__(256) colReduceKernel(const float* partial, float* out, int rows, long cols, long stride, int accumulate) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  const long c = (long)blockIdx.x * kColReduceCols + lane;
   float s = 0.f;
-#pragma unroll 8
-  for (int r = 0; r < rows; ++r) s += partial[(long)r * stride + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < cols) {
+    int r = wy;
+    for (; r + 24 < rows; r += 32) {
+      const float a0 = partial[(long)r * stride + c], a1 = partial[(long)(r + 8) * stride + c];
+      const float a2 = partial[(long)(r + 16) * stride + c], a3 = partial[(long)(r + 24) * stride + c];
+      s += (a0 + a1) + (a2 + a3);
+    }
+    for (; r < rows; r += 8) s += partial[(long)r * stride + c];
+  }
+  red[wy][lane] = s;
+  __syncthreads();
+  if (wy == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // ---------------------------------------------------------------- column sum of a bf16 matrix
@@ -529,8 +546,8 @@ extern "C" int cocclkLayerNormBwd(const void* dy, const void* x, const float* me
   if (nv <= 1) LN_BWD(1); else if (nv <= 2) LN_BWD(2); else if (nv <= 4) LN_BWD(4); else LN_BWD(8);
 #undef LN_BWD
   // scratch rows are [dgamma | dbeta], 2H floats each
-  colReduceKernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dgamma, grid, H, 2L * H, accumulate);
-  colReduceKernel<<<(H + 255) / 256, 256, 0, s>>>(scratch + H, dbeta, grid, H, 2L * H, accumulate);
+  colReduceKernel<<<(H + kColReduceCols - 1) / kColReduceCols, 256, 0, s>>>(scratch, dgamma, grid, H, 2L * H, accumulate);
+  colReduceKernel<<<(H + kColReduceCols - 1) / kColReduceCols, 256, 0, s>>>(scratch + H, dbeta, grid, H, 2L * H, accumulate);
   cocclkCountLaunches(3);
   return (int)cudaGetLastError();
 }
@@ -543,7 +560,7 @@ extern "C" int cocclkColSum(const void* x, float* out, int accumulate, float* sc
   const int rowsPer = (M + by - 1) / by;
   dim3 grid((N / 8 + 31) / 32, by);
   colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
-  colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
+  colReduceKernel<<<(N + kColReduceCols - 1) / kColReduceCols, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
   cocclkCountLaunches(2);
   return (int)cudaGetLastError();
 }
@@ -682,7 +699,7 @@ extern "C" int cocclkColSumNoAlloc(const void* x, float* out, int accumulate, in
   const int rowsPer = (M + by - 1) / by;
   dim3 grid((N / 8 + 31) / 32, by);
   colSumPartialKernel<<<grid, 256, 0, s>>>((const bf16*)x, scratch, M, N, rowsPer);
-  colReduceKernel<<<(N + 255) / 256, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
+  colReduceKernel<<<(N + kColReduceCols - 1) / kColReduceCols, 256, 0, s>>>(scratch, out, by, N, N, accumulate);
   cocclkCountLaunches(2);
   return (int)cudaGetLastError();
 }

@@ -18,8 +18,13 @@ OP_NAMES = {"reduce_scatter": OP_RS, "all_gather": OP_AG, "all_to_all": OP_A2A, 
             "all_reduce_twoshot": OP_AR2, "all_gather_delta": OP_AGD}
 
 
-def slot_bytes(cfg: CodecConfig, count: int, dtype) -> int:
-    return _lib.lib().cocclkSlotBytes(cfg.to_c(dtype), count)
+def as_c(cfg, dtype) -> _lib.Codec:
+    """A CodecConfig (Python description) or an already filled cocclkCodec (from the router) as the C struct."""
+    return cfg if isinstance(cfg, _lib.Codec) else cfg.to_c(dtype)
+
+
+def slot_bytes(cfg, count: int, dtype) -> int:
+    return _lib.lib().cocclkSlotBytes(as_c(cfg, dtype), count)
 
 
 def tile_elems() -> int:
@@ -43,7 +48,7 @@ def chunk_count(op: int, numel_in: int, n: int) -> int:
     return numel_in  # all-gather shard, one-shot all-reduce vector
 
 
-def workspace_bytes(op: int, cfg: CodecConfig, count: int, dtype, n: int) -> tuple[int, int, int]:
+def workspace_bytes(op: int, cfg, count: int, dtype, n: int) -> tuple[int, int, int]:
     """(slot_bytes, region_b_offset, total) of one parity half of the workspace."""
     sb = slot_bytes(cfg, count, dtype)
     region = -(-sb * n // 256) * 256

@@ -1,62 +1,183 @@
-"""Communicator: one per process group; routes every collective either to a fused
-compressed kernel over peer-mapped symmetric memory or to torch.distributed
-(NCCL on GPUs, gloo on CPU).
+"""Communicator: one per process group; runs every collective either as a fused compressed kernel over peer-mapped
+symmetric memory or on torch.distributed (NCCL on GPUs, gloo on CPU).
 
-Routing mirrors the reference router (src/coccl-extend/core/runtime/coccl_runtime.cc:181-229):
-compression must be enabled, a codec must be configured for (role, operation), the
-datatype must be one the codec handles, the reduction must be a sum, an all-reduce
-must be divisible by the group size, and the message must be LARGER than the
-threshold (`bytes <= threshold` stays native). Total bytes are scaled by the number
-of ranks for all-gather / reduce-scatter / all-to-all (coccl_runtime.cc:57-76).
+WHICH of the two is not decided here. Every call is described to a routing session of the native runtime
+(csrc/api/router_api.cc), which runs the same code as the C API: the rule order of the reference router
+(src/coccl-extend/core/runtime/coccl_runtime.cc:181-229: enabled, sum only, divisibility, role known in training
+mode, a codec configured for the scope, `bytes <= threshold` stays native, algorithm selection), on the policy model
+of its TOML files (COCCL_CONFIG_FILE schema: normal / training mode, per-operation default/intra/inter scopes,
+thresholds, autotune section). This module turns the decision into a kernel launch, owns the symmetric memory, and
+feeds the selector with measurements of the kernels that actually serve the calls.
 """
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+import hashlib
+import os
+import tempfile
+from dataclasses import dataclass
+from pathlib import Path
 
 import torch
 import torch.distributed as dist
 
 from .. import _lib
 from ..ops import collective as K
-from ..ops.codec import MXFP8, SDP4BIT_G128, CodecConfig, DTYPE_CODE
+from ..ops.codec import DTYPE_CODE
 from ..utils.trace import nvtx_range
 
 K_NAMES = {0: "reduce_scatter", 1: "all_gather", 2: "all_to_all", 3: "all_reduce_oneshot", 4: "all_reduce_twoshot",
            5: "all_gather_delta"}
+CONFIG_DIR = Path(__file__).resolve().parent.parent / "configs"
+PLUGIN_DIR = Path(__file__).resolve().parent.parent / "lib" / "plugins"
+NCCL_DTYPE = {torch.float32: 7, torch.float16: 6, torch.bfloat16: 9, torch.int8: 0, torch.int32: 2, torch.int64: 4}
+ROLE = {"dp": 1, "tp": 2, "pp": 3}                       # communicator name -> COCCL_ROLE_*; anything else: normal
+OP = {"all_gather": 0, "reduce_scatter": 1, "all_reduce": 2, "all_to_all": 3, "sendrecv": 4}   # COCCL_OP_*
+ALGO_AR_ONESHOT, ALGO_AR_TWOSHOT = 3, 4
+
+
+class Decision(C.Structure):
+    """Mirror of cocclRouteDecision (csrc/include/coccl/router.h)."""
+    _fields_ = [("compressed", C.c_int), ("algorithm", C.c_int), ("fusable", C.c_int), ("delta", C.c_int),
+                ("native_variant", C.c_int), ("role", C.c_int), ("threshold_bytes", C.c_size_t), ("total_bytes", C.c_size_t),
+                ("codec", _lib.Codec), ("compressor", C.c_char * 32)]
 
 
 @dataclass
 class Policy:
-    """Per (role, operation) codec selection; None = native."""
+    """Where the routing rules come from: a policy file in the reference's TOML schema (or its text), read by the native
+    router. `Policy()` is the shipped training policy (configs/training.toml: SDP4Bit on the data-parallel gradient
+    reduce-scatter, 8-bit deltas on the parameter all-gather, block-scaled FP8 on tensor-parallel traffic, threshold
+    8 MiB). The remaining fields are launch knobs of this layer, not routing rules."""
     enabled: bool = True
-    threshold_bytes: int = 8 << 20
-    codecs: dict = field(default_factory=lambda: {
-        ("dp", "reduce_scatter"): SDP4BIT_G128,
-        ("dp", "all_reduce"): SDP4BIT_G128,
-        ("dp", "all_gather"): None,            # parameters: kept exact (no delta codec state yet)
-        ("tp", "all_gather"): MXFP8,
-        ("tp", "reduce_scatter"): MXFP8,
-        ("tp", "all_reduce"): MXFP8,
-        ("ep", "all_to_all"): MXFP8,
-        ("default", "reduce_scatter"): SDP4BIT_G128,
-        ("default", "all_gather"): SDP4BIT_G128,
-        ("default", "all_reduce"): SDP4BIT_G128,
-        ("default", "all_to_all"): SDP4BIT_G128,
-    })
-    all_reduce_oneshot_max_bytes: int = 1 << 20
-    dp_param_delta: bool = False    # ZeRO-1 parameter all-gather as 8-bit deltas (subAdd); exact first round
-    nvls_all_reduce: bool = False   # uncompressed all-reduce below the threshold through multimem instead of NCCL
-    timeout_ms: float = 20000.0
-    max_ctas: int = 0
+    config_file: str | None = None   # default: configs/training.toml
+    toml: str | None = None          # inline policy text instead of a file
+    timeout_ms: float = 20000.0      # bound of every device-side wait
+    max_ctas: int = 0                # CTAs a fused kernel may occupy (0 = all it can keep resident)
+    measure: bool = True             # time one-shot / two-shot (and multimem) at first use where [autotune] enabled = true
+    nvls: bool = True                # the multimem all-reduce is a candidate for uncompressed calls below the threshold
 
-    def codec_for(self, role: str, op: str) -> CodecConfig | None:
+    def text(self) -> str | None:
         if not self.enabled:
             return None
-        return self.codecs.get((role, op), None)
+        if self.toml is not None:
+            return self.toml
+        return Path(self.config_file or CONFIG_DIR / "training.toml").read_text()
+
+    def base_dir(self) -> Path:
+        return Path(self.config_file).resolve().parent if (self.toml is None and self.config_file) else CONFIG_DIR
+
+    @staticmethod
+    def normal(compressor: str = "sdp4bit", options: dict | None = None, *, threshold_bytes: int = 8 << 20,
+               autotune: bool = False, all_reduce_algorithm: str = "auto", per_op: dict | None = None, **kw) -> "Policy":
+        """A normal-mode policy with one codec on every collective (per_op: {operation: (compressor, options)}
+        overrides single operations). The text is what a user would put in COCCL_CONFIG_FILE."""
+        if options is None:
+            options = {"sdp4bit": {"groupCount": 128, "quantBits": 4, "quantType": "Symmetric", "hadamard": True,
+                                   "rounding": "nearest"}}.get(compressor, {})
+        per_op = dict(per_op or {})
+        names = sorted({compressor} | {c for c, _ in per_op.values()})
+
+        def val(v):
+            return ("true" if v else "false") if isinstance(v, bool) else (f'"{v}"' if isinstance(v, str) else str(v))
+        lines = ["[runtime]", 'mode = "normal"', f"compression_threshold_bytes = {threshold_bytes}", "",
+                 "[compressor_plugins]", "compressors = [" + ", ".join(f'"{n}"' for n in names) + "]",
+                 f'library_path = "{PLUGIN_DIR}"', "", "[autotune]", f"enabled = {val(autotune)}",
+                 f'all_reduce_algorithm = "{all_reduce_algorithm}"', ""]
+        for op in ("all_gather", "reduce_scatter", "all_reduce", "all_to_all", "sendrecv"):
+            c, o = per_op.get(op, (compressor, options))
+            lines += [f"[normal.{op}.default]", f'compressor = "{c}"']
+            if o:
+                lines += [f"[normal.{op}.default.config]"] + [f"{k} = {val(v)}" for k, v in o.items()]
+            lines.append("")
+        return Policy(toml="\n".join(lines), **kw)
+
+    @staticmethod
+    def training(*, threshold_bytes: int = 8 << 20, dp_delta: bool = True, autotune: bool = True, **kw) -> "Policy":
+        """The shipped training policy with the threshold replaced (tests and small models use 0) and, with
+        dp_delta=False, without the delta codec on the parameter all-gather (it then stays native)."""
+        text = (CONFIG_DIR / "training.toml").read_text()
+        text = text.replace("compression_threshold_bytes = 8388608", f"compression_threshold_bytes = {threshold_bytes}")
+        text = text.replace('library_path = "../lib/plugins"', f'library_path = "{PLUGIN_DIR}"')
+        if not autotune:
+            text = text.replace("[autotune]\nenabled = true", "[autotune]\nenabled = false")
+        if not dp_delta:
+            a = text.index("[training.dp.all_gather.default]")
+            b = text.index("[training.tp.all_gather.default]")
+            text = text[:a] + text[b:]
+        return Policy(toml=text, **kw)
 
 
 NATIVE = Policy(enabled=False)
+
+
+class Router:
+    """One routing session of the native runtime per distinct policy text (process-wide cache)."""
+    _cache: dict = {}
+
+    def __init__(self, policy: Policy, devices_per_node: int):
+        self._open = _lib.declare("cocclRouterOpen", C.c_int, [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t])
+        self._decide = _lib.declare("cocclRouterDecide", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_int, C.c_int,
+                                                                   C.c_int, C.c_int, C.c_int, C.POINTER(Decision)])
+        self._eff = _lib.declare("cocclRouterEffectiveConfig", C.c_char_p, [C.c_void_p])
+        self._hash = _lib.declare("cocclRouterConfigHash", C.c_uint64, [C.c_void_p])
+        self._training = _lib.declare("cocclRouterTrainingMode", C.c_int, [C.c_void_p])
+        self._set = _lib.declare("cocclRouterSetMeasured", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double])
+        self._set_native = _lib.declare("cocclRouterSetMeasuredNative", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double])
+        self._stats = _lib.declare("cocclRouterStats", None, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)])
+        text = policy.text()
+        path = None
+        if text is not None:
+            # the parser resolves library_path against the file's directory: keep inline text next to the shipped files' plugins
+            tmp = Path(tempfile.gettempdir()) / f"coccl_policy_{os.getpid()}_{hashlib.sha1(text.encode()).hexdigest()[:12]}.toml"
+            fixed = text.replace('library_path = "../lib/plugins"', f'library_path = "{PLUGIN_DIR}"')
+            tmp.write_text(fixed)
+            path = str(tmp).encode()
+        h, err = C.c_void_p(), C.create_string_buffer(1024)
+        rc = self._open(path, 1, max(1, devices_per_node), C.byref(h), err, 1024)
+        if rc != 0:
+            raise RuntimeError(f"policy rejected by the router: {err.value.decode() or rc}")
+        self.handle = h
+        self.measured: set = set()     # (kind, dtype, nranks) already timed
+        self.tuning_log: list = []     # rows of what was timed and fed to the selector
+        self.autotune = "autotune.enabled = true" in self.effective_config()
+
+    @classmethod
+    def of(cls, policy: Policy, devices_per_node: int) -> "Router | None":
+        text = policy.text()
+        if text is None:
+            return None
+        key = (text, devices_per_node)
+        if key not in cls._cache:
+            cls._cache[key] = Router(policy, devices_per_node)
+        return cls._cache[key]
+
+    def decide(self, role: int, op: str, dtype: torch.dtype, count: int, n_ranks: int, rank: int, explicit: int = -1) -> Decision:
+        d = Decision()
+        rc = self._decide(self.handle, role, OP[op], NCCL_DTYPE.get(dtype, 1), count, n_ranks, 1, rank, 0, explicit, C.byref(d))
+        if rc != 0:
+            raise RuntimeError(f"cocclRouterDecide failed with {rc}")
+        return d
+
+    def effective_config(self) -> str:
+        return self._eff(self.handle).decode()
+
+    def config_hash(self) -> str:
+        return f"{int(self._hash(self.handle)):016x}"
+
+    def training_mode(self) -> bool:
+        return bool(self._training(self.handle))
+
+    def set_measured(self, op: str, dtype, n_ranks: int, log2_bytes: int, algorithm: int, seconds: float):
+        self._set(self.handle, OP[op], NCCL_DTYPE[dtype], n_ranks, log2_bytes, algorithm, seconds)
+
+    def set_measured_native(self, dtype, n_ranks: int, log2_bytes: int, variant: int, seconds: float):
+        self._set_native(self.handle, NCCL_DTYPE[dtype], n_ranks, log2_bytes, variant, seconds)
+
+    def stats(self) -> dict:
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._stats(self.handle, C.byref(a), C.byref(b), C.byref(c))
+        return {"native": a.value, "compressed": b.value, "policy_lookups": c.value}
 
 
 class PeerLost(RuntimeError):
@@ -202,9 +323,14 @@ class Communicator:
         self._nvls: dict | None = None
         self._trace: torch.Tensor | None = None
         self._health: dict | None = None
-        self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0}
+        self.stats = {"compressed_calls": 0, "native_calls": 0, "compressed_raw_bytes": 0, "native_bytes": 0,
+                      "unfused_codec_calls": 0, "nvls_calls": 0}
+        self.role = ROLE.get(name, 0)
+        self._last: Decision | None = None
+        self._decisions: dict = {}
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
+        self.router = Router.of(self.policy, self.size) if (self.cuda and self.size > 1) else None
 
     # ------------------------------------------------------------------ symmetric state
     def _ensure(self, half_bytes: int):
@@ -222,8 +348,9 @@ class Communicator:
         import warnings
         warnings.warn(f"coccl_b200: group '{self.name}' falls back to native collectives on every rank: {why}")
         self.policy = NATIVE
+        self.router = None
 
-    def _fused(self, opc: int, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig) -> bool:
+    def _fused(self, opc: int, inp: torch.Tensor, out: torch.Tensor, cfg) -> bool:
         """Launch the fused kernel; False (nothing launched, on any rank) when peer memory cannot be mapped."""
         n = self.size
         count = K.chunk_count(opc, inp.numel(), n)
@@ -240,7 +367,7 @@ class Communicator:
         a.sliceTiles = K.pick_slice_tiles(count, n)
         a.epoch = self.epoch & 0xFFFFFFFF
         a.timeoutNs = int(self.policy.timeout_ms * 1e6)
-        a.codec = cfg.to_c(inp.dtype)
+        a.codec = K.as_c(cfg, inp.dtype)
         a.slotBytes, a.regionBOffset = sb, region_b
         a.inp[self.rank], a.out[self.rank] = inp.data_ptr(), out.data_ptr()
         for p in range(n):
@@ -250,7 +377,7 @@ class Communicator:
         if self._trace is not None:
             self._trace.zero_()
             a.trace[self.rank] = self._trace.data_ptr()
-        with nvtx_range(f"coccl.fused.{K_NAMES.get(opc, opc)}.{cfg.kind}"):
+        with nvtx_range(f"coccl.fused.{K_NAMES.get(opc, opc)}.{a.codec.kind}"):
             rc = _lib.lib().cocclkFusedCollective(a, 1, self.policy.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkFusedCollective")
         self.stats["compressed_calls"] += 1
@@ -280,47 +407,76 @@ class Communicator:
         _lib.check(cudart_memcpy(self._sig.ptrs[self.rank] + self._flag_bytes, w), "cocclHostRead32")
         return int(w[0])
 
-    def _route(self, role: str, op: str, inp: torch.Tensor, total_bytes: int, divisible: bool = True):
-        if self.size == 1 or not self.cuda or not inp.is_cuda:
+    def _route(self, op: str, inp: torch.Tensor, count: int, explicit: int = -1) -> Decision | None:
+        """Ask the router. Returns the decision when the call runs as a fused compressed kernel, None when it runs
+        natively (`self._last` keeps the decision either way, e.g. for the multimem variant of a native all-reduce).
+        `count` is the count of the matching nccl* call."""
+        self._last = None
+        if self.router is None or not inp.is_cuda or inp.dtype not in NCCL_DTYPE:
             return None
-        cfg = self.policy.codec_for(role, op) or self.policy.codec_for("default", op) if self.policy.enabled else None
-        if cfg is None or inp.dtype not in DTYPE_CODE or not divisible:
+        key = (op, inp.dtype, count, explicit)
+        d = self._decisions.get(key)
+        if d is None:   # the router is deterministic between two measurement updates: ask once per call shape
+            d = self._decisions[key] = self.router.decide(self.role, op, inp.dtype, count, self.size, self.rank, explicit)
+        self._last = d
+        if not d.compressed:
             return None
-        if total_bytes <= self.policy.threshold_bytes:
+        if not d.fusable or inp.dtype not in DTYPE_CODE or not (inp.is_contiguous() and inp.data_ptr() % 4 == 0):
+            # a codec without a tile form (plugin-only: rANS, odd ZFP rates) is served by the staged pipeline of the
+            # C API; this layer launches fused kernels only and leaves such calls native
+            self.stats["unfused_codec_calls"] += 1
             return None
-        if not (inp.is_contiguous() and inp.data_ptr() % 4 == 0):
-            return None
-        return cfg
+        return d
 
     def _native(self, nbytes):
         self.stats["native_calls"] += 1
         self.stats["native_bytes"] += nbytes
 
+    def routing_summary(self) -> dict:
+        """Effective policy hash, router counters and what was measured for the selector."""
+        if self.router is None:
+            return {"policy": "native"}
+        return {"policy_hash": self.router.config_hash(), "training_mode": self.router.training_mode(),
+                "router": self.router.stats(), "measured": list(self.router.tuning_log)}
+
     # ------------------------------------------------------------------ collectives
-    def reduce_scatter(self, inp: torch.Tensor, out: torch.Tensor, role: str = "default"):
+    def reduce_scatter(self, inp: torch.Tensor, out: torch.Tensor, role: str | None = None):
         """out = sum over ranks of inp[rank chunk]; inp has size*out.numel() elements."""
         if self.size == 1:
             out.copy_(inp.reshape(out.shape))
             return out
         nbytes = inp.numel() * inp.element_size()
-        cfg = self._route(role, "reduce_scatter", inp, nbytes)
-        if cfg is None or not self._fused(K.OP_RS, inp, out, cfg):
+        d = self._route("reduce_scatter", inp, out.numel())
+        if d is None or not self._fused(K.OP_RS, inp, out, d.codec):
             self._native(nbytes)
             with nvtx_range("coccl.native.reduce_scatter"):
                 dist.reduce_scatter_tensor(out, inp, group=self.group)
         return out
 
-    def all_gather(self, inp: torch.Tensor, out: torch.Tensor, role: str = "default"):
+    def all_gather(self, inp: torch.Tensor, out: torch.Tensor, role: str | None = None, state=None):
+        """Gather `inp` of every rank into `out`. When the policy puts a delta codec on this call (sdp4bit subAdd)
+        the caller passes the state handle of the previous call (None the first time) and keeps the returned one;
+        see all_gather_delta. Returns `out`, or (out, state) when `state` was given or a delta codec applies."""
         if self.size == 1:
             out.copy_(inp.reshape(out.shape))
             return out
         nbytes = out.numel() * out.element_size()
-        cfg = self._route(role, "all_gather", inp, nbytes)
-        if cfg is None or not self._fused(K.OP_AG, inp, out, cfg):
+        d = self._route("all_gather", inp, inp.numel())
+        if d is not None and d.delta:
+            return out, self.all_gather_delta(inp, out, d.codec, state)
+        if d is None or not self._fused(K.OP_AG, inp, out, d.codec):
             self._native(nbytes)
             with nvtx_range("coccl.native.all_gather"):
                 dist.all_gather_into_tensor(out, inp, group=self.group)
         return out
+
+    def uses_delta_all_gather(self, numel_per_rank: int, dtype: torch.dtype) -> bool:
+        """Whether the policy routes an all-gather of this shape through a delta codec (the caller then keeps the
+        previous values until the call has subtracted them)."""
+        if self.router is None or self.size == 1:
+            return False
+        d = self.router.decide(self.role, "all_gather", dtype, numel_per_rank, self.size, self.rank)
+        return bool(d.compressed and d.fusable and d.delta)
 
     # ------------------------------------------------------------------ NVSwitch (multimem) all-reduce
     def _ensure_nvls(self, nbytes: int) -> bool:
@@ -370,31 +526,99 @@ class Communicator:
         self.stats["nvls_calls"] = self.stats.get("nvls_calls", 0) + 1
         return True
 
-    def all_reduce(self, x: torch.Tensor, role: str = "default"):
+    def all_reduce(self, x: torch.Tensor, role: str | None = None):
         if self.size == 1:
             return x
         nbytes = x.numel() * x.element_size()
-        cfg = self._route(role, "all_reduce", x, nbytes, divisible=(x.numel() % self.size == 0))
-        if cfg is None and self.policy.nvls_all_reduce and self.cuda and x.is_cuda and self.all_reduce_nvls(x):
+        if self.router is not None and self.router.autotune and self.policy.measure and x.is_cuda and x.dtype in DTYPE_CODE:
+            self._measure_all_reduce(x.dtype)
+        d = self._route("all_reduce", x, x.numel())
+        if d is not None:
+            op = K.OP_AR1 if d.algorithm == ALGO_AR_ONESHOT else K.OP_AR2
+            if self._fused(op, x, x, d.codec):
+                return x
+        last = self._last
+        if last is not None and last.native_variant == 1 and self.policy.nvls and self.all_reduce_nvls(x):
             return x
-        op = K.OP_AR1 if nbytes <= self.policy.all_reduce_oneshot_max_bytes else K.OP_AR2
-        if cfg is None or not self._fused(op, x, x, cfg):
-            self._native(nbytes)
-            with nvtx_range("coccl.native.all_reduce"):
-                dist.all_reduce(x, group=self.group)
+        self._native(nbytes)
+        with nvtx_range("coccl.native.all_reduce"):
+            dist.all_reduce(x, group=self.group)
         return x
 
-    def all_to_all(self, inp: torch.Tensor, out: torch.Tensor, role: str = "default"):
+    def all_to_all(self, inp: torch.Tensor, out: torch.Tensor, role: str | None = None):
         if self.size == 1:
             out.copy_(inp)
             return out
         nbytes = inp.numel() * inp.element_size()
-        cfg = self._route(role, "all_to_all", inp, nbytes, divisible=(inp.numel() % self.size == 0))
-        if cfg is None or not self._fused(K.OP_A2A, inp, out, cfg):
+        d = self._route("all_to_all", inp, inp.numel() // self.size) if inp.numel() % self.size == 0 else None
+        if d is None or not self._fused(K.OP_A2A, inp, out, d.codec):
             self._native(nbytes)
             with nvtx_range("coccl.native.all_to_all"):
                 dist.all_to_all_single(out, inp, group=self.group)
         return out
+
+    # ------------------------------------------------------------------ measurements for the selector
+    def _time_calls(self, fn, iters: int = 5, warmup: int = 2) -> float:
+        """Seconds per call of fn(): CUDA events on the current stream, maximum over the ranks of the group."""
+        for _ in range(warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters / 1e3], device=self.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())
+
+    def _measure_all_reduce(self, dtype: torch.dtype) -> None:
+        """Once per (datatype, group size) and routing session: time the fused one-shot and two-shot all-reduce on this
+        group for a ladder of sizes, and, for calls that stay uncompressed, NCCL against the multimem kernel; hand the
+        results to the selector (cocclRouterSetMeasured*), which from then on picks per call by nearest size. The
+        reference fits cost models to point-to-point and codec timings instead
+        (src/coccl-extend/core/tuning/coccl_autotune_profiler.cc:62-618); here the candidates themselves are timed.
+        Collective: every rank reaches the first all-reduce of a datatype at the same call."""
+        key = ("ar", dtype, self.size, self.role)
+        r = self.router
+        if key in r.measured:
+            return
+        r.measured.add(key)
+        es = torch.empty(0, dtype=dtype).element_size()
+        unit = self.size * 2048
+        probe = r.decide(self.role, "all_reduce", dtype, unit * 4096, self.size, self.rank, ALGO_AR_TWOSHOT)
+        sizes = [1 << 16, 1 << 18, 1 << 20, 1 << 22, 1 << 24, 1 << 26]
+        if probe.compressed and probe.fusable:
+            for nbytes in reversed(sizes):     # largest first: the workspace grows once
+                numel = max(unit, nbytes // es // unit * unit)
+                x = torch.zeros(numel, dtype=dtype, device=self.device)
+                lg = (numel * es).bit_length() - 1
+                row = {"what": "all_reduce", "dtype": str(dtype), "ranks": self.size, "bytes": numel * es}
+                for algo, opc in ((ALGO_AR_ONESHOT, K.OP_AR1), (ALGO_AR_TWOSHOT, K.OP_AR2)):
+                    if algo == ALGO_AR_ONESHOT and nbytes > (8 << 20):
+                        continue   # every rank receives everything: N x the traffic, never competitive up here
+                    t = self._time_calls(lambda: self._fused(opc, x, x, probe.codec))
+                    r.set_measured("all_reduce", dtype, self.size, lg, algo, t)
+                    row["oneshot_us" if algo == ALGO_AR_ONESHOT else "twoshot_us"] = t * 1e6
+                r.tuning_log.append(row)
+                del x
+        if self.policy.nvls and self._ensure_nvls(8 << 20):
+            for nbytes in (1 << 16, 1 << 18, 1 << 20, 1 << 22, 1 << 23):
+                numel = max(unit, nbytes // es // unit * unit)
+                x = torch.zeros(numel, dtype=dtype, device=self.device)
+                lg = (numel * es).bit_length() - 1
+                t_nccl = self._time_calls(lambda: dist.all_reduce(x, group=self.group))
+                t_nvls = self._time_calls(lambda: self.all_reduce_nvls(x))
+                r.set_measured_native(dtype, self.size, lg, 0, t_nccl)
+                r.set_measured_native(dtype, self.size, lg, 1, t_nvls)
+                r.tuning_log.append({"what": "all_reduce_uncompressed", "dtype": str(dtype), "ranks": self.size,
+                                     "bytes": numel * es, "nccl_us": t_nccl * 1e6, "multimem_us": t_nvls * 1e6})
+        self._decisions.clear()
+        if os.environ.get("COCCL_DEBUG", "").upper() in ("INFO", "TRACE") and self.rank == 0:
+            for row in r.tuning_log:
+                print("[coccl tuning]", row, flush=True)
 
     # ------------------------------------------------------------------ tensor-parallel fusions
     def _ensure_tp(self, half_bytes: int):
@@ -495,18 +719,21 @@ class Communicator:
     def tp_fusable(self, rows_total: int, n_out_rs: int | None = None, width: int | None = None) -> bool:
         """Whether the one-kernel TP fusions serve a problem with `rows_total` gathered rows (and, for gemm_rs,
         `n_out_rs` output columns). The fusions quantise the reduce-scattered partial sums to block-scaled FP8, so
-        they apply only where the policy asks for exactly that: an MX-FP8 codec on ('tp', 'reduce_scatter'), a
-        codec on ('tp', 'all_gather'), and a message above the threshold (`width` = columns of the gathered
-        operand; the router's `bytes <= threshold` rule, coccl_runtime.cc:214). Otherwise the caller takes the
-        unfused path, whose collectives are routed one by one."""
-        if not (self.cuda and self.policy.enabled and 1 < self.size <= _lib.MAX_RANKS):
+        they apply only where the router, asked about the two collectives the fusion replaces, answers "compressed" for
+        both and names the MX-FP8 codec for the reduce-scatter (`width` = columns of the gathered operand). Otherwise the
+        caller takes the unfused path, whose collectives are routed one by one."""
+        if not (self.cuda and self.router is not None and 1 < self.size <= _lib.MAX_RANKS):
             return False
-        rs = self.policy.codec_for("tp", "reduce_scatter")
-        ag = self.policy.codec_for("tp", "all_gather")
-        if rs is None or ag is None or rs.kind != "mxfp8":
-            return False
-        cols = max(width or 0, n_out_rs or 0)
-        if cols and rows_total * cols * 2 <= self.policy.threshold_bytes:
+        key = ("tp_fusable", rows_total, n_out_rs, width)
+        if key not in self._decisions:
+            self._decisions[key] = self._tp_fusable(rows_total, n_out_rs, width)
+        return self._decisions[key]
+
+    def _tp_fusable(self, rows_total: int, n_out_rs: int | None, width: int | None) -> bool:
+        per_rank = rows_total // self.size
+        ag = self.router.decide(self.role, "all_gather", torch.bfloat16, per_rank * (width or n_out_rs or 0), self.size, self.rank)
+        rs = self.router.decide(self.role, "reduce_scatter", torch.bfloat16, per_rank * (n_out_rs or width or 0), self.size, self.rank)
+        if not (ag.compressed and ag.fusable and rs.compressed and rs.fusable and rs.codec.kind == 1):   # 1 = MX-FP8
             return False
         if rows_total % (self.size * 128) != 0:
             return False
@@ -595,7 +822,7 @@ class Communicator:
     def moe_status(self) -> int:
         return 0 if self._moe is None else self._moe.status()
 
-    def all_gather_delta(self, inp: torch.Tensor, out: torch.Tensor, cfg: CodecConfig | None = None, state=None):
+    def all_gather_delta(self, inp: torch.Tensor, out: torch.Tensor, cfg=None, state=None):
         """All-gather that sends the CHANGE of `inp` since the previous call (parameters after an optimizer step move
         little, so 8 bits of a small delta carry far more precision than 8 bits of the value). `out` itself is the
         codec state: every rank adds the same decoded deltas to it. The caller owns the state handle: pass None
@@ -607,14 +834,16 @@ class Communicator:
         if self.size == 1:
             out.copy_(inp.reshape(out.shape))
             return None
-        cfg = cfg or CodecConfig("sdp4bit", 8, 2048, False, False)
+        if cfg is None:
+            from ..ops.codec import CodecConfig
+            cfg = CodecConfig("sdp4bit", 8, 2048, False, False)
         usable = self.cuda and inp.is_cuda and inp.dtype in DTYPE_CODE and inp.is_contiguous() and out.is_contiguous()
         seeded = (state is not None and state.get("out") is out and state.get("numel") == out.numel()
                   and state.get("version") == out._version)
         if not usable or not seeded or not self._fused(K.OP_AGD, inp, out, cfg):
             self._native(out.numel() * out.element_size())
             dist.all_gather_into_tensor(out, inp, group=self.group)
-        if not usable or not self.policy.enabled:
+        if not usable or self.router is None:
             return None
         # the kernel and the native call write `out` behind autograd's back; record the version counter after
         # our own write so that a later in-place write by anyone else is noticed

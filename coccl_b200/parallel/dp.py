@@ -26,7 +26,8 @@ class DistributedOptimizer:
         counts (ParamStore.norm_exclude_ranges); they are left out of this rank's sum of squares, so the clip
         coefficient equals the one of a run without tensor / pipeline parallelism.
         delta_param_gather: send the updated parameters as 8-bit deltas against what every rank already holds (the
-        reference's `training.dp.all_gather` policy with subAdd, training.toml:36-54); None = follow the policy."""
+        reference's `training.dp.all_gather` policy with subAdd, training.toml:36-54); None = follow the policy file
+        (the router answers whether a delta codec is configured for this all-gather)."""
         self.flat_param, self.flat_grad, self.comm = flat_param, flat_grad, dp_comm
         self.dp = dp_comm.size if dp_comm is not None else 1
         self.rank = dp_comm.rank if dp_comm is not None else 0
@@ -47,8 +48,9 @@ class DistributedOptimizer:
         self._excl = [(max(a, lo) - lo, min(b, lo + self.shard) - lo) for a, b in norm_exclude
                       if max(a, lo) < min(b, lo + self.shard)]
         self._sumsq_excl = torch.zeros(1, dtype=torch.float32, device=dev)
-        if delta_param_gather is None:
-            delta_param_gather = bool(dp_comm is not None and getattr(dp_comm.policy, "dp_param_delta", False))
+        if delta_param_gather is None:   # follow the policy: does the router put a delta codec on this all-gather?
+            delta_param_gather = bool(dp_comm is not None and hasattr(dp_comm, "uses_delta_all_gather") and
+                                      dp_comm.uses_delta_all_gather(self.shard, flat_param.dtype))
         self.delta = bool(delta_param_gather) and self.dp > 1 and flat_param.is_cuda
         # with deltas the optimizer must not overwrite the previous parameters before they are subtracted
         self._new_shard = torch.empty_like(self.param_shard) if self.delta else self.param_shard
@@ -62,7 +64,7 @@ class DistributedOptimizer:
         """grad_scale multiplies every gradient before clipping (e.g. 1/dp for averaging)."""
         self.step_count += 1
         if self.dp > 1:
-            self.comm.reduce_scatter(self.flat_grad, self.grad_shard, role="dp")
+            self.comm.reduce_scatter(self.flat_grad, self.grad_shard)
         g = self.grad_shard
         fused.sum_squares(g, self._sumsq)
         for a, b in self._excl:
@@ -77,9 +79,10 @@ class DistributedOptimizer:
                         beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count,
                         grad_scale=self._coef)
         if self.delta:
-            self._delta_state = self.comm.all_gather_delta(self._new_shard, self.flat_param, state=self._delta_state)
+            res = self.comm.all_gather(self._new_shard, self.flat_param, state=self._delta_state)
+            self._delta_state = res[1] if isinstance(res, tuple) else None
         elif self.dp > 1:
-            self.comm.all_gather(self.param_shard, self.flat_param, role="dp")
+            self.comm.all_gather(self.param_shard, self.flat_param)
 
     # ---- checkpointing (per-rank shard; see coccl_b200.utils.checkpoint)
     def state_dict(self):
@@ -93,4 +96,4 @@ class DistributedOptimizer:
         self.param_shard.copy_(self.master)
         self._delta_state = None   # the replicas no longer match what the deltas were taken against: re-seed exactly
         if self.dp > 1:
-            self.comm.all_gather(self.param_shard, self.flat_param, role="dp")
+            self.comm.all_gather(self.param_shard, self.flat_param)

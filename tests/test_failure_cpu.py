@@ -161,23 +161,26 @@ def test_status_word_raises_peer_lost_with_decoded_fields():
 
 
 def test_tp_fusion_follows_the_policy():
-    """The one-kernel TP fusions quantise to FP8: they are taken only when the policy configures MX-FP8 for the TP
-    reduce-scatter and a codec for the TP all-gather, and only above the threshold."""
-    from coccl_b200.ops.codec import MXFP8, SDP4BIT_G128
-    from coccl_b200.parallel.comm import Communicator, Policy
+    """The one-kernel TP fusions quantise to FP8: they are taken only when the router, reading the policy file, answers
+    "compressed" for the tensor-parallel all-gather and names the MX-FP8 codec for the tensor-parallel reduce-scatter,
+    i.e. also only above the threshold."""
+    from coccl_b200.parallel.comm import NATIVE, Communicator, Policy, Router
 
     def fusable(policy, rows=4096, n=1024, width=1024):
         c = Communicator(None, None, policy, "tp")
         c.cuda, c.size, c._tp_sig = True, 2, object()   # pretend: CUDA group of two with its signal region open
+        c.router = Router.of(policy, 2)
         return c.tp_fusable(rows, n, width)
 
-    assert fusable(Policy(threshold_bytes=0))
-    p = Policy(threshold_bytes=0); p.codecs[("tp", "reduce_scatter")] = None
-    assert not fusable(p)
-    p = Policy(threshold_bytes=0); p.codecs[("tp", "all_gather")] = None
-    assert not fusable(p)
-    p = Policy(threshold_bytes=0); p.codecs[("tp", "reduce_scatter")] = SDP4BIT_G128
-    assert not fusable(p)
-    assert not fusable(Policy(threshold_bytes=4096 * 1024 * 2))       # bytes <= threshold stays native
-    assert fusable(Policy(threshold_bytes=4096 * 1024 * 2 - 1))
-    assert not fusable(Policy(enabled=False))
+    base = Policy.training(threshold_bytes=0)
+    assert fusable(base)
+    rs = '[training.tp.reduce_scatter.default]\ncompressor = "fp8block"\n'
+    ag = '[training.tp.all_gather.default]\ncompressor = "fp8block"\n'
+    assert rs in base.toml and ag in base.toml
+    assert not fusable(Policy(toml=base.toml.replace(rs, "")))          # no codec on the reduce-scatter
+    assert not fusable(Policy(toml=base.toml.replace(ag, "")))          # no codec on the all-gather
+    sdp = rs.replace('"fp8block"', '"sdp4bit"')
+    assert not fusable(Policy(toml=base.toml.replace(rs, sdp)))         # another codec: the unfused path serves it
+    assert not fusable(Policy.training(threshold_bytes=4096 * 1024 * 2))      # bytes <= threshold stays native
+    assert fusable(Policy.training(threshold_bytes=4096 * 1024 * 2 - 1))
+    assert not fusable(NATIVE)

@@ -17,15 +17,17 @@ def _collectives_worker(rank, world):
     from coccl_b200.ops import codec as C
     from coccl_b200.parallel.comm import Communicator, Policy
     dev = torch.device("cuda", rank)
-    pol = Policy(threshold_bytes=0, all_reduce_oneshot_max_bytes=1 << 16)
-    comm = Communicator(None, dev, pol, "default")
+    # normal-mode policy files: SDP4Bit on every collective, threshold 0; one forces the one-shot all-reduce, one the
+    # two-shot (the selector's choice between them is covered by the autotune test)
+    comm = Communicator(None, dev, Policy.normal("sdp4bit", threshold_bytes=0, all_reduce_algorithm="twoshot"), "default")
+    comm1 = Communicator(None, dev, Policy.normal("sdp4bit", threshold_bytes=0, all_reduce_algorithm="oneshot"), "oneshot")
     for dtype in (torch.float32, torch.bfloat16):
         for numel in (world * 4096, world * 300000):
             torch.manual_seed(100 + rank)
             x = (torch.randn(numel, device=dev) * 0.01).to(dtype)
             xs = [torch.empty_like(x) for _ in range(world)]
             dist.all_gather(xs, x)
-            cfg = pol.codec_for("default", "reduce_scatter")
+            cfg = C.SDP4BIT_G128
             c = numel // world
             # reduce-scatter
             out = torch.empty(c, dtype=dtype, device=dev)
@@ -45,18 +47,22 @@ def _collectives_worker(rank, world):
             ref = torch.cat([C.reference_roundtrip(xq, cfg, world).reshape(world, c)[rank] for xq in xs])
             bad = ((out.float() - ref.to(dtype).float()).abs() > 1e-5 + 2e-2 * ref.abs().max()).float().mean().item()
             assert bad < 5e-3, ("a2a", dtype, numel, bad)
-            # all-reduce (one-shot for the small size, two-shot for the large one)
-            y = x.clone()
-            comm.all_reduce(y)
+            # all-reduce, both algorithms
             exact = sum(xq.float() for xq in xs)
-            rel = ((y.float() - exact).norm() / exact.norm()).item()
-            assert rel < 0.3, ("ar", dtype, numel, rel)
-            ys = [torch.empty_like(y) for _ in range(world)]
-            dist.all_gather(ys, y)
-            assert all(torch.equal(ys[0], t) for t in ys) or numel * x.element_size() <= pol.all_reduce_oneshot_max_bytes
+            for cm, twoshot in ((comm, True), (comm1, False)):
+                y = x.clone()
+                cm.all_reduce(y)
+                rel = ((y.float() - exact).norm() / exact.norm()).item()
+                assert rel < 0.3, ("ar", dtype, numel, twoshot, rel)
+                if twoshot:  # every rank decodes the same re-encoded bytes
+                    ys = [torch.empty_like(y) for _ in range(world)]
+                    dist.all_gather(ys, y)
+                    assert all(torch.equal(ys[0], t) for t in ys)
     assert comm.stats["compressed_calls"] == 16 and comm.stats["native_calls"] == 0
-    assert comm.status() == 0
+    assert comm1.stats["compressed_calls"] == 4 and comm1.stats["native_calls"] == 0
+    assert comm.status() == 0 and comm1.status() == 0
     comm.close()
+    comm1.close()
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -73,7 +79,7 @@ def _trainer_worker(rank, world, tp, pp, dp, compress, delta=False):
     dev = torch.device("cuda", rank)
     cfg = GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)
     mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress,
-                policy=Policy(threshold_bytes=0, dp_param_delta=delta))
+                policy=Policy.training(threshold_bytes=0, dp_delta=delta))
     tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=3e-4)
     g = torch.Generator().manual_seed(5 + mesh.dp_rank)
     tok = torch.randint(0, cfg.vocab, (8, cfg.seq_len + 1), generator=g).pin_memory()
@@ -227,8 +233,21 @@ def _nvls_worker(rank, world):
     import torch.distributed as dist
     from coccl_b200.parallel.comm import Communicator, Policy
     dev = torch.device("cuda", rank)
-    comm = Communicator(None, dev, Policy(nvls_all_reduce=True, threshold_bytes=1 << 30), "nvls")
+    # a policy whose threshold keeps every call uncompressed, autotune on: the first all-reduce of a datatype times
+    # NCCL against the multimem kernel and the router picks per size from those numbers
+    comm = Communicator(None, dev, Policy.normal("sdp4bit", threshold_bytes=1 << 30, autotune=True), "nvls")
     used, bad = 0, []
+    # the kernel itself, whatever the selector prefers: when the fabric offers multicast it must serve the call
+    torch.manual_seed(3 + rank)
+    x = torch.randn(1 << 18, device=dev)
+    ref = x.clone()
+    dist.all_reduce(ref)
+    served = comm.all_reduce_nvls(x)
+    have_mc = comm._nvls is not None and comm._nvls["mc"] != 0
+    assert served == have_mc
+    if served:
+        assert torch.allclose(x, ref, atol=1e-5 * ref.abs().max().item(), rtol=0)
+        assert comm.stats["nvls_calls"] == 1
     for dtype, n in ((torch.float32, 4096 * world), (torch.bfloat16, 1 << 20), (torch.float32, (1 << 22) + 64 * world)):
         for it in range(2):
             torch.manual_seed(11 + rank + it)
@@ -241,7 +260,9 @@ def _nvls_worker(rank, world):
                 bad.append((str(dtype), n, it))
     used = comm.stats.get("nvls_calls", 0)
     if rank == 0:
-        print(f"nvls_calls={used} (0 means the fabric offers no multicast and NCCL served the calls)")
+        print(f"multicast available: {have_mc}; nvls_calls={used}; measured: {comm.routing_summary().get('measured')}")
+    if have_mc:   # the measurements were taken and handed to the router
+        assert any(r["what"] == "all_reduce_uncompressed" for r in comm.routing_summary()["measured"])
     # leave in order before judging the result: no rank exits while its memory is still bound to the multicast object
     torch.cuda.synchronize()
     dist.barrier()
@@ -264,7 +285,7 @@ def _lost_peer_worker(rank, world):
     import torch.distributed as dist
     from coccl_b200.parallel.comm import Communicator, PeerLost, Policy
     dev = torch.device("cuda", rank)
-    comm = Communicator(None, dev, Policy(threshold_bytes=0, timeout_ms=50.0), "default")
+    comm = Communicator(None, dev, Policy.normal("sdp4bit", threshold_bytes=0, all_reduce_algorithm="twoshot", timeout_ms=50.0), "default")
     x = torch.randn(world * 65536, device=dev)
     comm.all_reduce(x.clone())          # both ranks: maps the peer memory, epoch 1
     comm.post_status_read()
