@@ -145,6 +145,65 @@ ncclResult_t cocclApiCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id,
   return ncclSuccess;
 }
 
+// ncclCommInitRankConfig: the configuration of NCCL 2.21 (blocking mode, CGA cluster size, CTA limits, network name,
+// split sharing; src/nccl.h.in:84-120) tunes NCCL's own kernels; the communicator here is always created blocking.
+ncclResult_t cocclApiCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank, void* /*config*/) {
+  return cocclApiCommInitRank(comm, nranks, id, rank);
+}
+
+// ncclCommInitAll: one process, one thread, ndev communicators (src/init.cc:1846 of the reference). The collective
+// start-up measurements of the autotuner need every rank to run at once, which a single thread cannot do: the
+// communicators created here select algorithms by heuristics (or by what the policy file forces).
+ncclResult_t cocclApiCommInitAll(ncclComm_t* comms, int ndev, const int* devlist) {
+  if (comms == nullptr || ndev <= 0) return ncclInvalidArgument;
+  ncclUniqueId id;
+  ncclResult_t r = ncclTransport().uniqueId(&id);
+  if (r != ncclSuccess) return r;
+  int previous = 0;
+  cudaGetDevice(&previous);
+  std::vector<Comm*> made((size_t)ndev, nullptr);
+  r = ncclTransport().groupStart();
+  for (int i = 0; i < ndev && r == ncclSuccess; ++i) {
+    if (cudaSetDevice(devlist ? devlist[i] : i) != cudaSuccess) { r = ncclUnhandledCudaError; break; }
+    r = ncclTransport().initRank(&made[(size_t)i], ndev, id, i);
+  }
+  ncclResult_t e = ncclTransport().groupEnd();
+  if (r == ncclSuccess) r = e;
+  for (int i = 0; i < ndev; ++i) {
+    if (made[(size_t)i] == nullptr) continue;
+    if (r == ncclSuccess) {
+      runtimeStart(made[(size_t)i]);
+      comms[i] = reinterpret_cast<ncclComm_t>(made[(size_t)i]);
+    } else {
+      ncclTransport().destroy(made[(size_t)i]);
+    }
+  }
+  cudaSetDevice(previous);
+  return r;
+}
+
+ncclResult_t cocclApiGetVersion(int* version) { return ncclTransport().version(version); }
+ncclResult_t cocclApiMemAlloc(void** ptr, size_t size) { return ncclTransport().memAlloc(ptr, size); }
+ncclResult_t cocclApiMemFree(void* ptr) { return ncclTransport().memFree(ptr); }
+ncclResult_t cocclApiCommRegister(ncclComm_t comm, void* buff, size_t size, void** handle) {
+  if (!comm) return ncclInvalidArgument;
+  return ncclTransport().commRegister(unwrap(comm), buff, size, handle);
+}
+ncclResult_t cocclApiCommDeregister(ncclComm_t comm, void* handle) {
+  if (!comm) return ncclInvalidArgument;
+  return ncclTransport().commDeregister(unwrap(comm), handle);
+}
+// A pre-multiplied sum is not the plain sum the codecs reduce: calls that use it are left native by the router
+// (rule "sum only", coccl_runtime.cc:159-167); the operator itself lives in the native library.
+ncclResult_t cocclApiRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, int residence, ncclComm_t comm) {
+  if (!comm || !op) return ncclInvalidArgument;
+  return ncclTransport().redOpCreatePreMulSum(op, scalar, datatype, residence, unwrap(comm));
+}
+ncclResult_t cocclApiRedOpDestroy(ncclRedOp_t op, ncclComm_t comm) {
+  if (!comm) return ncclInvalidArgument;
+  return ncclTransport().redOpDestroy(op, unwrap(comm));
+}
+
 ncclResult_t cocclApiCommDestroy(ncclComm_t comm) {
   Comm* c = unwrap(comm);
   if (c == nullptr) return ncclSuccess;
@@ -216,6 +275,10 @@ ncclResult_t cocclApiBroadcast(const void* s, void* r, size_t n, ncclDataType_t 
   if (!c) return ncclInvalidArgument;
   if (globalRuntime().groupDepth() > 0) ++tlsNativeInGroup;
   return ncclTransport().broadcast(unwrap(c), s, r, n, t, root, st);
+}
+// ncclBcast: the in-place form of ncclBroadcast
+ncclResult_t cocclApiBcast(void* buff, size_t n, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st) {
+  return cocclApiBroadcast(buff, buff, n, t, root, c, st);
 }
 ncclResult_t cocclApiReduce(const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t c, cudaStream_t st) {
   if (!c) return ncclInvalidArgument;

@@ -17,6 +17,16 @@ extern "C" {
 
 ncclResult_t cocclApiGetUniqueId(ncclUniqueId* id);
 ncclResult_t cocclApiCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank);
+ncclResult_t cocclApiCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank, void* config);
+ncclResult_t cocclApiCommInitAll(ncclComm_t* comms, int ndev, const int* devlist);
+ncclResult_t cocclApiGetVersion(int* version);
+ncclResult_t cocclApiMemAlloc(void** ptr, size_t size);
+ncclResult_t cocclApiMemFree(void* ptr);
+ncclResult_t cocclApiCommRegister(ncclComm_t comm, void* buff, size_t size, void** handle);
+ncclResult_t cocclApiCommDeregister(ncclComm_t comm, void* handle);
+ncclResult_t cocclApiRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, int residence, ncclComm_t comm);
+ncclResult_t cocclApiRedOpDestroy(ncclRedOp_t op, ncclComm_t comm);
+ncclResult_t cocclApiBcast(void* buff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream);
 ncclResult_t cocclApiCommDestroy(ncclComm_t comm);
 ncclResult_t cocclApiCommFinalize(ncclComm_t comm);
 ncclResult_t cocclApiCommAbort(ncclComm_t comm);

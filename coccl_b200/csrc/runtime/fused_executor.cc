@@ -57,6 +57,7 @@ struct FusedState {
   unsigned epoch = 0;
   bool broken = false;   // agreed by all ranks: the staged pipeline serves this communicator
   unsigned int* hostStatus = nullptr;  // pinned copy of the status word, refreshed after every fused launch
+  std::mutex mutex;  // one call at a time per communicator; different communicators (threads of one process) run in parallel
 };
 
 std::mutex gMutex;
@@ -99,9 +100,16 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
                        codec->plugin()->fusedQuery(codec->config(), (int)info.datatype, &kc) == 1 && cocclkTileCodecSupported(&kc);
   if (!fusable) { ++stagedCalls; return StagedExecutor::execute(rt, call); }
 
-  std::lock_guard<std::mutex> lock(gMutex);
-  FusedState& st = gStates[comm];
-  if (st.broken) { ++stagedCalls; return StagedExecutor::execute(rt, call); }
+  FusedState* stp;
+  {
+    std::lock_guard<std::mutex> lock(gMutex);  // guards the table only: map nodes never move
+    stp = &gStates[comm];
+  }
+  FusedState& st = *stp;
+  // The set-up below blocks on the other ranks (host-level exchange). Ranks that live in one process as threads must
+  // therefore not share a lock across it: each communicator has its own.
+  std::unique_lock<std::mutex> lock(st.mutex);
+  if (st.broken) { lock.unlock(); ++stagedCalls; return StagedExecutor::execute(rt, call); }
   const int n = comm->nRanks;
   const long count = (op == 0 || op == 1 || op == 2) ? (long)info.count : (op == 4 ? (long)(info.count / (size_t)n) : (long)info.count);
   const long slot = cocclkSlotBytes(&kc, count);
@@ -131,6 +139,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
       st.workspace.close(api, x);
       st.signals.close(api, x);
       st.half = 0;
+      lock.unlock();
       ++stagedCalls;
       return StagedExecutor::execute(rt, call);
     }
@@ -174,8 +183,9 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
 unsigned int FusedExecutor::asyncStatus(Comm* comm) {
   std::lock_guard<std::mutex> lock(gMutex);
   auto it = gStates.find(comm);
-  if (it == gStates.end() || it->second.hostStatus == nullptr) return 0;
-  return *static_cast<volatile unsigned int*>(it->second.hostStatus);
+  if (it == gStates.end()) return 0;
+  volatile unsigned int* p = it->second.hostStatus;   // set once, under the communicator's lock, never freed before release
+  return p == nullptr ? 0 : *p;
 }
 
 }  // namespace coccl

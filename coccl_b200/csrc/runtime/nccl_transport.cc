@@ -32,6 +32,14 @@ struct NcclApi {
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  // optional entry points (forwarded when the library has them)
+  ncclResult_t (*GetVersion)(int*) = nullptr;
+  ncclResult_t (*MemAlloc)(void**, size_t) = nullptr;
+  ncclResult_t (*MemFree)(void*) = nullptr;
+  ncclResult_t (*CommRegister)(void*, void*, size_t, void**) = nullptr;
+  ncclResult_t (*CommDeregister)(void*, void*) = nullptr;
+  ncclResult_t (*RedOpCreatePreMulSum)(ncclRedOp_t*, void*, ncclDataType_t, int, void*) = nullptr;
+  ncclResult_t (*RedOpDestroy)(ncclRedOp_t, void*) = nullptr;
   bool ok = false;
 };
 
@@ -53,6 +61,8 @@ NcclApi& api() {
     LOAD(GetUniqueId); LOAD(CommInitRank); LOAD(CommDestroy); LOAD(CommAbort); LOAD(CommSplit); LOAD(CommGetAsyncError); LOAD(CommCount); LOAD(CommUserRank);
     LOAD(AllReduce); LOAD(ReduceScatter); LOAD(AllGather); LOAD(Broadcast); LOAD(Reduce); LOAD(Send); LOAD(Recv);
     LOAD(GroupStart); LOAD(GroupEnd); LOAD(GetErrorString);
+    LOAD(GetVersion); LOAD(MemAlloc); LOAD(MemFree); LOAD(CommRegister); LOAD(CommDeregister);
+    LOAD(RedOpCreatePreMulSum); LOAD(RedOpDestroy);
 #undef LOAD
     a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.ReduceScatter && a.AllGather && a.Send &&
            a.Recv && a.GroupStart && a.GroupEnd;
@@ -189,6 +199,39 @@ ncclResult_t NcclTransport::abort(Comm* c) {
   c->native = nullptr;
   delete c;
   return r;
+}
+
+ncclResult_t NcclTransport::version(int* v) {
+  if (v == nullptr) return ncclInvalidArgument;
+  if (api().ok && api().GetVersion) return api().GetVersion(v);
+  *v = 22105;  // the API level this library implements (NCCL 2.21.5, the reference's base)
+  return ncclSuccess;
+}
+ncclResult_t NcclTransport::memAlloc(void** p, size_t bytes) {
+  if (p == nullptr) return ncclInvalidArgument;
+  if (api().ok && api().MemAlloc) return api().MemAlloc(p, bytes);
+  return cudaMalloc(p, bytes) == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+ncclResult_t NcclTransport::memFree(void* p) {
+  if (api().ok && api().MemFree) return api().MemFree(p);
+  return cudaFree(p) == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+ncclResult_t NcclTransport::commRegister(Comm* c, void* buff, size_t size, void** handle) {
+  if (api().ok && api().CommRegister && c->native) return api().CommRegister(c->native, buff, size, handle);
+  if (handle) *handle = nullptr;  // registration is an optimisation hint: without it calls still work
+  return ncclSuccess;
+}
+ncclResult_t NcclTransport::commDeregister(Comm* c, void* handle) {
+  if (api().ok && api().CommDeregister && c->native) return api().CommDeregister(c->native, handle);
+  return ncclSuccess;
+}
+ncclResult_t NcclTransport::redOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t t, int residence, Comm* c) {
+  if (api().ok && api().RedOpCreatePreMulSum && c->native) return api().RedOpCreatePreMulSum(op, scalar, t, residence, c->native);
+  return ncclInvalidUsage;
+}
+ncclResult_t NcclTransport::redOpDestroy(ncclRedOp_t op, Comm* c) {
+  if (api().ok && api().RedOpDestroy && c->native) return api().RedOpDestroy(op, c->native);
+  return ncclInvalidUsage;
 }
 
 NcclTransport& ncclTransport() {

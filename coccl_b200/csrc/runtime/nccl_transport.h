@@ -14,6 +14,14 @@ class NcclTransport : public Transport {
   ncclResult_t abort(Comm* c);
   ncclResult_t broadcast(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, int root, cudaStream_t st);
   ncclResult_t reduce(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, cudaStream_t st);
+  // pass-throughs of the rest of the NCCL surface (user-defined reductions, registration, allocation, version)
+  ncclResult_t version(int* v);
+  ncclResult_t memAlloc(void** p, size_t bytes);
+  ncclResult_t memFree(void* p);
+  ncclResult_t commRegister(Comm* c, void* buff, size_t size, void** handle);
+  ncclResult_t commDeregister(Comm* c, void* handle);
+  ncclResult_t redOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t t, int residence, Comm* c);
+  ncclResult_t redOpDestroy(ncclRedOp_t op, Comm* c);
 
   ncclResult_t allGather(Comm* c, const void* send, void* recv, size_t sendCount, ncclDataType_t t, cudaStream_t s) override;
   ncclResult_t reduceScatter(Comm* c, const void* send, void* recv, size_t recvCount, ncclDataType_t t, ncclRedOp_t op, cudaStream_t s) override;

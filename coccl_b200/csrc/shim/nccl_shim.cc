@@ -27,6 +27,16 @@ COCCL_ALIAS2(ncclResult_t, Send, (const void* s, size_t n, ncclDataType_t t, int
 COCCL_ALIAS2(ncclResult_t, Recv, (void* r, size_t n, ncclDataType_t t, int p, ncclComm_t c, cudaStream_t st), (r, n, t, p, c, st))
 COCCL_ALIAS2(ncclResult_t, Broadcast, (const void* s, void* r, size_t n, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st), (s, r, n, t, root, c, st))
 COCCL_ALIAS2(ncclResult_t, Reduce, (const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t c, cudaStream_t st), (s, r, n, t, op, root, c, st))
+COCCL_ALIAS2(ncclResult_t, GetVersion, (int* v), (v))
+COCCL_ALIAS2(ncclResult_t, CommInitAll, (ncclComm_t * c, int n, const int* devs), (c, n, devs))
+COCCL_ALIAS2(ncclResult_t, CommInitRankConfig, (ncclComm_t * c, int n, ncclUniqueId id, int r, void* cfg), (c, n, id, r, cfg))
+COCCL_ALIAS2(ncclResult_t, MemAlloc, (void** p, size_t n), (p, n))
+COCCL_ALIAS2(ncclResult_t, MemFree, (void* p), (p))
+COCCL_ALIAS2(ncclResult_t, CommRegister, (ncclComm_t c, void* b, size_t n, void** h), (c, b, n, h))
+COCCL_ALIAS2(ncclResult_t, CommDeregister, (ncclComm_t c, void* h), (c, h))
+COCCL_ALIAS2(ncclResult_t, RedOpCreatePreMulSum, (ncclRedOp_t * op, void* scalar, ncclDataType_t t, int residence, ncclComm_t c), (op, scalar, t, residence, c))
+COCCL_ALIAS2(ncclResult_t, RedOpDestroy, (ncclRedOp_t op, ncclComm_t c), (op, c))
+COCCL_ALIAS2(ncclResult_t, Bcast, (void* b, size_t n, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st), (b, n, t, root, c, st))
 COCCL_ALIAS2(ncclResult_t, GroupStart, (void), ())
 COCCL_ALIAS2(ncclResult_t, GroupEnd, (void), ())
 
