@@ -9,7 +9,7 @@
 //     median gap);
 //   3 evidence scoring per communicator over the detected iterations.
 // Thresholds follow src/coccl-extend/core/training/coccl_training_classifier.cc:13-18 and :500-716:
-// role evidence >= 0.60, overlap pattern >= 0.80, conflict margin 0.15, PP when the p2p share is
+// role evidence >= 0.60, overlap pattern (reduce-scatter buckets of two or more sizes repeating) >= 0.80, conflict margin 0.15, PP when the p2p share is
 // >= 0.70 and the two busiest peers carry >= 0.80 of it, all-gather/reduce-scatter byte ratio within
 // 20 % of 0.5 or 0.25, stable pattern = best per-iteration signature support >= 0.60, TP needs >= 2
 // collectives per iteration on one node, a sparse node-local DP tail needs median bytes >= 1.25x

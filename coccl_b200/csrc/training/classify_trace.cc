@@ -23,22 +23,50 @@ struct CommStats {
   size_t medianBytes = 0;
   double patternSupport = 0;     // share of iterations showing the most common (op, bytes) sequence
   bool stable = false;
-  double overlapSupport = 0;     // share of iterations whose reduce-scatters are interleaved with other traffic
+  double overlapSupport = 0;     // share of iterations showing the most common pattern with one op in >= 2 sizes (buckets)
   double ratioSupport = 0;       // share of iterations with AG/RS bytes near 0.5 or 0.25
   double agToRs = 0;
 };
+
+// One iteration as one communicator sees it.
+struct IterationView {
+  std::vector<uint64_t> pattern;         // (op, bytes) of its collectives, in order
+  uint64_t calls = 0;                    // collectives and point-to-point
+  double agBytes = 0, rsBytes = 0;
+  bool multiSize = false;                // some operation appears with two or more distinct sizes (gradient buckets)
+};
+
+IterationView viewOf(uint64_t id, const std::vector<TraceEvent>& ev, const IterationRange& it) {
+  IterationView v;
+  std::set<size_t> sizes[3];
+  const size_t end = std::min(it.end, ev.size());
+  for (size_t i = it.begin; i < end; ++i) {
+    const TraceEvent& e = ev[i];
+    if (e.commId != id) continue;
+    ++v.calls;
+    if (!isCollective(e.op)) continue;
+    v.pattern.push_back(((uint64_t)e.op << 56) ^ (uint64_t)e.logicalBytes);
+    sizes[(int)e.op].insert(e.logicalBytes);
+    if (e.op == TraceOp::AllGather) v.agBytes += (double)e.logicalBytes;
+    if (e.op == TraceOp::ReduceScatter) v.rsBytes += (double)e.logicalBytes;
+  }
+  for (const std::set<size_t>& s : sizes) v.multiSize = v.multiSize || s.size() >= 2;
+  return v;
+}
+
+bool nearRatio(double r, double target) { return std::fabs(r - target) <= 0.2 * target; }
 
 CommStats buildStats(const TraceComm& comm, const std::vector<TraceEvent>& ev, const std::vector<IterationRange>& its) {
   CommStats s;
   s.comm = comm;
   std::map<int, uint64_t> peers;
   std::vector<size_t> sizes;
+  // whole trace (a partial iteration after the last boundary counts as observed calls, nothing else)
   for (const TraceEvent& e : ev) {
     if (e.commId != comm.id) continue;
     ++s.calls;
-    sizes.push_back(e.logicalBytes);
     if (isP2p(e.op)) { ++s.p2p; ++peers[e.peer]; }
-    if (isCollective(e.op)) ++s.coll;
+    if (isCollective(e.op)) { ++s.coll; sizes.push_back(e.logicalBytes); }
     if (e.op == TraceOp::AllGather) ++s.ag;
     if (e.op == TraceOp::ReduceScatter) ++s.rs;
     if (e.op == TraceOp::AllReduce) ++s.ar;
@@ -46,86 +74,96 @@ CommStats buildStats(const TraceComm& comm, const std::vector<TraceEvent>& ev, c
   if (s.calls == 0) return s;
   s.p2pShare = (double)s.p2p / (double)s.calls;
   if (s.p2p) {
-    std::vector<uint64_t> c;
-    for (auto& kv : peers) c.push_back(kv.second);
-    std::sort(c.rbegin(), c.rend());
-    const uint64_t top2 = c[0] + (c.size() > 1 ? c[1] : 0);
-    s.peerConcentration = (double)top2 / (double)s.p2p;
+    uint64_t first = 0, second = 0;
+    for (auto& kv : peers) {
+      if (kv.second > first) { second = first; first = kv.second; }
+      else if (kv.second > second) second = kv.second;
+    }
+    s.peerConcentration = (double)(first + second) / (double)s.p2p;
   }
-  std::sort(sizes.begin(), sizes.end());
-  s.medianBytes = sizes[sizes.size() / 2];
+  if (!sizes.empty()) { std::sort(sizes.begin(), sizes.end()); s.medianBytes = sizes[sizes.size() / 2]; }
   if (its.empty()) return s;
 
-  std::map<std::vector<uint64_t>, int> signatures;
-  int overlapped = 0, ratioHits = 0, withCalls = 0;
-  uint64_t inIterations = 0;
+  std::map<std::vector<uint64_t>, int> all, buckets;
+  std::vector<uint64_t> perIteration;
   std::vector<double> ratios;
   for (const IterationRange& it : its) {
-    std::vector<uint64_t> sig;
-    long firstRs = -1, lastRs = -1;
-    int rsCount = 0;
-    double agBytes = 0, rsBytes = 0;
-    for (size_t i = it.begin; i < it.end && i < ev.size(); ++i) {
-      const TraceEvent& e = ev[i];
-      if (e.commId != comm.id) continue;
-      ++inIterations;
-      sig.push_back(((uint64_t)e.op << 56) ^ (uint64_t)e.logicalBytes);
-      if (e.op == TraceOp::ReduceScatter) { if (firstRs < 0) firstRs = (long)i; lastRs = (long)i; ++rsCount; rsBytes += (double)e.logicalBytes; }
-      if (e.op == TraceOp::AllGather) agBytes += (double)e.logicalBytes;
+    const IterationView v = viewOf(comm.id, ev, it);
+    perIteration.push_back(v.calls);
+    if (!v.pattern.empty()) {
+      ++all[v.pattern];
+      if (v.multiSize) ++buckets[v.pattern];
     }
-    if (!sig.empty()) ++withCalls;
-    ++signatures[sig];
-    if (rsCount >= 2) {
-      bool foreign = false;
-      for (long i = firstRs; i <= lastRs && !foreign; ++i) foreign = ev[(size_t)i].commId != comm.id;
-      if (foreign) ++overlapped;
-    }
-    if (agBytes > 0 && rsBytes > 0) {
-      const double r = agBytes / rsBytes;
-      ratios.push_back(r);
-      if (std::fabs(r - 0.5) <= 0.2 * 0.5 || std::fabs(r - 0.25) <= 0.2 * 0.25) ++ratioHits;
+    if (v.agBytes > 0 && v.rsBytes > 0) {
+      const double r = v.agBytes / v.rsBytes;
+      if (nearRatio(r, 0.5) || nearRatio(r, 0.25)) ratios.push_back(r);
     }
   }
   const double n = (double)its.size();
-  s.callsPerIteration = (double)inIterations / n;
-  int best = 0;
-  for (auto& kv : signatures)
-    if (!kv.first.empty()) best = std::max(best, kv.second);
+  std::sort(perIteration.begin(), perIteration.end());
+  s.callsPerIteration = (double)perIteration[perIteration.size() / 2];
+  int best = 0, bestBuckets = 0;
+  for (auto& kv : all) best = std::max(best, kv.second);
+  for (auto& kv : buckets) bestBuckets = std::max(bestBuckets, kv.second);
   s.patternSupport = (double)best / n;
-  s.stable = s.patternSupport >= kStablePattern && withCalls > 0;
-  s.overlapSupport = (double)overlapped / n;
-  s.ratioSupport = (double)ratioHits / n;
+  s.stable = s.coll != 0 && s.patternSupport >= kStablePattern;
+  s.overlapSupport = (double)bestBuckets / n;
+  s.ratioSupport = (double)ratios.size() / n;
   if (!ratios.empty()) { std::sort(ratios.begin(), ratios.end()); s.agToRs = ratios[ratios.size() / 2]; }
   return s;
 }
 
-// Share of iterations in which the `tp` communicator's burst comes before the `dp` communicator's
-// traffic ends: a data-parallel flow trails the tensor-parallel one (gradient buckets drain last).
+// Share of iterations in which the `tp` flow sits inside or right before the `dp` flow. Two shapes count:
+//   bracket: a dp all-gather, then at least two tp collectives, then a dp reduce-scatter (ZeRO / FSDP: parameters
+//            gathered before the layers run, gradients scattered after);
+//   tail:    at least two of the (up to eight) collectives that precede a dp reduce-scatter or all-reduce
+//            belong to tp (gradient buckets drain behind the last layers).
 double orderRelation(uint64_t dp, uint64_t tp, const std::vector<TraceEvent>& ev, const std::vector<IterationRange>& its) {
   if (its.empty()) return 0;
   int ok = 0;
   for (const IterationRange& it : its) {
-    long lastDp = -1, lastTp = -1, firstDp = -1, firstTp = -1;
-    for (size_t i = it.begin; i < it.end && i < ev.size(); ++i) {
-      if (ev[i].commId == dp) { if (firstDp < 0) firstDp = (long)i; lastDp = (long)i; }
-      if (ev[i].commId == tp) { if (firstTp < 0) firstTp = (long)i; lastTp = (long)i; }
+    const size_t end = std::min(it.end, ev.size());
+    bool bracket = false, tail = false;
+    int sinceGather = -1;  // tp collectives since the last dp all-gather; -1 before any
+    for (size_t i = it.begin; i < end && !bracket; ++i) {
+      const TraceEvent& e = ev[i];
+      if (e.commId == dp && e.op == TraceOp::AllGather) { if (sinceGather < 0) sinceGather = 0; }
+      else if (e.commId == tp && isCollective(e.op)) { if (sinceGather >= 0) ++sinceGather; }
+      else if (e.commId == dp && e.op == TraceOp::ReduceScatter && sinceGather >= 0) {
+        if (sinceGather >= 2) bracket = true;
+        else sinceGather = -1;  // this gather's window closed without a burst; a later gather opens a new one
+      }
     }
-    if (lastDp >= 0 && lastTp >= 0 && firstTp < firstDp && lastDp > lastTp) ++ok;
+    if (!bracket) {
+      std::vector<uint64_t> recent;  // communicator of the last eight collectives
+      for (size_t i = it.begin; i < end && !tail; ++i) {
+        const TraceEvent& e = ev[i];
+        if (!isCollective(e.op)) continue;
+        if (e.commId == dp && (e.op == TraceOp::ReduceScatter || e.op == TraceOp::AllReduce))
+          tail = std::count(recent.begin(), recent.end(), tp) >= 2;
+        recent.push_back(e.commId);
+        if (recent.size() > 8) recent.erase(recent.begin());
+      }
+    }
+    if (bracket || tail) ++ok;
   }
   return (double)ok / (double)its.size();
 }
 
-// Share of iterations in which the communicator's collectives sit between pipeline transfers.
+// Share of iterations in which at least two of the communicator's collectives sit between two pipeline transfers.
 double ppInterior(uint64_t id, const std::set<uint64_t>& pp, const std::vector<TraceEvent>& ev, const std::vector<IterationRange>& its) {
   if (its.empty() || pp.empty()) return 0;
   int ok = 0;
   for (const IterationRange& it : its) {
-    bool seenPp = false, burstAfterPp = false, closed = false;
-    for (size_t i = it.begin; i < it.end && i < ev.size(); ++i) {
-      if (pp.count(ev[i].commId)) { if (burstAfterPp) closed = true; seenPp = true; }
-      else if (ev[i].commId == id && seenPp) burstAfterPp = true;
+    const size_t end = std::min(it.end, ev.size());
+    int burst = -1;  // collectives of `id` since the last transfer; -1 before the first transfer
+    bool found = false;
+    for (size_t i = it.begin; i < end && !found; ++i) {
+      const TraceEvent& e = ev[i];
+      if (pp.count(e.commId) && isP2p(e.op)) { found = burst >= 2; burst = 0; }
+      else if (burst >= 0 && e.commId == id && isCollective(e.op)) ++burst;
     }
-    if (closed) ++ok;
+    if (found) ++ok;
   }
   return (double)ok / (double)its.size();
 }
