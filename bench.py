@@ -238,6 +238,8 @@ def main():
                        "seq_len": cfg.seq_len, "micro_batch": 2, "parallelism": f"tp{tp}pp{pp}dp{dp}",
                        "optimizer": "AdamW, fp32 master weights, sharded over DP",
                        "compressed_collectives": (n > 1 and not args.no_compress),
+                       # hash of the effective policy (the TOML the routing session parsed) per communicator of rank 0
+                       "policy_hash": {c.name: c.routing_summary().get("policy_hash", "native") for c in trainer._comms()},
                        "l2": "working set per step (>100 GB) is far larger than L2; no explicit flush"},
             "model_tflops_per_gpu": cfg.flops_per_token() * value / n / 1e12,
             "published_reference_tflops_per_gpu_32xh800": 163.2,

@@ -339,6 +339,28 @@ void cocclApiGetStats(cocclApiStats* out) {
   out->stagedCalls = state().executor ? state().executor->stagedCalls : 0;
 }
 
+ncclResult_t cocclApiCommTrainingRole(ncclComm_t comm, cocclApiTrainingRole* out) {
+  if (comm == nullptr || out == nullptr) return ncclInvalidArgument;
+  *out = cocclApiTrainingRole{};
+  ApiState& s = state();
+  std::lock_guard<std::mutex> lock(s.mutex);
+  if (s.assist == nullptr) return ncclInvalidUsage;
+  Comm* c = unwrap(comm);
+  Classification k;
+  uint64_t activation = 0;
+  if (!s.assist->query(c, &k, &activation)) return ncclSuccess;  // nothing decided yet
+  out->role = (int)k.role;
+  out->candidate = (int)k.candidate;
+  out->committed = 1;
+  out->active = s.assist->roleOf(c) == k.role && k.role != Role::Unknown ? 1 : 0;
+  out->confidence = k.confidence;
+  out->callsPerIteration = k.callsPerIteration;
+  out->agToRsRatio = k.agToRsRatio;
+  out->observedCalls = k.observedCalls;
+  out->activationCall = activation;
+  return ncclSuccess;
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------------

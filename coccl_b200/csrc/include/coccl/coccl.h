@@ -69,6 +69,17 @@ typedef struct cocclApiStats {
 } cocclApiStats;
 void cocclApiGetStats(cocclApiStats* out);
 
+// Training mode: what the classifier decided for this communicator. `committed` is 0 until a decision exists (all
+// other fields are then zero); `active` turns 1 at the call from which every rank routes by the role. Roles:
+// 0 normal, 1 data, 2 tensor, 3 pipeline parallel, 4 unknown (stays native). Outside training mode the call
+// returns ncclInvalidUsage.
+typedef struct cocclApiTrainingRole {
+  int role, candidate, committed, active;
+  double confidence, callsPerIteration, agToRsRatio;
+  unsigned long long observedCalls, activationCall;
+} cocclApiTrainingRole;
+ncclResult_t cocclApiCommTrainingRole(ncclComm_t comm, cocclApiTrainingRole* out);
+
 #ifdef __cplusplus
 }
 #endif

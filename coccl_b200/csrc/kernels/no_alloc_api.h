@@ -15,6 +15,8 @@ extern "C" {
 
 // Largest number of columns the built-in scratch can serve (any number of rows).
 #define COCCLK_NOALLOC_MAX_COLS 16384
+// Device indices the per-device address cache covers.
+#define COCCLK_NOALLOC_MAX_DEVICES 64
 
 // out[n] (+)= sum over m of x[m][n], x is a row-major bf16 matrix [M, N], out is fp32 [N].
 //
@@ -25,7 +27,9 @@ extern "C" {
 //    with COCCLK_NOALLOC_TOO_LARGE and a message retrievable by cocclkNoAllocLastError().
 //  * The first call on each device looks up the device address of the scratch array
 //    (cudaGetSymbolAddress, with that device current) and caches it. Make that first
-//    call before starting any stream capture on that device.
+//    call before starting any stream capture on that device. The cache has one slot per
+//    device index 0..COCCLK_NOALLOC_MAX_DEVICES-1; a call with a higher index current is
+//    refused with COCCLK_NOALLOC_BAD_SHAPE and a message (nothing is launched).
 //  * All calls on a device share the one scratch array, which keeps whatever the last
 //    call left in it. Nothing in it needs to start at zero (every partial sum that is
 //    read is written first by the same call), but two calls that overlap on the GPU

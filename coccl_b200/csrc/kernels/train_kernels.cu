@@ -654,7 +654,7 @@ extern "C" int cocclkAccumBf16(float* dst, const void* src, long n, int accumula
 namespace coccl {
 constexpr int kNoAllocRows = 64;  // == upper bound of cocclkColSumBlocks
 static __device__ __align__(256) float gColSumScratch[kNoAllocRows * COCCLK_NOALLOC_MAX_COLS];
-static float* gColSumScratchAddr[64];
+static float* gColSumScratchAddr[COCCLK_NOALLOC_MAX_DEVICES];
 static std::mutex gNoAllocMutex;
 static thread_local char gNoAllocError[256] = "";
 }  // namespace coccl
@@ -677,8 +677,9 @@ extern "C" int cocclkColSumNoAlloc(const void* x, float* out, int accumulate, in
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) {
-    snprintf(gNoAllocError, sizeof(gNoAllocError), "cocclkColSumNoAlloc: device index %d out of range", dev);
+  if (dev < 0 || dev >= COCCLK_NOALLOC_MAX_DEVICES) {
+    snprintf(gNoAllocError, sizeof(gNoAllocError), "cocclkColSumNoAlloc: device index %d is outside the address cache (0..%d)", dev,
+             COCCLK_NOALLOC_MAX_DEVICES - 1);
     return COCCLK_NOALLOC_BAD_SHAPE;
   }
   float* scratch;

@@ -114,7 +114,7 @@ bool TrainingAssist::query(Comm* comm, Classification* out, uint64_t* activation
   std::lock_guard<std::mutex> lock(mutex_);
   auto it = entries_.find(comm);
   if (it == entries_.end() || !it->second.classification.committed) return false;
-  if (out) *out = it->second.classification;
+  if (out) { *out = it->second.classification; out->observedCalls = it->second.observedCalls; }  // calls seen so far, not only those in the trace
   if (activationCall) *activationCall = it->second.activationCall;
   return true;
 }
