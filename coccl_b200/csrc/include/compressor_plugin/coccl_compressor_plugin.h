@@ -190,8 +190,18 @@ class ConfigReader {
       : values_(values), error_(error), errorCapacity_(errorCapacity) {
     if (error_ && errorCapacity_) error_[0] = '\0';
     const size_t n = values_ ? values_->count : 0;
+    if (n != 0 && values_->pairs == nullptr) { fail("?", "list is missing although its count is not zero"); return; }
     used_ = n ? new (std::nothrow) bool[n]() : nullptr;
-    if (n && used_ == nullptr) { failed_ = true; }
+    if (n && used_ == nullptr) { fail("?", "list could not be indexed (out of memory)"); return; }
+    // The list itself must be sound before any key is read: every entry names a key and carries a value, and
+    // no key appears twice (the second one would silently lose against the first).
+    for (size_t i = 0; i < n && !failed_; ++i) {
+      const char* key = values_->pairs[i].key;
+      if (key == nullptr || key[0] == '\0') { fail("?", "has no name"); break; }
+      if (values_->pairs[i].value == nullptr) { fail(key, "has no value"); break; }
+      for (size_t j = 0; j < i; ++j)
+        if (strcmp(values_->pairs[j].key, key) == 0) { fail(key, "is given twice"); break; }
+    }
   }
   ~ConfigReader() { delete[] used_; }
   ConfigReader(const ConfigReader&) = delete;
@@ -203,9 +213,12 @@ class ConfigReader {
     if (found && !failed_ && !parse(text, &out)) fail(key, "has an invalid value");
     return *this;
   }
+  // Range-checked read. The default the caller put into `out` is checked too, so a plugin cannot ship a default
+  // outside its own range; bounds given the wrong way round or (for floats) not finite are a plugin bug and fail.
   template <typename Value> ConfigReader& get(const char* key, Value& out, Value lo, Value hi) {
+    if (!failed_ && (!finite(lo) || !finite(hi) || hi < lo)) { fail(key, "was declared with an invalid range"); return *this; }
     get(key, out);
-    if (!failed_ && (out < lo || out > hi)) fail(key, "is out of range");
+    if (!failed_ && !(out >= lo && out <= hi)) fail(key, "is out of range");
     return *this;
   }
   template <typename Enum, size_t N> ConfigReader& getEnum(const char* key, Enum& out, const EnumEntry<Enum> (&table)[N]) {
@@ -266,9 +279,14 @@ class ConfigReader {
     errno = 0;
     char* end = nullptr;
     double v = strtod(text, &end);
-    if (errno || *end) return false;
+    if (errno || end == text || *end) return false;
+    // "nan", "inf" and values the target type cannot hold are not options a codec can work with
+    if (!(v == v) || v > (double)std::numeric_limits<V>::max() || v < -(double)std::numeric_limits<V>::max()) return false;
     *out = (V)v;
     return true;
+  }
+  template <typename V> static bool finite(V v) {
+    return !std::is_floating_point<V>::value || (v == v && v <= std::numeric_limits<V>::max() && v >= std::numeric_limits<V>::lowest());
   }
   static bool parse(const char* text, bool* out) {
     if (strcmp(text, "true") == 0) { *out = true; return true; }

@@ -9,6 +9,8 @@
 #include "runtime/log.h"
 #include "runtime/nccl_transport.h"
 
+#include <atomic>
+
 namespace coccl {
 namespace {
 
@@ -70,6 +72,11 @@ NcclApi& api() {
   return a;
 }
 
+uint64_t nextCommId() {
+  static std::atomic<uint64_t> next{1};
+  return next.fetch_add(1);
+}
+
 int envInt(const char* name, int fallback) {
   const char* v = getenv(name);
   return (v && *v) ? atoi(v) : fallback;
@@ -108,8 +115,7 @@ ncclResult_t NcclTransport::initRank(Comm** out, int nRanks, ncclUniqueId id, in
   cudaGetDevice(&c->cudaDev);
   c->transport = this;
   c->native = native;
-  static uint64_t nextId = 1;
-  c->id = nextId++;
+  c->id = nextCommId();
   fillTopology(c);
   *out = c;
   return ncclSuccess;
@@ -169,7 +175,7 @@ ncclResult_t NcclTransport::split(Comm* parent, int color, int key, Comm** child
   c->transport = this;
   c->native = native;
   c->cudaDev = parent->cudaDev;
-  c->id = parent->id * 1000003ull + (uint64_t)(unsigned)color + 1;
+  c->id = nextCommId();  // two splits with the same colour are two communicators: ids never repeat in a process
   int count = 1, rank = 0;
   if (api().CommCount) api().CommCount(native, &count);
   if (api().CommUserRank) api().CommUserRank(native, &rank);

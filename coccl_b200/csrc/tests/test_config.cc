@@ -1,6 +1,7 @@
 // Config reader, policy model, scope inheritance, formatter, environment singleton, SDK adapter.
 #include <stdlib.h>
 #include <unistd.h>
+#include <limits>
 #include <string>
 
 #include "config/config.h"
@@ -283,4 +284,92 @@ TEST(sdk_adapter_traits_config_and_commit_rules) {
   cocclCompressorSizeQuery q2{(uint32_t)sizeof(cocclCompressorSizeQuery), cocclCompressorOperationCompress, 16, 1, ncclFloat32, nocfg};
   EXPECT(f->getEncodedSizeBound(&q2, &nb) == ncclInvalidUsage);  // no bound known -> runtime plans raw size
   f->destroyConfig(nocfg);
+}
+
+TEST(sdk_config_reader_rejects_malformed_option_lists) {
+  // Checks of the option list itself and of declared ranges, as a plugin author sees them through ConfigReader
+  // (behaviour of the reference header: include/compressor_plugin/coccl_compressor_plugin.h:279-443).
+  char err[160];
+  auto contains = [&](const char* what) { return std::string(err).find(what) != std::string::npos; };
+  int rate = 4;
+  double scale = 1.0;
+  float ratio = 1.0f;
+  {  // the same key twice
+    cocclConfigPair p[] = {{"rate", "8"}, {"scale", "2"}, {"rate", "16"}};
+    cocclConfigView v{p, 3};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    EXPECT(!r.ok() && contains("rate") && contains("twice"));
+    r.get("rate", rate);
+    EXPECT_EQ(rate, 4);  // a failed reader leaves the defaults alone
+    EXPECT(r.finish() == ncclInvalidArgument);
+  }
+  {  // a key without a value, a value without a key
+    cocclConfigPair p[] = {{"rate", nullptr}};
+    cocclConfigView v{p, 1};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    EXPECT(!r.ok() && contains("no value"));
+    cocclConfigPair q[] = {{nullptr, "8"}};
+    cocclConfigView w{q, 1};
+    coccl::ConfigReader r2(&w, err, sizeof(err));
+    EXPECT(!r2.ok() && contains("no name"));
+    cocclConfigView broken{nullptr, 2};
+    coccl::ConfigReader r3(&broken, err, sizeof(err));
+    EXPECT(!r3.ok());
+  }
+  {  // a range declared the wrong way round, or with a bound that is not a number
+    cocclConfigPair p[] = {{"rate", "8"}};
+    cocclConfigView v{p, 1};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    r.get("rate", rate, 64, 1);
+    EXPECT(!r.ok() && contains("invalid range"));
+    cocclConfigPair ps[] = {{"scale", "2"}};
+    cocclConfigView vs{ps, 1};
+    coccl::ConfigReader r2(&vs, err, sizeof(err));
+    r2.get("scale", scale, 0.0, std::numeric_limits<double>::quiet_NaN());
+    EXPECT(!r2.ok() && contains("invalid range"));
+  }
+  {  // floats: not-a-number, infinity, junk after the number, a value the target type cannot hold
+    const char* bad[] = {"nan", "inf", "-inf", "1.5x", "", "1e999"};
+    for (const char* text : bad) {
+      cocclConfigPair p[] = {{"scale", text}};
+      cocclConfigView v{p, 1};
+      coccl::ConfigReader r(&v, err, sizeof(err));
+      scale = 1.0;
+      r.get("scale", scale);
+      EXPECT(!r.ok() && scale == 1.0);
+    }
+    cocclConfigPair p[] = {{"ratio", "1e60"}};  // finite as a double, not as a float
+    cocclConfigView v{p, 1};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    r.get("ratio", ratio);
+    EXPECT(!r.ok() && ratio == 1.0f);
+  }
+  {  // integers: overflow of the target type, sign on an unsigned option
+    unsigned char small = 3;
+    cocclConfigPair p[] = {{"small", "256"}};
+    cocclConfigView v{p, 1};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    r.get("small", small);
+    EXPECT(!r.ok() && small == 3);
+    unsigned count = 7;
+    cocclConfigPair q[] = {{"count", "-1"}};
+    cocclConfigView w{q, 1};
+    coccl::ConfigReader r2(&w, err, sizeof(err));
+    r2.get("count", count);
+    EXPECT(!r2.ok() && count == 7);
+  }
+  {  // a default outside the declared range is caught even when the key is absent
+    cocclConfigView none{nullptr, 0};
+    coccl::ConfigReader r(&none, err, sizeof(err));
+    int level = 100;
+    r.get("level", level, 1, 9);
+    EXPECT(!r.ok() && contains("out of range"));
+  }
+  {  // and a sound list still reads
+    cocclConfigPair p[] = {{"rate", "8"}, {"scale", "-0.25"}};
+    cocclConfigView v{p, 2};
+    coccl::ConfigReader r(&v, err, sizeof(err));
+    r.get("rate", rate, 1, 64).get("scale", scale, -1.0, 1.0);
+    EXPECT(r.ok() && r.finish() == ncclSuccess && rate == 8 && scale == -0.25);
+  }
 }

@@ -1,0 +1,99 @@
+"""Parallel layouts on real GPUs against the single-GPU run: same initial weights, same data, same optimizer, so the
+loss curve of tp2 / pp2 / dp2 (and 2x2x2 with eight GPUs) must follow the one-GPU curve. With compression off the only
+differences are bf16 summation orders; with the training policy on, the tensor-parallel sums travel as block-scaled
+FP8 and the gradients as SDP4Bit, and the curve must still stay inside a stated band. This is the GPU counterpart of
+tests/test_parallel_cpu.py: here the tensor-parallel fusions, the fused reduce-scatter and the codec kernels are on
+the path."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+STEPS, NSEQ = 4, 8
+# relative tolerance on the loss of every step: (first step, later steps)
+TOL_EXACT = (4e-3, 1.5e-2)
+TOL_LOSSY = (2e-2, 4e-2)
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _cfg():
+    from coccl_b200.models.gpt import GPTConfig
+    return GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)
+
+
+def _data(cfg):
+    g = torch.Generator().manual_seed(11)
+    return torch.randint(0, cfg.vocab, (NSEQ, cfg.seq_len + 1), generator=g)
+
+
+def _single_gpu():
+    from coccl_b200.train import Trainer
+    cfg = _cfg()
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1234)
+    tr = Trainer(cfg, dev, micro_batch=2, lr=3e-4)
+    params = {k: v.detach().cpu().clone() for k, v in tr.stage.store.params.items()}
+    tok = _data(cfg).pin_memory()
+    losses = [tr.train_step(tok).item() for _ in range(STEPS)]
+    tr.check_health()
+    del tr
+    torch.cuda.empty_cache()
+    return params, losses
+
+
+def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses):
+    import torch.distributed as dist
+    from coccl_b200.parallel.comm import Policy
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    from coccl_b200.utils.checkpoint import shard_param
+    dev = torch.device("cuda", rank)
+    cfg = _cfg()
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress, policy=Policy.training(threshold_bytes=0, dp_delta=False))
+    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=3e-4)
+    for name, p in tr.stage.store.params.items():
+        p.data.copy_(shard_param(name, ref_params[name], mesh.tp_rank, tp).to(dev))
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tok = _data(cfg)
+    per = NSEQ // dp
+    mine = tok[mesh.dp_rank * per:(mesh.dp_rank + 1) * per].contiguous().pin_memory()
+    first, later = TOL_LOSSY if compress else TOL_EXACT
+    got = []
+    for step, ref in enumerate(ref_losses):
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        got.append(t.item() / (tp * dp))
+    tr.check_health()
+    for step, (g, ref) in enumerate(zip(got, ref_losses)):
+        tol = first if step == 0 else later
+        assert abs(g - ref) <= tol * abs(ref), (f"tp{tp}pp{pp}dp{dp} compress={compress}", step, got, ref_losses)
+    assert got[-1] < got[0]
+    for c in (mesh.tp_comm, mesh.dp_comm):
+        if c is not None and compress:
+            assert c.stats["compressed_calls"] > 0 and c.status() == 0
+    mesh.close()
+
+
+@pytest.fixture(scope="module")
+def reference():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    return _single_gpu()
+
+
+@pytest.mark.parametrize("compress", [False, True], ids=["native", "compressed"])
+@pytest.mark.parametrize("tp,pp,dp", [(2, 1, 1), (1, 2, 1), (1, 1, 2)])
+def test_two_gpu_layouts_follow_the_single_gpu_curve(reference, tp, pp, dp, compress):
+    params, losses = reference
+    run_distributed(_worker, 2, "nccl", (tp, pp, dp, compress, params, losses), timeout=420)
+
+
+@pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("compress", [False, True], ids=["native", "compressed"])
+def test_3d_layout_follows_the_single_gpu_curve(reference, compress):
+    params, losses = reference
+    run_distributed(_worker, 8, "nccl", (2, 2, 2, compress, params, losses), timeout=420)
