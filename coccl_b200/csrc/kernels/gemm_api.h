@@ -26,6 +26,10 @@ int cocclkGemmBf16(const void* A, long lda, int aMN, const void* B, long ldb, in
                    int N, int K, int epi, const void* bias, void* Z, unsigned int* err, int maxCtas,
                    cudaStream_t stream);
 
+// Tensor maps of repeated (address, shape, pitch) requests come from a per-thread table instead of the driver:
+// (hits, misses) since the library was loaded.
+void cocclkTensorMapCacheStats(unsigned long long* hits, unsigned long long* misses);
+
 #ifdef __cplusplus
 }
 #endif

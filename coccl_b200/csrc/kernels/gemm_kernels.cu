@@ -10,6 +10,7 @@
 // epilogue (TMEM lane quadrant = warp % 4). Every mbarrier wait is bounded; on
 // a timeout the kernel raises the error word, drains its outstanding copies,
 // frees TMEM and returns.
+#include <atomic>
 #include "launch_count.h"
 #include "gemm_epilogue.cuh"
 #include <stdio.h>
@@ -207,6 +208,30 @@ static EncodeTiledFn encodeTiled() {
   return fn;
 }
 
+// Tensor maps are a pure function of (address, extents, pitch, box, type): the driver call that encodes one costs
+// about a microsecond, and a training step asks for the same few hundred maps several thousand times (weights,
+// activations and gradients sit at fixed addresses). A small direct-mapped table per thread returns the encoded
+// map for a repeated request; a colliding request simply replaces the entry.
+struct MapKey {
+  const void* base;
+  long d0, d1, ld;
+  int b0, b1, kind;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && kind == o.kind;
+  }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool valid; };
+constexpr int kMapSlots = 1024;
+static MapSlot* mapSlot(const MapKey& k) {
+  static thread_local MapSlot* table = nullptr;
+  if (table == nullptr) table = new MapSlot[kMapSlots]();
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+  h = (h ^ (uint64_t)k.d0 * 0x9e3779b97f4a7c15ull ^ (uint64_t)k.d1 * 0xc2b2ae3d27d4eb4full ^ (uint64_t)k.ld * 0x165667b19e3779f9ull ^
+       (uint64_t)(k.b0 * 131 + k.b1 * 17 + k.kind)) * 0xff51afd7ed558ccdull;
+  return &table[(h >> 40) % kMapSlots];
+}
+static std::atomic<unsigned long long> gMapHits{0}, gMapMisses{0};
+
 // 2-D tensor map of an output matrix for the epilogue boxes: 32 rows x 128 bytes (32 fp32 or 64 bf16 columns),
 // 128-byte swizzle.
 int makeOutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld, bool f32) {
@@ -216,6 +241,10 @@ int makeOutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld, boo
   if (!ctxBound) { cudaFree(nullptr); ctxBound = true; }
   const int es_ = f32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * es_) & 15)) return -3;
+  const MapKey key{base, cols, rows, ld, 128 / es_, 32, f32 ? 2 : 1};
+  MapSlot* slot = mapSlot(key);
+  if (slot->valid && slot->key == key) { *m = slot->map; ++gMapHits; return 0; }
+  ++gMapMisses;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * es_};
   cuuint32_t box[2] = {(cuuint32_t)(128 / es_), 32};
@@ -226,6 +255,7 @@ int makeOutputMap(CUtensorMap* m, void* base, long cols, long rows, long ld, boo
     fprintf(stderr, "coccl: cuTensorMapEncodeTiled (output) failed (%d): base=%p dims={%ld,%ld} ld=%ld\n", (int)r, base, cols, rows, ld);
     return -4;
   }
+  slot->key = key; slot->map = *m; slot->valid = true;
   return 0;
 }
 
@@ -238,6 +268,10 @@ static int makeMap(CUtensorMap* m, const void* base, long inner, long outer, lon
   static thread_local bool ctxBound = false;
   if (!ctxBound) { cudaFree(nullptr); ctxBound = true; }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * 2) & 15)) return -3;
+  const MapKey key{base, inner, outer, ld, boxInner, boxOuter, 0};
+  MapSlot* slot = mapSlot(key);
+  if (slot->valid && slot->key == key) { *m = slot->map; ++gMapHits; return 0; }
+  ++gMapMisses;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)boxInner, (cuuint32_t)boxOuter};
@@ -250,6 +284,7 @@ static int makeMap(CUtensorMap* m, const void* base, long inner, long outer, lon
             base, inner, outer, ld, boxInner, boxOuter);
     return -4;
   }
+  slot->key = key; slot->map = *m; slot->valid = true;
   return 0;
 }
 
@@ -258,6 +293,12 @@ int makeBf16TensorMap(CUtensorMap* m, const void* base, long inner, long outer, 
 }
 
 }  // namespace coccl
+
+// (hits, misses) of the tensor-map table since the library was loaded, all threads.
+extern "C" void cocclkTensorMapCacheStats(unsigned long long* hits, unsigned long long* misses) {
+  if (hits) *hits = coccl::gMapHits.load();
+  if (misses) *misses = coccl::gMapMisses.load();
+}
 
 using namespace coccl;
 

@@ -35,10 +35,15 @@ class GPTConfig:
     eps: float = 1e-5
     init_std: float = 0.02
     dtype: torch.dtype = torch.bfloat16
-    # MoE (expert parallel) variant: every `moe_every`-th layer uses experts
+    # Mixture-of-experts variant: with n_experts > 0 every `moe_every`-th layer (layers moe_every-1, 2*moe_every-1, ...)
+    # replaces its MLP by n_experts expert MLPs of width `ffn` behind a top-`moe_top_k` router; the experts are
+    # spread over the expert-parallel group (coccl_b200.models.moe.MoETransformerLayer)
     n_experts: int = 0
     moe_top_k: int = 2
     moe_every: int = 1
+
+    def is_moe_layer(self, idx: int) -> bool:
+        return self.n_experts > 0 and (idx + 1) % max(self.moe_every, 1) == 0
 
     @property
     def head_dim(self) -> int:
@@ -46,15 +51,21 @@ class GPTConfig:
 
     def num_params(self) -> int:
         h, f = self.hidden, self.ffn
-        per_layer = 4 * h * h + 4 * h + 2 * h * f + f + h + 4 * h
-        return self.n_layer * per_layer + self.vocab * h + self.seq_len * h + 2 * h
+        attn = 4 * h * h + 4 * h + 4 * h           # qkv, proj, their biases, two LayerNorms
+        mlp = 2 * h * f + f + h
+        moe = self.n_experts * (2 * h * f + f) + self.n_experts * h        # experts (up, bias, down), router
+        n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
+        return self.n_layer * attn + (self.n_layer - n_moe) * mlp + n_moe * moe + self.vocab * h + self.seq_len * h + 2 * h
 
     def flops_per_token(self) -> float:
         """Training FLOPs per token (fwd+bwd = 3x fwd). Attention: QK^T and PV are 2*s*h each per token for full
         attention; a causal mask needs half of it, so 2*s*h per layer in total."""
         h, f, s = self.hidden, self.ffn, self.seq_len
-        per_layer = 2 * (4 * h * h + 2 * h * f) + 2 * s * h
-        return 3.0 * (self.n_layer * per_layer + 2 * h * self.vocab)
+        attn = 2 * 4 * h * h + 2 * s * h
+        n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
+        dense = 2 * 2 * h * f
+        moe = self.moe_top_k * 2 * 2 * h * f + 2 * h * self.n_experts   # top-k experts per token + the router
+        return 3.0 * (self.n_layer * attn + (self.n_layer - n_moe) * dense + n_moe * moe + 2 * h * self.vocab)
 
 
 GPT_6P7B = GPTConfig()
@@ -156,15 +167,27 @@ class TransformerLayer(nn.Module):
         store.add(pre + "proj.bias", (h,), "zeros", replicated=True)
         store.add(pre + "ln2.weight", (h,), "ones", replicated=True)
         store.add(pre + "ln2.bias", (h,), "zeros", replicated=True)
+        self.add_mlp_params(store, out_std)
+
+    ATTENTION_PARAMS = ("ln1.weight", "ln1.bias", "qkv.weight", "qkv.bias", "proj.weight", "proj.bias", "ln2.weight", "ln2.bias")
+    MLP_PARAMS = ("fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias")
+
+    def add_mlp_params(self, store: ParamStore, out_std: float):
+        cfg, pre, t = self.cfg, self.prefix, self.tp.size
+        h, f = cfg.hidden, cfg.ffn
         store.add(pre + "fc1.weight", (f // t, h), "normal", cfg.init_std)
         store.add(pre + "fc1.bias", (f // t,), "zeros")
         store.add(pre + "fc2.weight", (h, f // t), "normal", out_std)
         store.add(pre + "fc2.bias", (h,), "zeros", replicated=True)
 
-    def bind(self, params: dict):
-        for short in ("ln1.weight", "ln1.bias", "qkv.weight", "qkv.bias", "proj.weight", "proj.bias", "ln2.weight",
-                      "ln2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"):
+    def bind(self, params: dict, expert_params: dict | None = None):
+        for short in self.ATTENTION_PARAMS + self.MLP_PARAMS:
             self.register_parameter(short.replace(".", "_"), params[self.prefix + short])
+
+    def mlp(self, y):
+        """Feed-forward block on the normalised residual stream; returns the update that the next LayerNorm adds."""
+        z = self.tp.gather_linear(y, self.fc1_weight, self.fc1_bias, gelu=True)
+        return self.tp.linear_scatter(z, self.fc2_weight, self.fc2_bias)
 
     def attention(self, qkv, batch, seq):
         cfg, t = self.cfg, self.tp.size
@@ -189,16 +212,17 @@ class TransformerLayer(nn.Module):
         # row-parallel: partial sums are reduce-scattered over the token shards; the bias is added once
         o = tp.linear_scatter(a, self.proj_weight, self.proj_bias)
         y, x = fused.layer_norm(x, self.ln2_weight, self.ln2_bias, self.cfg.eps, residual=o)
-        z = tp.gather_linear(y, self.fc1_weight, self.fc1_bias, gelu=True)
-        o = tp.linear_scatter(z, self.fc2_weight, self.fc2_bias)
-        return x, o
+        return x, self.mlp(y)
 
 
 class GPTStage(nn.Module):
     """Layers [first, last) of the model plus the embedding (first stage) and the head (last stage)."""
 
     def __init__(self, cfg: GPTConfig, device, tp=None, first_layer=0, last_layer=None, pre=True, post=True,
-                 seed=1234, pad_to=1, layer_factory=None):
+                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None):
+        """ep_comm: communicator of the expert-parallel group for a mixture-of-experts model (None: every expert is
+        local). Expert weights that differ between the ranks of that group live in a second flat buffer pair,
+        `expert_store`, which data parallelism must not reduce or gather."""
         super().__init__()
         self.cfg, self.tp = cfg, tp or NoTP()
         last_layer = cfg.n_layer if last_layer is None else last_layer
@@ -213,18 +237,31 @@ class GPTStage(nn.Module):
             store.add("wte", (vshard, cfg.hidden), "normal", cfg.init_std)
         if pre:
             store.add("wpe", (cfg.seq_len, cfg.hidden), "normal", cfg.init_std, replicated=True)
-        make = layer_factory or (lambda c, i, s, t: TransformerLayer(c, i, s, t))
+        self.ep_size = ep_comm.size if ep_comm is not None else 1
+        # experts spread over several ranks are not replicas of one another: their own buffers. With one rank per
+        # expert group they are ordinary (data-parallel replicated) parameters of the main store.
+        expert_store = ParamStore(cfg.dtype, device, 8) if (cfg.n_experts > 0 and self.ep_size > 1) else None
+
+        def default_layer(c, i, s, t):
+            if c.is_moe_layer(i):
+                from .moe import MoETransformerLayer
+                assert t.size == 1, "mixture-of-experts layers are built for expert + data + pipeline parallelism (tp = 1)"
+                return MoETransformerLayer(c, i, s, t, ep_comm, expert_store)
+            return TransformerLayer(c, i, s, t)
+
+        make = layer_factory or default_layer
         self.layers = nn.ModuleList([make(cfg, i, store, tp_) for i in range(first_layer, last_layer)])
         if post:
             store.add("lnf.weight", (cfg.hidden,), "ones", replicated=True)
             store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
         store.materialise(seed, tp_.rank)
         self.store = store
+        self.expert_store = expert_store.materialise(seed, 0) if (expert_store is not None and expert_store.specs) else None
         for name, p in store.params.items():
             if not name.startswith("layers."):
                 self.register_parameter(name.replace(".", "_"), p)
         for layer in self.layers:
-            layer.bind(store.params)
+            layer.bind(store.params, self.expert_store.params if self.expert_store is not None else None)
 
     # ---- embedding (vocab-parallel under TP)
     def embed(self, tokens):
@@ -268,6 +305,8 @@ class GPTStage(nn.Module):
     # ---- utilities
     def zero_grad_buffer(self):
         self.store.flat_grad.zero_()
+        if self.expert_store is not None:
+            self.expert_store.flat_grad.zero_()
 
     def post_backward_sync_autograd_grads(self):
         """Parameters touched by stock autograd ops (embeddings) receive `.grad`; fold it into main_grad."""

@@ -61,6 +61,11 @@ class _Combine(torch.autograd.Function):
         return d_y, d_g, None
 
 
+class _Solo:
+    """Stand-in for the communicator of a group of one."""
+    size, rank = 1, 0
+
+
 class MoELayer:
     """n_experts experts, n_experts / comm.size of them on this rank.
 
@@ -83,6 +88,18 @@ class MoELayer:
             self.w_up.append((torch.randn(ffn, hidden, generator=ge) * 0.02).to(dev, torch.bfloat16))
             self.b_up.append(torch.zeros(ffn, device=dev, dtype=torch.bfloat16))
             self.w_down.append((torch.randn(hidden, ffn, generator=ge) * 0.02).to(dev, torch.bfloat16))
+
+    @classmethod
+    def over(cls, comm, hidden: int, ffn: int, n_experts: int, topk: int, router, w_up, b_up, w_down):
+        """The layer over parameters that somebody else owns (a trainer's flat buffers): `w_up`, `b_up`, `w_down`
+        list this rank's experts in order of their global index; comm None means every expert is local."""
+        self = cls.__new__(cls)
+        self.comm = comm if comm is not None else _Solo()
+        assert n_experts % self.comm.size == 0 and len(w_up) == n_experts // self.comm.size
+        self.hidden, self.ffn, self.n_experts, self.topk = hidden, ffn, n_experts, topk
+        self.local = n_experts // self.comm.size
+        self.router, self.w_up, self.b_up, self.w_down = router, list(w_up), list(b_up), list(w_down)
+        return self
 
     def parameters(self):
         return [self.router, *self.w_up, *self.b_up, *self.w_down]
@@ -130,3 +147,54 @@ class MoELayer:
                     y = fused.linear(h, self.w_down[e])
                     out = out.index_add(0, tok, gates[tok, j:j + 1] * y.float())
         return out.to(torch.bfloat16)
+
+
+from .gpt import TransformerLayer  # noqa: E402  (gpt.py imports this module lazily, inside the layer factory)
+
+
+class MoETransformerLayer(TransformerLayer):
+    """Transformer layer whose feed-forward block is a mixture of experts: attention as in the dense layer, then
+    router -> FP8 dispatch over the expert-parallel group -> expert MLPs -> gate-weighted combine.
+
+    Parameters: `router.weight` [n_experts, hidden] is replicated (main store, reduced over data parallelism like
+    every dense parameter). Expert e owns `experts.e.w_up` [ffn, hidden], `experts.e.b_up` [ffn] and
+    `experts.e.w_down` [hidden, ffn]; the names carry the GLOBAL expert index and the initial values are seeded by
+    name, so every expert-parallel degree starts from the same model. With an expert-parallel group of more than one
+    rank a rank allocates only its own experts, in `expert_store` (they are not data-parallel replicas: every token
+    routed to an expert reaches its one copy, so its gradient is already complete and is never reduced)."""
+
+    def __init__(self, cfg, idx, store, tp, ep_comm, expert_store):
+        self.ep_comm, self._expert_store = ep_comm, expert_store
+        super().__init__(cfg, idx, store, tp)
+
+    def add_mlp_params(self, store, out_std):
+        cfg, pre = self.cfg, self.prefix
+        h, f, e_all = cfg.hidden, cfg.ffn, cfg.n_experts
+        ep = self.ep_comm.size if self.ep_comm is not None else 1
+        assert e_all % ep == 0, "n_experts must be a multiple of the expert-parallel size"
+        local = e_all // ep
+        first = (self.ep_comm.rank if self.ep_comm is not None else 0) * local
+        self.expert_ids = list(range(first, first + local))
+        store.add(pre + "router.weight", (e_all, h), "normal", cfg.init_std)
+        target = self._expert_store if self._expert_store is not None else store
+        for e in self.expert_ids:
+            target.add(f"{pre}experts.{e}.w_up", (f, h), "normal", cfg.init_std)
+            target.add(f"{pre}experts.{e}.b_up", (f,), "zeros")
+            target.add(f"{pre}experts.{e}.w_down", (h, f), "normal", out_std)
+
+    def bind(self, params, expert_params=None):
+        for short in self.ATTENTION_PARAMS + ("router.weight",):
+            self.register_parameter(short.replace(".", "_"), params[self.prefix + short])
+        src = expert_params if self._expert_store is not None else params
+        ups, biases, downs = [], [], []
+        for e in self.expert_ids:
+            for kind, bucket in (("w_up", ups), ("b_up", biases), ("w_down", downs)):
+                p = src[f"{self.prefix}experts.{e}.{kind}"]
+                self.register_parameter(f"experts_{e}_{kind}", p)
+                bucket.append(p)
+        cfg = self.cfg
+        self.moe = MoELayer.over(self.ep_comm, cfg.hidden, cfg.ffn, cfg.n_experts, cfg.moe_top_k, self.router_weight,
+                                 ups, biases, downs)
+
+    def mlp(self, y):
+        return self.moe.forward(y)

@@ -31,6 +31,16 @@ def check_errors(device=None) -> None:
             raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} reported error word {v & 0xFFFFFFFF:#x}")
 
 
+def tensor_map_cache_stats() -> tuple[int, int]:
+    """(hits, misses) of the table that returns the TMA descriptor of a repeated (address, shape, pitch) request
+    without a driver call."""
+    import ctypes as C
+    fn = _lib.declare("cocclkTensorMapCacheStats", None, [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)])
+    h, m = C.c_ulonglong(0), C.c_ulonglong(0)
+    fn(C.byref(h), C.byref(m))
+    return int(h.value), int(m.value)
+
+
 def set_variant(name: str) -> None:
     """Pick the kernel: "auto" (by shape), "1cta" (128x256 tiles, one SM per tile) or "2cta"
     (256x256 tiles on a CTA pair with tcgen05.mma.cta_group::2)."""

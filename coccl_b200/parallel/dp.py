@@ -18,13 +18,16 @@ from ..ops import fused
 class DistributedOptimizer:
     def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, dp_comm=None, *, lr=1e-4, betas=(0.9, 0.95),
                  eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=(), delta_param_gather: bool | None = None,
-                 norm_exclude=()):
+                 norm_exclude=(), extra_sumsq=None):
         """dp_comm: communicator of the data-parallel group (None = single replica).
         norm_groups: communicators over which the squared gradient norm must be summed besides DP
         (tensor- and pipeline-parallel groups).
         norm_exclude: [lo, hi) ranges of the flat buffers whose gradients another rank of `norm_groups` already
         counts (ParamStore.norm_exclude_ranges); they are left out of this rank's sum of squares, so the clip
         coefficient equals the one of a run without tensor / pipeline parallelism.
+        extra_sumsq: callable returning a device scalar that is added to this rank's sum of squared gradients before
+        the sums over the groups: the squares of parameters this optimizer does not hold but the clip coefficient
+        must count (the expert weights of a mixture-of-experts model, which differ per data-parallel rank).
         delta_param_gather: send the updated parameters as 8-bit deltas against what every rank already holds (the
         reference's `training.dp.all_gather` policy with subAdd, training.toml:36-54); None = follow the policy file
         (the router answers whether a delta codec is configured for this all-gather)."""
@@ -44,6 +47,7 @@ class DistributedOptimizer:
             self.shard, dtype=flat_grad.dtype, device=dev)
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         self.norm_groups = tuple(norm_groups)
+        self.extra_sumsq = extra_sumsq
         # the excluded ranges, cut to this rank's shard and expressed in shard coordinates
         self._excl = [(max(a, lo) - lo, min(b, lo + self.shard) - lo) for a, b in norm_exclude
                       if max(a, lo) < min(b, lo + self.shard)]
@@ -60,21 +64,32 @@ class DistributedOptimizer:
         self._coef = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
 
-    def step(self, grad_scale: float = 1.0):
-        """grad_scale multiplies every gradient before clipping (e.g. 1/dp for averaging)."""
+    def local_sum_squares(self) -> torch.Tensor:
+        """Sum of squares of the whole flat gradient as it stands (no collective)."""
+        fused.sum_squares(self.flat_grad, self._sumsq)
+        return self._sumsq
+
+    def step(self, grad_scale: float = 1.0, coef: torch.Tensor | None = None):
+        """grad_scale multiplies every gradient before clipping (e.g. 1/dp for averaging). coef: a clip coefficient
+        computed elsewhere (device scalar); the norm is then neither computed nor reduced here."""
         self.step_count += 1
         if self.dp > 1:
             self.comm.reduce_scatter(self.flat_grad, self.grad_shard)
         g = self.grad_shard
-        fused.sum_squares(g, self._sumsq)
-        for a, b in self._excl:
-            fused.sum_squares(g[a:b], self._sumsq_excl)
-            self._sumsq -= self._sumsq_excl
-        if self.dp > 1:
-            self.comm.all_reduce_small(self._sumsq)
-        for c in self.norm_groups:
-            c.all_reduce_small(self._sumsq)
-        fused.clip_coef(self._sumsq, self.clip, grad_scale, self._coef, self.grad_norm)
+        if coef is None:
+            fused.sum_squares(g, self._sumsq)
+            for a, b in self._excl:
+                fused.sum_squares(g[a:b], self._sumsq_excl)
+                self._sumsq -= self._sumsq_excl
+            if self.extra_sumsq is not None:
+                self._sumsq += self.extra_sumsq()
+            if self.dp > 1:
+                self.comm.all_reduce_small(self._sumsq)
+            for c in self.norm_groups:
+                c.all_reduce_small(self._sumsq)
+            fused.clip_coef(self._sumsq, self.clip, grad_scale, self._coef, self.grad_norm)
+        else:
+            self._coef.copy_(coef)
         fused.adam_step(self.master, self.m, self.v, g, self._new_shard, lr=self.lr, beta1=self.betas[0],
                         beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count,
                         grad_scale=self._coef)

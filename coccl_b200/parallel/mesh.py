@@ -1,4 +1,5 @@
-"""3-D process mesh (tensor x data x pipeline) and the communicators of each axis.
+"""3-D process mesh (tensor x data x pipeline) and the communicators of each axis; expert parallelism reuses the
+data-parallel axis (each data-parallel rank holds 1/ep of the experts of a mixture-of-experts model).
 
 Rank order follows Megatron: tp fastest, then dp, then pp:
     rank = tp_rank + tp * (dp_rank + dp * pp_rank)
@@ -15,10 +16,11 @@ from .tp import TPContext
 
 class Mesh:
     def __init__(self, tp=1, pp=1, dp=1, device=None, compress=True, policy: Policy | None = None,
-                 sequence_parallel=True):
+                 sequence_parallel=True, ep=1):
         world, rank = dist.get_world_size(), dist.get_rank()
         assert tp * pp * dp == world, (tp, pp, dp, world)
-        self.tp, self.pp, self.dp, self.device = tp, pp, dp, device
+        assert ep in (1, dp), "the expert-parallel group is the data-parallel group (ep = dp) or absent (ep = 1)"
+        self.tp, self.pp, self.dp, self.ep, self.device = tp, pp, dp, ep, device
         self.rank = rank
         self.tp_rank = rank % tp
         self.dp_rank = (rank // tp) % dp
@@ -50,6 +52,8 @@ class Mesh:
         self.tp_comm = Communicator(self.tp_group, device, pol, "tp") if tp > 1 else None
         self.dp_comm = Communicator(self.dp_group, device, pol, "dp") if dp > 1 else None
         self.pp_comm = Communicator(self.pp_group, device, NATIVE, "pp") if pp > 1 else None
+        # token exchange of the experts: the same ranks as data parallelism, its own workspace and flags
+        self.ep_comm = Communicator(self.dp_group, device, pol, "ep") if ep > 1 else None
         self.pp_prev_global = self.pp_ranks[self.pp_rank - 1] if self.pp_rank > 0 else None
         self.pp_next_global = self.pp_ranks[self.pp_rank + 1] if self.pp_rank < pp - 1 else None
 
@@ -79,6 +83,6 @@ class Mesh:
             dist.all_reduce(store.params["wte"].main_grad, group=self.emb_group)
 
     def close(self):
-        for c in (self.tp_comm, self.dp_comm, self.pp_comm):
+        for c in (self.tp_comm, self.dp_comm, self.pp_comm, self.ep_comm):
             if c is not None:
                 c.close()

@@ -22,6 +22,7 @@ class ParallelConfig:
     pp: int = 1
     dp: int = 1
     sequence_parallel: bool = True
+    ep: int = 1   # expert parallelism of a mixture-of-experts model: 1 (every rank holds all experts) or dp
 
 
 class Trainer:
@@ -37,8 +38,18 @@ class Trainer:
         per = cfg.n_layer // pp
         assert cfg.n_layer % pp == 0
         dp = self.parallel.dp
+        ep_comm = getattr(g, "ep_comm", None) if g is not None else None
+        assert self.parallel.ep == (ep_comm.size if ep_comm is not None else 1), "ParallelConfig.ep and the mesh disagree"
         self.stage = GPTStage(cfg, device, tp=tp_ctx, first_layer=pp_rank * per, last_layer=(pp_rank + 1) * per,
-                              pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * dp * 2048)
+                              pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * dp * 2048,
+                              ep_comm=ep_comm)
+        # experts spread over the expert-parallel group: updated locally (never reduced or gathered), clipped with
+        # the same coefficient as everything else; their squares enter the global norm through the main optimizer
+        self.expert_opt = None
+        es = self.stage.expert_store
+        if es is not None:
+            self.expert_opt = DistributedOptimizer(es.flat_param, es.flat_grad, None, lr=lr, weight_decay=weight_decay,
+                                                   clip_grad=clip_grad)
         norm_groups = []
         if g is not None:
             if g.tp_comm is not None and g.tp_comm.size > 1:
@@ -50,7 +61,8 @@ class Trainer:
                                         weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups,
                                         norm_exclude=self.stage.store.norm_exclude_ranges(
                                             g.tp_rank if g is not None else 0,
-                                            drop_wte=(pp > 1 and pp_rank == pp - 1)))
+                                            drop_wte=(pp > 1 and pp_rank == pp - 1)),
+                                        extra_sumsq=(self.expert_opt.local_sum_squares if self.expert_opt is not None else None))
         self.schedule = None
         if pp > 1:
             from .parallel.pp import PipelineSchedule
@@ -89,13 +101,16 @@ class Trainer:
         if self.groups is not None:
             self.groups.sync_shared_grads(self.stage)
         self.opt.step(grad_scale=1.0)
+        if self.expert_opt is not None:
+            self.expert_opt.step(coef=self.opt._coef)
         for c in self._comms():
             c.post_status_read()
         return self._loss_acc * self.parallel.dp  # this rank's mean loss
 
     def _comms(self):
         g = self.groups
-        return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm) if g is not None else ()) if c is not None]
+        return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm, getattr(g, "ep_comm", None)) if g is not None else ())
+                if c is not None]
 
     def check_health(self, wait: bool = True) -> None:
         """Raise coccl_b200.parallel.comm.PeerLost if a bounded wait inside a fused collective, a tensor-parallel

@@ -46,6 +46,12 @@ def save(trainer, directory: str, step: int, rank: int = 0, world: int = 1):
     sd = {
         "flat_param": trainer.stage.store.flat_param.detach().cpu(),
         "optimizer": {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in trainer.opt.state_dict().items()},
+        # experts of a mixture-of-experts model that are spread over the expert-parallel group (None otherwise)
+        "expert_flat_param": (trainer.stage.expert_store.flat_param.detach().cpu()
+                              if getattr(trainer.stage, "expert_store", None) is not None else None),
+        "expert_optimizer": ({k: (v.detach().cpu() if torch.is_tensor(v) else v)
+                              for k, v in trainer.expert_opt.state_dict().items()}
+                             if getattr(trainer, "expert_opt", None) is not None else None),
         "step": step,
         "torch_rng": torch.get_rng_state(),
         "cuda_rng": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
@@ -57,7 +63,7 @@ def save(trainer, directory: str, step: int, rank: int = 0, world: int = 1):
     if rank == 0:
         p = trainer.parallel
         with open(os.path.join(directory, "manifest.json"), "w") as f:
-            json.dump({"step": step, "world": world, "tp": p.tp, "pp": p.pp, "dp": p.dp,
+            json.dump({"step": step, "world": world, "tp": p.tp, "pp": p.pp, "dp": p.dp, "ep": getattr(p, "ep", 1),
                        "model": {k: (str(v) if not isinstance(v, (int, float, bool)) else v)
                                  for k, v in vars(trainer.cfg).items()}}, f)
 
@@ -66,11 +72,14 @@ def load(trainer, directory: str, rank: int = 0) -> int:
     with open(os.path.join(directory, "manifest.json")) as f:
         man = json.load(f)
     p = trainer.parallel
-    if (man["tp"], man["pp"], man["dp"]) != (p.tp, p.pp, p.dp):
-        raise ValueError(f"checkpoint was written with tp/pp/dp={man['tp']}/{man['pp']}/{man['dp']}")
+    if (man["tp"], man["pp"], man["dp"], man.get("ep", 1)) != (p.tp, p.pp, p.dp, getattr(p, "ep", 1)):
+        raise ValueError(f"checkpoint was written with tp/pp/dp/ep={man['tp']}/{man['pp']}/{man['dp']}/{man.get('ep', 1)}")
     sd = torch.load(os.path.join(directory, f"rank{rank:05d}.pt"), map_location="cpu", weights_only=False)
     trainer.stage.store.flat_param.copy_(sd["flat_param"])
     trainer.opt.load_state_dict(sd["optimizer"])
+    if sd.get("expert_flat_param") is not None:
+        trainer.stage.expert_store.flat_param.copy_(sd["expert_flat_param"])
+        trainer.expert_opt.load_state_dict(sd["expert_optimizer"])
     torch.set_rng_state(sd["torch_rng"])
     if sd.get("cuda_rng") is not None and torch.cuda.is_available():
         torch.cuda.set_rng_state(sd["cuda_rng"])

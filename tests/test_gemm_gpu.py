@@ -122,3 +122,24 @@ def test_gemm_consumes_every_k_block_once(cuda, M, N, K):
     lost = _ref(x[:, 64:], w[:, 64:])   # what a kernel that dropped the first block would return
     with pytest.raises(AssertionError):
         _check(lost, _ref(x, w), K)
+
+
+def test_tensor_maps_of_repeated_operands_come_from_the_table(cuda):
+    torch.manual_seed(6)
+    a = torch.randn(512, 256, device=cuda, dtype=torch.bfloat16)
+    b = torch.randn(384, 256, device=cuda, dtype=torch.bfloat16)
+    out = torch.empty(512, 384, device=cuda, dtype=torch.bfloat16)
+    G.gemm(a, b, out=out)
+    h0, m0 = G.tensor_map_cache_stats()
+    first = out.clone()
+    for _ in range(5):
+        G.gemm(a, b, out=out)
+    h1, m1 = G.tensor_map_cache_stats()
+    assert m1 == m0 and h1 >= h0 + 15      # three maps per launch, none encoded again
+    assert torch.equal(out, first)
+    # same addresses, another shape: new maps, right answer
+    c = G.gemm(a[:256], b)
+    _check(c, _ref(a[:256], b), 256)
+    assert G.tensor_map_cache_stats()[1] > m1
+    torch.cuda.synchronize()
+    G.check_errors()

@@ -63,3 +63,60 @@ def test_parallel_layouts_match_single_process(tp, pp, dp):
     tr2, _ = _reference_losses(steps=0)
     params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
     run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params))
+
+
+# ---------------------------------------------------------------------------- mixture of experts in the trainer
+def _moe_cfg():
+    from coccl_b200.models.gpt import GPTConfig
+    return GPTConfig(n_layer=4, hidden=64, n_head=4, ffn=128, seq_len=32, vocab=128, dtype=torch.float32,
+                     n_experts=4, moe_top_k=2, moe_every=2)
+
+
+def _moe_reference(steps=3):
+    from coccl_b200.train import Trainer
+    cfg = _moe_cfg()
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2)
+    params = {k: v.detach().clone() for k, v in tr.stage.store.params.items()}
+    tok = _data(cfg, 8)
+    out = []
+    for _ in range(steps):
+        out.append((tr.train_step(tok).item(), tr.opt.grad_norm.item()))
+    return params, out
+
+
+def _moe_worker(rank, world, pp, dp, ref_params, ref):
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = _moe_cfg()
+    mesh = Mesh(tp=1, pp=pp, dp=dp, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, pp, dp), groups=mesh, lr=1e-2)
+    assert tr.stage.expert_store is None          # ep = 1: the experts are ordinary replicated parameters
+    assert any(".experts.3.w_down" in n for n in tr.stage.store.params) or pp > 1
+    for name, p in tr.stage.store.params.items():
+        p.data.copy_(ref_params[name])
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tok = _data(cfg, 8)
+    per = 8 // dp
+    mine = tok[mesh.dp_rank * per:(mesh.dp_rank + 1) * per]
+    for step, (ref_loss, ref_norm) in enumerate(ref):
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        assert abs(t.item() / dp - ref_loss) < 2e-3 * abs(ref_loss) + 1e-4, (step, t.item() / dp, ref_loss)
+        assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6, (step, tr.opt.grad_norm.item(), ref_norm)
+
+
+def test_moe_model_trains_and_counts_its_parameters():
+    from coccl_b200.models.gpt import GPTStage
+    cfg = _moe_cfg()
+    assert [cfg.is_moe_layer(i) for i in range(4)] == [False, True, False, True]
+    stage = GPTStage(cfg, torch.device("cpu"))
+    assert sum(p.numel() for p in stage.store.params.values()) == cfg.num_params()
+    _, curve = _moe_reference(steps=6)
+    assert curve[-1][0] < curve[0][0] - 0.05, curve
+
+
+@pytest.mark.parametrize("pp,dp", [(1, 2), (2, 1), (2, 2)])
+def test_moe_layouts_match_single_process(pp, dp):
+    params, ref = _moe_reference()
+    run_distributed(_moe_worker, pp * dp, "gloo", (pp, dp, params, ref))

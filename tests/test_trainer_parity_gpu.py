@@ -97,3 +97,65 @@ def test_two_gpu_layouts_follow_the_single_gpu_curve(reference, tp, pp, dp, comp
 def test_3d_layout_follows_the_single_gpu_curve(reference, compress):
     params, losses = reference
     run_distributed(_worker, 8, "nccl", (2, 2, 2, compress, params, losses), timeout=420)
+
+
+# ---------------------------------------------------------------------------- expert parallelism
+def _moe_cfg():
+    from coccl_b200.models.gpt import GPTConfig
+    return GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=1024, seq_len=256, vocab=8192, n_experts=4, moe_top_k=2, moe_every=2)
+
+
+def _moe_single_gpu():
+    from coccl_b200.train import Trainer
+    cfg = _moe_cfg()
+    dev = torch.device("cuda", 0)
+    tr = Trainer(cfg, dev, micro_batch=2, lr=3e-4)
+    params = {k: v.detach().cpu().clone() for k, v in tr.stage.store.params.items()}
+    tok = _data(cfg).pin_memory()
+    out = [(tr.train_step(tok).item(), tr.opt.grad_norm.item()) for _ in range(STEPS)]
+    tr.check_health()
+    del tr
+    torch.cuda.empty_cache()
+    return params, out
+
+
+def _moe_worker(rank, world, ref_params, ref):
+    import torch.distributed as dist
+    from coccl_b200.parallel.comm import Policy
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    dev = torch.device("cuda", rank)
+    cfg = _moe_cfg()
+    mesh = Mesh(tp=1, pp=1, dp=2, ep=2, device=dev, policy=Policy.training(threshold_bytes=0, dp_delta=False))
+    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(1, 1, 2, ep=2), groups=mesh, lr=3e-4)
+    es = tr.stage.expert_store
+    assert es is not None and len(es.params) == 2 * 2 * 3   # two MoE layers x two local experts x (up, bias, down)
+    assert not any(".experts." in n for n in tr.stage.store.params)
+    for store in (tr.stage.store, es):
+        for name, p in store.params.items():
+            p.data.copy_(ref_params[name].to(dev))
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tr.expert_opt.master.copy_(tr.expert_opt.param_shard.float())
+    tok = _data(cfg)
+    mine = tok[rank * (NSEQ // 2):(rank + 1) * (NSEQ // 2)].contiguous().pin_memory()
+    got = []
+    for _ in ref:
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        got.append((t.item() / 2, tr.opt.grad_norm.item()))
+    tr.check_health()
+    for step, ((loss, norm), (rl, rn)) in enumerate(zip(got, ref)):
+        tol = TOL_LOSSY[0] if step == 0 else TOL_LOSSY[1]
+        assert abs(loss - rl) <= tol * abs(rl), (step, got, ref)
+        assert abs(norm - rn) <= 0.15 * rn, (step, got, ref)   # tokens reach the experts as FP8
+    assert mesh.ep_comm.moe_status() == 0 and mesh.ep_comm.stats["compressed_calls"] > 0
+    # this rank's experts moved away from their initial values
+    name = next(n for n in es.params if n.endswith("w_up"))
+    assert (es.params[name].detach().float().cpu() - ref_params[name].float()).abs().max().item() > 0
+    mesh.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_follows_the_single_gpu_curve():
+    params, ref = _moe_single_gpu()
+    run_distributed(_moe_worker, 2, "nccl", (params, ref), timeout=420)
