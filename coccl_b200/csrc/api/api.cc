@@ -39,6 +39,8 @@ thread_local int tlsNativeInGroup = 0;  // native calls issued inside the curren
 thread_local std::string tlsLastError;
 
 Comm* unwrap(ncclComm_t c) { return reinterpret_cast<Comm*>(c); }
+// A handle that does not start with this library's magic word belongs to the native library (runtime/comm.h).
+bool foreign(ncclComm_t c) { return c != nullptr && unwrap(c)->magic != kCommMagic; }
 
 // cocclInit: runs once per process when the first communicator is created; later communicators
 // only register themselves (core/runtime/coccl_init.cc:17-31).
@@ -97,7 +99,7 @@ void runtimeStop(Comm* comm) {
 }
 
 ncclResult_t route(CallInfo info) {
-  if (info.comm == nullptr) return ncclInvalidArgument;
+  if (info.comm == nullptr || info.comm->magic != kCommMagic) return ncclInvalidArgument;
   Runtime& rt = globalRuntime();
   bool taken = false;
   ncclResult_t r = rt.enqueueCheck(info, &taken);
@@ -115,7 +117,7 @@ CallInfo makeInfo(Operation op, Func f, const void* s, void* r, size_t n, ncclDa
 }
 
 ncclResult_t explicitCall(CallInfo info, Algorithm a) {
-  if (info.comm == nullptr) return ncclInvalidArgument;
+  if (info.comm == nullptr || info.comm->magic != kCommMagic) return ncclInvalidArgument;
   return globalRuntime().enqueueExplicit(info, a);
 }
 
@@ -232,11 +234,26 @@ ncclResult_t cocclApiCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* 
   *newcomm = reinterpret_cast<ncclComm_t>(child);
   return ncclSuccess;
 }
-ncclResult_t cocclApiCommCount(ncclComm_t comm, int* n) { if (!comm || !n) return ncclInvalidArgument; *n = unwrap(comm)->nRanks; return ncclSuccess; }
-ncclResult_t cocclApiCommUserRank(ncclComm_t comm, int* r) { if (!comm || !r) return ncclInvalidArgument; *r = unwrap(comm)->rank; return ncclSuccess; }
-ncclResult_t cocclApiCommCuDevice(ncclComm_t comm, int* d) { if (!comm || !d) return ncclInvalidArgument; *d = unwrap(comm)->cudaDev; return ncclSuccess; }
+ncclResult_t cocclApiCommCount(ncclComm_t comm, int* n) {
+  if (!comm || !n) return ncclInvalidArgument;
+  if (foreign(comm)) return ncclTransport().foreignCount(comm, n);
+  *n = unwrap(comm)->nRanks;
+  return ncclSuccess;
+}
+ncclResult_t cocclApiCommUserRank(ncclComm_t comm, int* r) {
+  if (!comm || !r) return ncclInvalidArgument;
+  if (foreign(comm)) return ncclTransport().foreignUserRank(comm, r);
+  *r = unwrap(comm)->rank;
+  return ncclSuccess;
+}
+ncclResult_t cocclApiCommCuDevice(ncclComm_t comm, int* d) {
+  if (!comm || !d || foreign(comm)) return ncclInvalidArgument;
+  *d = unwrap(comm)->cudaDev;
+  return ncclSuccess;
+}
 ncclResult_t cocclApiCommGetAsyncError(ncclComm_t comm, ncclResult_t* e) {
   if (!comm || !e) return ncclInvalidArgument;
+  if (foreign(comm)) return ncclTransport().foreignAsyncError(comm, e);
   // a fused kernel whose wait on a peer ran out reports here as a remote error (the reference inherits NCCL's
   // abort flag polling for this, src/device/prims_simple.h:97-132 and src/init.cc:2286)
   if (state().executor != nullptr) {

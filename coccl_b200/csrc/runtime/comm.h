@@ -42,7 +42,13 @@ class Transport {
   virtual void destroy(Comm* c) = 0;
 };
 
+// First word of every communicator object of this library. A handle that reaches the public API without it is not
+// ours: when this library's nccl* names sit in front of the native library's in the symbol search order (linked or
+// preloaded in its place), the native library's own internal calls of public functions can land here with ITS handles.
+constexpr uint64_t kCommMagic = 0x434f43434c423230ull;  // "COCCLB20"
+
 struct Comm {
+  uint64_t magic = kCommMagic;
   int rank = 0, nRanks = 1;
   int nNodes = 1, localRanks = 1, localRank = 0, node = 0;
   bool uniform = true;  // every node holds the same number of ranks

@@ -52,7 +52,9 @@ NcclApi& api() {
     const char* names[] = {getenv("COCCL_NCCL_LIBRARY"), "libnccl.so.2", "libnccl.so"};
     for (const char* n : names) {
       if (n == nullptr || *n == '\0') continue;
-      a.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+      // DEEPBIND: the native library resolves its internal references to public nccl* functions to ITSELF, also when
+      // a library that exports the same names (libcoccl_nccl.so) comes first in the global search order
+      a.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL | RTLD_DEEPBIND);
       if (a.handle) break;
     }
     if (!a.handle) {
@@ -106,15 +108,15 @@ void NcclTransport::fillTopology(Comm* c) {
 
 ncclResult_t NcclTransport::initRank(Comm** out, int nRanks, ncclUniqueId id, int rank) {
   if (!api().ok) return ncclSystemError;
-  void* native = nullptr;
-  ncclResult_t r = api().CommInitRank(&native, nRanks, id, rank);
-  if (r != ncclSuccess) return r;
+  // Inside a group the native library keeps the address it is given and writes the handle again when the group ends:
+  // the slot must outlive this function, so it is the communicator object's own field.
   Comm* c = new Comm();
+  ncclResult_t r = api().CommInitRank(&c->native, nRanks, id, rank);
+  if (r != ncclSuccess) { delete c; return r; }
   c->rank = rank;
   c->nRanks = nRanks;
   cudaGetDevice(&c->cudaDev);
   c->transport = this;
-  c->native = native;
   c->id = nextCommId();
   fillTopology(c);
   *out = c;
@@ -168,12 +170,11 @@ ncclResult_t NcclTransport::p2pBatch(Comm* c, const P2POp* ops, int n, cudaStrea
 
 ncclResult_t NcclTransport::split(Comm* parent, int color, int key, Comm** child) {
   if (!api().CommSplit) return ncclInternalError;
-  void* native = nullptr;
-  ncclResult_t r = api().CommSplit(parent->native, color, key, &native, nullptr);
-  if (r != ncclSuccess) return r;
-  Comm* c = new Comm();
+  Comm* c = new Comm();   // the handle slot must outlive a surrounding group (see initRank)
+  ncclResult_t r = api().CommSplit(parent->native, color, key, &c->native, nullptr);
+  if (r != ncclSuccess) { delete c; return r; }
   c->transport = this;
-  c->native = native;
+  void* native = c->native;
   c->cudaDev = parent->cudaDev;
   c->id = nextCommId();  // two splits with the same colour are two communicators: ids never repeat in a process
   int count = 1, rank = 0;
@@ -186,6 +187,17 @@ ncclResult_t NcclTransport::split(Comm* parent, int color, int key, Comm** child
   c->nNodes = 1; c->localRanks = count; c->localRank = rank; c->node = 0;
   *child = c;
   return ncclSuccess;
+}
+
+// Queries on a handle of the native library itself (see kCommMagic in runtime/comm.h).
+ncclResult_t NcclTransport::foreignAsyncError(void* native, ncclResult_t* out) {
+  return (api().ok && api().CommGetAsyncError) ? api().CommGetAsyncError(native, out) : ncclInvalidArgument;
+}
+ncclResult_t NcclTransport::foreignCount(void* native, int* out) {
+  return (api().ok && api().CommCount) ? api().CommCount(native, out) : ncclInvalidArgument;
+}
+ncclResult_t NcclTransport::foreignUserRank(void* native, int* out) {
+  return (api().ok && api().CommUserRank) ? api().CommUserRank(native, out) : ncclInvalidArgument;
 }
 
 void NcclTransport::destroy(Comm* c) {

@@ -11,6 +11,9 @@ class NcclTransport : public Transport {
   ncclResult_t initRank(Comm** out, int nRanks, ncclUniqueId id, int rank);
   const char* errorString(ncclResult_t r);
   ncclResult_t asyncError(Comm* c, ncclResult_t* out);
+  ncclResult_t foreignAsyncError(void* native, ncclResult_t* out);
+  ncclResult_t foreignCount(void* native, int* out);
+  ncclResult_t foreignUserRank(void* native, int* out);
   ncclResult_t abort(Comm* c);
   ncclResult_t broadcast(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, int root, cudaStream_t st);
   ncclResult_t reduce(Comm* c, const void* s, void* r, size_t n, ncclDataType_t t, ncclRedOp_t op, int root, cudaStream_t st);

@@ -110,7 +110,10 @@ class MoELayer:
         return self
 
     def route(self, x: torch.Tensor):
-        logits = fused.linear(x, self.router).float()
+        if self.n_experts % 8 == 0:
+            logits = fused.linear(x, self.router).float()
+        else:   # narrower than the tensor-core GEMM's 8-column granule: a library matmul (its gradient arrives as
+            logits = torch.nn.functional.linear(x, self.router).float()   # .grad and is folded into main_grad)
         top = logits.topk(self.topk, dim=1)
         return top.indices.to(torch.int32).contiguous(), torch.softmax(top.values, dim=1).contiguous()
 

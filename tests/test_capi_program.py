@@ -54,7 +54,7 @@ def test_c_program_runs_collectives_through_the_drop_in_library(tmp_path, enable
     if n < 2:
         pytest.skip("needs 2 GPUs")
     exe = _build(tmp_path)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_DEBUG="WARN")
     if enabled:
         env.update(COCCL_ENABLE="1", COCCL_CONFIG_FILE=str(ROOT / "coccl_b200" / "configs" / "normal-sdp4bit.toml"))
     else:

@@ -135,7 +135,8 @@ def test_tensor_maps_of_repeated_operands_come_from_the_table(cuda):
     for _ in range(5):
         G.gemm(a, b, out=out)
     h1, m1 = G.tensor_map_cache_stats()
-    assert m1 == m0 and h1 >= h0 + 15      # three maps per launch, none encoded again
+    assert m1 == m0 and h1 >= h0 + 10      # the operand maps of every launch (and the output map where the epilogue
+    # stores through TMA) come from the table, none is encoded again
     assert torch.equal(out, first)
     # same addresses, another shape: new maps, right answer
     c = G.gemm(a[:256], b)
