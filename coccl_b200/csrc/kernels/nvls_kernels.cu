@@ -45,26 +45,40 @@ __global__ void __launch_bounds__(256) nvlsAllReduceKernel(const NvlsArgs a) {
   const long bytes = a.count * (a.dtype == kF32 ? 4 : 2);
   const long sliceVecs = bytes / a.nRanks / 16;
   char* base = reinterpret_cast<char*>(a.mc) + (long)a.rank * sliceVecs * 16;
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < sliceVecs; i += (long)gridDim.x * blockDim.x) {
-    char* p = base + i * 16;
-    if (a.dtype == kF32) {
-      float x, y, z, w;
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=f"(x), "=f"(y), "=f"(z), "=f"(w) : "l"(p) : "memory");
-      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
-                   ::"l"(p), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-    } else if (a.dtype == kBF16) {
-      uint32_t x, y, z, w;
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(p) : "memory");
-      asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
-                   ::"l"(p), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-    } else {
-      uint32_t x, y, z, w;
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(p) : "memory");
-      asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};"
-                   ::"l"(p), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+  // four independent 16-byte reductions in flight per thread: one load per thread leaves the switch round trip exposed
+  constexpr int kUnroll = 4;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long i0 = (long)blockIdx.x * blockDim.x + threadIdx.x; i0 < sliceVecs; i0 += stride * kUnroll) {
+    uint32_t v[kUnroll][4];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long i = i0 + u * stride;
+      if (i >= sliceVecs) break;
+      char* p = base + i * 16;
+      if (a.dtype == kF32)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(p) : "memory");
+      else if (a.dtype == kBF16)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(p) : "memory");
+      else
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(p) : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long i = i0 + u * stride;
+      if (i >= sliceVecs) break;
+      char* p = base + i * 16;
+      if (a.dtype == kF32)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(p), "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3]) : "memory");
+      else if (a.dtype == kBF16)
+        asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                     ::"l"(p), "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3]) : "memory");
+      else
+        asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};"
+                     ::"l"(p), "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3]) : "memory");
     }
   }
   ctaBarrier(a, 1);
@@ -88,8 +102,9 @@ extern "C" int cocclkNvlsAllReduce(void* multicastPtr, long count, int dtype, in
   a.status = static_cast<StatusWord*>(status);
   a.epoch = epoch; a.timeoutNs = timeoutNs;
   // the grid must be the same on every rank: it depends on the size and on maxCtas only
-  long ctas = (bytes / nRanks / 16 + 255) / 256;
-  if (ctas > 64) ctas = 64;
+  // one CTA per 4 x 256 vectors of the slice, up to the number of per-CTA barrier slots
+  long ctas = (bytes / nRanks / 16 + 1023) / 1024;
+  if (ctas > kNvlsMaxCtas) ctas = kNvlsMaxCtas;
   if (maxCtas > 0 && ctas > maxCtas) ctas = maxCtas;
   if (ctas < 1) ctas = 1;
   nvlsAllReduceKernel<<<(unsigned)ctas, 256, 0, stream>>>(a);

@@ -1,6 +1,7 @@
 // CUDA-IPC backend of the symmetric memory interface (symm.h).
 #include "symm.h"
 #include <string.h>
+#include <unistd.h>
 #include <new>
 #include <vector>
 
@@ -9,9 +10,22 @@ struct cocclSymmBuffer {
   size_t bytes = 0;
   int device = -1;
   std::vector<void*> imported;  // by peer index; nullptr = not mapped
+  std::vector<char> direct;     // by peer index; 1 = same-process pointer, nothing to close
 };
 
-static_assert(sizeof(cudaIpcMemHandle_t) <= COCCL_SYMM_HANDLE_BYTES, "IPC handle does not fit");
+namespace {
+// What follows the IPC handle inside an export handle.
+struct SameProcess {
+  unsigned long long pid;
+  void* address;
+  int device;
+};
+constexpr size_t kIpcBytes = 64;
+static_assert(sizeof(cudaIpcMemHandle_t) <= kIpcBytes, "IPC handle does not fit");
+static_assert(kIpcBytes + sizeof(SameProcess) <= COCCL_SYMM_HANDLE_BYTES, "export handle too small");
+}  // namespace
+
+extern "C" int cocclSymmHandleBytes(void) { return COCCL_SYMM_HANDLE_BYTES; }
 
 extern "C" int cocclSymmAlloc(size_t bytes, cocclSymmBuffer** out) {
   if (out == nullptr || bytes == 0) return (int)cudaErrorInvalidValue;
@@ -38,18 +52,45 @@ extern "C" int cocclSymmExport(const cocclSymmBuffer* buf, void* handle) {
   if (e != cudaSuccess) return (int)e;
   memset(handle, 0, COCCL_SYMM_HANDLE_BYTES);
   memcpy(handle, &h, sizeof(h));
+  const SameProcess sp{(unsigned long long)getpid(), buf->local, buf->device};
+  memcpy(static_cast<char*>(handle) + kIpcBytes, &sp, sizeof(sp));
   return 0;
 }
 
 extern "C" int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void* handle, void** mapped) {
   if (!owner || !handle || !mapped || peerIndex < 0) return (int)cudaErrorInvalidValue;
+  if ((size_t)peerIndex >= owner->imported.size()) { owner->imported.resize(peerIndex + 1, nullptr); owner->direct.resize(peerIndex + 1, 0); }
+  SameProcess sp;
+  memcpy(&sp, static_cast<const char*>(handle) + kIpcBytes, sizeof(sp));
+  if (sp.pid == (unsigned long long)getpid() && sp.address != nullptr) {
+    // ranks that are threads of one process (one thread per GPU): the exporter's pointer is valid here as it is,
+    // the importing device only needs peer access to the exporter's device
+    int mine = -1;
+    cudaError_t e = cudaGetDevice(&mine);
+    if (e != cudaSuccess) return (int)e;
+    if (mine != sp.device) {
+      int can = 0;
+      e = cudaDeviceCanAccessPeer(&can, mine, sp.device);
+      if (e != cudaSuccess || !can) { cudaGetLastError(); return (int)(e != cudaSuccess ? e : cudaErrorPeerAccessUnsupported); }
+      e = cudaDeviceEnablePeerAccess(sp.device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+      if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    }
+    owner->imported[peerIndex] = sp.address;
+    owner->direct[peerIndex] = 1;
+    *mapped = sp.address;
+    return 0;
+  }
   cudaIpcMemHandle_t h;
   memcpy(&h, handle, sizeof(h));
   void* p = nullptr;
   cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
-  if (e != cudaSuccess) return (int)e;
-  if ((size_t)peerIndex >= owner->imported.size()) owner->imported.resize(peerIndex + 1, nullptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // the failure must not stay behind as the thread's last error: the caller falls back
+    return (int)e;
+  }
   owner->imported[peerIndex] = p;
+  owner->direct[peerIndex] = 0;
   *mapped = p;
   return 0;
 }
@@ -60,12 +101,13 @@ extern "C" size_t cocclSymmBytes(const cocclSymmBuffer* buf) { return buf ? buf-
 extern "C" int cocclSymmCloseImports(cocclSymmBuffer* buf) {
   if (!buf) return 0;
   cudaError_t first = cudaSuccess;
-  for (void*& p : buf->imported) {
-    if (p) {
+  for (size_t i = 0; i < buf->imported.size(); ++i) {
+    void*& p = buf->imported[i];
+    if (p && !buf->direct[i]) {
       cudaError_t e = cudaIpcCloseMemHandle(p);
       if (first == cudaSuccess) first = e;
-      p = nullptr;
     }
+    p = nullptr;
   }
   return (int)first;
 }

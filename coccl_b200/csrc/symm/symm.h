@@ -20,7 +20,10 @@
 extern "C" {
 #endif
 
-enum { COCCL_SYMM_HANDLE_BYTES = 64 };
+// export handle: the CUDA IPC handle (64 bytes) followed by the exporter's process id, address and device, which a
+// rank of the SAME process uses instead (CUDA IPC handles cannot be opened by the process that made them)
+enum { COCCL_SYMM_HANDLE_BYTES = 96 };
+int cocclSymmHandleBytes(void);
 
 typedef struct cocclSymmBuffer cocclSymmBuffer;
 

@@ -218,7 +218,8 @@ class _Symm:
             dist.barrier(group=comm.group)
             replaces.free()
         h = C.c_void_p()
-        buf = C.create_string_buffer(64)
+        hbytes = int(_lib.declare("cocclSymmHandleBytes", C.c_int, [])())
+        buf = C.create_string_buffer(hbytes)
         ok = self._alloc(nbytes, C.byref(h)) == 0 and self._export(h, buf) == 0
         self.handle = h if h.value else None
         offers = [None] * comm.size
@@ -230,7 +231,7 @@ class _Symm:
                     self.ptrs.append(self._local(h))
                     continue
                 m = C.c_void_p()
-                hb = C.create_string_buffer(offers[p][1], 64)
+                hb = C.create_string_buffer(offers[p][1], hbytes)
                 if self._import(h, p, hb, C.byref(m)) != 0:
                     ok = False
                     break
@@ -500,8 +501,33 @@ class Communicator:
             mc = 0
         flags = self._nvls["flags"] if self._nvls is not None else _Symm(self, _lib.lib().cocclkNvlsFlagBytes() + 256)
         epoch = self._nvls["epoch"] if self._nvls is not None else 0
-        self._nvls = {"t": t, "h": h, "mc": mc, "bytes": size, "flags": flags, "epoch": epoch}
+        self._nvls = {"t": t, "h": h, "mc": mc, "bytes": size, "flags": flags, "epoch": epoch, "used": 0}
         return mc != 0
+
+    def symmetric_tensor(self, numel: int, dtype: torch.dtype) -> torch.Tensor | None:
+        """A tensor inside this communicator's multicast-bound symmetric buffer (None when the fabric has no
+        multicast). `all_reduce` on such a tensor runs the multimem kernel IN PLACE: no copy in, no copy out. Every
+        rank must make the same sequence of requests (the offsets have to agree); the tensors live as long as the
+        communicator and are never handed back."""
+        nbytes = -(-numel * torch.empty(0, dtype=dtype).element_size() // 256) * 256
+        used = self._nvls["used"] if self._nvls is not None else 0
+        if used != 0 and used + nbytes > self._nvls["bytes"]:
+            return None   # growing would move the tensors handed out before; callers fall back to ordinary tensors
+        if not self._ensure_nvls(max(used + nbytes, 64 << 20)):
+            return None
+        st = self._nvls
+        off = st["used"]
+        st["used"] = off + nbytes
+        return st["t"][off:off + numel * torch.empty(0, dtype=dtype).element_size()].view(dtype)
+
+    def _nvls_offset(self, x: torch.Tensor):
+        """Byte offset of x inside the symmetric buffer, or None if it lives elsewhere."""
+        st = self._nvls
+        if st is None or st["t"] is None:
+            return None
+        base = st["t"].data_ptr()
+        off = x.data_ptr() - base
+        return off if 0 <= off and off + x.numel() * x.element_size() <= st["bytes"] else None
 
     def all_reduce_nvls(self, x: torch.Tensor) -> bool:
         """In-place sum over ranks through the switch. Returns False (x untouched) when multicast is unavailable or
@@ -509,20 +535,32 @@ class Communicator:
         nbytes = x.numel() * x.element_size()
         if x.dtype not in DTYPE_CODE or nbytes % (16 * self.size) != 0 or not x.is_contiguous():
             return False
-        if not self._ensure_nvls(nbytes):
-            return False
-        st = self._nvls
-        buf = st["t"][:nbytes].view(x.dtype)
-        buf.copy_(x.view(-1))
+        inplace = self._nvls_offset(x)
+        if inplace is not None and inplace % 16 == 0 and self._nvls["mc"] != 0:
+            st, mc = self._nvls, self._nvls["mc"] + inplace
+            buf = None
+        else:
+            # staging area = what is left of the buffer behind the tensors handed out by symmetric_tensor
+            used = self._nvls["used"] if self._nvls is not None else 0
+            if used != 0 and used + nbytes > self._nvls["bytes"]:
+                return False   # growing would move the tensors that symmetric_tensor handed out
+            if not self._ensure_nvls(used + nbytes):
+                return False
+            st = self._nvls
+            buf = st["t"][st["used"]:st["used"] + nbytes].view(x.dtype)
+            mc = st["mc"] + st["used"]
+            buf.copy_(x.view(-1))
+            self.stats["nvls_staged_copies"] = self.stats.get("nvls_staged_copies", 0) + 2
         st["epoch"] += 1
         fl = (C.c_void_p * self.size)(*[st["flags"].ptrs[p] for p in range(self.size)])
         status = st["flags"].ptrs[self.rank] + _lib.lib().cocclkNvlsFlagBytes()
         with nvtx_range("coccl.nvls.all_reduce"):
-            rc = _lib.lib().cocclkNvlsAllReduce(st["mc"], x.numel(), DTYPE_CODE[x.dtype], self.size, self.rank, fl, status,
+            rc = _lib.lib().cocclkNvlsAllReduce(mc, x.numel(), DTYPE_CODE[x.dtype], self.size, self.rank, fl, status,
                                                 st["epoch"] & 0xFFFFFFFF, int(self.policy.timeout_ms * 1e6),
                                                 self.policy.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkNvlsAllReduce")
-        x.view(-1).copy_(buf)
+        if buf is not None:
+            x.view(-1).copy_(buf)
         self.stats["nvls_calls"] = self.stats.get("nvls_calls", 0) + 1
         return True
 

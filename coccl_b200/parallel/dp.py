@@ -18,13 +18,17 @@ from ..ops import fused
 class DistributedOptimizer:
     def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, dp_comm=None, *, lr=1e-4, betas=(0.9, 0.95),
                  eps=1e-8, weight_decay=0.1, clip_grad=1.0, norm_groups=(), delta_param_gather: bool | None = None,
-                 norm_exclude=(), extra_sumsq=None):
+                 norm_exclude=(), extra_sumsq=None, strategy: str = "zero1"):
         """dp_comm: communicator of the data-parallel group (None = single replica).
         norm_groups: communicators over which the squared gradient norm must be summed besides DP
         (tensor- and pipeline-parallel groups).
         norm_exclude: [lo, hi) ranges of the flat buffers whose gradients another rank of `norm_groups` already
         counts (ParamStore.norm_exclude_ranges); they are left out of this rank's sum of squares, so the clip
         coefficient equals the one of a run without tensor / pipeline parallelism.
+        strategy: "zero1" (default: sharded optimizer state, reduce-scatter + all-gather) or "ddp": every rank keeps the
+        whole optimizer state, the gradients are ALL-REDUCED (one- or two-shot compressed all-reduce, or native, as the
+        policy's `all_reduce` slot says; the traffic the reference's classifier calls strategy "ddp",
+        core/training/coccl_training_classifier.cc:544-556) and nothing is gathered afterwards.
         extra_sumsq: callable returning a device scalar that is added to this rank's sum of squared gradients before
         the sums over the groups: the squares of parameters this optimizer does not hold but the clip coefficient
         must count (the expert weights of a mixture-of-experts model, which differ per data-parallel rank).
@@ -34,16 +38,18 @@ class DistributedOptimizer:
         self.flat_param, self.flat_grad, self.comm = flat_param, flat_grad, dp_comm
         self.dp = dp_comm.size if dp_comm is not None else 1
         self.rank = dp_comm.rank if dp_comm is not None else 0
+        assert strategy in ("zero1", "ddp"), strategy
+        self.ddp = strategy == "ddp" and self.dp > 1
         n = flat_param.numel()
         assert n % self.dp == 0, "flat buffers must be padded to a multiple of the DP size"
-        self.shard = n // self.dp
-        lo = self.rank * self.shard
+        self.shard = n if self.ddp else n // self.dp
+        lo = 0 if self.ddp else self.rank * self.shard
         self.param_shard = flat_param[lo:lo + self.shard]
         dev = flat_param.device
         self.master = self.param_shard.float().clone()
         self.m = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.v = torch.zeros(self.shard, dtype=torch.float32, device=dev)
-        self.grad_shard = flat_grad[lo:lo + self.shard] if self.dp == 1 else torch.empty(
+        self.grad_shard = flat_grad[lo:lo + self.shard] if (self.dp == 1 or self.ddp) else torch.empty(
             self.shard, dtype=flat_grad.dtype, device=dev)
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         self.norm_groups = tuple(norm_groups)
@@ -55,7 +61,7 @@ class DistributedOptimizer:
         if delta_param_gather is None:   # follow the policy: does the router put a delta codec on this all-gather?
             delta_param_gather = bool(dp_comm is not None and hasattr(dp_comm, "uses_delta_all_gather") and
                                       dp_comm.uses_delta_all_gather(self.shard, flat_param.dtype))
-        self.delta = bool(delta_param_gather) and self.dp > 1 and flat_param.is_cuda
+        self.delta = bool(delta_param_gather) and self.dp > 1 and flat_param.is_cuda and not self.ddp
         # with deltas the optimizer must not overwrite the previous parameters before they are subtracted
         self._new_shard = torch.empty_like(self.param_shard) if self.delta else self.param_shard
         self._delta_state = None   # handle of the seeded delta all-gather (see Communicator.all_gather_delta)
@@ -73,7 +79,9 @@ class DistributedOptimizer:
         """grad_scale multiplies every gradient before clipping (e.g. 1/dp for averaging). coef: a clip coefficient
         computed elsewhere (device scalar); the norm is then neither computed nor reduced here."""
         self.step_count += 1
-        if self.dp > 1:
+        if self.ddp:
+            self.comm.all_reduce(self.flat_grad)
+        elif self.dp > 1:
             self.comm.reduce_scatter(self.flat_grad, self.grad_shard)
         g = self.grad_shard
         if coef is None:
@@ -83,7 +91,7 @@ class DistributedOptimizer:
                 self._sumsq -= self._sumsq_excl
             if self.extra_sumsq is not None:
                 self._sumsq += self.extra_sumsq()
-            if self.dp > 1:
+            if self.dp > 1 and not self.ddp:   # ddp: every rank already holds the whole reduced gradient
                 self.comm.all_reduce_small(self._sumsq)
             for c in self.norm_groups:
                 c.all_reduce_small(self._sumsq)
@@ -96,7 +104,7 @@ class DistributedOptimizer:
         if self.delta:
             res = self.comm.all_gather(self._new_shard, self.flat_param, state=self._delta_state)
             self._delta_state = res[1] if isinstance(res, tuple) else None
-        elif self.dp > 1:
+        elif self.dp > 1 and not self.ddp:
             self.comm.all_gather(self.param_shard, self.flat_param)
 
     # ---- checkpointing (per-rank shard; see coccl_b200.utils.checkpoint)
@@ -110,5 +118,5 @@ class DistributedOptimizer:
         self.step_count = int(sd["step"])
         self.param_shard.copy_(self.master)
         self._delta_state = None   # the replicas no longer match what the deltas were taken against: re-seed exactly
-        if self.dp > 1:
+        if self.dp > 1 and not self.ddp:
             self.comm.all_gather(self.param_shard, self.flat_param)

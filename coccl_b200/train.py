@@ -22,6 +22,7 @@ class ParallelConfig:
     pp: int = 1
     dp: int = 1
     sequence_parallel: bool = True
+    dp_strategy: str = "zero1"   # "zero1": sharded optimizer (reduce-scatter + all-gather); "ddp": gradient all-reduce
     ep: int = 1   # expert parallelism of a mixture-of-experts model: 1 (every rank holds all experts) or dp
 
 
@@ -62,7 +63,8 @@ class Trainer:
                                         norm_exclude=self.stage.store.norm_exclude_ranges(
                                             g.tp_rank if g is not None else 0,
                                             drop_wte=(pp > 1 and pp_rank == pp - 1)),
-                                        extra_sumsq=(self.expert_opt.local_sum_squares if self.expert_opt is not None else None))
+                                        extra_sumsq=(self.expert_opt.local_sum_squares if self.expert_opt is not None else None),
+                                        strategy=self.parallel.dp_strategy)
         self.schedule = None
         if pp > 1:
             from .parallel.pp import PipelineSchedule

@@ -258,7 +258,26 @@ def _nvls_worker(rank, world):
             tol = 1e-5 if dtype == torch.float32 else 3e-2
             if not torch.allclose(x.float(), ref.float(), atol=tol * ref.float().abs().max().item(), rtol=0):
                 bad.append((str(dtype), n, it))
+    # a tensor that lives in the symmetric buffer is reduced in place: no staging copies
+    sym = comm.symmetric_tensor(1 << 20, torch.float32)
+    assert (sym is not None) == have_mc
+    if sym is not None:
+        torch.manual_seed(21 + rank)
+        sym.copy_(torch.randn(1 << 20, device=dev))
+        ref = sym.clone()
+        dist.all_reduce(ref)
+        copies, calls = comm.stats.get("nvls_staged_copies", 0), comm.stats["nvls_calls"]
+        assert comm.all_reduce_nvls(sym)
+        assert comm.stats["nvls_calls"] == calls + 1 and comm.stats.get("nvls_staged_copies", 0) == copies
+        assert torch.allclose(sym, ref, atol=1e-5 * ref.abs().max().item(), rtol=0)
+        # ordinary tensors still work afterwards (staged behind the handed-out tensor)
+        y = torch.randn(1 << 16, device=dev)
+        ref = y.clone()
+        dist.all_reduce(ref)
+        assert comm.all_reduce_nvls(y) and torch.allclose(y, ref, atol=1e-5 * ref.abs().max().item(), rtol=0)
     used = comm.stats.get("nvls_calls", 0)
+    if have_mc:
+        assert used > 0
     if rank == 0:
         print(f"multicast available: {have_mc}; nvls_calls={used}; measured: {comm.routing_summary().get('measured')}")
     if have_mc:   # the measurements were taken and handed to the router

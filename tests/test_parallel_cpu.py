@@ -120,3 +120,35 @@ def test_moe_model_trains_and_counts_its_parameters():
 def test_moe_layouts_match_single_process(pp, dp):
     params, ref = _moe_reference()
     run_distributed(_moe_worker, pp * dp, "gloo", (pp, dp, params, ref))
+
+
+def _ddp_worker(rank, world, ref_losses, ref_params):
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = _cfg()
+    mesh = Mesh(tp=1, pp=1, dp=2, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, 1, 2, dp_strategy="ddp"), groups=mesh, lr=1e-2)
+    assert tr.opt.ddp and tr.opt.master.numel() == tr.stage.store.flat_param.numel()   # whole optimizer state on every rank
+    for name, p in tr.stage.store.params.items():
+        p.data.copy_(ref_params[name])
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tok = _data(cfg, 8)
+    mine = tok[mesh.dp_rank * 4:(mesh.dp_rank + 1) * 4]
+    for step, (ref, ref_norm) in enumerate(ref_losses):
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        assert abs(t.item() / 2 - ref) < 2e-3 * abs(ref) + 1e-4, (step, t.item() / 2, ref)
+        assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6
+    # the replicas stayed identical without any parameter all-gather
+    mineflat = tr.stage.store.flat_param.clone()
+    other = mineflat.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(mineflat, other)
+
+
+def test_ddp_strategy_matches_single_process():
+    tr, losses = _reference_losses()
+    tr2, _ = _reference_losses(steps=0)
+    params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
+    run_distributed(_ddp_worker, 2, "gloo", (losses, params))
