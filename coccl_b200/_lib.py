@@ -42,7 +42,7 @@ class TpArgs(C.Structure):
                 ("a", c_void_p * MAX_RANKS), ("b", c_void_p * MAX_RANKS), ("c", c_void_p * MAX_RANKS),
                 ("bias", c_void_p * MAX_RANKS), ("z", c_void_p * MAX_RANKS), ("ws", c_void_p * MAX_RANKS),
                 ("flags", c_void_p * MAX_RANKS), ("status", c_void_p * MAX_RANKS), ("err", c_void_p * MAX_RANKS),
-                ("gathered", c_void_p * MAX_RANKS)]
+                ("gathered", c_void_p * MAX_RANKS), ("agPayload", c_int)]
 
 
 class MoeArgs(C.Structure):

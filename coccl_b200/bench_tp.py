@@ -71,8 +71,14 @@ def main():
     part = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
     out_ref = torch.empty(T // world, H, device=dev, dtype=torch.bfloat16)
 
-    def fused_up():
+    def fused_up():   # payload as the policy says (MX-FP8 on the tensor-parallel all-gather -> FP8 on the wire)
         return comm.ag_gemm(x, w_up, bias=b_up, gelu=True)
+
+    def fused_up_bf16():
+        return comm.ag_gemm(x, w_up, bias=b_up, gelu=True, payload="bf16")
+
+    def fused_up_fp8():
+        return comm.ag_gemm(x, w_up, bias=b_up, gelu=True, payload="fp8")
 
     def unfused_up():
         dist.all_gather_into_tensor(xg, x)
@@ -102,7 +108,11 @@ def main():
     y1, y0 = fused().float(), unfused().float()
     rel = ((y1 - y0).norm() / y0.norm()).item()
     res = {"what": "tp_mlp", "n_gpus": world, "tokens": T, "hidden": H, "ffn": F, "rel_diff_fused_vs_unfused": rel}
-    for name, fn in (("ag_gemm_fused", fused_up), ("ag_gemm_unfused", unfused_up), ("gemm_rs_fused", fused_down),
+    res["ag_payload_by_policy"] = "fp8" if comm._ag_payload_fp8(T // world, H, None) else "bf16"
+    y8, yb = fused_up_fp8().float(), fused_up_bf16().float()
+    res["rel_diff_ag_fp8_vs_bf16"] = ((y8 - yb).norm() / yb.norm()).item()
+    for name, fn in (("ag_gemm_fused", fused_up), ("ag_gemm_fused_bf16", fused_up_bf16), ("ag_gemm_fused_fp8", fused_up_fp8),
+                     ("ag_gemm_unfused", unfused_up), ("gemm_rs_fused", fused_down),
                      ("gemm_rs_unfused", unfused_down), ("mlp_fused", fused), ("mlp_unfused", unfused)):
         res[name + "_ms"] = _time(fn, a.iters, a.warmup, flush, dev)
     flops = 2.0 * T * H * f
@@ -110,8 +120,10 @@ def main():
     ag_bytes = (world - 1) * (T // world) * H * 2
     rs_bytes = (world - 1) * (T // world) * H * (1 + 1 / 32)
     res["ag_gemm_roofline_ms"] = max(t_gemm, ag_bytes / (a.link_gbs * 1e9) * 1e3)
+    res["ag_gemm_fp8_roofline_ms"] = max(t_gemm, ag_bytes * (1 + 1 / 32) / 2 / (a.link_gbs * 1e9) * 1e3)
+    res["ag_gemm_fp8_frac_of_roofline"] = res["ag_gemm_fp8_roofline_ms"] / res["ag_gemm_fused_fp8_ms"]
     res["gemm_rs_roofline_ms"] = max(t_gemm, rs_bytes / (a.link_gbs * 1e9) * 1e3)
-    res["ag_gemm_frac_of_roofline"] = res["ag_gemm_roofline_ms"] / res["ag_gemm_fused_ms"]
+    res["ag_gemm_frac_of_roofline"] = res["ag_gemm_roofline_ms"] / res["ag_gemm_fused_bf16_ms"]
     res["gemm_rs_frac_of_roofline"] = res["gemm_rs_roofline_ms"] / res["gemm_rs_fused_ms"]
     res["tp_status"] = list(comm.tp_status())
     G.check_errors()

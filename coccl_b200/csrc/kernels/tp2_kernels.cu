@@ -5,7 +5,10 @@
 //                    every moment each GPU sends to one peer and receives from one, and the shard the local tensor
 //                    cores need next is the one on the wire. A shard travels as pieces of 16 rows x K/4 columns
 //                    with one release flag each; the TMA producer of a CTA waits for the flags of its 128 rows
-//                    right before it loads them (from LOCAL memory; no multicast anywhere).
+//                    right before it loads them (from LOCAL memory; no multicast anywhere). With agPayload = 1 the
+//                    pieces travel as E4M3 + UE8M0 scales (MX-FP8, half the bytes): after pushing ring step s the
+//                    push warps dequantise the pieces of step s that arrive from the other side into the bf16 gather
+//                    buffer and raise a second, local set of flags, which the producer then waits for instead.
 //  gemmRsPairKernel  out = reduce_scatter(A * B^T). Tiles for the next rank in the ring are computed first, own rows
 //                    last. For a foreign row block the epilogue quantises the fp32 accumulator to E4M3 with one
 //                    UE8M0 scale per 32 columns and pushes it into the destination's slot. For an OWN row block the
@@ -46,6 +49,7 @@ constexpr int kRsStages = 6;                    // one stage goes to the epilogu
 constexpr int kThreads = 256;
 constexpr int kPartRows = 16;                   // rows per pushed piece of the gather
 constexpr int kFlagStride = 4096;               // flags per source rank
+constexpr int kReadyRegion = COCCLK_TP_MAX_RANKS;  // flag rows [kReadyRegion + shard]: piece dequantised (FP8 payload)
 constexpr int kStageRowBytes = 128 + 16;        // staging row: half a tile row of fp8 + padding against bank conflicts
 constexpr int kEpiStageBytes = 4 * 32 * kStageRowBytes;
 constexpr unsigned long long kPipeWaitNs = 4000000000ull;
@@ -218,6 +222,69 @@ __device__ __forceinline__ void copyPiece(const uint4* src, uint4* dst, long bas
   }
 }
 
+// Where the FP8 rows and their scales of the gather live inside a rank's workspace (behind the bf16 gather buffer).
+__device__ __host__ __forceinline__ long ag8Offset(long M, long K) { return (M * K * 2 + 255) & ~255L; }
+__device__ __host__ __forceinline__ long agScaleOffset(long M, long K) { return ag8Offset(M, K) + ((M * K + 255) & ~255L); }
+
+// One warp quantises a piece of 16 rows x (blocks * 32) columns: bf16 rows (pitch K) -> E4M3 rows (pitch K bytes) and
+// one UE8M0 byte per 32 columns (pitch K / 32), both in the PEER's memory. A lane owns whole 32-column blocks.
+__device__ __forceinline__ void quantPiece(const __nv_bfloat16* src, uint8_t* dst8, uint8_t* dstScale, long K, int blocks, int lane) {
+  const CodecCfg cfg{};
+  const int total = kPartRows * blocks;
+  for (int i = lane; i < total; i += 32) {
+    const int r = i / blocks, b = i - r * blocks;
+    const uint4* q = reinterpret_cast<const uint4*>(src + (long)r * K + b * 32);
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) raw[u] = __ldg(q + u);
+    float v[32];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[8 * u + 2 * k] = __uint_as_float(w[k] << 16);
+        v[8 * u + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+      }
+    }
+    const MxFp8Codec::Enc e = MxFp8Codec::encode(v, cfg, false, nullptr, 0);
+    uint4* d = reinterpret_cast<uint4*>(dst8 + (long)r * K + b * 32);
+    d[0] = make_uint4(e.w[0], e.w[1], e.w[2], e.w[3]);
+    d[1] = make_uint4(e.w[4], e.w[5], e.w[6], e.w[7]);
+    dstScale[(long)r * (K / 32) + b] = (uint8_t)e.scaleByte;
+  }
+}
+
+// The inverse on the receiving side: E4M3 rows + scales that a peer stored during this launch (L2 loads) -> bf16 rows of
+// the local gather buffer.
+__device__ __forceinline__ void dequantPiece(const uint8_t* src8, const uint8_t* srcScale, __nv_bfloat16* dst, long K, int blocks, int lane) {
+  const int total = kPartRows * blocks;
+  for (int i = lane; i < total; i += 32) {
+    const int r = i / blocks, b = i - r * blocks;
+    const uint4* q = reinterpret_cast<const uint4*>(src8 + (long)r * K + b * 32);
+    MxFp8Codec::Raw raw;
+    const uint4 x = __ldcg(q), y = __ldcg(q + 1);
+    raw.w[0] = x.x; raw.w[1] = x.y; raw.w[2] = x.z; raw.w[3] = x.w; raw.w[4] = y.x; raw.w[5] = y.y; raw.w[6] = y.z; raw.w[7] = y.w;
+    raw.biased = __ldcg(srcScale + (long)r * (K / 32) + b);
+    raw.valid = true;
+    float v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = 0.f;
+    MxFp8Codec::accumulate(raw, v);
+    uint4* d = reinterpret_cast<uint4*>(dst + (long)r * K + b * 32);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * u + 2 * k], v[8 * u + 2 * k + 1]);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      d[u] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_constant__ Params P) {
   extern __shared__ uint8_t smemRaw[];
   const cocclkTpArgs& a = P.a;
@@ -253,7 +320,9 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
       const int rowInShard = tmL * 2 * BM + (int)p.cta * BM;
       if (step > 0) {
         // this CTA's 128 rows of a remote shard: every piece of their eight 16-row parts must have landed
-        const unsigned int* f = a.flags[rank] + (long)shard * kFlagStride + (long)(rowInShard / kPartRows) * pieces;
+        // (FP8 payload: the flags the local push warps raise after dequantising a piece)
+        const unsigned int* f = a.flags[rank] + (long)((a.agPayload ? kReadyRegion : 0) + shard) * kFlagStride +
+                                (long)(rowInShard / kPartRows) * pieces;
         const int nFlags = (BM / kPartRows) * pieces;
         bool got = true;
         for (int i = lane; i < nFlags; i += 32) {
@@ -315,19 +384,57 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
     const long rowVecs = a.K / 8;
     const long items = (long)(rowsPerShard / kPartRows) * pieces;
     const uint4* src0 = reinterpret_cast<const uint4*>(a.a[rank]);
-    for (int step = 1; step < N; ++step) {
+    const bool fp8 = a.agPayload != 0;
+    const long K = a.K;
+    const int blocks = pieceCols / 32;                  // 32-column scale blocks per row of a piece (FP8 payload)
+    bool pushAlive = true;
+    for (int step = 1; step < N && pushAlive; ++step) {
       const int peer = (rank - step + N) % N;        // the peer whose ring step `step` reads this shard
       uint4* dst0 = reinterpret_cast<uint4*>(a.ws[peer]) + (long)rank * rowsPerShard * rowVecs;
       unsigned int* pf = a.flags[peer] + (long)rank * kFlagStride;
+      uint8_t* peer8 = reinterpret_cast<uint8_t*>(a.ws[peer]) + ag8Offset(a.M, K) + (long)rank * rowsPerShard * K;
+      uint8_t* peerScale = reinterpret_cast<uint8_t*>(a.ws[peer]) + agScaleOffset(a.M, K) + (long)rank * rowsPerShard * (K / 32);
       for (long itx = cw; itx < items; itx += W) {
         const long part = itx / pieces;
         const int piece = (int)(itx - part * pieces);
-        const long base = part * kPartRows * rowVecs + (long)piece * pcv;
-        copyPiece<false>(src0, dst0, base, rowVecs, pcv, lane);
+        if (fp8) {
+          const long row0 = part * kPartRows, col0 = (long)piece * pieceCols;
+          quantPiece(reinterpret_cast<const __nv_bfloat16*>(a.a[rank]) + row0 * K + col0, peer8 + row0 * K + col0,
+                     peerScale + row0 * (K / 32) + col0 / 32, K, blocks, lane);
+        } else {
+          const long base = part * kPartRows * rowVecs + (long)piece * pcv;
+          copyPiece<false>(src0, dst0, base, rowVecs, pcv, lane);
+        }
         __syncwarp();
         if (lane == 0) {
           __threadfence_system();
           stReleaseSys(pf + itx, a.epoch);
+        }
+      }
+      if (!fp8) continue;
+      // the same ring step seen from the receiving side: the shard of rank+step lands here piece by piece
+      const int shard = (rank + step) % N;
+      const unsigned int* arrived = a.flags[rank] + (long)shard * kFlagStride;
+      unsigned int* ready = a.flags[rank] + (long)(kReadyRegion + shard) * kFlagStride;
+      const uint8_t* my8 = reinterpret_cast<const uint8_t*>(a.ws[rank]) + ag8Offset(a.M, K) + (long)shard * rowsPerShard * K;
+      const uint8_t* myScale = reinterpret_cast<const uint8_t*>(a.ws[rank]) + agScaleOffset(a.M, K) + (long)shard * rowsPerShard * (K / 32);
+      __nv_bfloat16* myRows = reinterpret_cast<__nv_bfloat16*>(a.ws[rank]) + (long)shard * rowsPerShard * K;
+      for (long itx = cw; itx < items; itx += W) {
+        bool got = true;
+        if (lane == 0) {
+          got = !*p.abortFlag && waitFlag(arrived + itx, a.epoch, a.timeoutNs);
+          if (!got) { reportTimeout(st, 5, shard, (int)itx); raiseAbort(p); }
+        }
+        pushAlive = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (!pushAlive) break;
+        const long part = itx / pieces;
+        const int piece = (int)(itx - part * pieces);
+        const long row0 = part * kPartRows, col0 = (long)piece * pieceCols;
+        dequantPiece(my8 + row0 * K + col0, myScale + row0 * (K / 32) + col0 / 32, myRows + row0 * K + col0, K, blocks, lane);
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          stReleaseSys(ready + itx, a.epoch);
         }
       }
     }
@@ -336,12 +443,12 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmPairKernel(const __grid_con
     uint4* keep = reinterpret_cast<uint4*>(a.gathered[rank]);
     if (keep != nullptr) {
       const uint4* wsLocal = reinterpret_cast<const uint4*>(a.ws[rank]);
-      bool alive = true;
+      bool alive = pushAlive;
       for (int step = 0; step < N && alive; ++step) {
         const int shard = (rank + step) % N;
         const uint4* from = step == 0 ? src0 : wsLocal + (long)shard * rowsPerShard * rowVecs;
         uint4* to = keep + (long)shard * rowsPerShard * rowVecs;
-        const unsigned int* f = a.flags[rank] + (long)shard * kFlagStride;
+        const unsigned int* f = a.flags[rank] + (long)((fp8 ? kReadyRegion : 0) + shard) * kFlagStride;
         for (long itx = cw; itx < items && alive; itx += W) {
           if (step > 0) {
             bool got = true;
@@ -619,19 +726,27 @@ extern "C" int cocclkTpPairUsable(const cocclkTpArgs* a, int isRs) {
   return (a->N & 7) == 0 && (long)(rows / kPartRows) <= kFlagStride;
 }
 
-static int agPieces(int rowsPerShard, int K) {
+static int agPieces(int rowsPerShard, int K, int payload) {
   // column pieces per 16-row part: finer pieces let the first tiles of a shard start earlier; a piece stays a
-  // multiple of 16 bytes per row, at least 256 columns wide, and the flags of one source must fit its stride
+  // multiple of 16 bytes per row (of 32 columns with the FP8 payload: whole scale blocks), at least 256 columns wide,
+  // and the flags of one source must fit its stride
+  const int unit = payload ? 32 : 8;
   for (int pcs = 4; pcs > 1; pcs >>= 1)
-    if (K % (pcs * 8) == 0 && K / pcs >= 256 && (long)(rowsPerShard / kPartRows) * pcs <= kFlagStride) return pcs;
+    if (K % (pcs * unit) == 0 && K / pcs >= 256 && (long)(rowsPerShard / kPartRows) * pcs <= kFlagStride) return pcs;
   return 1;
+}
+
+extern "C" long cocclkAgGemmWorkspaceBytesFor(int M, int K, int agPayload) {
+  if (!agPayload) return (long)M * K * 2;
+  return agScaleOffset(M, K) + (((long)M * (K / 32) + 255) & ~255L);
 }
 
 extern "C" int cocclkAgGemmPair(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream) {
   const int N = args->nRanks, rowsPerShard = args->M / N;
   Params P;
   memcpy(&P.a, args, sizeof(cocclkTpArgs));
-  P.pieces = agPieces(rowsPerShard, args->K);
+  if (args->agPayload && (args->K % 32) != 0) return -1;
+  P.pieces = agPieces(rowsPerShard, args->K, args->agPayload);
   for (int e = 0; e < emulatedRanks; ++e) {
     const int r = args->rankBase + e;
     if ((args->epi != GEMM_EPI_NONE) && args->bias[r] == nullptr) return -1;

@@ -37,6 +37,11 @@ typedef struct {
   void* gathered[COCCLK_TP_MAX_RANKS];       // ag_gemm (CTA-pair kernel only), optional: [M, K] bf16 that receives the whole
                                              // gathered operand (the backward pass needs it for the weight gradient);
                                              // the kernel's push warps copy it out of the gather buffer as shards arrive
+  int agPayload;      // ag_gemm (CTA-pair kernel only): what travels between the ranks. 0: the bf16 rows as they are.
+                      // 1: E4M3 with one UE8M0 scale per 32 columns (half the bytes on the wire); the push warps of the
+                      // sender quantise, the push warps of the receiver dequantise each piece on arrival into the bf16
+                      // gather buffer the tensor cores read. Needs K % 32 == 0 and the larger workspace of
+                      // cocclkAgGemmWorkspaceBytesFor; the single-CTA kernel ignores it.
 } cocclkTpArgs;
 
 // Which kernel family served the last fusion call of this process: 1 = single-CTA tiles, 2 = CTA pairs. The single-CTA
@@ -45,6 +50,7 @@ int cocclkTpLastVariant(void);
 
 // Bytes of ws[] per rank.
 long cocclkAgGemmWorkspaceBytes(int M, int K);
+long cocclkAgGemmWorkspaceBytesFor(int M, int K, int agPayload);   // bf16 gather buffer [+ FP8 rows + scales]
 long cocclkGemmRsWorkspaceBytes(int M, int N, int nRanks);
 
 // Constraints: M % (nRanks * 128) == 0, K % 8 == 0; gemm_rs also N % 256 == 0; ag_gemm N % 8 == 0.

@@ -26,8 +26,14 @@ def last_variant() -> str:
     return {0: "none", 1: "1cta", 2: "2cta"}[_lib.declare("cocclkTpLastVariant", C.c_int, [])()]
 
 
-def ag_ws_bytes(M: int, K: int) -> int:
-    return _lib.lib().cocclkAgGemmWorkspaceBytes(M, K)
+PAYLOAD_BF16, PAYLOAD_FP8 = 0, 1
+
+
+def ag_ws_bytes(M: int, K: int, payload: int = PAYLOAD_BF16) -> int:
+    """Workspace per rank of the all-gather fusion: the bf16 gather buffer, plus the FP8 rows and their scales when the
+    shards travel as block-scaled FP8."""
+    import ctypes as C
+    return int(_lib.declare("cocclkAgGemmWorkspaceBytesFor", C.c_long, [C.c_int, C.c_int, C.c_int])(M, K, payload))
 
 
 def rs_ws_bytes(M: int, N: int, n: int) -> int:
@@ -62,13 +68,15 @@ def check_state(state) -> None:
 
 
 def emulate_ag_gemm(x_shards, w_shards, *, bias=None, gelu=False, state=None, epoch=1, max_ctas=0,
-                    timeout_ms=5000.0, b_mn=False):
-    """C_r = concat(x_shards) @ w_shards[r].T (+ bias_r, GELU) for every emulated rank r (w [K, N] with b_mn)."""
+                    timeout_ms=5000.0, b_mn=False, payload=PAYLOAD_BF16, gathered=None):
+    """C_r = concat(x_shards) @ w_shards[r].T (+ bias_r, GELU) for every emulated rank r (w [K, N] with b_mn).
+    payload=PAYLOAD_FP8: the shards cross between the ranks as E4M3 + UE8M0 scales (CTA-pair kernel only).
+    gathered: optional list of [M, K] tensors that receive each rank's gathered operand."""
     n = len(x_shards)
     m, K = x_shards[0].shape
     N = w_shards[0].shape[1] if b_mn else w_shards[0].shape[0]
     dev = x_shards[0].device
-    state = _state(state if state is not None else {}, n, dev, ag_ws_bytes(m * n, K))
+    state = _state(state if state is not None else {}, n, dev, ag_ws_bytes(m * n, K, payload))
     outs = [torch.empty(m * n, N, dtype=torch.bfloat16, device=dev) for _ in range(n)]
     a = _lib.TpArgs()
     a.nRanks, a.rankBase, a.M, a.N, a.K = n, 0, m * n, N, K
@@ -80,6 +88,9 @@ def emulate_ag_gemm(x_shards, w_shards, *, bias=None, gelu=False, state=None, ep
         assert x_shards[r].is_contiguous() and w_shards[r].is_contiguous()
         a.a[r], a.b[r], a.c[r] = x_shards[r].data_ptr(), w_shards[r].data_ptr(), outs[r].data_ptr()
         a.bias[r] = bias[r].data_ptr() if bias is not None else None
+        if gathered is not None:
+            a.gathered[r] = gathered[r].data_ptr()
+    a.agPayload = payload
     _lib.check(_lib.lib().cocclkAgGemm(a, n, max_ctas, _lib.cur_stream()), "cocclkAgGemm")
     return outs, state
 

@@ -686,20 +686,24 @@ class Communicator:
 
     def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gelu: bool = False,
                 out: torch.Tensor | None = None, *, b_mn: bool = False, save_preact: bool = False,
-                gathered: torch.Tensor | None = None):
+                gathered: torch.Tensor | None = None, payload: str | None = None):
         """concat_over_ranks(x_local) @ w.T (+ bias, GELU) in ONE kernel: the shards travel over peer memory
         while the tensor cores already work on the local shard. x_local [m, K] bf16; w [N, K], or [K, N] with
         b_mn=True (then the product is gather(x) @ w). save_preact: also return the pre-activation (GELU only).
-        gathered: optional [M, K] tensor that receives the gathered input (for a later weight gradient)."""
+        gathered: optional [M, K] tensor that receives the gathered input (for a later weight gradient).
+        payload: "bf16", "fp8" (block-scaled E4M3 on the wire, dequantised on arrival) or None = what the policy's
+        all-gather slot of this communicator's role says (MX-FP8 codec -> "fp8"); COCCL_TP_AG_PAYLOAD overrides."""
         from ..ops import tp_fused as T
         m, K = x_local.shape
+        fp8 = self._ag_payload_fp8(m, K, payload)
         N = w.shape[1] if b_mn else w.shape[0]
         M = m * self.size
         assert x_local.is_contiguous() and w.is_contiguous() and x_local.dtype == torch.bfloat16
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
-        self._ensure_tp(T.ag_ws_bytes(M, K))
+        self._ensure_tp(T.ag_ws_bytes(M, K, T.PAYLOAD_FP8 if fp8 else T.PAYLOAD_BF16))
         a = self._tp_args(M, N, K)
+        a.agPayload = T.PAYLOAD_FP8 if fp8 else T.PAYLOAD_BF16
         a.epi = T.EPI_NONE if bias is None else (T.EPI_BIAS_GELU if gelu else T.EPI_BIAS)
         a.bMN = int(b_mn)
         a.a[self.rank], a.b[self.rank], a.c[self.rank] = x_local.data_ptr(), w.data_ptr(), out.data_ptr()
@@ -726,6 +730,22 @@ class Communicator:
                 _lib.check(cp(gathered.data_ptr() + off, ws + off, (self.size - r - 1) * m * row, st), "cocclDeviceCopy")
             gathered[r * m:(r + 1) * m].copy_(x_local)
         return (out, z) if save_preact else out
+
+    def _ag_payload_fp8(self, m: int, K: int, payload: str | None) -> bool:
+        """Whether the shards of an all-gather fusion travel as block-scaled FP8 (needs whole 32-column blocks)."""
+        forced = os.environ.get("COCCL_TP_AG_PAYLOAD", "") or payload
+        if K % 32 != 0:
+            return False
+        if forced in ("bf16", "fp8"):
+            return forced == "fp8"
+        key = ("ag_payload", m, K)
+        if key not in self._decisions:
+            fp8 = False
+            if self.router is not None:
+                d = self.router.decide(self.role, "all_gather", torch.bfloat16, m * K, self.size, self.rank)
+                fp8 = bool(d.compressed and d.fusable and d.codec.kind == 1)   # 1 = MX-FP8
+            self._decisions[key] = fp8
+        return self._decisions[key]
 
     def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, b_mn: bool = False,
                 bias: torch.Tensor | None = None) -> torch.Tensor:

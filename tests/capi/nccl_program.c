@@ -42,7 +42,7 @@ ncclResult_t ncclCommGetAsyncError(ncclComm_t c, ncclResult_t* e);
 /* One thread per GPU issues the collectives (the layout of the reference's benchmarks, `-t N -g 1`,
  * examples/benchmarks_scripts/communication_benchmarks.sh:73): a compressed call may block on its peers during set-up,
  * so the ranks of one process must not be driven from a single thread. */
-typedef struct { int rank, n; ncclComm_t comm; cudaStream_t stream; size_t count; double worst, norm; int rc; } Job;
+typedef struct { int rank, n; ncclComm_t comm; cudaStream_t stream; size_t count; double err2, ref2; int rc; } Job;
 
 static void* allreduce_thread(void* arg) {
   Job* j = (Job*)arg;
@@ -57,13 +57,13 @@ static void* allreduce_thread(void* arg) {
   if (r != ncclSuccess) { printf("FAIL ncclAllReduce on %d -> %d (%s)\n", j->rank, r, ncclGetErrorString(r)); return NULL; }
   if (cudaStreamSynchronize(j->stream) != cudaSuccess) return NULL;
   cudaMemcpy(host, buf, j->count * sizeof(float), cudaMemcpyDeviceToHost);
-  j->worst = j->norm = 0.0;
+  j->err2 = j->ref2 = 0.0;
   for (size_t k = 0; k < j->count; k += 97) {
     double want = 0.0;
     for (int q = 0; q < j->n; ++q) want += 0.01 * (double)((k * 7 + (size_t)q * 13) % 101) - 0.5;
-    const double d = fabs((double)host[k] - want);
-    if (d > j->worst) j->worst = d;
-    if (fabs(want) > j->norm) j->norm = fabs(want);
+    const double d = (double)host[k] - want;
+    j->err2 += d * d;
+    j->ref2 += want * want;
   }
   ncclResult_t async = ncclSuccess;
   if (ncclCommGetAsyncError(j->comm, &async) != ncclSuccess || async != ncclSuccess) { printf("FAIL async error %d\n", async); return NULL; }
@@ -81,16 +81,17 @@ static int allreduce_case(int n, ncclComm_t* comms, cudaStream_t* streams, size_
     pthread_create(&th[i], NULL, allreduce_thread, &jobs[i]);
   }
   int bad = 0;
-  double worst = 0.0, norm = 0.0;
+  double worst = 0.0;
   for (int i = 0; i < n; ++i) {
     pthread_join(th[i], NULL);
     bad |= jobs[i].rc;
-    if (jobs[i].worst > worst) worst = jobs[i].worst;
-    if (jobs[i].norm > norm) norm = jobs[i].norm;
+    const double rel = sqrt(jobs[i].err2 / (jobs[i].ref2 > 0.0 ? jobs[i].ref2 : 1.0));
+    if (rel > worst) worst = rel;
   }
-  printf("allreduce count=%zu max_abs_err=%.4g of max %.4g\n", count, worst, norm);
+  printf("allreduce count=%zu relative_rms_err=%.4g\n", count, worst);
   if (bad) return 1;
-  return worst <= 0.35 * norm + 1e-5 ? 0 : 1;   /* exact when native, within the 4-bit codec's step when compressed */
+  /* exact when native; a 4-bit code with two encodes (two-shot) stays near 0.2 of the signal's rms */
+  return worst <= 0.3 ? 0 : 1;
 }
 
 int main(int argc, char** argv) {

@@ -139,9 +139,20 @@ def _tp_fused_worker(rank, world):
         b = torch.randn(N, device=dev, dtype=torch.bfloat16)
         xs = [torch.empty_like(x) for _ in range(world)]
         dist.all_gather(xs, x)
-        y = comm.ag_gemm(x, w, bias=b, gelu=True)
+        y = comm.ag_gemm(x, w, bias=b, gelu=True, payload="bf16")
         ref = torch.nn.functional.gelu(torch.cat(xs).float() @ w.float().t() + b.float(), approximate="tanh")
         assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+        # the same product with the shards on the wire as block-scaled FP8: remote shards equal the codec's round trip
+        kept = torch.empty(m * world, K, device=dev, dtype=torch.bfloat16)
+        y8 = comm.ag_gemm(x, w, bias=b, gelu=True, payload="fp8", gathered=kept)
+        from coccl_b200.ops import tp_fused as T8
+        if T8.last_variant() == "2cta":
+            seen = torch.cat([xs[q] if q == rank else C.reference_roundtrip(xs[q].float().contiguous(), C.MXFP8, 1).to(torch.bfloat16)
+                              for q in range(world)])
+            assert torch.equal(kept, seen)
+            ref8 = torch.nn.functional.gelu(seen.float() @ w.float().t() + b.float(), approximate="tanh")
+            assert (y8.float() - ref8).abs().max().item() <= 2e-2 * ref8.abs().max().item() + 1e-3
+        assert ((y8.float() - ref).norm() / ref.norm()).item() < 0.05
         # second half of the MLP: y [M, N] @ w2[N2, N]^T, partial sums reduce-scattered as FP8
         w2 = torch.randn(512, N, device=dev, dtype=torch.bfloat16) * 0.05
         out = comm.gemm_rs(y, w2)

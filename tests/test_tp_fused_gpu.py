@@ -95,3 +95,32 @@ def test_weights_stored_contraction_major(cuda):
     for r in range(n):
         ref = exact[r * m:(r + 1) * m]
         assert ((outs[r].float() - ref).norm() / ref.norm()).item() < 0.05
+
+
+@pytest.mark.parametrize("n,m,N,K,keep", [(2, 256, 512, 256, False), (4, 256, 264, 1024, True), (2, 1024, 1024, 4096, True)])
+def test_ag_gemm_fp8_payload_emulated(cuda, n, m, N, K, keep):
+    """Shards that cross between ranks as E4M3 + UE8M0 scales: a rank's own shard stays exact, every remote shard equals
+    the MX-FP8 codec's round trip (32 columns per block), bit for bit, in the gathered copy, and the product follows."""
+    T.set_variant("auto")
+    torch.manual_seed(5)
+    xs = [torch.randn(m, K, device=cuda, dtype=torch.bfloat16) * (0.5 + r) for r in range(n)]
+    ws = [torch.randn(N, K, device=cuda, dtype=torch.bfloat16) * 0.05 for _ in range(n)]
+    xq = [C.reference_roundtrip(x.float().contiguous(), C.MXFP8, 1).to(torch.bfloat16) for x in xs]
+    state = {}
+    for epoch in (1, 2):
+        kept = [torch.zeros(m * n, K, device=cuda, dtype=torch.bfloat16) for _ in range(n)] if keep else None
+        outs, state = T.emulate_ag_gemm(xs, ws, state=state, epoch=epoch, max_ctas=148 // n, payload=T.PAYLOAD_FP8, gathered=kept)
+        torch.cuda.synchronize()
+        T.check_state(state)
+        assert T.last_variant() == "2cta"
+        for r in range(n):
+            seen = torch.cat([xs[q] if q == r else xq[q] for q in range(n)])   # what rank r multiplies
+            if keep:
+                assert torch.equal(kept[r], seen), (r, (kept[r].float() - seen.float()).abs().max().item())
+            ref = seen.float() @ ws[r].float().t()
+            err = (outs[r].float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-3, (r, err)
+            exact = torch.cat(xs).float() @ ws[r].float().t()
+            assert ((outs[r].float() - exact).norm() / exact.norm()).item() < 0.05
+        xs = [x * 0.5 for x in xs]
+        xq = [C.reference_roundtrip(x.float().contiguous(), C.MXFP8, 1).to(torch.bfloat16) for x in xs]
