@@ -145,3 +145,19 @@ def ptr(t) -> int | None:
 def cur_stream() -> int:
     import torch
     return torch.cuda.current_stream().cuda_stream
+
+
+class _RawCudaMemory:
+    """Exposes a device address range through __cuda_array_interface__ so that torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.owner = owner   # kept alive for as long as the tensor lives
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device, owner=None):
+    """uint8 tensor over device memory that this library allocated itself (symmetric buffers). The memory must stay
+    valid while the tensor or any view of it is in use; `owner` is an object the tensor keeps alive."""
+    import torch
+    return torch.as_tensor(_RawCudaMemory(ptr, nbytes, owner), device=device)

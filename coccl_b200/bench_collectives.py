@@ -107,6 +107,34 @@ def _reference(a) -> None:
     subprocess.run(cmd, check=False)
 
 
+def table(path: str, min_mib: float) -> None:
+    """Markdown table of a sweep written with --out: time per codec, speed-up over NCCL and bus bandwidth."""
+    with open(path) as f:
+        d = json.load(f)
+    names = [k[:-3] for k in d["rows"][0] if k.endswith("_ms") and k != "native_ms"]
+    head = ["op", "dtype", "MiB", "native ms"] + [f"{n} ms" for n in names] + [f"{n} x" for n in names] + \
+           ["native busbw"] + [f"{n} busbw" for n in names]
+    print("| " + " | ".join(head) + " |")
+    print("|" + "---|" * len(head))
+    for r in d["rows"]:
+        mib = r["bytes"] / (1 << 20)
+        if mib < min_mib:
+            continue
+        cells = [r["op"], r["dtype"], f"{mib:g}", f"{r['native_ms']:.3f}"]
+        cells += [f"{r[n + '_ms']:.3f}" for n in names]
+        cells += [f"{r['native_ms'] / r[n + '_ms']:.2f}" for n in names]
+        cells += [f"{r['native_busbw_gbs']:.0f}"] + [f"{r[n + '_busbw_gbs']:.0f}" for n in names]
+        print("| " + " | ".join(cells) + " |")
+    for name, info in d.get("routing", {}).items():
+        log = info.get("measured") if isinstance(info, dict) else None
+        if log:
+            print(f"\nselector input measured by communicator '{name}' (policy {info.get('policy_hash')}):")
+            for m in log:
+                times = ", ".join(f"{k[:-3]} {v:.1f} us" for k, v in m.items() if k.endswith("_us"))
+                print(f"  {m['what']} {m['dtype'].replace('torch.', '')} {m['bytes'] / (1 << 20):g} MiB: {times}")
+            break
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-mib", type=float, default=1)
@@ -123,7 +151,11 @@ def main():
                     help="reference: run the reference's own stock *_perf binaries (baseline/run_reference.py), "
                          "nothing of this library; launch WITHOUT torchrun, with --gpus N")
     ap.add_argument("--gpus", type=int, default=2, help="--impl reference only: ranks of the single-process run")
+    ap.add_argument("--table", default="", metavar="JSON", help="print the markdown table of an earlier --out file and exit")
+    ap.add_argument("--table-min-mib", type=float, default=16)
     a = ap.parse_args()
+    if a.table:
+        return table(a.table, a.table_min_mib)
     if a.impl == "reference":
         return _reference(a)
 

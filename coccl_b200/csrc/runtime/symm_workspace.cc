@@ -7,7 +7,7 @@ namespace coccl {
 
 const SymmApi& cudaSymmApi() {
   static const SymmApi api = {&cocclSymmAlloc, &cocclSymmExport, &cocclSymmImport, &cocclSymmLocalPtr,
-                              &cocclSymmCloseImports, &cocclSymmFree};
+                              &cocclSymmCloseImports, &cocclSymmFree, &cocclSymmGrow};
   return api;
 }
 
@@ -49,6 +49,26 @@ bool SymmRegion::reopen(const SymmApi& api, HostExchange& x, size_t bytes) {
   // 1. size agreement; also the rendezvous after which nobody uses the old mapping
   int64_t need = 0;
   if (!agree(x, (int64_t)bytes, nullptr, &need)) { closeLocal(api); return false; }
+  // in place, where the backend can: grow, export, exchange, map the new chunks; every rank learns whether all managed
+  if (buf_ && api.grow != nullptr) {
+    Offer mine;
+    memset(&mine, 0, sizeof(mine));
+    mine.ok = api.grow(buf_, (size_t)need) == 0 && api.exportHandle(buf_, mine.handle) == 0 ? 1 : 0;
+    std::vector<Offer> all((size_t)n);
+    bool ok = x.allGather(&mine, all.data(), sizeof(Offer));
+    for (int p = 0; ok && p < n; ++p) ok = all[p].ok == 1;
+    for (int p = 0; ok && p < n; ++p) {
+      if (p == me) continue;
+      void* again = nullptr;
+      ok = api.importPeer(buf_, p, all[p].handle, &again) == 0 && again == ptrs_[p];
+    }
+    int64_t everyone = 0;
+    if (agree(x, ok ? 1 : 0, &everyone, nullptr) && everyone == 1) {
+      bytes_ = (size_t)need;
+      return true;
+    }
+    // some rank could not (IPC-backed buffer, address range exhausted, ...): all ranks start over below
+  }
   // 2. old region: imports first, allocations after everybody has unmapped
   if (buf_) api.closeImports(buf_);
   if (!agree(x, 1, nullptr, nullptr)) { closeLocal(api); return false; }

@@ -11,6 +11,9 @@
 //   3. allocate, export; all-gather {ok, handle}; import every peer
 //   4. all-gather the outcome; unless EVERY rank succeeded, every rank unwinds (close imports, meet, free)
 //      and returns false, so that all of them take the same fallback
+// With a backend that can grow a buffer in place (cuMem VMM) steps 2-3 become "grow, export, all-gather, import the
+// new chunks": nothing is unmapped or freed and no pointer changes; if that fails on any rank, all ranks close the
+// region and open a fresh one by the steps above.
 //
 // The reference grows its workspace in place with cuMem VMM and never unmaps
 // (src/coccl-extend/core/memory/coccl_buffer_vmm.cc:200-240); a failure there is local because NCCL moves the
@@ -33,6 +36,9 @@ struct SymmApi {
   void* (*localPtr)(const cocclSymmBuffer* buf);
   int (*closeImports)(cocclSymmBuffer* buf);
   int (*free)(cocclSymmBuffer* buf);
+  // Optional (null where the backend cannot): make the buffer longer where it is. Peers then import the buffer's new
+  // export handle, which maps only what they do not have yet and leaves every pointer as it was.
+  int (*grow)(cocclSymmBuffer* buf, size_t bytes);
 };
 const SymmApi& cudaSymmApi();
 

@@ -1,17 +1,13 @@
-// CUDA-IPC backend of the symmetric memory interface (symm.h).
+// Symmetric memory interface (symm.h): the CUDA-IPC backend, and the dispatch to the cuMem VMM backend (symm_vmm.cc)
+// for buffers that were allocated by it.
 #include "symm.h"
+#include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 #include <new>
 #include <vector>
 
-struct cocclSymmBuffer {
-  void* local = nullptr;
-  size_t bytes = 0;
-  int device = -1;
-  std::vector<void*> imported;  // by peer index; nullptr = not mapped
-  std::vector<char> direct;     // by peer index; 1 = same-process pointer, nothing to close
-};
+#include "symm/symm_internal.h"
 
 namespace {
 // What follows the IPC handle inside an export handle.
@@ -27,8 +23,34 @@ static_assert(kIpcBytes + sizeof(SameProcess) <= COCCL_SYMM_HANDLE_BYTES, "expor
 
 extern "C" int cocclSymmHandleBytes(void) { return COCCL_SYMM_HANDLE_BYTES; }
 
+namespace coccl {
+static int gBackend = -1;
+int symmBackend() {
+  if (gBackend < 0) {
+    const char* v = getenv("COCCL_SYMM_BACKEND");
+    gBackend = (v && strcmp(v, "vmm") == 0) ? COCCL_SYMM_BACKEND_VMM : COCCL_SYMM_BACKEND_IPC;
+  }
+  return gBackend;
+}
+}  // namespace coccl
+
+extern "C" int cocclSymmSetBackend(int backend) {
+  if (backend != COCCL_SYMM_BACKEND_IPC && backend != COCCL_SYMM_BACKEND_VMM) return (int)cudaErrorInvalidValue;
+  if (backend == COCCL_SYMM_BACKEND_VMM && !coccl::vmmAvailable()) return (int)cudaErrorNotSupported;
+  coccl::gBackend = backend;
+  return 0;
+}
+extern "C" int cocclSymmGetBackend(void) { return coccl::symmBackend(); }
+
+extern "C" int cocclSymmGrow(cocclSymmBuffer* buf, size_t bytes) {
+  if (!buf) return (int)cudaErrorInvalidValue;
+  if (!buf->vmm) return (int)cudaErrorNotSupported;   // cudaMalloc'd memory cannot grow where it is
+  return coccl::vmmGrow(buf, bytes);
+}
+
 extern "C" int cocclSymmAlloc(size_t bytes, cocclSymmBuffer** out) {
   if (out == nullptr || bytes == 0) return (int)cudaErrorInvalidValue;
+  if (coccl::symmBackend() == COCCL_SYMM_BACKEND_VMM) return coccl::vmmAlloc(bytes, out);
   cocclSymmBuffer* b = new (std::nothrow) cocclSymmBuffer();
   if (!b) return (int)cudaErrorMemoryAllocation;
   cudaError_t e = cudaGetDevice(&b->device);
@@ -47,6 +69,7 @@ extern "C" int cocclSymmAlloc(size_t bytes, cocclSymmBuffer** out) {
 
 extern "C" int cocclSymmExport(const cocclSymmBuffer* buf, void* handle) {
   if (!buf || !handle) return (int)cudaErrorInvalidValue;
+  if (buf->vmm) return coccl::vmmExport(buf, handle);
   cudaIpcMemHandle_t h;
   cudaError_t e = cudaIpcGetMemHandle(&h, buf->local);
   if (e != cudaSuccess) return (int)e;
@@ -59,6 +82,7 @@ extern "C" int cocclSymmExport(const cocclSymmBuffer* buf, void* handle) {
 
 extern "C" int cocclSymmImport(cocclSymmBuffer* owner, int peerIndex, const void* handle, void** mapped) {
   if (!owner || !handle || !mapped || peerIndex < 0) return (int)cudaErrorInvalidValue;
+  if (owner->vmm) return coccl::vmmImport(owner, peerIndex, handle, mapped);
   if ((size_t)peerIndex >= owner->imported.size()) { owner->imported.resize(peerIndex + 1, nullptr); owner->direct.resize(peerIndex + 1, 0); }
   SameProcess sp;
   memcpy(&sp, static_cast<const char*>(handle) + kIpcBytes, sizeof(sp));
@@ -100,6 +124,7 @@ extern "C" size_t cocclSymmBytes(const cocclSymmBuffer* buf) { return buf ? buf-
 
 extern "C" int cocclSymmCloseImports(cocclSymmBuffer* buf) {
   if (!buf) return 0;
+  if (buf->vmm) return coccl::vmmCloseImports(buf);
   cudaError_t first = cudaSuccess;
   for (size_t i = 0; i < buf->imported.size(); ++i) {
     void*& p = buf->imported[i];
@@ -114,6 +139,7 @@ extern "C" int cocclSymmCloseImports(cocclSymmBuffer* buf) {
 
 extern "C" int cocclSymmFree(cocclSymmBuffer* buf) {
   if (!buf) return 0;
+  if (buf->vmm) return coccl::vmmFree(buf);
   cudaError_t first = (cudaError_t)cocclSymmCloseImports(buf);
   if (buf->local) {
     cudaError_t e = cudaFree(buf->local);

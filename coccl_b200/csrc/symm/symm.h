@@ -9,8 +9,12 @@
 // thing the fused kernels need. Handle exchange itself is left to the caller
 // (torch.distributed store, NCCL all-gather, a socket): handles are plain bytes.
 //
-// This interface is the CUDA-IPC backend (cudaMalloc + 64-byte IPC handles). The cuMem VMM backend with
-// POSIX file descriptors and the NVSwitch multicast binding is symm_vmm.h.
+// Two backends sit behind this interface. CUDA IPC (default): cudaMalloc + 64-byte IPC handles; growing means a new
+// allocation and a new mapping on every peer. cuMem VMM (COCCL_SYMM_BACKEND=vmm or cocclSymmSetBackend): physical
+// chunks from cuMemCreate, exported as POSIX file descriptors that travel between processes over a Unix socket
+// (fd_channel.h), mapped into a virtual range that is reserved larger than the buffer, so that cocclSymmGrow adds
+// chunks behind the existing ones and every pointer stays valid; such a buffer can also be bound to an NVSwitch
+// multicast object (cocclSymmMulticast*), which gives the multimem kernels one address that reaches every rank.
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -41,6 +45,32 @@ size_t cocclSymmBytes(const cocclSymmBuffer* buf);
 int cocclSymmCloseImports(cocclSymmBuffer* buf);
 // Unmap every imported peer (if still mapped) and free the local allocation.
 int cocclSymmFree(cocclSymmBuffer* buf);
+
+enum { COCCL_SYMM_BACKEND_IPC = 0, COCCL_SYMM_BACKEND_VMM = 1 };
+// Backend of the buffers allocated from now on (existing buffers keep theirs). VMM is refused with
+// cudaErrorNotSupported where the driver lacks cuMem or POSIX-descriptor handles.
+int cocclSymmSetBackend(int backend);
+int cocclSymmGetBackend(void);
+// VMM buffers only: make the buffer at least `bytes` long WITHOUT moving it. The local pointer and every mapping a
+// peer holds stay valid; peers see the new part after they import the buffer's next export handle (the import maps
+// only the chunks it does not have yet and returns the same pointer). Collective use: every rank grows, exports,
+// the handles are exchanged, every rank imports every peer again.
+int cocclSymmGrow(cocclSymmBuffer* buf, size_t bytes);
+
+// ---- NVSwitch multicast over a VMM buffer (collective; the caller moves the small handles between the ranks) ----
+// 1. the root calls cocclSymmMulticastCreate(buf, nRanks, handle) and sends `handle` to every rank;
+// 2. every rank (the root too) calls cocclSymmMulticastJoin(buf, handle): imports the object where needed and adds
+//    its device; ALL ranks must have joined before any of them binds (the caller's barrier);
+// 3. every rank calls cocclSymmMulticastBind(buf, &ptr): binds the first chunk of its buffer and maps the object;
+//    `ptr` is the multicast address of byte 0 of the buffer;
+// 4. teardown: every rank calls cocclSymmMulticastUnbind while all ranks are still alive, the ranks meet, then the
+//    buffers are freed as usual. A rank must not exit with its memory still bound.
+// The multicast range covers the buffer as it was when the object was created (later growth is not part of it).
+int cocclSymmMulticastSupported(void);
+int cocclSymmMulticastCreate(cocclSymmBuffer* buf, int nRanks, void* handle);
+int cocclSymmMulticastJoin(cocclSymmBuffer* buf, const void* handle);
+int cocclSymmMulticastBind(cocclSymmBuffer* buf, void** multicastPtr);
+int cocclSymmMulticastUnbind(cocclSymmBuffer* buf);
 
 #ifdef __cplusplus
 }

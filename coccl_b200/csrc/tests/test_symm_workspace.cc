@@ -4,6 +4,7 @@
 #include <condition_variable>
 #include <mutex>
 #include <string.h>
+#include <atomic>
 #include <thread>
 
 #include "host_test.h"
@@ -113,6 +114,22 @@ int fFree(cocclSymmBuffer* b) {
 }
 const SymmApi kFakeApi = {&fAlloc, &fExport, &fImport, &fLocal, &fCloseImports, &fFree};
 
+// a backend that grows where it is (the cuMem VMM one): same fake, plus grow
+int gFailGrowOnRank = -1;
+std::atomic<int> gGrows{0};
+int fGrow(cocclSymmBuffer* b, size_t bytes) {
+  if (gFailGrowOnRank == tRank) return 3;
+  if (bytes > b->bytes) b->bytes = bytes;
+  ++gGrows;
+  return 0;
+}
+// importing a peer a second time maps "the new chunks" and must not count as a second live mapping
+int fImportAgain(cocclSymmBuffer* owner, int peer, const void* h, void** mapped) {
+  if (owner->mapped[peer]) { *mapped = reinterpret_cast<void*>((uintptr_t)(0x1000 * (peer + 1))); return 0; }
+  return fImport(owner, peer, h, mapped);
+}
+const SymmApi kGrowingApi = {&fAlloc, &fExport, &fImportAgain, &fLocal, &fCloseImports, &fFree, &fGrow};
+
 template <class F>
 void runRanks(F&& body) {
   std::vector<std::thread> th;
@@ -144,6 +161,38 @@ TEST(symm_region_opens_grows_and_closes_in_order) {
   runRanks([&](int r) { ThreadExchange x(r); regions[r].close(kFakeApi, x); });
   EXPECT_EQ(w.frees, 2 * kRanks);
   EXPECT_EQ(w.freedWhileMapped, 0);
+  for (int r = 0; r < kRanks; ++r) EXPECT_EQ(w.liveImportsOf[r], 0);
+}
+
+TEST(symm_region_grows_in_place_where_the_backend_can) {
+  World w;
+  gWorld = &w;
+  gFailGrowOnRank = -1;
+  gGrows = 0;
+  SymmRegion regions[kRanks];
+  bool ok1[kRanks], ok2[kRanks], ok3[kRanks];
+  runRanks([&](int r) {
+    ThreadExchange x(r);
+    ok1[r] = regions[r].reopen(kGrowingApi, x, 1000);
+    ok2[r] = regions[r].reopen(kGrowingApi, x, 5000 + r);   // in place: nothing freed, nothing unmapped
+  });
+  for (int r = 0; r < kRanks; ++r) {
+    EXPECT(ok1[r] && ok2[r]);
+    EXPECT_EQ(regions[r].bytes(), (size_t)(5000 + kRanks - 1));
+  }
+  EXPECT_EQ(w.allocs, kRanks);
+  EXPECT_EQ(w.frees, 0);
+  EXPECT_EQ((int)gGrows, kRanks);
+  for (int r = 0; r < kRanks; ++r) EXPECT_EQ(w.liveImportsOf[r], kRanks - 1);
+  // one rank cannot grow (its address range is used up): every rank closes and opens a fresh region together
+  gFailGrowOnRank = 1;
+  runRanks([&](int r) { ThreadExchange x(r); ok3[r] = regions[r].reopen(kGrowingApi, x, 20000); });
+  for (int r = 0; r < kRanks; ++r) { EXPECT(ok3[r]); EXPECT_EQ(regions[r].bytes(), (size_t)20000); }
+  EXPECT_EQ(w.allocs, 2 * kRanks);
+  EXPECT_EQ(w.frees, kRanks);
+  EXPECT_EQ(w.freedWhileMapped, 0);
+  gFailGrowOnRank = -1;
+  runRanks([&](int r) { ThreadExchange x(r); regions[r].close(kGrowingApi, x); });
   for (int r = 0; r < kRanks; ++r) EXPECT_EQ(w.liveImportsOf[r], 0);
 }
 

@@ -201,7 +201,8 @@ class _Symm:
     frees its allocation only after every peer has unmapped it, and a failure on one rank makes every rank raise
     SymmUnavailable, so that all of them leave the fused path at the same call."""
 
-    def __init__(self, comm: "Communicator", nbytes: int, replaces: "_Symm | None" = None):
+    def __init__(self, comm: "Communicator", nbytes: int, replaces: "_Symm | None" = None, backend: int | None = None):
+        """backend: None = the process default (COCCL_SYMM_BACKEND), 0 = CUDA IPC, 1 = cuMem VMM for this region only."""
         lib = _lib.lib()
         self._alloc = _lib.declare("cocclSymmAlloc", C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)])
         self._export = _lib.declare("cocclSymmExport", C.c_int, [C.c_void_p, C.c_void_p])
@@ -209,6 +210,11 @@ class _Symm:
         self._local = _lib.declare("cocclSymmLocalPtr", C.c_void_p, [C.c_void_p])
         self._close = _lib.declare("cocclSymmCloseImports", C.c_int, [C.c_void_p])
         self._free = _lib.declare("cocclSymmFree", C.c_int, [C.c_void_p])
+        self._grow = _lib.declare("cocclSymmGrow", C.c_int, [C.c_void_p, C.c_size_t])
+        get_backend = _lib.declare("cocclSymmGetBackend", C.c_int, [])
+        set_backend = _lib.declare("cocclSymmSetBackend", C.c_int, [C.c_int])
+        default_backend = int(get_backend())
+        self.backend = default_backend if backend is None else backend   # 0: CUDA IPC, 1: cuMem VMM
         self.handle, self.nbytes, self.ptrs = None, nbytes, []
         if replaces is not None:
             # nobody's kernels use the old mapping any more, then nobody maps it, then it is freed
@@ -220,7 +226,9 @@ class _Symm:
         h = C.c_void_p()
         hbytes = int(_lib.declare("cocclSymmHandleBytes", C.c_int, [])())
         buf = C.create_string_buffer(hbytes)
-        ok = self._alloc(nbytes, C.byref(h)) == 0 and self._export(h, buf) == 0
+        ok = self.backend == default_backend or set_backend(self.backend) == 0
+        ok = ok and self._alloc(nbytes, C.byref(h)) == 0 and self._export(h, buf) == 0
+        set_backend(default_backend)
         self.handle = h if h.value else None
         offers = [None] * comm.size
         dist.all_gather_object(offers, (ok, bytes(buf.raw)), group=comm.group)
@@ -244,6 +252,43 @@ class _Symm:
             self.free()
             raise SymmUnavailable(f"peer memory of group '{comm.name}' could not be mapped on ranks "
                                   f"{[i for i, o in enumerate(outcome) if not o]}")
+
+    @classmethod
+    def resized(cls, comm: "Communicator", old: "_Symm | None", nbytes: int) -> "_Symm":
+        """Collective: a region of at least `nbytes` in place of `old`. A cuMem VMM region grows where it is (no pointer
+        on any rank changes, nothing is unmapped); otherwise, or when that fails on some rank, the old region is closed
+        and a new one opened by the protocol of __init__."""
+        if old is not None and old.backend == 1 and old.grow(comm, nbytes):
+            return old
+        return cls(comm, nbytes, replaces=old)
+
+    def grow(self, comm: "Communicator", nbytes: int) -> bool:
+        """Collective, VMM regions only: every rank adds physical chunks behind its buffer, the new export handles are
+        exchanged and every rank maps the new chunks of every peer behind the old ones. True only if every rank
+        managed and every pointer is what it was."""
+        torch.cuda.synchronize()
+        dist.barrier(group=comm.group)   # nobody's kernels still use the old extent (callers re-split the region)
+        hbytes = int(_lib.declare("cocclSymmHandleBytes", C.c_int, [])())
+        buf = C.create_string_buffer(hbytes)
+        ok = self._grow(self.handle, nbytes) == 0 and self._export(self.handle, buf) == 0
+        offers = [None] * comm.size
+        dist.all_gather_object(offers, (ok, bytes(buf.raw)), group=comm.group)
+        ok = all(o[0] for o in offers)
+        if ok:
+            for p in range(comm.size):
+                if p == comm.rank:
+                    continue
+                m = C.c_void_p()
+                hb = C.create_string_buffer(offers[p][1], hbytes)
+                if self._import(self.handle, p, hb, C.byref(m)) != 0 or m.value != self.ptrs[p]:
+                    ok = False
+                    break
+        outcome = [None] * comm.size
+        dist.all_gather_object(outcome, ok, group=comm.group)
+        if all(outcome):
+            self.nbytes = nbytes
+            return True
+        return False
 
     def close_imports(self):
         if self.handle is not None:
@@ -270,7 +315,7 @@ class _Arena:
         if self.ws is None or self.half < half_bytes:
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
             old, self.ws, self.half = self.ws, None, 0
-            self.ws = _Symm(self.comm, 2 * half, replaces=old)
+            self.ws = _Symm.resized(self.comm, old, 2 * half)
             self.half = half
 
     def next(self):
@@ -342,7 +387,7 @@ class Communicator:
         if self._ws is None or self._ws_half < half_bytes:
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
             old, self._ws, self._ws_half = self._ws, None, 0
-            self._ws = _Symm(self, 2 * half, replaces=old)
+            self._ws = _Symm.resized(self, old, 2 * half)
             self._ws_half = half
 
     def _leave_fused_path(self, why: Exception) -> None:
@@ -487,14 +532,20 @@ class Communicator:
             return self._nvls["mc"] != 0
         if self._nvls is not None and self._nvls["mc"] == 0:
             return False
-        import torch.distributed._symmetric_memory as symm_mem
         size = max(nbytes, 64 << 20)
-        try:
-            t = symm_mem.empty(size, dtype=torch.uint8, device=self.device)
-            h = symm_mem.rendezvous(t, (self.group or dist.group.WORLD).group_name)
-            mc = int(h.multicast_ptr or 0)
-        except Exception:  # noqa: BLE001 - no symmetric memory support in this build / on this fabric
-            t, h, mc = None, None, 0
+        if self._nvls is not None and isinstance(self._nvls.get("h"), _Symm):   # a larger region replaces the old one
+            old = self._nvls["h"]
+            self._nvls["t"] = self._nvls["h"] = None
+            self._release_own_multicast(old)
+        t, h, mc = self._own_multicast(size) if os.environ.get("COCCL_NVLS_BACKEND", "own") == "own" else (None, None, 0)
+        if mc == 0:
+            import torch.distributed._symmetric_memory as symm_mem
+            try:
+                t = symm_mem.empty(size, dtype=torch.uint8, device=self.device)
+                h = symm_mem.rendezvous(t, (self.group or dist.group.WORLD).group_name)
+                mc = int(h.multicast_ptr or 0)
+            except Exception:  # noqa: BLE001 - no symmetric memory support in this build / on this fabric
+                t, h, mc = None, None, 0
         ok = torch.tensor([1 if mc else 0], device=self.device)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         if int(ok.item()) == 0:
@@ -503,6 +554,61 @@ class Communicator:
         epoch = self._nvls["epoch"] if self._nvls is not None else 0
         self._nvls = {"t": t, "h": h, "mc": mc, "bytes": size, "flags": flags, "epoch": epoch, "used": 0}
         return mc != 0
+
+    def _own_multicast(self, size: int):
+        """(tensor over the local buffer, region, multicast address) from this library's own cuMem VMM region bound to an
+        NVSwitch multicast object (csrc/symm/symm_vmm.cc), or (None, None, 0) on every rank when any rank cannot."""
+        supported = _lib.declare("cocclSymmMulticastSupported", C.c_int, [])
+        ok = torch.tensor([1 if supported() == 1 else 0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            return None, None, 0
+        try:
+            region = _Symm(self, size, backend=1)
+        except SymmUnavailable:
+            return None, None, 0
+        create = _lib.declare("cocclSymmMulticastCreate", C.c_int, [C.c_void_p, C.c_int, C.c_void_p])
+        join = _lib.declare("cocclSymmMulticastJoin", C.c_int, [C.c_void_p, C.c_void_p])
+        bind = _lib.declare("cocclSymmMulticastBind", C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)])
+        hbytes = int(_lib.declare("cocclSymmHandleBytes", C.c_int, [])())
+        blob = C.create_string_buffer(hbytes)
+        made = create(region.handle, self.size, blob) == 0 if self.rank == 0 else True
+        box = [(made, bytes(blob.raw))]
+        root = dist.get_global_rank(self.group, 0) if self.group is not None else 0
+        dist.broadcast_object_list(box, src=root, group=self.group)
+
+        def agreed(flag: bool) -> bool:   # also the barrier the protocol needs between its steps
+            v = torch.tensor([1 if flag else 0], device=self.device)
+            dist.all_reduce(v, op=dist.ReduceOp.MIN, group=self.group)
+            return int(v.item()) == 1
+
+        good = box[0][0]
+        if good:
+            good = join(region.handle, C.create_string_buffer(box[0][1], hbytes)) == 0
+        good = agreed(good)            # every device has been added before anyone binds
+        ptr = C.c_void_p()
+        if good:
+            good = bind(region.handle, C.byref(ptr)) == 0 and bool(ptr.value)
+        good = agreed(good)
+        if not good:
+            self._release_own_multicast(region)
+            return None, None, 0
+        t = _lib.tensor_from_ptr(region.ptrs[self.rank], size, self.device, owner=region)
+        return t, region, int(ptr.value)
+
+    def _release_own_multicast(self, region) -> None:
+        """Collective and ordered: unbind while every rank is alive, meet, unmap the peers, meet, free."""
+        unbind = _lib.declare("cocclSymmMulticastUnbind", C.c_int, [C.c_void_p])
+        torch.cuda.synchronize()
+        if self.size > 1:
+            dist.barrier(group=self.group)
+        unbind(region.handle)
+        if self.size > 1:
+            dist.barrier(group=self.group)
+        region.close_imports()
+        if self.size > 1:
+            dist.barrier(group=self.group)
+        region.free()
 
     def symmetric_tensor(self, numel: int, dtype: torch.dtype) -> torch.Tensor | None:
         """A tensor inside this communicator's multicast-bound symmetric buffer (None when the fabric has no
@@ -667,7 +773,7 @@ class Communicator:
         if self._tp_ws is None or self._tp_half < half_bytes:
             half = -(-max(half_bytes, 1 << 20) // (1 << 20)) * (1 << 20)
             old, self._tp_ws, self._tp_half = self._tp_ws, None, 0
-            self._tp_ws = _Symm(self, 2 * half, replaces=old)
+            self._tp_ws = _Symm.resized(self, old, 2 * half)
             self._tp_half = half
 
     def _tp_args(self, M: int, N: int, K: int):
@@ -981,4 +1087,10 @@ class Communicator:
         for x in arenas:
             if x is not None:
                 x.free()
+        if self._nvls is not None and isinstance(self._nvls.get("h"), _Symm):
+            region = self._nvls["h"]
+            self._nvls["t"] = None
+            self._nvls["h"] = None
+            self._nvls["mc"] = 0
+            self._release_own_multicast(region)
         self._ws = self._sig = self._tp_ws = self._tp_sig = self._moe = None
