@@ -27,8 +27,12 @@ namespace coccl {
 static int gBackend = -1;
 int symmBackend() {
   if (gBackend < 0) {
+    // default: cuMem VMM where the driver offers it (buffers grow in place, multicast can be bound), CUDA IPC otherwise;
+    // COCCL_SYMM_BACKEND=ipc|vmm forces one
     const char* v = getenv("COCCL_SYMM_BACKEND");
-    gBackend = (v && strcmp(v, "vmm") == 0) ? COCCL_SYMM_BACKEND_VMM : COCCL_SYMM_BACKEND_IPC;
+    if (v && strcmp(v, "ipc") == 0) gBackend = COCCL_SYMM_BACKEND_IPC;
+    else if (v && strcmp(v, "vmm") == 0) gBackend = COCCL_SYMM_BACKEND_VMM;
+    else gBackend = vmmAvailable() ? COCCL_SYMM_BACKEND_VMM : COCCL_SYMM_BACKEND_IPC;
   }
   return gBackend;
 }

@@ -9,8 +9,8 @@
 // thing the fused kernels need. Handle exchange itself is left to the caller
 // (torch.distributed store, NCCL all-gather, a socket): handles are plain bytes.
 //
-// Two backends sit behind this interface. CUDA IPC (default): cudaMalloc + 64-byte IPC handles; growing means a new
-// allocation and a new mapping on every peer. cuMem VMM (COCCL_SYMM_BACKEND=vmm or cocclSymmSetBackend): physical
+// Two backends sit behind this interface. CUDA IPC (COCCL_SYMM_BACKEND=ipc, or where cuMem is missing): cudaMalloc +
+// 64-byte IPC handles; growing means a new allocation and a new mapping on every peer. cuMem VMM (the default): physical
 // chunks from cuMemCreate, exported as POSIX file descriptors that travel between processes over a Unix socket
 // (fd_channel.h), mapped into a virtual range that is reserved larger than the buffer, so that cocclSymmGrow adds
 // chunks behind the existing ones and every pointer stays valid; such a buffer can also be bound to an NVSwitch

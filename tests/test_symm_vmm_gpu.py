@@ -31,6 +31,7 @@ def _api():
 def test_vmm_buffer_grows_where_it_is(cuda):
     from coccl_b200 import _lib
     a = _api()
+    before = a["get"]()
     if a["set"](1) != 0:
         pytest.skip("cuMem VMM with POSIX descriptors is not available on this device")
     try:
@@ -56,7 +57,7 @@ def test_vmm_buffer_grows_where_it_is(cuda):
         del t, big
         assert a["free"](g) == 0 and a["free"](h) == 0
     finally:
-        a["set"](0)
+        a["set"](before)
 
 
 def _collectives_over_vmm(rank, world):
