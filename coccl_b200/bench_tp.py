@@ -108,7 +108,7 @@ def main():
     y1, y0 = fused().float(), unfused().float()
     rel = ((y1 - y0).norm() / y0.norm()).item()
     res = {"what": "tp_mlp", "n_gpus": world, "tokens": T, "hidden": H, "ffn": F, "rel_diff_fused_vs_unfused": rel}
-    res["ag_payload_by_policy"] = "fp8" if comm._ag_payload_fp8(T // world, H, None) else "bf16"
+    res["ag_payload_by_policy"] = "fp8" if (comm._ag_payload_fp8(T // world, H, None) and comm._ag_payload_pays(T // world, H, f)) else "bf16"
     y8, yb = fused_up_fp8().float(), fused_up_bf16().float()
     res["rel_diff_ag_fp8_vs_bf16"] = ((y8 - yb).norm() / yb.norm()).item()
     for name, fn in (("ag_gemm_fused", fused_up), ("ag_gemm_fused_bf16", fused_up_bf16), ("ag_gemm_fused_fp8", fused_up_fp8),

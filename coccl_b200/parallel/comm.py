@@ -802,6 +802,9 @@ class Communicator:
         from ..ops import tp_fused as T
         m, K = x_local.shape
         fp8 = self._ag_payload_fp8(m, K, payload)
+        if fp8 and payload is None and not os.environ.get("COCCL_TP_AG_PAYLOAD") and \
+                not self._ag_payload_pays(m, K, w.shape[1] if b_mn else w.shape[0]):
+            fp8 = False
         N = w.shape[1] if b_mn else w.shape[0]
         M = m * self.size
         assert x_local.is_contiguous() and w.is_contiguous() and x_local.dtype == torch.bfloat16
@@ -852,6 +855,16 @@ class Communicator:
                 fp8 = bool(d.compressed and d.fusable and d.codec.kind == 1)   # 1 = MX-FP8
             self._decisions[key] = fp8
         return self._decisions[key]
+
+    def _ag_payload_pays(self, m: int, K: int, n_out: int) -> bool:
+        """Inside the fusion the shards travel behind the tensor cores' work on the local shard, so halving the bytes
+        helps only when the wire would otherwise be the longer of the two: bf16 bytes over the measured 770 GB/s per
+        direction against the GEMM at the measured sustained 1.4 PFLOP/s (at 4 ranks and the MLP shapes the FP8
+        payload was measured 1.46x SLOWER than bf16: the dequantisation on arrival is serial work the bf16 path does
+        not have)."""
+        wire_s = (self.size - 1) * m * K * 2 / 770e9
+        gemm_s = 2.0 * m * self.size * n_out * K / 1.4e15
+        return wire_s > gemm_s
 
     def gemm_rs(self, a_mat: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, b_mn: bool = False,
                 bias: torch.Tensor | None = None) -> torch.Tensor:
