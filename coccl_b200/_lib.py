@@ -45,6 +45,14 @@ class TpArgs(C.Structure):
                 ("gathered", c_void_p * MAX_RANKS), ("agPayload", c_int)]
 
 
+class ExchangeArgs(C.Structure):
+    """Mirror of cocclkExchangeArgs (csrc/kernels/kernels_api.h)."""
+    _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("gather", c_int), ("frames", c_int), ("pieces", c_int),
+                ("frameStride", c_long), ("pieceBytes", c_long)] + \
+               [(n, c_void_p * MAX_RANKS) for n in ("send", "recv", "sendMeta", "recvMeta", "staging", "flags", "status")] + \
+               [("epoch", c_uint), ("timeoutNs", c_ulonglong)]
+
+
 class MoeArgs(C.Structure):
     """Mirror of cocclkMoeArgs (csrc/kernels/moe_api.h)."""
     _fields_ = [("nRanks", c_int), ("rankBase", c_int), ("tokens", c_int), ("hidden", c_int), ("topk", c_int),

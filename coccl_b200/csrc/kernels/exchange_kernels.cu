@@ -22,6 +22,8 @@
 #include "kernels_api.h"
 #include "launch_count.h"
 
+#include <string.h>
+
 namespace coccl {
 
 constexpr int kExchangeMaxItems = 4096;   // flags per source rank (one region of the flag block)

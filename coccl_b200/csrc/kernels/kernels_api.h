@@ -86,6 +86,31 @@ int cocclkReduceChunks(const void* in, void* out, long count, int numChunks, lon
                        cudaStream_t stream);
 int cocclkPackSlice(const void* src, void* dst, long sliceBytes, long srcPitchBytes, long srcOffsetBytes, int chunks,
                     int ranksPerNode, int nNodes, int unpack, cudaStream_t stream);
+/* Byte exchange over peer memory for the staged pipeline (kernels/exchange_kernels.cu): all-to-all (gather = 0: block p
+   of send goes to rank p) or all-gather (gather = 1: the one block of send goes to every rank) of blocks made of
+   `frames` frames of `frameStride` bytes capacity. With sendMeta (one 16-byte record per frame: payload bytes as a
+   64-bit integer, then encoding) only the bytes that exist travel, and recvMeta receives the records in source order.
+   staging[r]: cocclkExchangeStagingBytes() bytes on rank r as mapped here; flags[r]: cocclkFlagBytes() bytes.
+   Arrays are indexed by rank; a production launch (emulatedRanks == 1) reads send/recv/meta at [rankBase] only. */
+typedef struct {
+  int nRanks, rankBase;
+  int gather;
+  int frames;
+  int pieces;                    /* from cocclkExchangePieces */
+  long frameStride, pieceBytes;  /* multiples of 16 */
+  const uint8_t* send[COCCLK_MAX_RANKS];
+  uint8_t* recv[COCCLK_MAX_RANKS];
+  const void* sendMeta[COCCLK_MAX_RANKS];
+  void* recvMeta[COCCLK_MAX_RANKS];
+  uint8_t* staging[COCCLK_MAX_RANKS];
+  unsigned int* flags[COCCLK_MAX_RANKS];
+  void* status[COCCLK_MAX_RANKS];
+  unsigned int epoch;
+  unsigned long long timeoutNs;
+} cocclkExchangeArgs;
+long cocclkExchangeStagingBytes(int nRanks, int frames, long frameStride);
+int cocclkExchangePieces(int frames, long frameStride, long* pieceBytes);
+int cocclkPeerExchange(const cocclkExchangeArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream);
 /* Uncompressed all-reduce of a symmetric buffer through the NVSwitch (multimem.ld_reduce / multimem.st).
    multicastPtr: multicast address of element 0 of a buffer every rank has bound to the same multicast object;
    flags[r]: cocclkNvlsFlagBytes() zero-initialised bytes on rank r as mapped here. count * size must be a multiple of
