@@ -13,6 +13,7 @@
 #include "runtime/nccl_transport.h"
 #include "runtime/primitives.h"
 #include "runtime/runtime.h"
+#include "runtime/peer_exchange.h"
 #include "training/assist.h"
 #include "tuning/autotune.h"
 
@@ -91,6 +92,8 @@ void runtimeStop(Comm* comm) {
   Runtime& rt = globalRuntime();
   if (rt.enabled()) {
     if (s.executor) s.executor->releaseComm(comm);
+    PeerDataPath::release(comm);
+    for (Comm* child : {comm->intra, comm->inter}) if (child != nullptr) PeerDataPath::release(child);
     if (s.assist) s.assist->unregisterComm(comm);
     rt.commDestroy(comm);
     if (s.buffers) s.buffers->commDestroy(comm);
@@ -257,7 +260,8 @@ ncclResult_t cocclApiCommGetAsyncError(ncclComm_t comm, ncclResult_t* e) {
   // a fused kernel whose wait on a peer ran out reports here as a remote error (the reference inherits NCCL's
   // abort flag polling for this, src/device/prims_simple.h:97-132 and src/init.cc:2286)
   if (state().executor != nullptr) {
-    const unsigned int w = state().executor->asyncStatus(unwrap(comm));
+    unsigned int w = state().executor->asyncStatus(unwrap(comm));
+    if (w == 0) w = PeerDataPath::asyncStatusOf(unwrap(comm));
     if (w != 0) {
       COCCL_WARN("comm %llu: a fused collective gave up waiting (phase %u, peer %u, slice %u)", (unsigned long long)unwrap(comm)->id,
                  (w >> 23) & 0xffu, (w >> 15) & 0xffu, w & 0x7fffu);
@@ -355,6 +359,8 @@ void cocclApiGetStats(cocclApiStats* out) {
   out->fusedCalls = state().executor ? state().executor->fusedCalls : 0;
   out->stagedCalls = state().executor ? state().executor->stagedCalls : 0;
 }
+
+unsigned long long cocclApiPeerExchangeCalls(void) { return (unsigned long long)PeerDataPath::calls(); }
 
 ncclResult_t cocclApiCommTrainingRole(ncclComm_t comm, cocclApiTrainingRole* out) {
   if (comm == nullptr || out == nullptr) return ncclInvalidArgument;

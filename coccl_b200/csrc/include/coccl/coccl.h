@@ -68,6 +68,9 @@ typedef struct cocclApiStats {
   unsigned long long nativeCalls, compressedCalls, deferredCalls, policyLookups, fusedCalls, stagedCalls;
 } cocclApiStats;
 void cocclApiGetStats(cocclApiStats* out);
+// How many exchanges of encoded bytes of the staged pipeline (codecs without a fused kernel form: rANS, ZFP at rates
+// without one, third-party plugins) this process served by its own peer-memory kernel instead of a library collective.
+unsigned long long cocclApiPeerExchangeCalls(void);
 
 // Training mode: what the classifier decided for this communicator. `committed` is 0 until a decision exists (all
 // other fields are then zero); `active` turns 1 at the call from which every rank routes by the role. Roles:

@@ -4,6 +4,7 @@
 #include "kernels/kernels_api.h"
 #include "pipeline/pipeline.h"
 #include "runtime/log.h"
+#include "runtime/peer_exchange.h"
 
 namespace coccl {
 
@@ -126,6 +127,19 @@ ncclResult_t exchangeFramed(SliceCtx& c, const Stage& st, const StagePlan& p, Ed
   const bool gather = st.kind == StageKind::AllGather;
   const int n = comm->nRanks;
   const size_t framesPerRank = gather ? in.chunks : in.chunks / (size_t)n;
+  // one node: the kernel reads the sizes on the device and stores the frames into the receivers' memory; no host
+  // round trip, no library collective
+  if (PeerDataPath::serves(framesPerRank, in.frameStride)) {
+    if (PeerDataPath* path = PeerDataPath::of(comm, s)) {
+      ncclResult_t pr = path->exchange(gather, in.ptr, out.ptr, framesPerRank, in.frameStride, in.meta, out.meta, s);
+      if (pr != ncclSuccess) return pr;
+      out.bytes = p.outChunks * in.frameStride;
+      out.elements = out.bytes;
+      out.frameStride = in.frameStride;
+      out.datatype = in.datatype;
+      return ncclSuccess;
+    }
+  }
   // 1. metadata travels first, as ordinary fixed-size bytes
   ncclResult_t r = gather
       ? comm->transport->allGather(comm, in.meta, out.meta, in.chunks * kFrameMetaBytes, ncclUint8, s)
@@ -188,12 +202,22 @@ ncclResult_t runStage(SliceCtx& c, size_t planIndex, const StagePlan& p, bool la
       const bool framed = in.meta != nullptr;
       if (framed) { r = exchangeFramed(c, *st, p, in, out, s); break; }
       Comm* comm = st->comm;
-      if (p.kind == StageKind::AllToAll) {
-        r = comm->transport->allToAll(comm, in.ptr, out.ptr, in.bytes / (size_t)comm->nRanks, ncclUint8, s);
+      const bool a2a = p.kind == StageKind::AllToAll;
+      const size_t block = a2a ? in.bytes / (size_t)comm->nRanks : in.bytes;   // bytes from one rank to one rank
+      PeerDataPath* path = PeerDataPath::serves(1, block) &&
+                                   (!a2a || in.bytes % (size_t)comm->nRanks == 0)
+                               ? PeerDataPath::of(comm, s) : nullptr;
+      if (path != nullptr) {
+        r = path->exchange(!a2a, in.ptr, out.ptr, 1, block, nullptr, nullptr, s);
+      } else if (a2a) {
+        r = comm->transport->allToAll(comm, in.ptr, out.ptr, block, ncclUint8, s);
+      } else {
+        r = comm->transport->allGather(comm, in.ptr, out.ptr, in.bytes, ncclUint8, s);
+      }
+      if (a2a) {
         out.bytes = in.bytes;
         out.chunks = in.chunks;
       } else {
-        r = comm->transport->allGather(comm, in.ptr, out.ptr, in.bytes, ncclUint8, s);
         out.bytes = in.bytes * (size_t)comm->nRanks;
         out.chunks = in.chunks * (size_t)comm->nRanks;
       }

@@ -40,6 +40,9 @@ class Transport {
   // ncclCommSplit equivalent: ranks with the same color form a child, ordered by key.
   virtual ncclResult_t split(Comm* parent, int color, int key, Comm** child) = 0;
   virtual void destroy(Comm* c) = 0;
+  // Whether the ranks behind this transport are real GPUs of one machine whose memory can be mapped into one another
+  // (the peer-memory data path of the staged pipeline asks; test doubles answer no).
+  virtual bool peerMemoryCapable() const { return false; }
 };
 
 // First word of every communicator object of this library. A handle that reaches the public API without it is not

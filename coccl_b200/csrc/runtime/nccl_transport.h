@@ -10,6 +10,7 @@ class NcclTransport : public Transport {
   ncclResult_t uniqueId(ncclUniqueId* id);
   ncclResult_t initRank(Comm** out, int nRanks, ncclUniqueId id, int rank);
   const char* errorString(ncclResult_t r);
+  bool peerMemoryCapable() const override { return true; }
   ncclResult_t asyncError(Comm* c, ncclResult_t* out);
   ncclResult_t foreignAsyncError(void* native, ncclResult_t* out);
   ncclResult_t foreignCount(void* native, int* out);

@@ -160,3 +160,110 @@ def test_c_api_two_gpus(tmp_path):
     p = tmp_path / "policy.toml"
     p.write_text(CONFIG)
     run_distributed(_worker, 2, "nccl", (str(p),))
+
+
+STAGED_CONFIG = f"""
+[runtime]
+mode = "normal"
+compression_threshold_bytes = 65536
+[compressor_plugins]
+compressors = ["ans", "zfp"]
+library_path = "{PLUGINS}"
+[autotune]
+enabled = false
+[pipeline]
+depth = 2
+[normal.all_gather.default]
+compressor = "ans"
+[normal.all_gather.default.config]
+probBits = 10
+[normal.all_to_all.default]
+compressor = "ans"
+[normal.all_to_all.default.config]
+probBits = 10
+[normal.all_reduce.default]
+compressor = "ans"
+[normal.all_reduce.default.config]
+probBits = 10
+[normal.reduce_scatter.default]
+compressor = "zfp"
+[normal.reduce_scatter.default.config]
+rate = 12
+"""
+
+
+def _staged_worker(rank, world, cfg_path, transport):
+    """Codecs that have no fused kernel form (rANS with its variable-size frames, ZFP at a rate without a tile codec)
+    run through the staged pipeline; on one node their encoded bytes must travel through this library's own
+    peer-memory exchange kernel, not through a library collective, and give the same answers either way."""
+    import torch.distributed as dist
+    os.environ["COCCL_ENABLE"] = "1"
+    os.environ["COCCL_CONFIG_FILE"] = cfg_path
+    if transport:
+        os.environ["COCCL_STAGED_TRANSPORT"] = transport
+    from coccl_b200 import _lib
+    dev = torch.device("cuda", rank)
+    vp, sz, i32 = C.c_void_p, C.c_size_t, C.c_int
+    uid = UniqueId()
+    if rank == 0:
+        assert _lib.declare("cocclApiGetUniqueId", i32, [C.POINTER(UniqueId)])(C.byref(uid)) == 0
+    box = [bytes(uid)]
+    dist.broadcast_object_list(box, src=0)
+    uid = UniqueId.from_buffer_copy(box[0])
+    comm = vp()
+    assert _lib.declare("cocclApiCommInitRank", i32, [C.POINTER(vp), i32, UniqueId, i32])(C.byref(comm), world, uid, rank) == 0
+    st = torch.cuda.current_stream().cuda_stream
+    F32 = 7
+    ar = _lib.declare("cocclApiAllReduce", i32, [vp, vp, sz, i32, i32, vp, vp])
+    rs = _lib.declare("cocclApiReduceScatter", i32, [vp, vp, sz, i32, i32, vp, vp])
+    ag = _lib.declare("cocclApiAllGather", i32, [vp, vp, sz, i32, vp, vp])
+    a2a = _lib.declare("cocclApiAllToAll", i32, [vp, vp, sz, i32, vp, vp])
+    peer_calls = _lib.declare("cocclApiPeerExchangeCalls", C.c_ulonglong, [])
+    stats_fn = _lib.declare("cocclApiGetStats", None, [C.POINTER(Stats)])
+    torch.manual_seed(40 + rank)
+    n = world * (1 << 18)
+    # values with few distinct bytes, so that the entropy coder really shortens the frames (and a constant block,
+    # whose frames come out tiny, next to a noisy one that stays raw)
+    x = (torch.randint(-8, 8, (n,), device=dev).float() * 0.125)
+    x[: n // 4] = 1.0
+    x[n // 2: n // 2 + 65536] = torch.randn(65536, device=dev)
+    xs = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(xs, x)
+    for rnd in range(2):   # the second round reuses staging halves and flags
+        full = torch.empty(n * world, device=dev)
+        assert ag(x.data_ptr(), full.data_ptr(), n, F32, comm, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(full, torch.cat(xs)), ("all_gather", rnd)          # lossless
+        o = torch.empty_like(x)
+        assert a2a(x.data_ptr(), o.data_ptr(), n // world, F32, comm, st) == 0
+        torch.cuda.synchronize()
+        per = n // world
+        assert torch.equal(o, torch.cat([t[rank * per:(rank + 1) * per] for t in xs])), ("all_to_all", rnd)
+        y = x.clone()
+        assert ar(y.data_ptr(), y.data_ptr(), n, F32, 0, comm, st) == 0
+        torch.cuda.synchronize()
+        assert torch.allclose(y, sum(xs), atol=1e-5), ("all_reduce", rnd)
+        out = torch.empty(per, device=dev)
+        assert rs(x.data_ptr(), out.data_ptr(), per, F32, 0, comm, st) == 0
+        torch.cuda.synchronize()
+        exact = sum(xs)[rank * per:(rank + 1) * per]
+        assert ((out - exact).norm() / exact.norm()).item() < 2e-2, ("reduce_scatter zfp rate 12", rnd)
+    s = Stats()
+    stats_fn(C.byref(s))
+    assert s.staged >= 8 and s.fused == 0
+    calls = int(peer_calls())
+    if transport == "nccl":
+        assert calls == 0
+    else:
+        assert calls >= 8, calls     # every exchange of every staged call went through the peer-memory kernel
+    err = C.c_int(0)
+    assert _lib.declare("cocclApiCommGetAsyncError", i32, [vp, C.POINTER(C.c_int)])(comm, C.byref(err)) == 0 and err.value == 0
+    assert _lib.declare("cocclApiCommDestroy", i32, [vp])(comm) == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("transport", ["", "nccl"], ids=["peer-memory", "nccl"])
+def test_staged_codecs_travel_over_peer_memory(tmp_path, transport):
+    p = tmp_path / "staged.toml"
+    p.write_text(STAGED_CONFIG)
+    run_distributed(_staged_worker, 2, "nccl", (str(p), transport), timeout=300)
