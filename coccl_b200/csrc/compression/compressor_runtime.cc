@@ -345,9 +345,13 @@ ncclResult_t decompressReduce(CompressorPolicy* policy, const cocclCompressorVie
   if (policy == nullptr || output == nullptr || reduceChunks == 0 || input.chunks % reduceChunks != 0)
     return ncclInvalidArgument;
   const bool raw = input.datatype == COCCL_COMPRESSOR_RAW_PASSTHROUGH;
-  if (!raw && policy->has(cocclCompressorCapabilityDecompressReduce) && !policy->has(cocclCompressorCapabilityFramed))
-    return runPlugin(policy, cocclCompressorOperationDecompressReduce, input, output, reduceChunks, output->datatype,
-                     output->elements, env);
+  if (!raw && policy->has(cocclCompressorCapabilityDecompressReduce) && !policy->has(cocclCompressorCapabilityFramed)) {
+    const ncclResult_t fusedResult = runPlugin(policy, cocclCompressorOperationDecompressReduce, input, output, reduceChunks,
+                                               output->datatype, output->elements, env);
+    // a codec may have the fused form for some of its configurations only (ZFP: the rates with a tile codec) and
+    // answers "invalid usage" for the others before it touches anything: those take the generic path below
+    if (fusedResult != ncclInvalidUsage) return fusedResult;
+  }
   // generic path: decode all copies into scratch, then sum the chunks
   const DeviceAllocator* alloc = env.alloc ? env.alloc : &cudaDeviceAllocator();
   const size_t width = cocclTypeSize(output->datatype);
@@ -381,9 +385,11 @@ ncclResult_t decompressReduceCompress(CompressorPolicy* decoder, CompressorPolic
     return ncclInvalidArgument;
   const bool raw = input.datatype == COCCL_COMPRESSOR_RAW_PASSTHROUGH;
   if (!raw && decoder == encoder && decoder->has(cocclCompressorCapabilityDecompressReduceCompress) &&
-      !decoder->has(cocclCompressorCapabilityFramed))
-    return runPlugin(decoder, cocclCompressorOperationDecompressReduceCompress, input, output, reduceChunks,
-                     originalDatatype, originalElements, env);
+      !decoder->has(cocclCompressorCapabilityFramed)) {
+    const ncclResult_t fusedResult = runPlugin(decoder, cocclCompressorOperationDecompressReduceCompress, input, output,
+                                               reduceChunks, originalDatatype, originalElements, env);
+    if (fusedResult != ncclInvalidUsage) return fusedResult;   // see decompressReduce
+  }
   const DeviceAllocator* alloc = env.alloc ? env.alloc : &cudaDeviceAllocator();
   const size_t width = cocclTypeSize(originalDatatype);
   if (width == 0 || originalElements == 0 || originalElements > SIZE_MAX / width) return ncclInvalidArgument;
