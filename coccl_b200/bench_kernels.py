@@ -41,7 +41,7 @@ def timed(fn, iters=20, warmup=5, flush_mib=256):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "codec", "collective", "tp", "moe"])
+    ap.add_argument("what", choices=["gemm", "codec", "collective", "tp", "moe", "train", "exchange"])
     ap.add_argument("--tp-variant", default="auto", choices=["auto", "1cta", "2cta"])
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=4096)
@@ -124,6 +124,71 @@ def main():
         out.update(ranks=n, m=a.m, n=a.n, k=a.k, variant=var_ag, ag_gemm_ms=t_ag, ag_gemm_tflops_all_ranks=fl / t_ag / 1e9,
                    gemm_rs_ms=t_rs, gemm_rs_tflops_all_ranks=fl / t_rs / 1e9,
                    note="all ranks emulated on one GPU: TFLOP/s over the whole device, no NVLink involved")
+    elif a.what == "train":
+        # the trainer's own kernels on one transformer layer's shapes: LayerNorm forward + backward (with the column sums of
+        # the gamma / beta gradients), bias-gradient column sums (inside the linear's backward), cross-entropy forward +
+        # backward, AdamW with fp32 master weights
+        from .ops import fused as F_
+        T_, H_ = a.tokens, a.hidden
+        x = torch.randn(T_, H_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        g = torch.ones(H_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        b = torch.zeros(H_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        dy = torch.randn(T_, H_, device=dev, dtype=torch.bfloat16)
+
+        def ln():
+            y = F_.layer_norm(x, g, b)
+            y.backward(dy)
+            x.grad = g.grad = b.grad = None
+        w = torch.randn(a.n, H_, device=dev, dtype=torch.bfloat16, requires_grad=True) * 0.02
+        w = w.detach().requires_grad_(True)
+        wb = torch.zeros(a.n, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        xin = torch.randn(T_, H_, device=dev, dtype=torch.bfloat16)
+        dz = torch.randn(T_, a.n, device=dev, dtype=torch.bfloat16)
+
+        def lin():   # forward GEMM, then wgrad GEMM + bias-gradient column sum (no dgrad: the input needs no gradient)
+            z = F_.linear(xin, w, wb)
+            z.backward(dz)
+            w.grad = wb.grad = None
+        V_ = 50304
+        logits = torch.randn(T_, V_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        tgt = torch.randint(0, V_, (T_,), device=dev)
+
+        def ce():
+            loss = F_.cross_entropy(logits, tgt, 1.0 / T_)
+            loss.backward()
+            logits.grad = None
+        np_ = 64 << 20
+        master = torch.randn(np_, device=dev)
+        m1, v1 = torch.zeros_like(master), torch.zeros_like(master)
+        gr = torch.randn(np_, device=dev) * 1e-3
+        pb = torch.empty(np_, device=dev, dtype=torch.bfloat16)
+        step = [0]
+
+        def adam():
+            step[0] += 1
+            F_.adam_step(master, m1, v1, gr, pb, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step[0])
+        t_ln, t_lin, t_ce, t_adam = (timed(f, a.iters, a.warmup) for f in (ln, lin, ce, adam))
+        out.update(tokens=T_, hidden=H_, layer_norm_fwd_bwd_ms=t_ln, ln_gbs=(5 * T_ * H_ * 2) / t_ln / 1e6,
+                   linear_fwd_wgrad_bias_ms=t_lin, cross_entropy_fwd_bwd_ms=t_ce, ce_gbs=(3 * T_ * V_ * 2) / t_ce / 1e6,
+                   adam_64mi_params_ms=t_adam, adam_gbs=(np_ * (4 * 4 + 3 * 4 + 2)) / t_adam / 1e6,
+                   note="GB/s = algorithmic bytes (LN: x, dy read twice + y, dx written; CE: logits read twice + gradient "
+                        "written; Adam: master, m, v read and written, gradient read, bf16 parameter written)")
+    elif a.what == "exchange":
+        # peer-memory byte exchange of the staged pipeline, all ranks emulated on this GPU
+        from .ops import exchange as X_
+        n = a.ranks
+        block = (a.mib << 20) // n // 16 * 16
+        send = [torch.randint(0, 256, (n * block,), dtype=torch.uint8, device=dev) for _ in range(n)]
+        st_, ep = {}, [0]
+
+        def ex():
+            ep[0] += 1
+            X_.emulate(send, gather=False, frames=1, frame_stride=block, state=st_, epoch=ep[0], max_ctas=max(1, 296 // n))
+        ms = timed(ex, a.iters, a.warmup)
+        X_.check_state(st_)
+        out.update(ranks=n, per_rank_mib=a.mib, ms=ms, copy_gbs_all_ranks=(2.0 * n * n * block * 2) / ms / 1e6,
+                   note="all-to-all of per_rank_mib from every rank; every byte is stored into staging and copied out "
+                        "(2 reads + 2 writes per byte), all ranks on one GPU, so GB/s is HBM traffic of the whole device")
     elif a.what == "moe":
         from .ops import moe as M
         n = a.ranks
