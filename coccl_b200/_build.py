@@ -61,9 +61,9 @@ def _run(cmd, verbose):
     return r
 
 
-def _compile(src: Path, verbose: bool, hdr_mtime: float, extra=()) -> Path:
+def _compile(src: Path, verbose: bool, hdr_mtime: float, extra=(), tag: str = "") -> Path:
     rel = src.relative_to(CSRC)
-    out = OBJ / rel.with_suffix(rel.suffix + ".o")
+    out = OBJ / rel.with_suffix(rel.suffix + tag + ".o")
     out.parent.mkdir(parents=True, exist_ok=True)
     if _needs(src, out, hdr_mtime):
         if src.suffix == ".cu":
@@ -102,6 +102,16 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     so = LIB / "libcoccl.so"
     if not so.exists() or any(o.stat().st_mtime > so.stat().st_mtime for o in objs):
         _run([NVCC, "-shared", "-o", so, *objs, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
+
+    # bounds-checked twin (COCCL_CHECKED_KERNELS=1 makes the Python layer load it): the same objects, except that the
+    # translation units with the codec accesses are compiled with -DCOCCL_BOUNDS_CHECK
+    checked_units = {CSRC / "kernels" / "collective_kernels.cu", CSRC / "kernels" / "codec_kernels.cu"}
+    with cf.ThreadPoolExecutor(jobs) as ex:
+        cobjs = list(ex.map(lambda s: _compile(s, verbose, hdr, ("-DCOCCL_BOUNDS_CHECK",), ".checked"), sorted(checked_units)))
+    cso = LIB / "libcoccl_checked.so"
+    rest = [o for s_, o in zip(srcs, objs) if s_ not in checked_units]
+    if not cso.exists() or any(o.stat().st_mtime > cso.stat().st_mtime for o in cobjs + rest):
+        _run([NVCC, "-shared", "-o", cso, *cobjs, *rest, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
 
     # plugins: one shared library per codec source
     if PLUGIN_DIR.is_dir():

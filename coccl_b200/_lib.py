@@ -7,10 +7,15 @@ missing or stale library is an error, never a silent slow path.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _ROOT = Path(__file__).resolve().parent
 _SO = _ROOT / "lib" / "libcoccl.so"
+# COCCL_CHECKED_KERNELS=1: load the bounds-checked twin (codec accesses range-checked, violations recorded in a
+# device word instead of touching memory; see bounds_word())
+if os.environ.get("COCCL_CHECKED_KERNELS", "") not in ("", "0"):
+    _SO = _SO.with_name("libcoccl_checked.so")
 _lib = None
 
 c_void_p, c_int, c_long, c_float, c_uint, c_ulonglong = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint, C.c_ulonglong
@@ -169,3 +174,12 @@ def tensor_from_ptr(ptr: int, nbytes: int, device, owner=None):
     valid while the tensor or any view of it is in use; `owner` is an object the tensor keeps alive."""
     import torch
     return torch.as_tensor(_RawCudaMemory(ptr, nbytes, owner), device=device)
+
+
+def bounds_word(reset: bool = False) -> tuple[bool, list[int]]:
+    """(whether the loaded library is the bounds-checked build, its error word: [0] = 0 or 0x80000000 | site, then the
+    element index and the offending / allowed byte ends). Synchronises the device."""
+    checked = bool(declare("cocclkBoundsChecked", C.c_int, [])())
+    w = (C.c_uint * 8)()
+    check(declare("cocclkBoundsWord", C.c_int, [C.POINTER(C.c_uint), C.c_int])(w, int(reset)), "cocclkBoundsWord")
+    return checked, [int(v) for v in w]

@@ -105,3 +105,19 @@ extern "C" int cocclkDecodeReduceEncode(const void* in, void* out, long count, l
   cocclkCountLaunches(1);
   return (int)cudaGetLastError();
 }
+
+// Bounds-checked build: the error word of this translation unit's codec kernels (see codecs.cuh).
+extern "C" int cocclkBoundsWordCodec(unsigned int* out, int reset) {
+#ifdef COCCL_BOUNDS_CHECK
+  cudaError_t e = cudaMemcpyFromSymbol(out, coccl::gBoundsWord, 8 * sizeof(unsigned int));
+  if (e == cudaSuccess && reset) {
+    const unsigned int zero[8] = {};
+    e = cudaMemcpyToSymbol(coccl::gBoundsWord, zero, sizeof(zero));
+  }
+  return (int)e;
+#else
+  for (int i = 0; i < 8; ++i) out[i] = 0;
+  (void)reset;
+  return 0;
+#endif
+}

@@ -74,6 +74,29 @@ __host__ __device__ inline ChunkLayout makeChunkLayout(const CodecCfg& c, long c
   return L;
 }
 
+// ------------------------------------------------------------------ bounds-checked build
+// With -DCOCCL_BOUNDS_CHECK (libcoccl_checked.so) every access of a codec to an encoded chunk is preceded by a check
+// of the byte ranges it is about to touch against the chunk's layout: the payload part must end inside the payload,
+// the parameter part inside the chunk. A violation records {site, element, offending end, limit} once in a device
+// word that the host reads (cocclkBoundsWord) and the access is SKIPPED, so a wrong index shows up as an error word
+// and wrong numbers, never as a fault. The normal build compiles the checks away.
+#ifdef COCCL_BOUNDS_CHECK
+static __device__ unsigned int gBoundsWord[8];   // one per translation unit; each checked unit exports a reader
+__device__ __forceinline__ bool chunkRangeOk(const ChunkLayout& L, long elem, long payloadEnd, long totalEnd, int site) {
+  if (elem >= 0 && payloadEnd <= L.payloadBytes && totalEnd <= L.totalBytes && L.totalBytes <= L.stride) return true;
+  if (atomicCAS(&gBoundsWord[0], 0u, 0x80000000u | (unsigned)site) == 0u) {
+    gBoundsWord[1] = (unsigned)elem; gBoundsWord[2] = (unsigned)((unsigned long long)elem >> 32);
+    gBoundsWord[3] = (unsigned)payloadEnd; gBoundsWord[4] = (unsigned)L.payloadBytes;
+    gBoundsWord[5] = (unsigned)totalEnd; gBoundsWord[6] = (unsigned)L.totalBytes;
+  }
+  return false;
+}
+#define COCCL_CHUNK_RANGE_OK(Codec, L, c, elem, site) \
+  ([&] { long pe_, te_; Codec::touched(L, c, elem, &pe_, &te_); return chunkRangeOk(L, elem, pe_, te_, site); }())
+#else
+#define COCCL_CHUNK_RANGE_OK(Codec, L, c, elem, site) true
+#endif
+
 // ------------------------------------------------------------------ helpers
 // Unnormalised 32-point Walsh-Hadamard transform of one run, entirely in registers.
 __device__ __forceinline__ void hadamard32(float (&v)[32]) {
@@ -234,6 +257,19 @@ struct SdpCodec {
     return e;
   }
 
+  // Exclusive ends of the payload bytes and of the parameter bytes that store / fetch touch for the run at `elem`
+  // (0 when the run lies in the padding and nothing is touched); used by the bounds-checked build.
+  static __device__ __forceinline__ void touched(const ChunkLayout& L, const CodecCfg& c, long elem, long* payloadEnd, long* totalEnd) {
+    const int gs = 31 - __clz(c.group);
+    const long padded = L.groups << gs;
+    if (elem >= padded) { *payloadEnd = 0; *totalEnd = 0; return; }
+    const long last = elem + 32 < padded ? elem + 32 : padded;
+    *payloadEnd = last * BITS / 8;
+    long g = (last - 1) >> gs;
+    if (g >= L.groups) g = L.groups - 1;
+    *totalEnd = L.payloadBytes + (g + 1) * c.paramBytes;
+  }
+
   // elem = chunk-relative index of the run's first element
   static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L,
                                                const CodecCfg& c, long elem) {
@@ -388,6 +424,12 @@ struct MxFp8Codec {
     return e;
   }
 
+  static __device__ __forceinline__ void touched(const ChunkLayout& L, const CodecCfg&, long elem, long* payloadEnd, long* totalEnd) {
+    if (elem >= L.groups * 32) { *payloadEnd = 0; *totalEnd = 0; return; }
+    *payloadEnd = elem + 32;
+    *totalEnd = L.payloadBytes + elem / 32 + 1;
+  }
+
   static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/,
                                                long elem) {
     if (elem >= L.groups * 32) return;
@@ -519,6 +561,12 @@ struct TacoCodec {
     return e;
   }
 
+  static __device__ __forceinline__ void touched(const ChunkLayout& L, const CodecCfg& c, long elem, long* payloadEnd, long* totalEnd) {
+    if (elem >= L.payloadBytes) { *payloadEnd = 0; *totalEnd = 0; return; }
+    *payloadEnd = elem + 32;
+    *totalEnd = L.payloadBytes + (L.groups + elem / c.group + 1) * 4;   // the group's scale, then its adaptive factor
+  }
+
   static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& c,
                                                long elem) {
     if (elem >= L.payloadBytes) return;  // runs of the padded last group are part of the stream
@@ -642,6 +690,15 @@ struct ZfpCodec {
     return e;
   }
 
+  static __device__ __forceinline__ void touched(const ChunkLayout& L, const CodecCfg&, long elem, long* payloadEnd, long* totalEnd) {
+    const long off = (elem >> 5) * (4 * RATE);
+    if (off >= L.totalBytes) { *payloadEnd = 0; *totalEnd = 0; return; }
+    long end = off + 4 * RATE;
+    if (end > L.totalBytes) end = L.totalBytes / 4 * 4;   // the tail is written word by word, whole words only
+    *payloadEnd = end < L.payloadBytes ? end : L.payloadBytes;   // a ZFP chunk has no parameter part
+    *totalEnd = end;
+  }
+
   static __device__ __forceinline__ void store(const Enc& e, uint8_t* chunk, const ChunkLayout& L, const CodecCfg& /*c*/,
                                                long elem) {
     const long off = (elem >> 5) * (4 * RATE);
@@ -716,7 +773,7 @@ __device__ __forceinline__ void decodeSum(const uint8_t* base, long stride, int 
     typename Codec::Raw r[Codec::kBatch];
 #pragma unroll
     for (int j = 0; j < Codec::kBatch; ++j) {
-      if (q + j < n) r[j] = Codec::fetch(base + (long)(q + j) * stride, L, c, elem, mul, sm);
+      if (q + j < n && COCCL_CHUNK_RANGE_OK(Codec, L, c, elem, 2)) r[j] = Codec::fetch(base + (long)(q + j) * stride, L, c, elem, mul, sm);
       else r[j].valid = false;
     }
 #pragma unroll

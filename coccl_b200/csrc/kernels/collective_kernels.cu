@@ -69,3 +69,38 @@ extern "C" int cocclkFusedCollective(const cocclkCollArgs* args, int emulatedRan
   });
   return ok ? rc : -1;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Bounds-checked build (libcoccl_checked.so, -DCOCCL_BOUNDS_CHECK): 1 when the codec accesses of the fused collectives
+// and the stand-alone codec kernels are range-checked, and the first violation they recorded:
+// out[0] = 0x80000000 | site (1 encode store, 2 decode fetch, 3 re-encode store of the two-shot all-reduce) or 0,
+// out[1..2] = element index, out[3] / out[4] = payload end touched / payload bytes, out[5] / out[6] = chunk end touched /
+// chunk bytes. Synchronises the device.
+extern "C" int cocclkBoundsWordCodec(unsigned int* out, int reset);
+extern "C" int cocclkBoundsChecked(void) {
+#ifdef COCCL_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+extern "C" int cocclkBoundsWord(unsigned int* out, int reset) {
+  if (out == nullptr) return -1;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  unsigned int other[8];
+  int rc = cocclkBoundsWordCodec(other, reset);
+  if (rc != 0) return rc;
+#ifdef COCCL_BOUNDS_CHECK
+  e = cudaMemcpyFromSymbol(out, coccl::gBoundsWord, 8 * sizeof(unsigned int));
+  if (e == cudaSuccess && reset) {
+    const unsigned int zero[8] = {};
+    e = cudaMemcpyToSymbol(coccl::gBoundsWord, zero, sizeof(zero));
+  }
+  if (e != cudaSuccess) return (int)e;
+#else
+  for (int i = 0; i < 8; ++i) out[i] = 0;
+#endif
+  if (out[0] == 0) for (int i = 0; i < 8; ++i) out[i] = other[i];
+  return 0;
+}

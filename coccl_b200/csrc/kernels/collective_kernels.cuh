@@ -87,6 +87,7 @@ __device__ __forceinline__ void encodeTiles(const T* src, const ChunkLayout& L, 
       for (int i = 0; i < 32; ++i) v[i] -= pv[i];
     }
     const typename Codec::Enc enc = Codec::encode(v, c, true, sm, rngBase + (uint64_t)e);
+    if (!COCCL_CHUNK_RANGE_OK(Codec, L, c, e, 1)) continue;
     for (int d = 0; d < nDst; ++d) Codec::store(enc, dst[d], L, c, e);
   }
 }
@@ -134,6 +135,12 @@ __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollecti
   StatusWord* st = a.status[rank];
   unsigned long long* tr = a.trace[rank];
   tracePhase(tr, 0);
+  // The slot geometry comes from the host: a chunk that does not fit its slot, or a second region that overlaps the
+  // first, would make ranks write over each other's data. Checked in every build, before anything is touched.
+  if (L.stride > a.slotBytes || (a.op == kOpAllReduceTwoShot && a.regionBOffset < (long)N * a.slotBytes)) {
+    if (threadIdx.x == 0) reportTimeout(st, 0xB, rank, 0);
+    return;
+  }
   bool failed = false;
   const bool perPeer = (a.op == kOpReduceScatter || a.op == kOpAllToAll || a.op == kOpAllReduceTwoShot);
 
@@ -205,7 +212,8 @@ __global__ void __launch_bounds__(kTileThreads, Codec::kMinBlocks) fusedCollecti
         if (a.op == kOpAllReduceTwoShot) {
           // stay in the rotated domain: the sum of rotated values is the rotation of the sum
           const typename Codec::Enc enc = Codec::encode(acc, c, false, sm, ((uint64_t)(0x80 + rank) << 40) + (uint64_t)e);
-          for (int d = 0; d < N; ++d) Codec::store(enc, sDst[d], L, c, e);
+          if (COCCL_CHUNK_RANGE_OK(Codec, L, c, e, 3))
+            for (int d = 0; d < N; ++d) Codec::store(enc, sDst[d], L, c, e);
         } else {
           Codec::finish(acc, c);
           const bool fast = TileIO<T>::fastTile(dstChunk, L.count, e0);

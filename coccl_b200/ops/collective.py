@@ -58,8 +58,10 @@ def workspace_bytes(op: int, cfg, count: int, dtype, n: int) -> tuple[int, int, 
 
 def emulate_collective(op: str, inputs: list[torch.Tensor], cfg: CodecConfig, *, slice_tiles: int | None = None,
                        timeout_ms: float = 2000.0, max_ctas: int = 0, epoch: int = 1,
-                       state: dict | None = None) -> list[torch.Tensor]:
-    """Run one fused collective for all ranks on the current GPU; inputs[r] is rank r's send buffer."""
+                       state: dict | None = None, slot_bytes: int | None = None) -> list[torch.Tensor]:
+    """Run one fused collective for all ranks on the current GPU; inputs[r] is rank r's send buffer.
+    slot_bytes: tests only: hand the kernel another slot size than the layout needs (a too small one must be refused by
+    the kernel's entry check, which reports through the status words and touches nothing)."""
     opc = OP_NAMES[op]
     n = len(inputs)
     x0 = inputs[0]
@@ -88,7 +90,7 @@ def emulate_collective(op: str, inputs: list[torch.Tensor], cfg: CodecConfig, *,
     a.epoch = epoch
     a.timeoutNs = int(timeout_ms * 1e6)
     a.codec = cfg.to_c(dtype)
-    a.slotBytes, a.regionBOffset = sb, region_b
+    a.slotBytes, a.regionBOffset = (sb if slot_bytes is None else slot_bytes), region_b
     for r in range(n):
         assert inputs[r].is_contiguous() and inputs[r].numel() == numel
         a.inp[r], a.out[r] = inputs[r].data_ptr(), outs[r].data_ptr()
