@@ -52,6 +52,13 @@ def _needs(src: Path, out: Path, hdr_mtime: float) -> bool:
     return src.stat().st_mtime > t or hdr_mtime > t
 
 
+def _link(cmd_before_out, out: Path, cmd_after_out, verbose):
+    """Link into a temporary name and rename: a reader (a loader, a snapshot of the tree) never sees a half-written file."""
+    tmp = out.with_name(out.name + ".tmp")
+    _run([*cmd_before_out, tmp, *cmd_after_out], verbose)
+    os.replace(tmp, out)
+
+
 def _run(cmd, verbose):
     if verbose:
         print(" ".join(map(str, cmd)), flush=True)
@@ -101,7 +108,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
         objs = list(ex.map(lambda s: _compile(s, verbose, hdr), srcs))
     so = LIB / "libcoccl.so"
     if not so.exists() or any(o.stat().st_mtime > so.stat().st_mtime for o in objs):
-        _run([NVCC, "-shared", "-o", so, *objs, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
+        _link([NVCC, "-shared", "-o"], so, [*objs, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
 
     # bounds-checked twin (COCCL_CHECKED_KERNELS=1 makes the Python layer load it): the same objects, except that the
     # translation units with the codec accesses are compiled with -DCOCCL_BOUNDS_CHECK
@@ -111,7 +118,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     cso = LIB / "libcoccl_checked.so"
     rest = [o for s_, o in zip(srcs, objs) if s_ not in checked_units]
     if not cso.exists() or any(o.stat().st_mtime > cso.stat().st_mtime for o in cobjs + rest):
-        _run([NVCC, "-shared", "-o", cso, *cobjs, *rest, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
+        _link([NVCC, "-shared", "-o"], cso, [*cobjs, *rest, "-ldl", "-lpthread", "-Xlinker", "--no-undefined"], verbose)
 
     # plugins: one shared library per codec source
     if PLUGIN_DIR.is_dir():
@@ -119,7 +126,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
             name = src.stem.replace("_plugin", "")
             out = LIB / "plugins" / f"lib{name}.so"
             if _needs(src, out, hdr):
-                _run([NVCC, *NVCC_FLAGS, "-shared", src, "-o", out, f"-L{LIB}", "-lcoccl",
+                _link([NVCC, *NVCC_FLAGS, "-shared", src, "-o"], out, [f"-L{LIB}", "-lcoccl",
                       "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."], verbose)
             return out
         with cf.ThreadPoolExecutor(jobs) as ex:
@@ -131,18 +138,18 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     if shim.exists():
         out = LIB / "libcoccl_nccl.so"
         if _needs(shim, out, hdr) or so.stat().st_mtime > out.stat().st_mtime:
-            _run([CXX, *CXX_FLAGS, "-shared", shim, "-o", out, *rpath], verbose)
+            _link([CXX, *CXX_FLAGS, "-shared", shim, "-o"], out, rpath, verbose)
     if TOOLS_DIR.is_dir():
         for src in sorted(TOOLS_DIR.glob("*.cc")):
             out = LIB / src.stem.replace("_", "-")
             if _needs(src, out, hdr) or so.stat().st_mtime > out.stat().st_mtime:
-                _run([CXX, *CXX_FLAGS, src, "-o", out, *rpath, "-ldl", "-lpthread"], verbose)
+                _link([CXX, *CXX_FLAGS, src, "-o"], out, [*rpath, "-ldl", "-lpthread"], verbose)
     if TESTS_DIR.is_dir():
         tsrcs = sorted(TESTS_DIR.glob("*.cc"))
         if tsrcs:
             out = LIB / "coccl_host_tests"
             if any(_needs(s, out, hdr) for s in tsrcs) or so.stat().st_mtime > out.stat().st_mtime:
-                _run([CXX, *CXX_FLAGS, *tsrcs, "-o", out, *rpath, "-ldl", "-lpthread"], verbose)
+                _link([CXX, *CXX_FLAGS, *tsrcs, "-o"], out, [*rpath, "-ldl", "-lpthread"], verbose)
     return so
 
 

@@ -143,6 +143,7 @@ extern "C" void cocclRouterClose(cocclRouter* r) { delete r; }
 extern "C" const char* cocclRouterEffectiveConfig(cocclRouter* r) { return r ? r->effective.c_str() : ""; }
 extern "C" uint64_t cocclRouterConfigHash(cocclRouter* r) { return r ? r->hash : 0; }
 extern "C" int cocclRouterEnabled(cocclRouter* r) { return r != nullptr && r->enabled ? 1 : 0; }
+extern "C" int cocclRouterFusedMaxCtas(cocclRouter* r) { return r != nullptr && r->enabled ? r->rt.config().fusedMaxCtas : 0; }
 extern "C" int cocclRouterTrainingMode(cocclRouter* r) { return r != nullptr && r->enabled && r->rt.config().mode == Mode::Training ? 1 : 0; }
 
 extern "C" int cocclRouterDecide(cocclRouter* r, int role, int op, int ncclDatatype, size_t count, int nRanks, int nNodes, int rank,

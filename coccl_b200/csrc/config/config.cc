@@ -229,13 +229,14 @@ bool loadConfigText(const std::string& text, const std::string& baseDir, Config*
   const TomlValue* rt = nullptr;
   if (!childTable(c, &root, "runtime", "<root>", &rt)) return false;
   if (rt == nullptr) return c.fail("[runtime] is required");
-  if (!onlyKeys(c, *rt, {"mode", "compression_threshold_bytes"}, "runtime")) return false;
+  if (!onlyKeys(c, *rt, {"mode", "compression_threshold_bytes", "fused_kernel_max_ctas"}, "runtime")) return false;
   std::string mode;
   if (!readString(c, *rt, "mode", &mode, true, "runtime")) return false;
   if (mode == "normal") cfg.mode = Mode::Normal;
   else if (mode == "training") cfg.mode = Mode::Training;
   else return c.fail("runtime.mode must be \"normal\" or \"training\"");
   if (!readSize(c, *rt, "compression_threshold_bytes", &cfg.thresholdBytes, "runtime")) return false;
+  if (!readInt(c, *rt, "fused_kernel_max_ctas", &cfg.fusedMaxCtas, 0, 4096, false, "runtime")) return false;
 
   // [compressor_plugins]
   const TomlValue* pl = nullptr;
@@ -391,6 +392,7 @@ std::string formatConfig(const Config& cfg) {
   std::ostringstream o;
   o << "runtime.mode = " << (cfg.mode == Mode::Normal ? "normal" : "training") << "\n";
   o << "runtime.compression_threshold_bytes = " << cfg.thresholdBytes << "\n";
+  o << "runtime.fused_kernel_max_ctas = " << cfg.fusedMaxCtas << "\n";
   o << "compressor_plugins.compressors = [";
   for (size_t i = 0; i < cfg.compressors.size(); ++i) o << (i ? ", " : "") << cfg.compressors[i];
   o << "]\n";

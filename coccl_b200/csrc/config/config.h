@@ -78,6 +78,10 @@ struct Config {
   std::string libraryPath;  // resolved against the config file's directory
   // [pipeline]
   int pipelineDepth = 1;
+  // [runtime] fused_kernel_max_ctas: CTAs one fused kernel may occupy per GPU; 0 = as many as stay resident. A job that
+  // overlaps collectives with compute (or runs two communicators at once) leaves the rest of the SMs to the other work,
+  // so that the fused kernel's CTAs, which wait on one another's flags, are all resident.
+  int fusedMaxCtas = 0;
   // [buffer]
   size_t poolLimitBytes = 0, legacyBlockBytes = 0, physicalChunkBytes = 8ull << 20;
   // [autotune]

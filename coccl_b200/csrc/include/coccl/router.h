@@ -46,6 +46,8 @@ void cocclRouterClose(cocclRouter* r);
 const char* cocclRouterEffectiveConfig(cocclRouter* r);
 uint64_t cocclRouterConfigHash(cocclRouter* r);
 int cocclRouterEnabled(cocclRouter* r);
+// [runtime] fused_kernel_max_ctas of the policy (0 = no limit).
+int cocclRouterFusedMaxCtas(cocclRouter* r);
 int cocclRouterTrainingMode(cocclRouter* r);
 
 // What happens to a collective of `count` elements (the count of the matching nccl* call) on a communicator of

@@ -137,7 +137,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
     a.flags[p] = static_cast<unsigned int*>(st.signals.ptr(p));
     a.status[p] = static_cast<char*>(st.signals.ptr(p)) + cocclkFlagBytes();
   }
-  const int rc = cocclkFusedCollective(&a, 1, 0, info.stream);
+  const int rc = cocclkFusedCollective(&a, 1, rt->config().fusedMaxCtas, info.stream);
   if (rc != 0) return rc < 0 ? ncclInvalidArgument : ncclUnhandledCudaError;
   // the status word (written by a bounded wait that ran out) follows the kernel to pinned host memory, where
   // asyncStatus reads it without touching the device

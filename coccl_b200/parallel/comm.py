@@ -122,6 +122,10 @@ class Router:
         self._eff = _lib.declare("cocclRouterEffectiveConfig", C.c_char_p, [C.c_void_p])
         self._hash = _lib.declare("cocclRouterConfigHash", C.c_uint64, [C.c_void_p])
         self._training = _lib.declare("cocclRouterTrainingMode", C.c_int, [C.c_void_p])
+        try:
+            self._max_ctas = _lib.declare("cocclRouterFusedMaxCtas", C.c_int, [C.c_void_p])
+        except AttributeError:   # a library built before the key existed
+            self._max_ctas = None
         self._set = _lib.declare("cocclRouterSetMeasured", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double])
         self._set_native = _lib.declare("cocclRouterSetMeasuredNative", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double])
         self._stats = _lib.declare("cocclRouterStats", None, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)])
@@ -161,6 +165,10 @@ class Router:
 
     def effective_config(self) -> str:
         return self._eff(self.handle).decode()
+
+    def fused_max_ctas(self) -> int:
+        """[runtime] fused_kernel_max_ctas of the policy file (0 = no limit)."""
+        return int(self._max_ctas(self.handle)) if self._max_ctas is not None else 0
 
     def config_hash(self) -> str:
         return f"{int(self._hash(self.handle)):016x}"
@@ -377,6 +385,8 @@ class Communicator:
         if self.size > _lib.MAX_RANKS:
             self.policy = NATIVE  # fused kernels cover one NVSwitch domain of up to 8 ranks
         self.router = Router.of(self.policy, self.size) if (self.cuda and self.size > 1) else None
+        # CTAs a fused kernel may occupy: the Policy object's own field, else the policy file's [runtime] key
+        self.max_ctas = self.policy.max_ctas or (self.router.fused_max_ctas() if self.router is not None else 0)
 
     # ------------------------------------------------------------------ symmetric state
     def _ensure(self, half_bytes: int):
@@ -424,7 +434,7 @@ class Communicator:
             self._trace.zero_()
             a.trace[self.rank] = self._trace.data_ptr()
         with nvtx_range(f"coccl.fused.{K_NAMES.get(opc, opc)}.{a.codec.kind}"):
-            rc = _lib.lib().cocclkFusedCollective(a, 1, self.policy.max_ctas, _lib.cur_stream())
+            rc = _lib.lib().cocclkFusedCollective(a, 1, self.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkFusedCollective")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += inp.numel() * inp.element_size()
@@ -663,7 +673,7 @@ class Communicator:
         with nvtx_range("coccl.nvls.all_reduce"):
             rc = _lib.lib().cocclkNvlsAllReduce(mc, x.numel(), DTYPE_CODE[x.dtype], self.size, self.rank, fl, status,
                                                 st["epoch"] & 0xFFFFFFFF, int(self.policy.timeout_ms * 1e6),
-                                                self.policy.max_ctas, _lib.cur_stream())
+                                                self.max_ctas, _lib.cur_stream())
         _lib.check(rc, "cocclkNvlsAllReduce")
         if buf is not None:
             x.view(-1).copy_(buf)
@@ -825,7 +835,7 @@ class Communicator:
             assert gathered.is_contiguous() and gathered.shape == (M, K) and gathered.dtype == torch.bfloat16
             a.gathered[self.rank] = gathered.data_ptr()   # the CTA-pair kernel copies the operand out itself
         with nvtx_range("coccl.fused.ag_gemm"):
-            _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
+            _lib.check(_lib.lib().cocclkAgGemm(a, 1, self.max_ctas, _lib.cur_stream()), "cocclkAgGemm")
         self.stats["compressed_calls"] += 1
         if gathered is not None and _lib.lib().cocclkTpLastVariant() != 2:
             # the peers' shards are in this call's half of the workspace, the own shard never left x_local
@@ -886,7 +896,7 @@ class Communicator:
             assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
             a.bias[self.rank] = bias.data_ptr()
         with nvtx_range("coccl.fused.gemm_rs"):
-            _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
+            _lib.check(_lib.lib().cocclkGemmRs(a, 1, self.max_ctas, _lib.cur_stream()), "cocclkGemmRs")
         if bias is not None and _lib.lib().cocclkTpLastVariant() != 2:
             out += bias   # the single-CTA kernel's reducer has no bias operand
         self.stats["compressed_calls"] += 1
@@ -969,7 +979,7 @@ class Communicator:
         if row_scale is not None:
             assert row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.shape == expert_ids.shape
             a.rowScale[r] = row_scale.data_ptr()
-        _lib.check(_lib.lib().cocclkMoeDispatch(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeDispatch")
+        _lib.check(_lib.lib().cocclkMoeDispatch(a, 1, self.max_ctas, _lib.cur_stream()), "cocclkMoeDispatch")
         self.stats["compressed_calls"] += 1
         self.stats["compressed_raw_bytes"] += tokens * topk * hidden * 2
         h = M.Handle(expert_ids, pos, rcnt, roff, capacity, n_experts)
@@ -993,7 +1003,7 @@ class Communicator:
             assert dot_with.dtype == torch.bfloat16 and dot_with.is_contiguous() and dot_with.shape == (tokens, hidden)
             dots = torch.empty(tokens, topk, dtype=torch.float32, device=y.device)
             a.dotWith[r], a.dotOut[r] = dot_with.data_ptr(), dots.data_ptr()
-        _lib.check(_lib.lib().cocclkMoeCombine(a, 1, self.policy.max_ctas, _lib.cur_stream()), "cocclkMoeCombine")
+        _lib.check(_lib.lib().cocclkMoeCombine(a, 1, self.max_ctas, _lib.cur_stream()), "cocclkMoeCombine")
         return out if dot_with is None else (out, dots)
 
     def moe_status(self) -> int:

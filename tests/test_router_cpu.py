@@ -94,3 +94,17 @@ def test_explicit_call_ignores_the_threshold_and_codecs_without_tile_form_are_re
     # integer payloads: a lossy codec leaves them native, a bytewise-lossless one takes them
     assert not _decide(zfp, 0, "all_gather", torch.int32, 1 << 20)[1].compressed
     assert _decide(ans, 0, "all_gather", torch.int32, 1 << 20)[1].compressed
+
+
+def test_policy_file_limits_the_ctas_of_the_fused_kernels():
+    """[runtime] fused_kernel_max_ctas: the share of the GPU a fused kernel may take (its CTAs wait on one another, so
+    whatever runs next to it must leave them resident); the communicator launches with that limit."""
+    base = Policy.training(threshold_bytes=0)
+    assert Router.of(base, 2).fused_max_ctas() == 0
+    limited = Policy(toml=base.toml.replace('mode = "training"', 'mode = "training"\nfused_kernel_max_ctas = 96', 1))
+    r = Router.of(limited, 2)
+    assert r.fused_max_ctas() == 96 and "fused_kernel_max_ctas = 96" in r.effective_config()
+    import pytest
+    bad = Policy(toml=base.toml.replace('mode = "training"', 'mode = "training"\nfused_kernel_max_ctas = -3', 1))
+    with pytest.raises(Exception):
+        Router.of(bad, 2)
