@@ -101,10 +101,11 @@ def test_policy_file_limits_the_ctas_of_the_fused_kernels():
     whatever runs next to it must leave them resident); the communicator launches with that limit."""
     base = Policy.training(threshold_bytes=0)
     assert Router.of(base, 2).fused_max_ctas() == 0
-    limited = Policy(toml=base.toml.replace('mode = "training"', 'mode = "training"\nfused_kernel_max_ctas = 96', 1))
+    assert "fused_kernel_max_ctas = 0" in base.toml
+    limited = Policy(toml=base.toml.replace("fused_kernel_max_ctas = 0", "fused_kernel_max_ctas = 96", 1))
     r = Router.of(limited, 2)
     assert r.fused_max_ctas() == 96 and "fused_kernel_max_ctas = 96" in r.effective_config()
     import pytest
-    bad = Policy(toml=base.toml.replace('mode = "training"', 'mode = "training"\nfused_kernel_max_ctas = -3', 1))
+    bad = Policy(toml=base.toml.replace("fused_kernel_max_ctas = 0", "fused_kernel_max_ctas = -3", 1))
     with pytest.raises(Exception):
         Router.of(bad, 2)
