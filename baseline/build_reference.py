@@ -17,7 +17,8 @@ through baseline/cmake_sm100.sh (make variable CMAKE), which swaps the
 hard-coded COCCL_CUDA_ARCHITECTURES=80 of dietgpu/Makefile:30 for 100 and adds
 the policy flag the vendored glog needs under a current CMake.
 
-Usage:  python baseline/build_reference.py [--jobs N] [--src /root/reference] [--scratch /tmp/coccl_ref_src]
+Usage:  python baseline/build_reference.py [--jobs N] [--src <reference checkout>] [--scratch /tmp/coccl_ref_src]
+(--src defaults to the directory `reference` beside this repository, or $COCCL_REFERENCE_SRC)
 Outputs under baseline/_ref/build: lib/libnccl.so.2, bin/coccl-config-check,
 obj/coccl-extend/compressor_plugin/libcompress/lib{sdp4bit,taco,zfp,dietgpu}.so, tests/*_perf.
 """
@@ -57,7 +58,7 @@ def prune() -> None:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=os.environ.get("COCCL_REFERENCE_SRC", str(Path(__file__).resolve().parents[2] / "reference")))
     ap.add_argument("--scratch", default="/tmp/coccl_ref_src")
     ap.add_argument("--cuda-home", default=os.environ.get("CUDA_HOME", "/usr/local/cuda"))
     a = ap.parse_args()

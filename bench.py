@@ -81,7 +81,7 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    # Two independent reasons, both recorded in DESIGN.md:
+    # Two independent reasons:
     #  * the reference is a C++/CUDA fork of NCCL with no Python package and no trainer: a pip install of its source
     #    tree fails ("Neither 'setup.py' nor 'pyproject.toml' found") and its Megatron submodule is empty, so no
     #    stock code path of it produces GPT tokens/s;
