@@ -527,6 +527,11 @@ extern "C" int cocclkTpLastVariant() { return gTpLast; }
 static int tryPair(const cocclkTpArgs* args, int emulatedRanks, int maxCtas, cudaStream_t stream, int isRs, int* rc) {
   const int v = cocclkTpGetVariant();
   if (v == 1) return 0;
+  // "auto": the CTA-pair kernels up to four ranks. At eight ranks (2048 rows per rank on the MLP shapes) they were
+  // measured slower than the single-CTA kernels (all-gather GEMM 0.442 against 0.360 ms, reduce-scatter GEMM 0.457
+  // against 0.361 ms): with seven ring steps the two push warps of 74 pairs cannot keep the next shard ahead of the
+  // tensor cores, and the own-rows reducer waits for seven copies.
+  if (v == 0 && args->nRanks > 4) return 0;
   if (!cocclkTpPairUsable(args, isRs)) {
     if (v == 2) { *rc = -1; return 1; }
     return 0;
