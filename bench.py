@@ -133,6 +133,8 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--parallelism", default=None, help="override as tp,pp,dp")
     ap.add_argument("--no-compress", action="store_true", help="route collectives through NCCL only")
+    ap.add_argument("--virtual-stages", type=int, default=1,
+                    help="model chunks per pipeline rank (> 1: interleaved 1F1B); the default is the measured schedule")
     ap.add_argument("--profile-step", default="", metavar="FILE",
                     help="after the timed regions, run ONE more step under torch.profiler and write rank 0's per-kernel "
                          "device-time table (shares; never a bench value) to FILE")
@@ -167,7 +169,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         from coccl_b200.parallel.mesh import Mesh
         mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=not args.no_compress)
-    par = ParallelConfig(tp=tp, pp=pp, dp=dp)
+    par = ParallelConfig(tp=tp, pp=pp, dp=dp, virtual_stages=args.virtual_stages if pp > 1 else 1)
     trainer = Trainer(cfg, dev, micro_batch=2, parallel=par, groups=mesh)
 
     # this DP rank's share of the global batch: seqs_per_gpu * (tp*pp) sequences per step
@@ -235,7 +237,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
             "config": {"model": f"{args.model}: L{cfg.n_layer} h{cfg.hidden} heads{cfg.n_head} ffn{cfg.ffn} gelu "
                                 f"seq{cfg.seq_len} vocab{cfg.vocab}", "global_batch": global_batch,
-                       "seq_len": cfg.seq_len, "micro_batch": 2, "parallelism": f"tp{tp}pp{pp}dp{dp}",
+                       "seq_len": cfg.seq_len, "micro_batch": 2, "parallelism": f"tp{tp}pp{pp}dp{dp}" + (f"v{par.virtual_stages}" if par.virtual_stages > 1 else ""),
                        "optimizer": "AdamW, fp32 master weights, sharded over DP",
                        "compressed_collectives": (n > 1 and not args.no_compress),
                        # hash of the effective policy (the TOML the routing session parsed) per communicator of rank 0

@@ -216,10 +216,15 @@ class TransformerLayer(nn.Module):
 
 
 class GPTStage(nn.Module):
-    """Layers [first, last) of the model plus the embedding (first stage) and the head (last stage)."""
+    """Layers [first, last) of the model plus the embedding (first stage) and the head (last stage).
+
+    With `layer_ranges` the stage holds several model chunks (the virtual stages of an interleaved pipeline schedule,
+    parallel/pp.py): chunk c is layers [first_c, last_c); the embedding belongs to chunk 0 and the head to the last
+    chunk. All chunks share ONE parameter store, so the optimizer, the checkpoint and the gradient reduction see one
+    flat buffer whatever the schedule."""
 
     def __init__(self, cfg: GPTConfig, device, tp=None, first_layer=0, last_layer=None, pre=True, post=True,
-                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None):
+                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None, layer_ranges=None):
         """ep_comm: communicator of the expert-parallel group for a mixture-of-experts model (None: every expert is
         local). Expert weights that differ between the ranks of that group live in a second flat buffer pair,
         `expert_store`, which data parallelism must not reduce or gather."""
@@ -250,7 +255,11 @@ class GPTStage(nn.Module):
             return TransformerLayer(c, i, s, t)
 
         make = layer_factory or default_layer
-        self.layers = nn.ModuleList([make(cfg, i, store, tp_) for i in range(first_layer, last_layer)])
+        ranges = list(layer_ranges) if layer_ranges is not None else [(first_layer, last_layer)]
+        assert all(0 <= a <= b <= cfg.n_layer for a, b in ranges), ranges
+        chunks = [[make(cfg, i, store, tp_) for i in range(a, b)] for a, b in ranges]
+        self.layers = nn.ModuleList([layer for chunk in chunks for layer in chunk])
+        self.chunks = chunks   # plain lists: the modules are registered through self.layers
         if post:
             store.add("lnf.weight", (cfg.hidden,), "ones", replicated=True)
             store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
@@ -284,17 +293,26 @@ class GPTStage(nn.Module):
             e = e + pos
         return e.to(cfg.dtype)
 
-    def forward(self, tokens_or_hidden, targets=None, loss_scale: float = 1.0, batch=None, seq=None):
+    def chunk_is_first(self, chunk=None) -> bool:
+        """Whether model chunk `chunk` (None: the whole stage) starts with the embedding."""
+        return self.pre and (chunk is None or chunk == 0)
+
+    def chunk_is_last(self, chunk=None) -> bool:
+        """Whether model chunk `chunk` (None: the whole stage) ends with the head and the loss."""
+        return self.post and (chunk is None or chunk == len(self.chunks) - 1)
+
+    def forward(self, tokens_or_hidden, targets=None, loss_scale: float = 1.0, batch=None, seq=None, chunk=None):
         """First stage takes token ids [b, s]; later stages take (x, delta) from the previous stage.
-        The last stage returns the scaled summed loss; others return (x, delta)."""
-        if self.pre:
+        The last stage returns the scaled summed loss; others return (x, delta). `chunk` runs one model chunk of a
+        stage built with `layer_ranges`; None runs all of the stage's layers in order."""
+        if self.chunk_is_first(chunk):
             batch, seq = tokens_or_hidden.shape
             x, delta = self.embed(tokens_or_hidden), None
         else:
             x, delta = tokens_or_hidden
-        for layer in self.layers:
+        for layer in (self.layers if chunk is None else self.chunks[chunk]):
             x, delta = layer(x, delta, batch, seq)
-        if not self.post:
+        if not self.chunk_is_last(chunk):
             return x, delta
         y, _ = fused.layer_norm(x, self.lnf_weight, self.lnf_bias, self.cfg.eps, residual=delta)
         y = self.tp.gather_tokens(y)

@@ -24,6 +24,7 @@ class ParallelConfig:
     sequence_parallel: bool = True
     dp_strategy: str = "zero1"   # "zero1": sharded optimizer (reduce-scatter + all-gather); "ddp": gradient all-reduce
     ep: int = 1   # expert parallelism of a mixture-of-experts model: 1 (every rank holds all experts) or dp
+    virtual_stages: int = 1   # model chunks per pipeline rank; > 1 selects the interleaved 1F1B schedule
 
 
 class Trainer:
@@ -36,12 +37,15 @@ class Trainer:
         tp_ctx = g.tp_context() if g is not None else None
         pp_rank = g.pp_rank if g is not None else 0
         pp = self.parallel.pp
-        per = cfg.n_layer // pp
-        assert cfg.n_layer % pp == 0
+        chunks = self.parallel.virtual_stages if pp > 1 else 1
+        per = cfg.n_layer // (pp * chunks)
+        assert chunks >= 1 and cfg.n_layer % (pp * chunks) == 0, "layers must divide evenly over the (virtual) pipeline stages"
+        # virtual stage c * pp + pp_rank is this rank's chunk c (one chunk: the plain contiguous split)
+        ranges = [((c * pp + pp_rank) * per, (c * pp + pp_rank + 1) * per) for c in range(chunks)]
         dp = self.parallel.dp
         ep_comm = getattr(g, "ep_comm", None) if g is not None else None
         assert self.parallel.ep == (ep_comm.size if ep_comm is not None else 1), "ParallelConfig.ep and the mesh disagree"
-        self.stage = GPTStage(cfg, device, tp=tp_ctx, first_layer=pp_rank * per, last_layer=(pp_rank + 1) * per,
+        self.stage = GPTStage(cfg, device, tp=tp_ctx, layer_ranges=ranges,
                               pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * dp * 2048,
                               ep_comm=ep_comm)
         # experts spread over the expert-parallel group: updated locally (never reduced or gathered), clipped with
@@ -67,8 +71,9 @@ class Trainer:
                                         strategy=self.parallel.dp_strategy)
         self.schedule = None
         if pp > 1:
-            from .parallel.pp import PipelineSchedule
-            self.schedule = PipelineSchedule(self.stage, g, cfg, micro_batch)
+            from .parallel.pp import InterleavedSchedule, PipelineSchedule
+            self.schedule = (InterleavedSchedule(self.stage, g, cfg, micro_batch, chunks) if chunks > 1
+                             else PipelineSchedule(self.stage, g, cfg, micro_batch))
         self._loss_acc = torch.zeros(1, dtype=torch.float32, device=device)
         self._dev_tokens = None
 

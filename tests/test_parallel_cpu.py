@@ -29,14 +29,15 @@ def _reference_losses(steps=3, n_seq=8):
     return tr, list(zip(losses, norms))
 
 
-def _worker(rank, world, tp, pp, dp, ref_losses, ref_params):
+def _worker(rank, world, tp, pp, dp, ref_losses, ref_params, virtual_stages=1):
     import torch.distributed as dist
     from coccl_b200.parallel.mesh import Mesh
     from coccl_b200.train import ParallelConfig, Trainer
     from coccl_b200.utils.checkpoint import shard_param
     cfg = _cfg()
     mesh = Mesh(tp=tp, pp=pp, dp=dp, device=torch.device("cpu"))
-    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=1e-2)
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages),
+                 groups=mesh, lr=1e-2)
     # load the single-process model's initial weights, re-sharded for this rank
     for name, p in tr.stage.store.params.items():
         p.data.copy_(shard_param(name, ref_params[name], mesh.tp_rank, tp))
@@ -63,6 +64,49 @@ def test_parallel_layouts_match_single_process(tp, pp, dp):
     tr2, _ = _reference_losses(steps=0)
     params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
     run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params))
+
+
+@pytest.mark.parametrize("tp,pp,dp,chunks", [(1, 2, 1, 2), (1, 2, 2, 2), (2, 2, 1, 2), (1, 4, 1, 1)])
+def test_interleaved_pipeline_matches_single_process(tp, pp, dp, chunks):
+    """Two model chunks per pipeline rank (virtual stages c * pp + rank): same losses and gradient norms as one process."""
+    tr, losses = _reference_losses()
+    tr2, _ = _reference_losses(steps=0)
+    params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
+    run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params, chunks))
+
+
+def test_interleaved_plan_is_complete_and_ordered():
+    from coccl_b200.parallel.pp import interleaved_order, plan_ticks
+    for pp, chunks, n_micro in [(2, 2, 4), (2, 2, 16), (4, 2, 8), (4, 3, 12), (8, 2, 16), (2, 4, 2)]:
+        ticks = plan_ticks(pp, chunks, n_micro)
+        when = {}
+        for t, row in enumerate(ticks):
+            for r, a in enumerate(row):
+                if a is not None:
+                    key = (a[0], a[1] * pp + r, a[2])
+                    assert key not in when
+                    when[key] = t
+        last = pp * chunks - 1
+        assert len(when) == 2 * n_micro * pp * chunks
+        for (kind, vs, m), t in when.items():
+            if kind == "F" and vs > 0:
+                assert when[("F", vs - 1, m)] < t
+            if kind == "B":
+                assert when[("F", vs, m)] < t
+                if vs < last:
+                    assert when[("B", vs + 1, m)] < t
+        # each rank runs its passes in its own 1F1B order, and never holds more forward passes than the warm-up allows
+        for r in range(pp):
+            mine = [a for row in ticks for q, a in enumerate(row) if q == r and a is not None]
+            assert mine == interleaved_order(pp, r, chunks, n_micro)
+            live = peak = 0
+            for a in mine:
+                live += 1 if a[0] == "F" else -1
+                peak = max(peak, live)
+            assert peak <= min((pp - r - 1) * 2 + (chunks - 1) * pp, n_micro * chunks) + 1
+        # the bubble: idle ticks per rank do not grow with the number of chunks (each tick is 1/chunks as long)
+        idle = sum(a is None for row in ticks for a in row) / pp
+        assert idle <= 2 * (pp - 1) + 1, (pp, chunks, n_micro, idle)
 
 
 # ---------------------------------------------------------------------------- mixture of experts in the trainer

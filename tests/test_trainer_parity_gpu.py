@@ -45,7 +45,7 @@ def _single_gpu():
     return params, losses
 
 
-def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses):
+def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses, virtual_stages=1):
     import torch.distributed as dist
     from coccl_b200.parallel.comm import Policy
     from coccl_b200.parallel.mesh import Mesh
@@ -54,7 +54,8 @@ def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses):
     dev = torch.device("cuda", rank)
     cfg = _cfg()
     mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress, policy=Policy.training(threshold_bytes=0, dp_delta=False))
-    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp), groups=mesh, lr=3e-4)
+    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages), groups=mesh,
+                 lr=3e-4)
     for name, p in tr.stage.store.params.items():
         p.data.copy_(shard_param(name, ref_params[name], mesh.tp_rank, tp).to(dev))
     tr.opt.master.copy_(tr.opt.param_shard.float())
@@ -90,6 +91,12 @@ def reference():
 def test_two_gpu_layouts_follow_the_single_gpu_curve(reference, tp, pp, dp, compress):
     params, losses = reference
     run_distributed(_worker, 2, "nccl", (tp, pp, dp, compress, params, losses), timeout=420)
+
+
+def test_interleaved_pipeline_follows_the_single_gpu_curve(reference):
+    """pp = 2 with two model chunks per rank (four virtual stages of one layer): NCCL batches of the tick plan."""
+    params, losses = reference
+    run_distributed(_worker, 2, "nccl", (1, 2, 1, False, params, losses, 2), timeout=420)
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
