@@ -1,0 +1,238 @@
+"""GPT pre-training launcher: the command a user runs, one process per GPU.
+
+    python -m coccl_b200.pretrain --model gpt-tiny --steps 50                                   # one GPU
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m coccl_b200.pretrain \\
+        --model gpt-6.7b --tp 2 --pp 2 --dp 2 --global-batch 128 --data tokens.bin --save ckpt --save-interval 500
+
+The reference's counterpart is a bash launcher that exports COCCL_ENABLE / COCCL_CONFIG_FILE, preloads the library
+into PyTorch and starts an external Megatron trainer with TP / PP / EP sizes, batch sizes, a learning-rate schedule and
+save / load directories (examples/training_scripts/train_qwen_coccl.sh:60-131). Here the trainer is part of the
+package, so the launcher is this module: the same two environment variables choose the policy (or --policy /
+--no-compress), the parallel sizes are flags, and the loop adds what a long run needs: a data loader with prefetch
+into pinned memory, warm-up + cosine learning-rate schedule, periodic logs (loss, gradient norm, tokens/s, model
+TFLOP/s per GPU), checkpoints with resume, and the heartbeat that notices a lost rank between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+MODELS = {
+    "gpt-6.7b": dict(),
+    "gpt-1.3b": dict(n_layer=24, hidden=2048, n_head=16, ffn=8192),
+    "gpt-small": dict(n_layer=4, hidden=2048, n_head=16, ffn=8192),
+    "gpt-tiny": dict(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
+    "moe-tiny": dict(n_layer=4, hidden=512, n_head=8, ffn=1024, seq_len=256, vocab=8192, n_experts=4, moe_top_k=2, moe_every=2),
+}
+
+
+def parse(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m coccl_b200.pretrain", description=__doc__.split("\n\n")[0])
+    m = ap.add_argument_group("model")
+    m.add_argument("--model", default="gpt-tiny", choices=sorted(MODELS))
+    for name, typ in (("layers", int), ("hidden", int), ("heads", int), ("ffn", int), ("seq-len", int), ("vocab", int),
+                      ("experts", int), ("moe-top-k", int), ("moe-every", int)):
+        m.add_argument(f"--{name}", type=typ, default=None, help="overrides the preset")
+    m.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"], help="fp32 is for CPU runs")
+    p = ap.add_argument_group("parallelism (tp * pp * dp = world size)")
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--pp", type=int, default=1)
+    p.add_argument("--dp", type=int, default=0, help="0: world size / (tp * pp)")
+    p.add_argument("--ep", type=int, default=1, help="expert parallelism: 1 or the data-parallel size")
+    p.add_argument("--virtual-stages", type=int, default=1, help="model chunks per pipeline rank (interleaved 1F1B)")
+    p.add_argument("--no-sequence-parallel", action="store_true")
+    p.add_argument("--dp-strategy", default="zero1", choices=["zero1", "ddp"])
+    c = ap.add_argument_group("collectives")
+    c.add_argument("--policy", default=None, help="policy file (TOML); default: $COCCL_CONFIG_FILE, else the shipped training policy")
+    c.add_argument("--no-compress", action="store_true", help="native collectives only (also COCCL_ENABLE=0)")
+    t = ap.add_argument_group("training")
+    t.add_argument("--steps", type=int, default=100)
+    t.add_argument("--global-batch", type=int, default=0, help="sequences per step over all ranks; 0: 8 per data-parallel rank")
+    t.add_argument("--micro-batch", type=int, default=2)
+    t.add_argument("--lr", type=float, default=3e-4)
+    t.add_argument("--min-lr", type=float, default=3e-5)
+    t.add_argument("--warmup-steps", type=int, default=10)
+    t.add_argument("--decay-steps", type=int, default=0, help="0: decay over --steps")
+    t.add_argument("--weight-decay", type=float, default=0.1)
+    t.add_argument("--clip-grad", type=float, default=1.0)
+    t.add_argument("--seed", type=int, default=1234)
+    d = ap.add_argument_group("data")
+    d.add_argument("--data", default=None, help="flat token file (uint16 / uint32, or .npy); default: synthetic ids")
+    d.add_argument("--data-dtype", default="auto", choices=["auto", "uint16", "uint32"])
+    k = ap.add_argument_group("checkpoints and logs")
+    k.add_argument("--save", default=None, metavar="DIR")
+    k.add_argument("--save-interval", type=int, default=0, help="0: only at the end")
+    k.add_argument("--resume", action="store_true", help="continue from --save if it holds a checkpoint")
+    k.add_argument("--log-interval", type=int, default=10)
+    k.add_argument("--log-json", default=None, metavar="FILE", help="rank 0 appends one JSON line per log interval")
+    k.add_argument("--heartbeat-stale-s", type=float, default=120.0, help="a peer silent for this long counts as lost; 0: off")
+    ap.add_argument("--device", default="auto", choices=["auto", "cuda", "cpu"])
+    return ap.parse_args(argv)
+
+
+def learning_rate(step: int, *, peak: float, floor: float, warmup: int, decay: int) -> float:
+    """Linear warm-up to `peak` over `warmup` steps, then a half cosine down to `floor` at step `decay`."""
+    if warmup > 0 and step < warmup:
+        return peak * (step + 1) / warmup
+    if step >= decay:
+        return floor
+    frac = (step - warmup) / max(decay - warmup, 1)
+    return floor + 0.5 * (peak - floor) * (1.0 + math.cos(math.pi * frac))
+
+
+def model_config(args):
+    from .models.gpt import GPTConfig
+    kw = dict(MODELS[args.model])
+    for flag, field in (("layers", "n_layer"), ("hidden", "hidden"), ("heads", "n_head"), ("ffn", "ffn"), ("seq_len", "seq_len"),
+                        ("vocab", "vocab"), ("experts", "n_experts"), ("moe_top_k", "moe_top_k"), ("moe_every", "moe_every")):
+        v = getattr(args, flag)
+        if v is not None:
+            kw[field] = v
+    kw["dtype"] = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    return GPTConfig(**kw)
+
+
+def main(argv=None) -> int:
+    args = parse(argv)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
+    dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(dev)
+    dp = args.dp or world // (args.tp * args.pp)
+    if args.tp * args.pp * dp != world:
+        raise SystemExit(f"tp * pp * dp = {args.tp} * {args.pp} * {dp} does not equal the world size {world}")
+    if not use_cuda and args.dtype == "bf16":
+        args.dtype = "fp32"
+    cfg = model_config(args)
+
+    from .parallel.comm import Policy
+    from .train import ParallelConfig, Trainer
+    from .utils import checkpoint
+    from .utils.data import BatchLoader, SyntheticTokens, TokenFile
+    from .utils.health import Heartbeat, default_store
+
+    enabled = not args.no_compress and os.environ.get("COCCL_ENABLE", "1") != "0"
+    policy_file = args.policy or os.environ.get("COCCL_CONFIG_FILE")
+    policy = Policy(enabled=enabled, config_file=policy_file)
+    mesh = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if use_cuda:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
+        from .parallel.mesh import Mesh
+        mesh = Mesh(tp=args.tp, pp=args.pp, dp=dp, device=dev, compress=enabled, policy=policy,
+                    sequence_parallel=not args.no_sequence_parallel, ep=args.ep)
+    par = ParallelConfig(tp=args.tp, pp=args.pp, dp=dp, sequence_parallel=not args.no_sequence_parallel,
+                         dp_strategy=args.dp_strategy, ep=args.ep, virtual_stages=args.virtual_stages if args.pp > 1 else 1)
+    trainer = Trainer(cfg, dev, micro_batch=args.micro_batch, parallel=par, groups=mesh, lr=args.lr,
+                      weight_decay=args.weight_decay, clip_grad=args.clip_grad, seed=args.seed)
+
+    global_batch = args.global_batch or 8 * dp
+    if global_batch % (dp * args.micro_batch):
+        raise SystemExit("--global-batch must be a multiple of dp * micro-batch")
+    if args.pp > 1 and par.virtual_stages > 1 and (global_batch // dp // args.micro_batch) % args.pp:
+        raise SystemExit("interleaved 1F1B needs the micro-batches per step to be a multiple of --pp")
+
+    start = 0
+    if args.resume and args.save and os.path.exists(os.path.join(args.save, "manifest.json")):
+        start = checkpoint.load(trainer, args.save, rank=rank)
+        if rank == 0:
+            print(f"resumed from {args.save} at step {start}", flush=True)
+
+    source = TokenFile(args.data, args.data_dtype) if args.data else SyntheticTokens(cfg.vocab, seed=args.seed)
+    loader = BatchLoader(source, seq_len=cfg.seq_len, global_batch=global_batch, dp_rank=mesh.dp_rank if mesh else 0,
+                         dp_size=dp, seed=args.seed, start_step=start, vocab=cfg.vocab)
+    heartbeat = None
+    if world > 1 and args.heartbeat_stale_s > 0 and default_store() is not None:
+        heartbeat = Heartbeat(default_store(), rank, world, stale_after_s=args.heartbeat_stale_s)
+
+    decay = args.decay_steps or args.steps
+    tokens_per_step = global_batch * cfg.seq_len
+    loss_group_size = args.tp * dp   # ranks of the last pipeline stage that hold a loss
+    if rank == 0:
+        print(json.dumps({"model": args.model, "params": cfg.num_params(), "world": world, "tp": args.tp, "pp": args.pp, "dp": dp,
+                          "ep": args.ep, "virtual_stages": par.virtual_stages, "global_batch": global_batch,
+                          "seq_len": cfg.seq_len, "compressed_collectives": enabled and world > 1,
+                          "policy": policy_file or ("shipped training policy" if enabled else "native"),
+                          "data": args.data or "synthetic"}), flush=True)
+
+    def save(step):
+        if args.save:
+            checkpoint.save(trainer, args.save, step, rank=rank, world=world)
+            if world > 1:
+                dist.barrier()
+            if rank == 0:
+                print(f"saved step {step} to {args.save}", flush=True)
+
+    window_loss = torch.zeros(1, dtype=torch.float32, device=dev)
+    window_steps, t_window = 0, time.time()
+    last_loss = float("nan")
+    try:
+        for step in range(start, args.steps):
+            if heartbeat is not None:
+                # peers must have finished the previous step before this one's kernels launch
+                heartbeat.check_peers(expect_step=step - 1, wait_s=args.heartbeat_stale_s)
+            lr = learning_rate(step, peak=args.lr, floor=args.min_lr, warmup=args.warmup_steps, decay=decay)
+            trainer.opt.lr = lr
+            if trainer.expert_opt is not None:
+                trainer.expert_opt.lr = lr
+            batch = loader.next()
+            loss = trainer.train_step(batch)
+            loader.copied()
+            window_loss += loss
+            window_steps += 1
+            if heartbeat is not None:
+                heartbeat.beat(step)
+            done = step + 1
+            if done % args.log_interval == 0 or done == args.steps:
+                t = window_loss.clone()
+                if world > 1:
+                    dist.all_reduce(t)   # only the last pipeline stage contributes; every rank takes part
+                if use_cuda:
+                    torch.cuda.synchronize()
+                dt = time.time() - t_window
+                last_loss = t.item() / (loss_group_size * window_steps)
+                if rank == 0:
+                    rate = tokens_per_step * window_steps / dt
+                    rec = {"step": done, "loss": round(last_loss, 5), "grad_norm": round(trainer.opt.grad_norm.item(), 4),
+                           "lr": lr, "tokens_per_s": round(rate, 1),
+                           "model_tflops_per_gpu": round(cfg.flops_per_token() * rate / world / 1e12, 2),
+                           "ms_per_step": round(1e3 * dt / window_steps, 2)}
+                    print(json.dumps(rec), flush=True)
+                    if args.log_json:
+                        with open(args.log_json, "a") as f:
+                            f.write(json.dumps(rec) + "\n")
+                trainer.check_health(wait=True)
+                window_loss.zero_()
+                window_steps, t_window = 0, time.time()
+            if args.save_interval and done % args.save_interval == 0 and done != args.steps:
+                save(done)
+        save(args.steps)
+    finally:
+        loader.close()
+        if heartbeat is not None:
+            heartbeat.leave(args.steps)
+        if mesh is not None:
+            mesh.close()
+        if world > 1 and dist.is_initialized():
+            dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps({"final_loss": last_loss, "steps": args.steps}), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

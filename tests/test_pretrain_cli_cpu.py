@@ -1,0 +1,113 @@
+"""The pre-training launcher and its data loader on CPU: schedule, data determinism, resume, a two-rank run."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = ["--model", "gpt-tiny", "--layers", "2", "--hidden", "64", "--heads", "4", "--ffn", "128", "--seq-len", "32",
+        "--vocab", "128", "--device", "cpu", "--log-interval", "1", "--warmup-steps", "2", "--lr", "1e-2"]
+
+
+def _token_file(tmp_path, n=6000, vocab=128):
+    # a stream with structure (each id determines the next one most of the time), so that a few steps lower the loss
+    rng = np.random.default_rng(5)
+    path = str(tmp_path / "tokens.bin")
+    ids = (np.arange(n) * 7) % vocab
+    noise = rng.random(n) < 0.1
+    ids[noise] = rng.integers(0, vocab, int(noise.sum()))
+    ids.astype("<u2").tofile(path)
+    return path
+
+
+def _records(text):
+    return [json.loads(l) for l in text.splitlines() if l.startswith("{")]
+
+
+def test_learning_rate_schedule():
+    from coccl_b200.pretrain import learning_rate
+    kw = dict(peak=1.0, floor=0.1, warmup=4, decay=20)
+    assert [round(learning_rate(s, **kw), 3) for s in range(4)] == [0.25, 0.5, 0.75, 1.0]
+    assert learning_rate(4, **kw) == pytest.approx(1.0)
+    assert learning_rate(12, **kw) == pytest.approx(0.55)
+    assert learning_rate(20, **kw) == learning_rate(500, **kw) == 0.1
+    vals = [learning_rate(s, **kw) for s in range(4, 21)]
+    assert all(a >= b for a, b in zip(vals, vals[1:]))
+
+
+def test_loader_is_a_pure_function_of_seed_step_and_rank(tmp_path):
+    from coccl_b200.utils.data import BatchLoader, SyntheticTokens, TokenFile, sequence_starts
+    path = _token_file(tmp_path)
+    src = TokenFile(path)
+    raw = np.fromfile(path, dtype="<u2").astype(np.int64)
+    kw = dict(seq_len=32, global_batch=8, seed=3, vocab=128, pin=False)
+    whole = BatchLoader(src, dp_rank=0, dp_size=1, **kw)
+    halves = [BatchLoader(src, dp_rank=r, dp_size=2, **kw) for r in range(2)]
+    seen = []
+    for step in range(30):   # 6000 tokens = 187 windows: crosses an epoch boundary at step 23
+        b = whole.next()
+        assert torch.equal(b, torch.cat([h.next() for h in halves]))
+        starts = sequence_starts(src.length, 32, 3, step, 8)
+        for row, s in zip(b, starts):
+            assert np.array_equal(row.numpy(), raw[s:s + 33])
+        seen.extend(int(s) for s in starts)
+    windows = (6000 - 1) // 32
+    assert sorted(seen[:windows]) == [w * 32 for w in range(windows)]   # one epoch visits every window exactly once
+    resumed = BatchLoader(src, dp_rank=1, dp_size=2, start_step=30, **kw)
+    assert torch.equal(resumed.next(), halves[1].next())
+    for l in [whole, resumed] + halves:
+        l.close()
+    syn = SyntheticTokens(1000, seed=9)
+    assert np.array_equal(syn.tokens(4000, 300)[90:110], syn.tokens(4090, 20))
+    with pytest.raises(RuntimeError):
+        bad = BatchLoader(src, dp_rank=0, dp_size=1, seq_len=32, global_batch=8, seed=3, vocab=64, pin=False)
+        try:
+            bad.next()
+        finally:
+            bad.close()
+
+
+def test_resume_continues_the_uninterrupted_run(tmp_path, capsys):
+    from coccl_b200.pretrain import main
+    data = _token_file(tmp_path)
+    common = TINY + ["--data", data, "--global-batch", "4", "--decay-steps", "8"]
+    main(common + ["--steps", "8"])
+    full = _records(capsys.readouterr().out)
+    ck = str(tmp_path / "ck")
+    main(common + ["--steps", "4", "--save", ck])
+    capsys.readouterr()
+    main(common + ["--steps", "8", "--save", ck, "--resume"])
+    tail = _records(capsys.readouterr().out)
+    want = {r["step"]: r["loss"] for r in full if "step" in r}
+    got = {r["step"]: r["loss"] for r in tail if "step" in r}
+    assert sorted(got) == [5, 6, 7, 8]
+    for s in got:
+        assert got[s] == pytest.approx(want[s], rel=1e-5), (s, got, want)
+    assert want[8] < want[1]
+
+
+def test_two_rank_launch_matches_one_process(tmp_path, capsys):
+    """The command a user runs: torch.distributed.run, two gloo ranks, pipeline-parallel with two chunks per rank."""
+    from coccl_b200.pretrain import main
+    data = _token_file(tmp_path)
+    common = TINY + ["--data", data, "--global-batch", "8", "--steps", "3", "--layers", "4"]
+    main(common)
+    one = {r["step"]: r["loss"] for r in _records(capsys.readouterr().out) if "step" in r}
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""), OMP_NUM_THREADS="2")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "coccl_b200.pretrain"] + common +
+                         ["--pp", "2", "--virtual-stages", "2", "--log-json", str(tmp_path / "log.jsonl")],
+                         env=env, cwd=REPO, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    two = {r["step"]: r["loss"] for r in _records(open(tmp_path / "log.jsonl").read())}
+    assert sorted(two) == [1, 2, 3]
+    for s in two:
+        assert two[s] == pytest.approx(one[s], rel=2e-3), (two, one)
