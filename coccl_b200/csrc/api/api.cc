@@ -16,6 +16,8 @@
 #include "runtime/peer_exchange.h"
 #include "training/assist.h"
 #include "tuning/autotune.h"
+#include "tuning/fused_timer.h"
+#include "tuning/measured.h"
 
 using namespace coccl;
 
@@ -27,7 +29,9 @@ struct ApiState {
   BufferManager* buffers = nullptr;
   FusedExecutor* executor = nullptr;
   ModelStore models;
-  AutotuneSelector* selector = nullptr;
+  MeasuredTable measured;
+  FusedTimer* timer = nullptr;
+  MeasuredSelector* selector = nullptr;
   TrainingAssist* assist = nullptr;
   int comms = 0;
 };
@@ -68,7 +72,9 @@ ncclResult_t runtimeStart(Comm* comm) {
         bo.vmm = cudaVmmDriverApi();
         s.buffers = new BufferManager(bo);
         s.executor = new FusedExecutor(s.buffers);
-        s.selector = new AutotuneSelector(&s.models);
+        // measured one-shot / two-shot times of the fused kernels first, the cost model and heuristics behind them
+        s.timer = new FusedTimer(s.executor);
+        s.selector = new MeasuredSelector(&s.models, &s.measured, s.timer);
         rt.setExecutor(s.executor);
         rt.setSelector(s.selector);
         if (pc.config.mode == Mode::Training) {
@@ -92,6 +98,7 @@ void runtimeStop(Comm* comm) {
   Runtime& rt = globalRuntime();
   if (rt.enabled()) {
     if (s.executor) s.executor->releaseComm(comm);
+    if (s.timer) s.timer->release(comm);
     PeerDataPath::release(comm);
     for (Comm* child : {comm->intra, comm->inter}) if (child != nullptr) PeerDataPath::release(child);
     if (s.assist) s.assist->unregisterComm(comm);
@@ -361,6 +368,13 @@ void cocclApiGetStats(cocclApiStats* out) {
 }
 
 unsigned long long cocclApiPeerExchangeCalls(void) { return (unsigned long long)PeerDataPath::calls(); }
+
+void cocclApiMeasuredSelection(unsigned long long* bucketsTimed, unsigned long long* bucketsInTable) {
+  ApiState& s = state();
+  std::lock_guard<std::mutex> lock(s.mutex);
+  if (bucketsTimed) *bucketsTimed = s.selector ? s.selector->measuredBuckets() : 0;
+  if (bucketsInTable) *bucketsInTable = (unsigned long long)s.measured.size();
+}
 
 ncclResult_t cocclApiCommTrainingRole(ncclComm_t comm, cocclApiTrainingRole* out) {
   if (comm == nullptr || out == nullptr) return ncclInvalidArgument;

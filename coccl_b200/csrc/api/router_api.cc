@@ -11,6 +11,7 @@
 #include "runtime/log.h"
 #include "runtime/runtime.h"
 #include "tuning/autotune.h"
+#include "tuning/measured.h"
 
 using namespace coccl;
 
@@ -34,64 +35,6 @@ class FixedRole : public RoleOracle {
   Role role = Role::Normal;
 };
 
-struct MeasuredKey {
-  int op, dtype, nRanks, log2Bytes;
-  bool operator<(const MeasuredKey& o) const {
-    if (op != o.op) return op < o.op;
-    if (dtype != o.dtype) return dtype < o.dtype;
-    if (nRanks != o.nRanks) return nRanks < o.nRanks;
-    return log2Bytes < o.log2Bytes;
-  }
-};
-struct MeasuredEntry { int algorithm = 0; double seconds = 0.0; };
-
-// Measured table first (nearest bucket below, else above), then the production selector.
-class MeasuredSelector : public AlgorithmSelector {
- public:
-  MeasuredSelector(ModelStore* store, std::map<MeasuredKey, std::map<int, double>>* table) : inner_(store), table_(table) {}
-  ncclResult_t select(Runtime* rt, PreparedCall* call) override {
-    const Config& cfg = rt->config();
-    const bool forced = call->info.op == Operation::ReduceScatter ? cfg.rsAlgorithm != RsAlgorithmPolicy::Auto
-                                                                  : cfg.arAlgorithm != ArAlgorithmPolicy::Auto;
-    if (cfg.autotune && !forced && !table_->empty()) {
-      const size_t bytes = call->info.count * cocclTypeSize(call->info.datatype);
-      int lg = 0;
-      while ((bytes >> (lg + 1)) != 0) ++lg;
-      const int op = (int)call->info.op, dt = (int)call->info.datatype, n = call->info.comm->nRanks;
-      const std::map<int, double>* best = nullptr;
-      for (int d = 0; d < 40 && best == nullptr; ++d) {
-        auto it = table_->find(MeasuredKey{op, dt, n, lg - d});
-        if (it != table_->end()) best = &it->second;
-      }
-      for (int d = 1; d < 40 && best == nullptr; ++d) {
-        auto it = table_->find(MeasuredKey{op, dt, n, lg + d});
-        if (it != table_->end()) best = &it->second;
-      }
-      if (best != nullptr) {
-        int algo = 0;
-        double t = 0.0;
-        for (const auto& kv : *best) {
-          if (!algorithmSupported(*call, (Algorithm)kv.first)) continue;
-          if (algo == 0 || kv.second < t) { algo = kv.first; t = kv.second; }
-        }
-        if (algo != 0) {
-          call->algorithm = (Algorithm)algo;
-          if (call->info.comm->rank == 0) {
-            std::string all;
-            for (const auto& kv : *best) all += std::string(algorithmName((Algorithm)kv.first)) + "=" + std::to_string(kv.second * 1e6) + "us ";
-            COCCL_INFO(kLogTuning, "select bytes=%zu measured %s-> %s", bytes, all.c_str(), algorithmName(call->algorithm));
-          }
-          return ncclSuccess;
-        }
-      }
-    }
-    return inner_.select(rt, call);
-  }
- private:
-  AutotuneSelector inner_;
-  std::map<MeasuredKey, std::map<int, double>>* table_;
-};
-
 }  // namespace
 
 struct cocclRouter {
@@ -100,8 +43,8 @@ struct cocclRouter {
   RecordingExecutor exec;
   FixedRole roles;
   ModelStore models;
-  std::map<MeasuredKey, std::map<int, double>> measured;          // compressed algorithms
-  std::map<MeasuredKey, std::map<int, double>> measuredNative;    // uncompressed all-reduce variants
+  MeasuredTable measured;          // compressed algorithms, written by the front end that timed them
+  MeasuredTable measuredNative;    // uncompressed all-reduce variants
   MeasuredSelector selector{&models, &measured};
   Transport* noTransport = nullptr;
   std::string effective;
@@ -213,18 +156,14 @@ extern "C" int cocclRouterDecide(cocclRouter* r, int role, int op, int ncclDatat
   }
   // native: a small all-reduce may still prefer the multimem kernel when it was measured faster
   if (info.op == Operation::AllReduce && !r->measuredNative.empty()) {
-    const size_t bytes = count * width;
-    int lg = 0;
-    while ((bytes >> (lg + 1)) != 0) ++lg;
-    const std::map<int, double>* best = nullptr;
-    for (int d = 0; d < 40 && best == nullptr; ++d) {
-      auto it = r->measuredNative.find(MeasuredKey{op, ncclDatatype, nRanks, lg - d});
-      if (it != r->measuredNative.end()) best = &it->second;
-    }
-    if (best != nullptr) {
+    // the bucket of the call or the nearest measured one BELOW it: a variant that won at a larger size says nothing
+    // about a smaller call
+    MeasuredTable::Times best;
+    const bool have = r->measuredNative.nearest(op, ncclDatatype, nRanks, count * width, &best, /*belowOnly=*/true);
+    if (have) {
       double t = 0.0;
       bool first = true;
-      for (const auto& kv : *best)
+      for (const auto& kv : best)
         if (first || kv.second < t) { out->nativeVariant = kv.first; t = kv.second; first = false; }
     }
   }
@@ -234,13 +173,13 @@ extern "C" int cocclRouterDecide(cocclRouter* r, int role, int op, int ncclDatat
 extern "C" int cocclRouterSetMeasured(cocclRouter* r, int op, int ncclDatatype, int nRanks, int log2Bytes, int algorithm, double seconds) {
   if (r == nullptr || algorithm <= 0 || !(seconds > 0.0)) return (int)ncclInvalidArgument;
   std::lock_guard<std::mutex> lock(r->mutex);
-  r->measured[MeasuredKey{op, ncclDatatype, nRanks, log2Bytes}][algorithm] = seconds;
+  r->measured.set(op, ncclDatatype, nRanks, log2Bytes, algorithm, seconds);
   return 0;
 }
 extern "C" int cocclRouterSetMeasuredNative(cocclRouter* r, int ncclDatatype, int nRanks, int log2Bytes, int nativeVariant, double seconds) {
   if (r == nullptr || !(seconds > 0.0)) return (int)ncclInvalidArgument;
   std::lock_guard<std::mutex> lock(r->mutex);
-  r->measuredNative[MeasuredKey{(int)Operation::AllReduce, ncclDatatype, nRanks, log2Bytes}][nativeVariant] = seconds;
+  r->measuredNative.set((int)Operation::AllReduce, ncclDatatype, nRanks, log2Bytes, nativeVariant, seconds);
   return 0;
 }
 extern "C" void cocclRouterStats(cocclRouter* r, uint64_t* nativeCalls, uint64_t* compressedCalls, uint64_t* policyLookups) {

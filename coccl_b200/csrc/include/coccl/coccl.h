@@ -71,6 +71,12 @@ void cocclApiGetStats(cocclApiStats* out);
 // How many exchanges of encoded bytes of the staged pipeline (codecs without a fused kernel form: rANS, ZFP at rates
 // without one, third-party plugins) this process served by its own peer-memory kernel instead of a library collective.
 unsigned long long cocclApiPeerExchangeCalls(void);
+// Algorithm selection from measured times ([autotune] enabled = true): at the first all-reduce of a size bucket
+// (64 KiB - 256 MiB) that a fused kernel can serve, the one-shot and the two-shot kernel are timed on the call's own
+// input and stream (output to scratch memory, maximum over the ranks), and calls of that bucket, or of the nearest
+// measured one, take the faster. bucketsTimed: how many buckets this process timed; bucketsInTable: how many hold
+// at least one time. COCCL_AUTOTUNE_MEASURE=0 turns the timing off (the cost model and heuristics decide).
+void cocclApiMeasuredSelection(unsigned long long* bucketsTimed, unsigned long long* bucketsInTable);
 
 // Training mode: what the classifier decided for this communicator. `committed` is 0 until a decision exists (all
 // other fields are then zero); `active` turns 1 at the call from which every rank routes by the role. Roles:

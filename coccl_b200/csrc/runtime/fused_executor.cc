@@ -45,25 +45,39 @@ void FusedExecutor::releaseComm(Comm* comm) {
   gStates.erase(it);
 }
 
-ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
+// Kernel operation of a prepared call (-1: none) and, when a fused kernel can serve it, the codec's tile form.
+static int fusedOperation(const PreparedCall& call, Algorithm algorithm, cocclkCodec* kc) {
   const CallInfo& info = call.info;
   Comm* comm = info.comm;
   CompressorPolicy* codec = flatCodec(call);
   int op = -1;
   switch (info.op) {
-    case Operation::ReduceScatter: if (call.algorithm == Algorithm::RsOneShot) op = 0; break;
+    case Operation::ReduceScatter: if (algorithm == Algorithm::RsOneShot) op = 0; break;
     case Operation::AllGather: op = 1; break;
     case Operation::AllToAll: op = 2; break;
     case Operation::AllReduce:
-      if (call.algorithm == Algorithm::ArOneShot) op = 3;
-      if (call.algorithm == Algorithm::ArTwoShot) op = 4;
+      if (algorithm == Algorithm::ArOneShot) op = 3;
+      if (algorithm == Algorithm::ArTwoShot) op = 4;
       break;
     default: break;
   }
-  cocclkCodec kc;
   const bool fusable = op >= 0 && codec != nullptr && comm->nNodes == 1 && comm->nRanks <= COCCLK_MAX_RANKS &&
                        kernelDtype(info.datatype) >= 0 && codec->plugin()->fusedQuery != nullptr &&
-                       codec->plugin()->fusedQuery(codec->config(), (int)info.datatype, &kc) == 1 && cocclkTileCodecSupported(&kc);
+                       codec->plugin()->fusedQuery(codec->config(), (int)info.datatype, kc) == 1 && cocclkTileCodecSupported(kc);
+  return fusable ? op : -1;
+}
+
+bool FusedExecutor::serves(const PreparedCall& call, Algorithm algorithm) {
+  cocclkCodec kc;
+  return fusedOperation(call, algorithm, &kc) >= 0;
+}
+
+ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
+  const CallInfo& info = call.info;
+  Comm* comm = info.comm;
+  cocclkCodec kc;
+  const int op = fusedOperation(call, call.algorithm, &kc);
+  const bool fusable = op >= 0;
   if (!fusable) { ++stagedCalls; return StagedExecutor::execute(rt, call); }
 
   FusedState* stp;

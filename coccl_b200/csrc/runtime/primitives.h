@@ -40,6 +40,9 @@ class FusedExecutor : public StagedExecutor {
  public:
   FusedExecutor(BufferManager* buffers) : StagedExecutor(buffers) {}
   ncclResult_t execute(Runtime* rt, const PreparedCall& call) override;
+  // Whether ONE fused kernel serves this call with this algorithm (one node, at most 8 ranks, a codec with a tile
+  // form for the datatype, a flat algorithm). Depends on the call's description only: equal on every rank.
+  static bool serves(const PreparedCall& call, Algorithm algorithm);
   void releaseComm(Comm* comm);
   // Status word of the communicator's last completed fused kernels (0 = fine; otherwise the {phase, peer, slice}
   // of the first bounded wait that ran out). Reads pinned host memory only.

@@ -8,6 +8,7 @@
 #include "runtime/primitives.h"
 #include "runtime/runtime.h"
 #include "tuning/autotune.h"
+#include "tuning/measured.h"
 
 using namespace coccl;
 using fakes::FakeTransport;
@@ -371,4 +372,93 @@ TEST(hierarchy_cache_and_recipes) {
   EXPECT(spec.stages[0].kind == StageKind::ReduceScatter && spec.stages[1].kind == StageKind::Compress && spec.stages[2].kind == StageKind::AllToAll);
   f.rt.commDestroy(&f.comm);
   EXPECT(f.comm.intra == nullptr && f.comm.inter == nullptr);
+}
+
+// ---------------------------------------------------------------------------- measured selection (tuning/measured.h)
+namespace {
+// One-shot costs a fixed 10 us plus 4 ns per KiB, two-shot 30 us plus 1 ns per KiB: they cross near 6.7 MiB.
+struct FakeTimer : AlgorithmTimer {
+  int asked = 0, timed = 0;
+  bool allow = true, failTwoShot = false;
+  bool measurable(Runtime*, const PreparedCall&) override { ++asked; return allow; }
+  bool time(Runtime*, const PreparedCall& call, Algorithm a, double* seconds) override {
+    ++timed;
+    if (failTwoShot && a == Algorithm::ArTwoShot) return false;
+    const double kib = (double)(call.info.count * cocclTypeSize(call.info.datatype)) / 1024.0;
+    *seconds = a == Algorithm::ArOneShot ? 10e-6 + 4e-9 * kib : 30e-6 + 1e-9 * kib;
+    return true;
+  }
+};
+const char* kAutotuneAr = "[autotune]\nenabled = true\n[normal.all_reduce.default]\ncompressor = \"fake\"\n"
+                          "[normal.reduce_scatter.default]\ncompressor = \"fake\"\n";
+}  // namespace
+
+TEST(measured_selector_times_each_bucket_once_and_picks_the_faster) {
+  Fixture f("normal", kAutotuneAr);
+  MeasuredTable table;
+  FakeTimer timer;
+  MeasuredSelector sel(&f.store, &table, &timer);
+  f.rt.setSelector(&sel);
+  bool taken = false;
+  // 1 MiB: one-shot wins (14 us against 31 us); the second call of the bucket is not timed again
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot && timer.timed == 2 && sel.measuredBuckets() == 1);
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, (1 << 18) + 8), &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot && timer.timed == 2);
+  // 64 MiB: its own bucket, two-shot wins (96 us against 272 us)
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 24), &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArTwoShot && timer.timed == 4 && table.size() == 2);
+  // reduce-scatter on one node has a single flat algorithm: never timed
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::ReduceScatter, 1 << 18), &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::RsOneShot && timer.timed == 4);
+  // inside a group nothing is timed; the nearest measured bucket decides
+  f.rt.groupStart();
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 21), &taken) == ncclSuccess && taken);
+  EXPECT(timer.timed == 4);
+  EXPECT(f.rt.groupEnd(&f.transport, false) == ncclSuccess);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot);   // 8 MiB falls back on the 1 MiB bucket below it
+}
+
+TEST(measured_selector_failures_forced_algorithms_and_disabled_autotune) {
+  {  // a candidate that cannot be timed gets no entry; the other one is chosen; the bucket is not tried again
+    Fixture f("normal", kAutotuneAr);
+    MeasuredTable table;
+    FakeTimer timer;
+    timer.failTwoShot = true;
+    MeasuredSelector sel(&f.store, &table, &timer);
+    f.rt.setSelector(&sel);
+    bool taken = false;
+    EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 24), &taken) == ncclSuccess && taken);
+    EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot && timer.timed == 2);
+    EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 24), &taken) == ncclSuccess && taken);
+    EXPECT(timer.timed == 2);
+  }
+  {  // calls that cannot be timed are asked about once per bucket and fall back on the model / heuristics
+    Fixture f("normal", kAutotuneAr);
+    MeasuredTable table;
+    FakeTimer timer;
+    timer.allow = false;
+    MeasuredSelector sel(&f.store, &table, &timer);
+    f.rt.setSelector(&sel);
+    bool taken = false;
+    EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+    EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+    EXPECT(timer.asked == 1 && timer.timed == 0 && table.empty() && f.exec.algorithms.back() == Algorithm::ArTwoShot);
+  }
+  {  // a forced algorithm and a disabled autotuner bypass both the table and the timer
+    Fixture f("normal", "[autotune]\nenabled = true\nall_reduce_algorithm = \"twoshot\"\n[normal.all_reduce.default]\ncompressor = \"fake\"\n");
+    MeasuredTable table;
+    table.set((int)Operation::AllReduce, (int)ncclFloat32, 8, 20, (int)Algorithm::ArOneShot, 1e-6);
+    FakeTimer timer;
+    MeasuredSelector sel(&f.store, &table, &timer);
+    f.rt.setSelector(&sel);
+    bool taken = false;
+    EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+    EXPECT(f.exec.algorithms.back() == Algorithm::ArTwoShot && timer.asked == 0);
+    Fixture g("normal", "[autotune]\nenabled = false\n[normal.all_reduce.default]\ncompressor = \"fake\"\n");
+    MeasuredSelector sel2(&g.store, &table, &timer);
+    g.rt.setSelector(&sel2);
+    EXPECT(g.rt.enqueueCheck(g.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+    EXPECT(g.exec.algorithms.back() == Algorithm::ArTwoShot && timer.asked == 0);
+  }
 }

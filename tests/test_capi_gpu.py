@@ -267,3 +267,67 @@ def test_staged_codecs_travel_over_peer_memory(tmp_path, transport):
     p = tmp_path / "staged.toml"
     p.write_text(STAGED_CONFIG)
     run_distributed(_staged_worker, 2, "nccl", (str(p), transport), timeout=300)
+
+
+# ---------------------------------------------------------------------------- selection from measured times
+def _measured_worker(rank, world, cfg_path):
+    """[autotune] enabled: the first all-reduce of a size bucket times the one-shot and the two-shot fused kernel in
+    place of guessing; the user's buffers are untouched by the trial runs, the result is the compressed sum, and later
+    calls of the bucket are not timed again."""
+    import torch.distributed as dist
+    os.environ["COCCL_ENABLE"] = "1"
+    os.environ["COCCL_CONFIG_FILE"] = cfg_path
+    from coccl_b200 import _lib
+    dev = torch.device("cuda", rank)
+    vp, sz, i32 = C.c_void_p, C.c_size_t, C.c_int
+    uid = UniqueId()
+    if rank == 0:
+        assert _lib.declare("cocclApiGetUniqueId", i32, [C.POINTER(UniqueId)])(C.byref(uid)) == 0
+    box = [bytes(uid)]
+    dist.broadcast_object_list(box, src=0)
+    uid = UniqueId.from_buffer_copy(box[0])
+    comm = vp()
+    assert _lib.declare("cocclApiCommInitRank", i32, [C.POINTER(vp), i32, UniqueId, i32])(C.byref(comm), world, uid, rank) == 0
+    ar = _lib.declare("cocclApiAllReduce", i32, [vp, vp, sz, i32, i32, vp, vp])
+    measured = _lib.declare("cocclApiMeasuredSelection", None, [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)])
+    stats_fn = _lib.declare("cocclApiGetStats", None, [C.POINTER(Stats)])
+
+    def table():
+        a, b = C.c_ulonglong(), C.c_ulonglong()
+        measured(C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    st = torch.cuda.current_stream().cuda_stream
+    F32, SUM = 7, 0
+    torch.manual_seed(20 + rank)
+    seen = []
+    for n in (1 << 18, 1 << 18, 1 << 22, (1 << 18) + 1024 * world):   # 1 MiB twice, 16 MiB, 1 MiB again (same bucket)
+        x = torch.randn(n, device=dev) * 0.01
+        keep = x.clone()
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x)
+        exact = torch.stack(xs).sum(0)
+        y = torch.full_like(x, float("nan"))
+        assert ar(x.data_ptr(), y.data_ptr(), n, F32, SUM, comm, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, keep), "the trial runs must not write the send buffer"
+        rel = ((y - exact).float().norm() / exact.float().norm()).item()
+        assert 1e-4 < rel < 0.3, (n, rel)
+        seen.append(table())
+    assert seen[0] == (1, 1) and seen[1] == (1, 1) and seen[2] == (2, 2) and seen[3] == (2, 2), seen
+    s = Stats()
+    stats_fn(C.byref(s))
+    # four real calls plus (1 warm-up + 3 timed) x 2 algorithms x 2 buckets, all through the fused kernels
+    assert s.fused == 4 + 16 and s.staged == 0, (s.fused, s.staged)
+    err = i32(-1)
+    assert _lib.declare("cocclApiCommGetAsyncError", i32, [vp, C.POINTER(i32)])(comm, C.byref(err)) == 0 and err.value == 0
+    dist.barrier()
+    assert _lib.declare("cocclApiCommDestroy", i32, [vp])(comm) == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_all_reduce_algorithm_from_measured_times(tmp_path):
+    p = tmp_path / "policy.toml"
+    p.write_text(CONFIG.replace("[autotune]\nenabled = false", "[autotune]\nenabled = true"))
+    assert "enabled = true" in p.read_text()
+    run_distributed(_measured_worker, 2, "nccl", (str(p),), timeout=300)
