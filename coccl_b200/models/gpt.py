@@ -192,11 +192,21 @@ class TransformerLayer(nn.Module):
     def attention(self, qkv, batch, seq):
         cfg, t = self.cfg, self.tp.size
         nh, d = cfg.n_head // t, cfg.head_dim
+        cp = getattr(self, "cp", None)
+        if cp is not None:
+            # context parallelism: trade the sequence split for a head split (q, k and v of a head travel together)
+            assert nh % cp.size == 0, "heads per tensor-parallel rank must divide by the context-parallel size"
+            qkv = cp.seq_to_heads(qkv.view(batch, seq, nh, 3 * d))
+            seq, nh = seq * cp.size, nh // cp.size
         qkv = qkv.view(batch, seq, nh, 3, d)
         # unbind: its backward is ONE stack of dq/dk/dv into the packed gradient (three selects would each
         # materialise a zero-filled copy of the whole tensor and add them up)
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(3))  # [b, heads, s, d] views
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        if cp is not None:
+            o = cp.heads_to_seq(o.transpose(1, 2).contiguous())   # [b, s / cp, all local heads, d]
+            seq, nh = seq // cp.size, nh * cp.size
+            return o.reshape(batch * seq, nh * d)
         return o.transpose(1, 2).reshape(batch * seq, nh * d)
 
     def forward(self, x, delta, batch, seq):
@@ -224,12 +234,15 @@ class GPTStage(nn.Module):
     flat buffer whatever the schedule."""
 
     def __init__(self, cfg: GPTConfig, device, tp=None, first_layer=0, last_layer=None, pre=True, post=True,
-                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None, layer_ranges=None):
+                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None, layer_ranges=None, cp=None):
         """ep_comm: communicator of the expert-parallel group for a mixture-of-experts model (None: every expert is
         local). Expert weights that differ between the ranks of that group live in a second flat buffer pair,
         `expert_store`, which data parallelism must not reduce or gather."""
         super().__init__()
         self.cfg, self.tp = cfg, tp or NoTP()
+        # context parallelism (parallel.tp.CPContext or None): this rank sees positions [cp.rank * s, (cp.rank + 1) * s)
+        # of every sequence, s = seq_len / cp.size
+        self.cp = cp if (cp is not None and cp.size > 1) else None
         last_layer = cfg.n_layer if last_layer is None else last_layer
         self.pre, self.post = pre, post
         tp_ = self.tp
@@ -260,6 +273,10 @@ class GPTStage(nn.Module):
         chunks = [[make(cfg, i, store, tp_) for i in range(a, b)] for a, b in ranges]
         self.layers = nn.ModuleList([layer for chunk in chunks for layer in chunk])
         self.chunks = chunks   # plain lists: the modules are registered through self.layers
+        if self.cp is not None:
+            for layer in self.layers:
+                assert not cfg.is_moe_layer(layer.idx), "context parallelism is built for dense layers"
+                layer.cp = self.cp
         if post:
             store.add("lnf.weight", (cfg.hidden,), "ones", replicated=True)
             store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
@@ -285,7 +302,8 @@ class GPTStage(nn.Module):
             mask = (local < 0) | (local >= self.wte.shape[0])
             e = F.embedding(local.masked_fill(mask, 0), self.wte)
             e = e.masked_fill(mask[:, None], 0)
-        pos = self.wpe[:s].unsqueeze(0).expand(b, s, cfg.hidden).reshape(b * s, cfg.hidden)
+        first = self.cp.rank * s if self.cp is not None else 0   # s is this rank's part of the sequence
+        pos = self.wpe[first:first + s].unsqueeze(0).expand(b, s, cfg.hidden).reshape(b * s, cfg.hidden)
         if tp.size > 1:
             e = e + pos / tp.size  # the position term is summed over ranks below
             e = tp.scatter_sum_tokens(e) if tp.sequence_parallel else tp.all_reduce_sum(e)

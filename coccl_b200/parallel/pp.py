@@ -20,7 +20,9 @@ class PipelineSchedule:
         self.pp_rank, self.pp_size = mesh.pp_rank, mesh.pp
         self.prev = mesh.pp_prev_global if self.pp_rank > 0 else None
         self.next = mesh.pp_next_global if self.pp_rank < self.pp_size - 1 else None
-        tokens = micro_batch * cfg.seq_len
+        # with context parallelism a rank holds seq_len / cp positions of every sequence
+        self.seq = cfg.seq_len // (stage.cp.size if getattr(stage, "cp", None) is not None else 1)
+        tokens = micro_batch * self.seq
         tp = stage.tp
         self.act_shape = (tokens // tp.size if tp.sequence_parallel else tokens, cfg.hidden)
         self.dtype = cfg.dtype
@@ -47,7 +49,7 @@ class PipelineSchedule:
     def _forward(self, tokens, i, inp, scale, loss_acc, chunk=None):
         """Returns the stage output to send on (None where the model ends) and what backward needs."""
         mb = tokens[i * self.mb:(i + 1) * self.mb]
-        b, s = self.mb, self.cfg.seq_len
+        b, s = self.mb, self.seq
         first, last = self.stage.chunk_is_first(chunk), self.stage.chunk_is_last(chunk)
         tgt = mb[:, 1:] if last else None
         if first:

@@ -267,3 +267,64 @@ class TPContext:
         if self.size == 1:
             return fused.cross_entropy(logits, targets, scale)
         return _VocabParallelCE.apply(logits, targets, scale, self.comm)
+
+
+# ---------------------------------------------------------------------------- context parallelism (head exchange)
+class _SeqToHeads(torch.autograd.Function):
+    """[b, s / cp, heads, w] on every context-parallel rank -> [b, s, heads / cp, w]: rank j receives head group j of
+    every rank's part of the sequence (one all-to-all); the backward is the opposite exchange."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return _seq_to_heads(x, comm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _heads_to_seq(g.contiguous(), ctx.comm), None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return _heads_to_seq(x, comm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_heads(g.contiguous(), ctx.comm), None
+
+
+def _seq_to_heads(x, comm):
+    cp = comm.size
+    b, sl, nh, w = x.shape
+    send = x.view(b, sl, cp, nh // cp, w).permute(2, 0, 1, 3, 4).contiguous()      # [destination, b, s / cp, heads / cp, w]
+    recv = torch.empty_like(send)
+    comm.all_to_all(send.view(-1), recv.view(-1))
+    return recv.permute(1, 0, 2, 3, 4).reshape(b, cp * sl, nh // cp, w)              # source rank j holds sequence part j
+
+
+def _heads_to_seq(x, comm):
+    cp = comm.size
+    b, s, nhl, w = x.shape
+    send = x.view(b, cp, s // cp, nhl, w).permute(1, 0, 2, 3, 4).contiguous()      # [destination, b, s / cp, heads / cp, w]
+    recv = torch.empty_like(send)
+    comm.all_to_all(send.view(-1), recv.view(-1))
+    return recv.permute(1, 2, 0, 3, 4).reshape(b, s // cp, cp * nhl, w)              # source rank j holds head group j
+
+
+class CPContext:
+    """Context parallelism by head exchange (the scheme known as Ulysses): every rank of the group holds 1 / cp of each
+    sequence for everything that works token by token; around the attention one all-to-all trades the sequence split
+    for a head split, so that every rank attends over the WHOLE sequence for heads / cp heads, and a second one trades
+    it back. The reference has no attention code; its launcher only forwards a context-parallel size to the external
+    trainer (examples/training_scripts/train_qwen_coccl.sh:21-29)."""
+
+    def __init__(self, comm):
+        self.comm, self.size, self.rank = comm, comm.size, comm.rank
+
+    def seq_to_heads(self, x):
+        return _SeqToHeads.apply(x, self.comm)
+
+    def heads_to_seq(self, x):
+        return _HeadsToSeq.apply(x, self.comm)

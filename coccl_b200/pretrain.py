@@ -41,10 +41,11 @@ def parse(argv=None):
                       ("experts", int), ("moe-top-k", int), ("moe-every", int)):
         m.add_argument(f"--{name}", type=typ, default=None, help="overrides the preset")
     m.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"], help="fp32 is for CPU runs")
-    p = ap.add_argument_group("parallelism (tp * pp * dp = world size)")
+    p = ap.add_argument_group("parallelism (tp * cp * pp * dp = world size)")
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--pp", type=int, default=1)
-    p.add_argument("--dp", type=int, default=0, help="0: world size / (tp * pp)")
+    p.add_argument("--cp", type=int, default=1, help="context parallelism: ranks sharing every sequence (head exchange around attention)")
+    p.add_argument("--dp", type=int, default=0, help="0: world size / (tp * pp * cp)")
     p.add_argument("--ep", type=int, default=1, help="expert parallelism: 1 or the data-parallel size")
     p.add_argument("--virtual-stages", type=int, default=1, help="model chunks per pipeline rank (interleaved 1F1B)")
     p.add_argument("--no-sequence-parallel", action="store_true")
@@ -108,9 +109,9 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(dev)
-    dp = args.dp or world // (args.tp * args.pp)
-    if args.tp * args.pp * dp != world:
-        raise SystemExit(f"tp * pp * dp = {args.tp} * {args.pp} * {dp} does not equal the world size {world}")
+    dp = args.dp or world // (args.tp * args.pp * args.cp)
+    if args.tp * args.pp * args.cp * dp != world:
+        raise SystemExit(f"tp * cp * pp * dp = {args.tp} * {args.cp} * {args.pp} * {dp} does not equal the world size {world}")
     if not use_cuda and args.dtype == "bf16":
         args.dtype = "fp32"
     cfg = model_config(args)
@@ -134,9 +135,9 @@ def main(argv=None) -> int:
             dist.init_process_group("gloo")
         from .parallel.mesh import Mesh
         mesh = Mesh(tp=args.tp, pp=args.pp, dp=dp, device=dev, compress=enabled, policy=policy,
-                    sequence_parallel=not args.no_sequence_parallel, ep=args.ep)
+                    sequence_parallel=not args.no_sequence_parallel, ep=args.ep, cp=args.cp)
     par = ParallelConfig(tp=args.tp, pp=args.pp, dp=dp, sequence_parallel=not args.no_sequence_parallel,
-                         dp_strategy=args.dp_strategy, ep=args.ep, virtual_stages=args.virtual_stages if args.pp > 1 else 1)
+                         dp_strategy=args.dp_strategy, ep=args.ep, cp=args.cp, virtual_stages=args.virtual_stages if args.pp > 1 else 1)
     trainer = Trainer(cfg, dev, micro_batch=args.micro_batch, parallel=par, groups=mesh, lr=args.lr,
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad, seed=args.seed)
 
@@ -163,7 +164,7 @@ def main(argv=None) -> int:
     tokens_per_step = global_batch * cfg.seq_len
     loss_group_size = args.tp * dp   # ranks of the last pipeline stage that hold a loss
     if rank == 0:
-        print(json.dumps({"model": args.model, "params": cfg.num_params(), "world": world, "tp": args.tp, "pp": args.pp, "dp": dp,
+        print(json.dumps({"model": args.model, "params": cfg.num_params(), "world": world, "tp": args.tp, "cp": args.cp, "pp": args.pp, "dp": dp,
                           "ep": args.ep, "virtual_stages": par.virtual_stages, "global_batch": global_batch,
                           "seq_len": cfg.seq_len, "compressed_collectives": enabled and world > 1,
                           "policy": policy_file or ("shipped training policy" if enabled else "native"),

@@ -25,6 +25,7 @@ class ParallelConfig:
     dp_strategy: str = "zero1"   # "zero1": sharded optimizer (reduce-scatter + all-gather); "ddp": gradient all-reduce
     ep: int = 1   # expert parallelism of a mixture-of-experts model: 1 (every rank holds all experts) or dp
     virtual_stages: int = 1   # model chunks per pipeline rank; > 1 selects the interleaved 1F1B schedule
+    cp: int = 1   # context parallelism: ranks that share every sequence, each holding seq_len / cp positions of it
 
 
 class Trainer:
@@ -43,11 +44,16 @@ class Trainer:
         # virtual stage c * pp + pp_rank is this rank's chunk c (one chunk: the plain contiguous split)
         ranges = [((c * pp + pp_rank) * per, (c * pp + pp_rank + 1) * per) for c in range(chunks)]
         dp = self.parallel.dp
+        cp = self.parallel.cp
+        assert cp == (g.cp if g is not None else 1), "ParallelConfig.cp and the mesh disagree"
+        assert cfg.seq_len % cp == 0, "the sequence length must divide by the context-parallel size"
+        self.cp_ctx = g.cp_context() if (g is not None and cp > 1) else None
+        replicas = dp * cp   # ranks that hold the same parameters: the gradient / optimizer-shard group
         ep_comm = getattr(g, "ep_comm", None) if g is not None else None
         assert self.parallel.ep == (ep_comm.size if ep_comm is not None else 1), "ParallelConfig.ep and the mesh disagree"
         self.stage = GPTStage(cfg, device, tp=tp_ctx, layer_ranges=ranges,
-                              pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * dp * 2048,
-                              ep_comm=ep_comm)
+                              pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * replicas * 2048,
+                              ep_comm=ep_comm, cp=self.cp_ctx)
         # experts spread over the expert-parallel group: updated locally (never reduced or gathered), clipped with
         # the same coefficient as everything else; their squares enter the global norm through the main optimizer
         self.expert_opt = None
@@ -62,7 +68,7 @@ class Trainer:
             if g.pp_comm is not None and g.pp_comm.size > 1:
                 norm_groups.append(g.pp_comm)
         self.opt = DistributedOptimizer(self.stage.store.flat_param, self.stage.store.flat_grad,
-                                        g.dp_comm if (g is not None and dp > 1) else None, lr=lr,
+                                        g.dp_comm if (g is not None and replicas > 1) else None, lr=lr,
                                         weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups,
                                         norm_exclude=self.stage.store.norm_exclude_ranges(
                                             g.tp_rank if g is not None else 0,
@@ -78,7 +84,9 @@ class Trainer:
         self._dev_tokens = None
 
     def train_step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """tokens: [n_seq, seq_len+1] int64 (pinned host or device). Returns the mean token loss (device scalar)."""
+        """tokens: [n_seq, seq_len+1] int64 (pinned host or device). Returns the mean token loss (device scalar); with
+        context parallelism every rank of the group passes the same sequences and the returned values of the group
+        add up to the mean."""
         cfg = self.cfg
         n_seq = tokens.shape[0]
         assert n_seq % self.micro_batch == 0
@@ -88,6 +96,11 @@ class Trainer:
                 self._dev_tokens = torch.empty(tokens.shape, dtype=tokens.dtype, device=self.device)
             self._dev_tokens.copy_(tokens, non_blocking=True)
             tokens = self._dev_tokens
+        if self.cp_ctx is not None:
+            # this rank's part of every sequence: positions [lo, lo + s) as inputs, [lo + 1, lo + s + 1) as targets
+            s_local = cfg.seq_len // self.parallel.cp
+            lo = self.cp_ctx.rank * s_local
+            tokens = tokens[:, lo:lo + s_local + 1]
         # health: the status words copied at the end of the previous step (no synchronisation); a wait that gave
         # up inside a fused kernel means that step's gradients or parameters are not valid
         self.check_health(wait=False)
@@ -116,7 +129,8 @@ class Trainer:
 
     def _comms(self):
         g = self.groups
-        return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm, getattr(g, "ep_comm", None)) if g is not None else ())
+        return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm, getattr(g, "ep_comm", None), getattr(g, "cp_comm", None))
+                            if g is not None else ())
                 if c is not None]
 
     def check_health(self, wait: bool = True) -> None:

@@ -64,7 +64,7 @@ def save(trainer, directory: str, step: int, rank: int = 0, world: int = 1):
         p = trainer.parallel
         with open(os.path.join(directory, "manifest.json"), "w") as f:
             json.dump({"step": step, "world": world, "tp": p.tp, "pp": p.pp, "dp": p.dp, "ep": getattr(p, "ep", 1),
-                       "virtual_stages": getattr(p, "virtual_stages", 1),
+                       "virtual_stages": getattr(p, "virtual_stages", 1), "cp": getattr(p, "cp", 1),
                        "model": {k: (str(v) if not isinstance(v, (int, float, bool)) else v)
                                  for k, v in vars(trainer.cfg).items()}}, f)
 
@@ -75,6 +75,9 @@ def load(trainer, directory: str, rank: int = 0) -> int:
     p = trainer.parallel
     if (man["tp"], man["pp"], man["dp"], man.get("ep", 1)) != (p.tp, p.pp, p.dp, getattr(p, "ep", 1)):
         raise ValueError(f"checkpoint was written with tp/pp/dp/ep={man['tp']}/{man['pp']}/{man['dp']}/{man.get('ep', 1)}")
+    if man.get("cp", 1) != getattr(p, "cp", 1):
+        # the optimizer shards are cut over data x context ranks
+        raise ValueError(f"checkpoint was written with context-parallel size {man.get('cp', 1)}")
     if man.get("virtual_stages", 1) != getattr(p, "virtual_stages", 1):
         # the layers a pipeline rank holds depend on the number of model chunks per rank
         raise ValueError(f"checkpoint was written with {man.get('virtual_stages', 1)} model chunk(s) per pipeline rank")

@@ -29,14 +29,14 @@ def _reference_losses(steps=3, n_seq=8):
     return tr, list(zip(losses, norms))
 
 
-def _worker(rank, world, tp, pp, dp, ref_losses, ref_params, virtual_stages=1):
+def _worker(rank, world, tp, pp, dp, ref_losses, ref_params, virtual_stages=1, cp=1):
     import torch.distributed as dist
     from coccl_b200.parallel.mesh import Mesh
     from coccl_b200.train import ParallelConfig, Trainer
     from coccl_b200.utils.checkpoint import shard_param
     cfg = _cfg()
-    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=torch.device("cpu"))
-    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages),
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, cp=cp, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages, cp=cp),
                  groups=mesh, lr=1e-2)
     # load the single-process model's initial weights, re-sharded for this rank
     for name, p in tr.stage.store.params.items():
@@ -73,6 +73,15 @@ def test_interleaved_pipeline_matches_single_process(tp, pp, dp, chunks):
     tr2, _ = _reference_losses(steps=0)
     params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
     run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params, chunks))
+
+
+@pytest.mark.parametrize("tp,pp,dp,cp", [(1, 1, 1, 2), (2, 1, 1, 2), (1, 2, 1, 2), (1, 1, 2, 2), (1, 1, 1, 4)])
+def test_context_parallel_layouts_match_single_process(tp, pp, dp, cp):
+    """Every sequence split over cp ranks, whole-sequence attention by head exchange: same losses and gradient norms."""
+    tr, losses = _reference_losses()
+    tr2, _ = _reference_losses(steps=0)
+    params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
+    run_distributed(_worker, tp * pp * dp * cp, "gloo", (tp, pp, dp, losses, params, 1, cp))
 
 
 def test_interleaved_plan_is_complete_and_ordered():

@@ -45,7 +45,7 @@ def _single_gpu():
     return params, losses
 
 
-def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses, virtual_stages=1):
+def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses, virtual_stages=1, cp=1):
     import torch.distributed as dist
     from coccl_b200.parallel.comm import Policy
     from coccl_b200.parallel.mesh import Mesh
@@ -53,8 +53,8 @@ def _worker(rank, world, tp, pp, dp, compress, ref_params, ref_losses, virtual_s
     from coccl_b200.utils.checkpoint import shard_param
     dev = torch.device("cuda", rank)
     cfg = _cfg()
-    mesh = Mesh(tp=tp, pp=pp, dp=dp, device=dev, compress=compress, policy=Policy.training(threshold_bytes=0, dp_delta=False))
-    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages), groups=mesh,
+    mesh = Mesh(tp=tp, pp=pp, dp=dp, cp=cp, device=dev, compress=compress, policy=Policy.training(threshold_bytes=0, dp_delta=False))
+    tr = Trainer(cfg, dev, micro_batch=2, parallel=ParallelConfig(tp, pp, dp, virtual_stages=virtual_stages, cp=cp), groups=mesh,
                  lr=3e-4)
     for name, p in tr.stage.store.params.items():
         p.data.copy_(shard_param(name, ref_params[name], mesh.tp_rank, tp).to(dev))
@@ -97,6 +97,14 @@ def test_interleaved_pipeline_follows_the_single_gpu_curve(reference):
     """pp = 2 with two model chunks per rank (four virtual stages of one layer): NCCL batches of the tick plan."""
     params, losses = reference
     run_distributed(_worker, 2, "nccl", (1, 2, 1, False, params, losses, 2), timeout=420)
+
+
+@pytest.mark.parametrize("compress", [False, True], ids=["native", "compressed"])
+def test_context_parallel_follows_the_single_gpu_curve(reference, compress):
+    """cp = 2: each GPU holds half of every sequence, attention sees the whole sequence through the head exchange; the
+    gradients of the two halves meet in the (compressed) reduce-scatter of the data x context group."""
+    params, losses = reference
+    run_distributed(_worker, 2, "nccl", (1, 1, 1, compress, params, losses, 1, 2), timeout=420)
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
