@@ -28,6 +28,20 @@ class ParallelConfig:
     cp: int = 1   # context parallelism: ranks that share every sequence, each holding seq_len / cp positions of it
 
 
+def split_layers(n_layer: int, stages: int) -> list[tuple[int, int]]:
+    """Layer range [first, last) of each of `stages` consecutive (virtual) pipeline stages. Layers that do not divide
+    evenly go to the FIRST stages: the last one also runs the final LayerNorm, the output head and the loss, which cost
+    about one transformer layer (2 * hidden * vocab against 24 * hidden^2 FLOPs per token for GPT-6.7B)."""
+    assert 1 <= stages <= n_layer, f"{n_layer} layers cannot fill {stages} pipeline stages"
+    base, extra = divmod(n_layer, stages)
+    out, first = [], 0
+    for s in range(stages):
+        n = base + (1 if s < extra else 0)
+        out.append((first, first + n))
+        first += n
+    return out
+
+
 class Trainer:
     def __init__(self, cfg: GPTConfig, device, *, micro_batch=2, parallel: ParallelConfig | None = None, groups=None,
                  lr=1e-4, weight_decay=0.1, clip_grad=1.0, seed=1234):
@@ -39,10 +53,10 @@ class Trainer:
         pp_rank = g.pp_rank if g is not None else 0
         pp = self.parallel.pp
         chunks = self.parallel.virtual_stages if pp > 1 else 1
-        per = cfg.n_layer // (pp * chunks)
-        assert chunks >= 1 and cfg.n_layer % (pp * chunks) == 0, "layers must divide evenly over the (virtual) pipeline stages"
+        assert chunks >= 1
         # virtual stage c * pp + pp_rank is this rank's chunk c (one chunk: the plain contiguous split)
-        ranges = [((c * pp + pp_rank) * per, (c * pp + pp_rank + 1) * per) for c in range(chunks)]
+        stages = split_layers(cfg.n_layer, pp * chunks)
+        ranges = [stages[c * pp + pp_rank] for c in range(chunks)]
         dp = self.parallel.dp
         cp = self.parallel.cp
         assert cp == (g.cp if g is not None else 1), "ParallelConfig.cp and the mesh disagree"

@@ -84,6 +84,45 @@ def test_context_parallel_layouts_match_single_process(tp, pp, dp, cp):
     run_distributed(_worker, tp * pp * dp * cp, "gloo", (tp, pp, dp, losses, params, 1, cp))
 
 
+def _uneven_worker(rank, world, ref_losses, ref_params):
+    import dataclasses as dc
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = dc.replace(_cfg(), n_layer=3)
+    mesh = Mesh(tp=1, pp=2, dp=1, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, 2, 1), groups=mesh, lr=1e-2)
+    assert len(tr.stage.layers) == (2 if rank == 0 else 1)   # the stage with the head gets the smaller share
+    for name, p in tr.stage.store.params.items():
+        p.data.copy_(ref_params[name])
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tok = _data(cfg, 8)
+    for step, (ref, ref_norm) in enumerate(ref_losses):
+        t = tr.train_step(tok).clone()
+        dist.all_reduce(t)
+        assert abs(t.item() - ref) < 2e-3 * abs(ref) + 1e-4, (step, t.item(), ref)
+        assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6
+
+
+def test_layers_that_do_not_divide_over_the_stages():
+    import dataclasses as dc
+    from coccl_b200.train import Trainer, split_layers
+    assert split_layers(32, 2) == [(0, 16), (16, 32)]
+    assert split_layers(6, 4) == [(0, 2), (2, 4), (4, 5), (5, 6)]
+    assert split_layers(7, 3) == [(0, 3), (3, 5), (5, 7)]
+    with pytest.raises(AssertionError):
+        split_layers(2, 3)
+    cfg = dc.replace(_cfg(), n_layer=3)
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2)
+    params = {k: v.detach().clone() for k, v in tr.stage.store.params.items()}
+    tok = _data(cfg, 8)
+    ref = []
+    for _ in range(3):
+        loss = tr.train_step(tok).item()
+        ref.append((loss, tr.opt.grad_norm.item()))
+    run_distributed(_uneven_worker, 2, "gloo", (ref, params))
+
+
 def test_interleaved_plan_is_complete_and_ordered():
     from coccl_b200.parallel.pp import interleaved_order, plan_ticks
     for pp, chunks, n_micro in [(2, 2, 4), (2, 2, 16), (4, 2, 8), (4, 3, 12), (8, 2, 16), (2, 4, 2)]:
