@@ -111,3 +111,22 @@ def test_two_rank_launch_matches_one_process(tmp_path, capsys):
     assert sorted(two) == [1, 2, 3]
     for s in two:
         assert two[s] == pytest.approx(one[s], rel=2e-3), (two, one)
+
+
+def test_example_launchers_parse_and_name_existing_modules():
+    """The shell launchers under examples/ are syntactically valid and call modules and files that exist."""
+    import importlib.util
+    import re
+    ex = os.path.join(REPO, "examples")
+    scripts = sorted(f for f in os.listdir(ex) if f.endswith(".sh"))
+    assert scripts == ["build.sh", "communication_benchmarks.sh", "preload.sh", "train_gpt.sh"]
+    for name in scripts:
+        path = os.path.join(ex, name)
+        assert os.access(path, os.X_OK), name
+        out = subprocess.run(["bash", "-n", path], capture_output=True, text=True)
+        assert out.returncode == 0, out.stderr
+        text = open(path).read()
+        for mod in re.findall(r"-m (coccl_b200[\w.]*)", text):
+            assert importlib.util.find_spec(mod) is not None, (name, mod)
+        for rel in re.findall(r"\$root/(coccl_b200/configs/[\w.-]+\.toml)", text):
+            assert os.path.exists(os.path.join(REPO, rel)), (name, rel)
