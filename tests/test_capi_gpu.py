@@ -126,7 +126,7 @@ def _worker(rank, world, cfg_path):
     ref = torch.cat([K.reference_roundtrip(t, K.MXFP8, world).reshape(world, -1)[rank] for t in xs])
     assert torch.allclose(o2, ref, atol=1e-6, rtol=1e-2)
     fused_before = stats().fused
-    # all-gather with the stateful delta codec: staged pipeline; round 1 raw (exact), round 2 deltas
+    # all-gather with the stateful delta codec: staged pipeline; the first call is raw (exact), the second sends deltas
     full = torch.empty(n * world, device=dev)
     for rnd in range(2):
         assert ag(x.data_ptr(), full.data_ptr(), n, F32, comm, st) == 0

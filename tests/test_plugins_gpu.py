@@ -54,7 +54,7 @@ def test_sdp4bit_plugin_fused_reduce_and_rejections(cuda):
 
 
 def test_sdp4bit_subadd_seeds_then_sends_deltas(cuda):
-    """Stateful delta codec: round 1 passes raw data through (exact) and seeds the state; later rounds encode
+    """Stateful delta codec: the first call passes raw data through (exact) and seeds the state; later calls encode
     x - prev at 8 bits, so a value that did not change is reproduced exactly and the error shrinks."""
     torch.manual_seed(2)
     x = torch.randn(1 << 16, device=cuda, dtype=torch.bfloat16)
