@@ -149,7 +149,7 @@ class MoELayer:
                     h = fused.linear(x[tok].contiguous(), self.w_up[e], self.b_up[e], gelu=True)
                     y = fused.linear(h, self.w_down[e])
                     out = out.index_add(0, tok, gates[tok, j:j + 1] * y.float())
-        return out.to(torch.bfloat16)
+        return out.to(x.dtype)
 
 
 from .gpt import TransformerLayer  # noqa: E402  (gpt.py imports this module lazily, inside the layer factory)

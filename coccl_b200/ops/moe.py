@@ -21,11 +21,27 @@ def route_layout(expert_ids: torch.Tensor, n_experts: int, n_ranks: int):
     token order inside an expert)."""
     ids = expert_ids.contiguous()
     assert ids.dtype == torch.int32 and n_experts % n_ranks == 0
+    if not ids.is_cuda:
+        return _route_layout_host(ids, n_experts, n_ranks)
     pos = torch.empty_like(ids)
     counts = torch.empty(n_experts, dtype=torch.int32, device=ids.device)
     _lib.check(_lib.lib().cocclkMoeLayout(ids.data_ptr(), ids.numel(), n_experts, n_experts // n_ranks, pos.data_ptr(),
                                           counts.data_ptr(), _lib.cur_stream()), "cocclkMoeLayout")
     return pos, counts
+
+
+def _route_layout_host(ids: torch.Tensor, n_experts: int, n_ranks: int):
+    """PyTorch restatement of the layout kernel for CPU tensors (the gloo tests)."""
+    flat = ids.reshape(-1).long()
+    counts = torch.bincount(flat, minlength=n_experts)
+    order = torch.sort(flat, stable=True).indices            # by expert, then (token, choice)
+    start = torch.cumsum(counts, 0) - counts
+    within = torch.empty_like(flat)
+    within[order] = torch.arange(flat.numel()) - start[flat[order]]
+    per_rank = counts.view(n_ranks, n_experts // n_ranks)
+    block_off = (torch.cumsum(per_rank, 1) - per_rank).reshape(-1)   # where an expert's queue starts inside its rank's block
+    pos = (block_off[flat] + within).to(torch.int32).view_as(ids)
+    return pos, counts.to(torch.int32)
 
 
 def ws_bytes(n_ranks: int, capacity: int, hidden: int, local_experts: int) -> int:

@@ -969,6 +969,8 @@ class Communicator:
         capacity = capacity or tokens * topk
         le = n_experts // self.size
         pos, counts = layout if layout is not None else M.route_layout(expert_ids, n_experts, self.size)
+        if not x.is_cuda:
+            return self._moe_dispatch_host(x, expert_ids, n_experts, capacity, row_scale, pos, counts)
         recv = torch.empty(self.size * capacity, hidden, dtype=torch.bfloat16, device=x.device)
         roff = torch.zeros(le + 1, dtype=torch.int32, device=x.device)
         rcnt = torch.zeros(self.size, le, dtype=torch.int32, device=x.device)
@@ -993,6 +995,8 @@ class Communicator:
         dots[t, j] = <y_j, dot_with[t]> (the gate gradients when dot_with is the output gradient)."""
         tokens, topk = gates.shape
         hidden = y.shape[1]
+        if not y.is_cuda:
+            return self._moe_combine_host(y, gates, handle, dot_with)
         out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=y.device)
         a = self._moe_args(tokens, hidden, topk, handle.n_experts, handle.capacity)
         r = self.rank
@@ -1005,6 +1009,53 @@ class Communicator:
             a.dotWith[r], a.dotOut[r] = dot_with.data_ptr(), dots.data_ptr()
         _lib.check(_lib.lib().cocclkMoeCombine(a, 1, self.max_ctas, _lib.cur_stream()), "cocclkMoeCombine")
         return out if dot_with is None else (out, dots)
+
+    # CPU tensors (the gloo tests, a launcher run without GPUs): the same exchange as plain PyTorch over
+    # all_to_all_single, rows in the tensor's own datatype (no FP8 on the way), same row order and handle contents.
+    def _moe_dispatch_host(self, x, expert_ids, n_experts, capacity, row_scale, pos, counts):
+        from ..ops import moe as M
+        n, le = self.size, n_experts // self.size
+        tokens, topk = expert_ids.shape
+        flat = expert_ids.reshape(-1).long()
+        per_rank = counts.long().view(n, le)
+        send_rows = per_rank.sum(1)
+        slot = (torch.cumsum(send_rows, 0) - send_rows)[flat // le] + pos.reshape(-1).long()   # row of entry (t, j) in the send buffer
+        rows = x.repeat_interleave(topk, dim=0)
+        if row_scale is not None:
+            rows = (rows.float() * row_scale.reshape(-1, 1)).to(x.dtype)
+        send = torch.empty_like(rows)
+        send[slot] = rows
+        got = torch.empty_like(per_rank)                       # got[s, e]: rows source s sends to my local expert e
+        dist.all_to_all_single(got, per_rank.contiguous(), group=self.group)
+        recv_rows = got.sum(1)
+        recv = x.new_empty(int(recv_rows.sum()), x.shape[1])
+        dist.all_to_all_single(recv, send, output_split_sizes=recv_rows.tolist(), input_split_sizes=send_rows.tolist(),
+                               group=self.group)
+        # arrival order is source-major; the experts want their rows together: local expert, then source
+        src_off = torch.cumsum(recv_rows, 0) - recv_rows
+        in_src = torch.cumsum(got, 1) - got
+        perm = torch.cat([torch.arange(int(got[s_, e]), dtype=torch.long) + int(src_off[s_] + in_src[s_, e])
+                          for e in range(le) for s_ in range(n)]) if recv.shape[0] else torch.zeros(0, dtype=torch.long)
+        roff = torch.zeros(le + 1, dtype=torch.int32)
+        roff[1:] = torch.cumsum(got.sum(0), 0).to(torch.int32)
+        h = M.Handle(expert_ids, pos, got.to(torch.int32), roff, capacity, n_experts)
+        h.counts = counts
+        h.host = (perm, send_rows.tolist(), recv_rows.tolist(), slot)
+        self._native(rows.numel() * rows.element_size())
+        return recv[perm], h
+
+    def _moe_combine_host(self, y, gates, handle, dot_with):
+        perm, send_rows, recv_rows, slot = handle.host
+        tokens, topk = gates.shape
+        back = y.new_empty(len(perm), y.shape[1])
+        back[perm] = y[:len(perm)]
+        ret = y.new_empty(tokens * topk, y.shape[1])
+        dist.all_to_all_single(ret, back, output_split_sizes=send_rows, input_split_sizes=recv_rows, group=self.group)
+        rows = ret[slot].view(tokens, topk, -1).float()
+        out = (gates.float().unsqueeze(-1) * rows).sum(1).to(y.dtype)
+        if dot_with is None:
+            return out
+        return out, (rows * dot_with.float().unsqueeze(1)).sum(-1)
 
     def moe_status(self) -> int:
         return 0 if self._moe is None else self._moe.status()

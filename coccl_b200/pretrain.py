@@ -159,6 +159,7 @@ def main(argv=None) -> int:
     heartbeat = None
     if world > 1 and args.heartbeat_stale_s > 0 and default_store() is not None:
         heartbeat = Heartbeat(default_store(), rank, world, stale_after_s=args.heartbeat_stale_s)
+        heartbeat.beat(start - 1)   # a resumed run has the steps before `start` behind it
 
     decay = args.decay_steps or args.steps
     tokens_per_step = global_batch * cfg.seq_len

@@ -113,6 +113,35 @@ def test_two_rank_launch_matches_one_process(tmp_path, capsys):
         assert two[s] == pytest.approx(one[s], rel=2e-3), (two, one)
 
 
+def _launch(argv, tmp_path, nproc=2):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""), OMP_NUM_THREADS="2")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "coccl_b200.pretrain"] + argv,
+                         env=env, cwd=REPO, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    return out.stdout
+
+
+def test_expert_parallel_launch_saves_and_resumes(tmp_path):
+    """Mixture-of-experts model, experts over the two data-parallel ranks: the checkpoint carries the expert buffers of
+    each rank, and the resumed run (whose peers start with the earlier steps behind them) reproduces the full run."""
+    data = _token_file(tmp_path)
+    common = ["--model", "moe-tiny", "--hidden", "64", "--heads", "4", "--ffn", "128", "--seq-len", "32", "--vocab", "128",
+              "--device", "cpu", "--ep", "2", "--data", data, "--global-batch", "8", "--log-interval", "1", "--lr", "1e-2",
+              "--warmup-steps", "2", "--decay-steps", "6", "--heartbeat-stale-s", "20"]
+    full = {r["step"]: r["loss"] for r in _records(_launch(common + ["--steps", "6"], tmp_path)) if "step" in r}
+    ck = str(tmp_path / "ck")
+    _launch(common + ["--steps", "3", "--save", ck], tmp_path)
+    assert sorted(os.listdir(ck)) == ["manifest.json", "rank00000.pt", "rank00001.pt"]
+    tail = {r["step"]: r["loss"] for r in _records(_launch(common + ["--steps", "6", "--save", ck, "--resume"], tmp_path)) if "step" in r}
+    assert sorted(tail) == [4, 5, 6]
+    for s in tail:
+        assert tail[s] == pytest.approx(full[s], rel=1e-4), (tail, full)
+
+
 def test_example_launchers_parse_and_name_existing_modules():
     """The shell launchers under examples/ are syntactically valid and call modules and files that exist."""
     import importlib.util
