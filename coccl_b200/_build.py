@@ -4,6 +4,7 @@ Produces, next to the sources (nothing goes to a JIT cache):
   coccl_b200/lib/libcoccl.so          host runtime (C++17) + sm_100a kernels, C ABI
   coccl_b200/lib/plugins/lib<name>.so  compressor plugins (one shared library per codec)
   coccl_b200/lib/coccl-config-check    TOML policy checker CLI
+  coccl_b200/lib/coccl-perf            collective benchmark through the C API (one process, one thread per GPU)
   coccl_b200/lib/coccl_host_tests      host-only unit-test runner for the C++ runtime
   coccl_b200/_pg.so                    torch.distributed backend (built on demand, needs torch headers)
 
@@ -143,7 +144,8 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
         for src in sorted(TOOLS_DIR.glob("*.cc")):
             out = LIB / src.stem.replace("_", "-")
             if _needs(src, out, hdr) or so.stat().st_mtime > out.stat().st_mtime:
-                _link([CXX, *CXX_FLAGS, src, "-o"], out, [*rpath, "-ldl", "-lpthread"], verbose)
+                _link([CXX, *CXX_FLAGS, src, "-o"], out, [*rpath, f"-L{CUDA_HOME}/lib64", "-lcudart", "-ldl", "-lpthread",
+                                                         f"-Wl,-rpath,{CUDA_HOME}/lib64"], verbose)
     if TESTS_DIR.is_dir():
         tsrcs = sorted(TESTS_DIR.glob("*.cc"))
         if tsrcs:

@@ -1,0 +1,62 @@
+"""coccl-perf, the native collective benchmark through the C API: command line on CPU, a short sweep on two GPUs."""
+import os
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+EXE = ROOT / "coccl_b200" / "lib" / "coccl-perf"
+
+
+def _exe():
+    from coccl_b200 import _lib
+    _lib.lib()   # builds the tools if they are missing
+    assert EXE.exists()
+    return str(EXE)
+
+
+def _rows(text):
+    return [[float(x) if x != "-" else None for x in ln.split()] for ln in text.splitlines() if ln.startswith("  ")]
+
+
+def test_command_line_is_checked_before_any_gpu_work():
+    exe = _exe()
+    r = subprocess.run([exe, "-h"], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage: coccl-perf" in r.stderr
+    for bad in (["-o", "scan"], ["-x", "oneshot", "-o", "all_gather"], ["-x", "tripleshot", "-o", "reduce_scatter"],
+                ["-x", "explicit", "-o", "all_reduce"], ["-b", "4M", "-e", "1M"], ["-d", "int8"], ["-f", "1"], ["-n"]):
+        r = subprocess.run([exe] + bad, capture_output=True, text=True)
+        assert r.returncode == 2 and "coccl-perf:" in r.stderr, bad
+
+
+@pytest.mark.gpu
+def test_sweep_on_two_gpus_native_and_compressed(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    exe = _exe()
+    base = [exe, "-g", "2", "-b", "1M", "-e", "4M", "-w", "2", "-n", "5", "-c", "1"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.pop("COCCL_CONFIG_FILE", None)
+    native = subprocess.run(base + ["-o", "all_reduce"], capture_output=True, text=True, timeout=300, env=dict(env, COCCL_ENABLE="0"))
+    assert native.returncode == 0, native.stdout + native.stderr
+    rows = _rows(native.stdout)
+    assert [r[0] for r in rows] == [float(1 << 20), float(2 << 20), float(4 << 20)]
+    assert all(r[2] > 0 and r[5] < 1e-6 for r in rows)                       # exact sums, positive times
+    assert "compressed 0 " in native.stdout
+    # the shipped SDP4Bit policy with a 64 KiB threshold, so that the standard calls of this short sweep are compressed
+    text = (ROOT / "coccl_b200" / "configs" / "normal-sdp4bit.toml").read_text()
+    text = text.replace("compression_threshold_bytes = 8388608", "compression_threshold_bytes = 65536")
+    text = text.replace('library_path = "../lib/plugins"', f'library_path = "{ROOT / "coccl_b200" / "lib" / "plugins"}"')
+    assert "65536" in text
+    policy = tmp_path / "policy.toml"
+    policy.write_text(text)
+    on = dict(env, COCCL_ENABLE="1", COCCL_CONFIG_FILE=str(policy))
+    for args in (["-o", "all_reduce"], ["-o", "all_reduce", "-x", "oneshot"], ["-o", "reduce_scatter", "-d", "bfloat16"],
+                 ["-o", "all_gather", "-x", "explicit"], ["-o", "alltoall"]):
+        r = subprocess.run(base + args, capture_output=True, text=True, timeout=300, env=on)
+        assert r.returncode == 0, (args, r.stdout + r.stderr)
+        rows = _rows(r.stdout)
+        assert len(rows) == 3 and all(0 < row[5] < 0.3 for row in rows), (args, r.stdout)   # 4-bit groups: lossy, bounded
+        assert "compressed 0 " not in r.stdout and "fused kernels 0," not in r.stdout, (args, r.stdout)
