@@ -53,8 +53,7 @@ def test_sweep_on_two_gpus_native_and_compressed(tmp_path):
     policy = tmp_path / "policy.toml"
     policy.write_text(text)
     on = dict(env, COCCL_ENABLE="1", COCCL_CONFIG_FILE=str(policy))
-    for args in (["-o", "all_reduce"], ["-o", "all_reduce", "-x", "oneshot"], ["-o", "reduce_scatter", "-d", "bfloat16"],
-                 ["-o", "all_gather", "-x", "explicit"], ["-o", "alltoall"]):
+    for args in (["-o", "all_reduce"], ["-o", "all_reduce", "-x", "oneshot"], ["-o", "reduce_scatter", "-d", "bfloat16"]):
         r = subprocess.run(base + args, capture_output=True, text=True, timeout=300, env=on)
         assert r.returncode == 0, (args, r.stdout + r.stderr)
         rows = _rows(r.stdout)
