@@ -93,23 +93,31 @@ def sequence_starts(length: int, seq_len: int, seed: int, step: int, global_batc
 
 
 _ORDER_CACHE: dict = {}
+_ORDER_LOCK = threading.Lock()
 
 
-def _epoch_order(windows: int, seed: int, epoch: int) -> np.ndarray:
+def _epoch_order(windows: int, seed: int, epoch: int):
+    """The visiting order of one epoch (an index array, or a stride walk for very long streams). Kept for the last few
+    (stream, seed, epoch) triples; loaders of several ranks in one process share it from their worker threads."""
     key = (windows, seed, epoch)
-    if key not in _ORDER_CACHE:
-        if len(_ORDER_CACHE) > 2:
+    with _ORDER_LOCK:
+        order = _ORDER_CACHE.get(key)
+    if order is not None:
+        return order
+    rng = np.random.default_rng([seed, epoch])
+    if windows > (1 << 26):
+        # a permutation of a very long stream would not fit comfortably: a stride walk that is a bijection instead
+        stride = int(rng.integers(windows // 3, windows)) | 1
+        while np.gcd(stride, windows) != 1:
+            stride += 2
+        order = _StrideOrder(windows, stride, int(rng.integers(0, windows)))
+    else:
+        order = rng.permutation(windows)
+    with _ORDER_LOCK:
+        if len(_ORDER_CACHE) > 3:
             _ORDER_CACHE.clear()
-        if windows > (1 << 26):
-            # a permutation of a very long stream would not fit comfortably: a stride walk that is a bijection instead
-            rng = np.random.default_rng([seed, epoch])
-            stride = int(rng.integers(windows // 3, windows)) | 1
-            while np.gcd(stride, windows) != 1:
-                stride += 2
-            _ORDER_CACHE[key] = _StrideOrder(windows, stride, int(rng.integers(0, windows)))
-        else:
-            _ORDER_CACHE[key] = np.random.default_rng([seed, epoch]).permutation(windows)
-    return _ORDER_CACHE[key]
+        _ORDER_CACHE[key] = order
+    return order
 
 
 class _StrideOrder:
