@@ -419,6 +419,34 @@ TEST(measured_selector_times_each_bucket_once_and_picks_the_faster) {
   EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot);   // 8 MiB falls back on the 1 MiB bucket below it
 }
 
+TEST(measured_selector_times_every_communicator_on_its_own) {
+  // A rank belongs to several communicators of the same size (tensor- and data-parallel groups of two, say). Whether a
+  // call is timed may depend on that communicator's history only: its other ranks have not seen this rank's calls
+  // elsewhere, and would wait in the collective timing for a rank that skipped it.
+  Fixture f("normal", kAutotuneAr);
+  MeasuredTable table;
+  FakeTimer timer;
+  MeasuredSelector sel(&f.store, &table, &timer);
+  f.rt.setSelector(&sel);
+  Comm other = fakes::makeComm(&f.transport, 1, 8, 1);
+  other.id = f.comm.id + 1000;
+  bool taken = false;
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 18), &taken) == ncclSuccess && taken);
+  EXPECT(timer.timed == 2);
+  CallInfo i = f.coll(Operation::AllReduce, 1 << 18);
+  i.comm = &other;
+  EXPECT(f.rt.enqueueCheck(i, &taken) == ncclSuccess && taken);
+  EXPECT(timer.timed == 4 && sel.measuredBuckets() == 2 && table.size() == 2);
+  // entries of one communicator do not decide for the other: a bucket only the first one has measured
+  EXPECT(f.rt.enqueueCheck(f.coll(Operation::AllReduce, 1 << 24), &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArTwoShot && timer.timed == 6);
+  timer.allow = false;
+  i = f.coll(Operation::AllReduce, 1 << 24);
+  i.comm = &other;
+  EXPECT(f.rt.enqueueCheck(i, &taken) == ncclSuccess && taken);
+  EXPECT(f.exec.algorithms.back() == Algorithm::ArOneShot && timer.timed == 6);   // its own 1 MiB entry, the nearest below
+}
+
 TEST(measured_selector_failures_forced_algorithms_and_disabled_autotune) {
   {  // a candidate that cannot be timed gets no entry; the other one is chosen; the bucket is not tried again
     Fixture f("normal", kAutotuneAr);

@@ -8,6 +8,7 @@ namespace coccl {
 
 void MeasuredSelector::measure(Runtime* rt, PreparedCall* call, int log2Bytes) {
   const int op = (int)call->info.op, dt = (int)call->info.datatype, n = call->info.comm->nRanks;
+  const uint64_t scope = call->info.comm->id;
   std::vector<Algorithm> candidates;
   for (const Candidate& c : candidateTable())
     if (c.op == call->info.op && !c.hierarchical && algorithmSupported(*call, c.algorithm) &&
@@ -17,7 +18,7 @@ void MeasuredSelector::measure(Runtime* rt, PreparedCall* call, int log2Bytes) {
   ++measuredBuckets_;
   for (Algorithm a : candidates) {
     double seconds = 0.0;
-    if (timer_->time(rt, *call, a, &seconds) && seconds > 0.0) table_->set(op, dt, n, log2Bytes, (int)a, seconds);
+    if (timer_->time(rt, *call, a, &seconds) && seconds > 0.0) table_->set(op, dt, n, log2Bytes, (int)a, seconds, scope);
   }
 }
 
@@ -31,17 +32,19 @@ ncclResult_t MeasuredSelector::select(Runtime* rt, PreparedCall* call) {
     const int lg = MeasuredTable::bucketOf(bytes);
     // First call of a size bucket: time the candidates (once per bucket, also when nothing could be timed). Never
     // inside a group: the grouped calls run later, together.
+    // with a timer the table is shared by the communicators of the process: entries carry the communicator's id
+    const uint64_t scope = timer_ != nullptr ? call->info.comm->id : 0;
     if (timer_ != nullptr && rt->groupDepth() == 0) {
       bool first;
       {
         std::lock_guard<std::mutex> lock(mutex_);
-        first = attempted_.insert(std::make_pair((const Comm*)call->info.comm, MeasuredTable::Key{op, dt, n, lg})).second;
+        first = attempted_.insert(MeasuredTable::Key{scope, op, dt, n, lg}).second;
       }
       // the lock is not held while timing: the ranks of the communicator, threads of this process among them, meet there
-      if (first && !table_->exact(op, dt, n, lg) && timer_->measurable(rt, *call)) measure(rt, call, lg);
+      if (first && timer_->measurable(rt, *call)) measure(rt, call, lg);
     }
     MeasuredTable::Times best;
-    if (table_->nearest(op, dt, n, bytes, &best)) {
+    if (table_->nearest(op, dt, n, bytes, &best, false, scope)) {
       int algo = 0;
       double t = 0.0;
       for (const auto& kv : best) {

@@ -11,7 +11,7 @@
 // Both front ends share it. The Python communicator times the candidates itself and writes the table through the
 // routing session (cocclRouterSetMeasured). The C API gives the selector an AlgorithmTimer: at the first call of a
 // size bucket the candidates are timed in place of the call (tuning/fused_timer.cc), every rank takes the maximum
-// over the ranks, and the table is identical everywhere, so every rank selects the same algorithm.
+// over the ranks, and the communicator's entries are identical on all of its ranks, so they select the same algorithm.
 #pragma once
 #include <atomic>
 #include <map>
@@ -27,9 +27,13 @@ namespace coccl {
 
 class MeasuredTable {
  public:
+  // `scope` separates communicators that share one table (the C API's process-wide table: the communicator's id,
+  // which is never reused); a table that belongs to one communicator (a routing session) uses scope 0.
   struct Key {
+    uint64_t scope;
     int op, dtype, nRanks, log2Bytes;
     bool operator<(const Key& o) const {
+      if (scope != o.scope) return scope < o.scope;
       if (op != o.op) return op < o.op;
       if (dtype != o.dtype) return dtype < o.dtype;
       if (nRanks != o.nRanks) return nRanks < o.nRanks;
@@ -44,31 +48,31 @@ class MeasuredTable {
     return lg;
   }
   // Every method takes the table's lock: ranks that live in one process as threads share the table.
-  void set(int op, int dtype, int nRanks, int log2Bytes, int algorithm, double seconds) {
+  void set(int op, int dtype, int nRanks, int log2Bytes, int algorithm, double seconds, uint64_t scope = 0) {
     std::lock_guard<std::mutex> lock(mutex_);
-    table_[Key{op, dtype, nRanks, log2Bytes}][algorithm] = seconds;
+    table_[Key{scope, op, dtype, nRanks, log2Bytes}][algorithm] = seconds;
   }
   bool empty() const { std::lock_guard<std::mutex> lock(mutex_); return table_.empty(); }
   size_t size() const { std::lock_guard<std::mutex> lock(mutex_); return table_.size(); }
   // Times of exactly this bucket (a copy); false when the bucket holds none.
-  bool exact(int op, int dtype, int nRanks, int log2Bytes, Times* out = nullptr) const {
+  bool exact(int op, int dtype, int nRanks, int log2Bytes, Times* out = nullptr, uint64_t scope = 0) const {
     std::lock_guard<std::mutex> lock(mutex_);
-    return find(op, dtype, nRanks, log2Bytes, out);
+    return find(scope, op, dtype, nRanks, log2Bytes, out);
   }
   // The bucket of `bytes`, else the nearest measured bucket below it, else (unless belowOnly) the nearest above.
-  bool nearest(int op, int dtype, int nRanks, size_t bytes, Times* out, bool belowOnly = false) const {
+  bool nearest(int op, int dtype, int nRanks, size_t bytes, Times* out, bool belowOnly = false, uint64_t scope = 0) const {
     std::lock_guard<std::mutex> lock(mutex_);
     const int lg = bucketOf(bytes);
     for (int d = 0; d < 48; ++d)
-      if (find(op, dtype, nRanks, lg - d, out)) return true;
+      if (find(scope, op, dtype, nRanks, lg - d, out)) return true;
     for (int d = 1; d < 48 && !belowOnly; ++d)
-      if (find(op, dtype, nRanks, lg + d, out)) return true;
+      if (find(scope, op, dtype, nRanks, lg + d, out)) return true;
     return false;
   }
 
  private:
-  bool find(int op, int dtype, int nRanks, int log2Bytes, Times* out) const {
-    auto it = table_.find(Key{op, dtype, nRanks, log2Bytes});
+  bool find(uint64_t scope, int op, int dtype, int nRanks, int log2Bytes, Times* out) const {
+    auto it = table_.find(Key{scope, op, dtype, nRanks, log2Bytes});
     if (it == table_.end()) return false;
     if (out) *out = it->second;
     return true;
@@ -102,10 +106,11 @@ class MeasuredSelector : public AlgorithmSelector {
   MeasuredTable* table_;
   AlgorithmTimer* timer_;
   std::atomic<uint64_t> measuredBuckets_{0};
-  // (communicator, bucket) pairs whose timing was tried: every rank of a communicator decides alike, also when
-  // several ranks are threads of this process and share this selector
+  // Buckets (per communicator) whose timing was tried. Whether a call is timed must depend on the communicator's own
+  // history only: the ranks of a communicator have seen the same calls on IT, but not on the other communicators each
+  // of them belongs to, and a rank that timed alone would wait for peers that never come.
   std::mutex mutex_;
-  std::set<std::pair<const Comm*, MeasuredTable::Key>> attempted_;
+  std::set<MeasuredTable::Key> attempted_;
 };
 
 }  // namespace coccl
