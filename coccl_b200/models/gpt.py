@@ -150,6 +150,167 @@ class ParamStore:
         return out
 
 
+class FsdpParamStore(ParamStore):
+    """Fully sharded parameters (the scheme known as FSDP / ZeRO-3) over a data-parallel communicator.
+
+    A rank keeps 1 / R of every parameter and gradient (`flat_param_shard`, `flat_grad_shard`, R = ranks). The
+    parameters of a transformer layer exist in full only while the layer runs: two buffers of the size of the largest
+    layer take turns (layer k uses buffer k % 2), `gather(unit)` fills one from the shards of all ranks before the
+    layer's forward and again before its backward, and `reduce_scatter_grads(unit)` sums the layer's gradients into
+    the owners' shards as soon as its backward is done (GPTStage places the two calls with autograd functions around
+    the layer). What does not belong to a layer (embeddings, final LayerNorm: the unit "outer") stays resident for
+    the whole step; its gradients are reduced at the end. This is the traffic the reference's classifier calls
+    strategy "fsdp": a steady flow of all-gathers and reduce-scatters on the data-parallel communicator
+    (core/training/coccl_training_classifier.cc:555-563), served here by the same (compressed or native) collectives
+    as the sharded optimizer's.
+
+    The buffers that take turns are written through aliases with their own version counters: autograd has saved
+    parameter views of several layers that share one buffer, and only the layer whose turn it is reads them."""
+
+    OUTER = "outer"
+
+    def __init__(self, dtype, device, comm):
+        super().__init__(dtype, device, 1)
+        self.comm = comm
+        self.ranks = comm.size if comm is not None else 1
+        self.rank = comm.rank if comm is not None else 0
+
+    @staticmethod
+    def unit_of(name: str) -> str:
+        return name.split(".")[1] if name.startswith("layers.") else FsdpParamStore.OUTER
+
+    def materialise(self, seed=1234, tp_rank=0, grad_dtype=torch.float32):
+        import zlib
+        R, dev = self.ranks, self.device
+        units: dict[str, list] = {}
+        for spec in self.specs:
+            units.setdefault(self.unit_of(spec[0]), []).append(spec)
+        self.unit_names = [u for u in units if u != self.OUTER]
+        # layout of every unit: 8-element aligned parameters, total a multiple of 8 * R so that shards stay aligned
+        self.layout, self.unit_size = {}, {}
+        for u, specs in units.items():
+            off = 0
+            for name, shape, _, _ in specs:
+                n = math.prod(shape)
+                self.layout[name] = (u, off, n)
+                off += -(-n // 8) * 8
+            self.unit_size[u] = -(-off // (8 * R)) * (8 * R)
+        biggest = max((self.unit_size[u] for u in self.unit_names), default=0)
+        self.full = [torch.zeros(biggest, dtype=self.dtype, device=dev) for _ in range(2)]
+        self.gfull = [torch.zeros(biggest, dtype=grad_dtype, device=dev) for _ in range(2)]
+        outer = self.unit_size.get(self.OUTER, 0)
+        self.outer_full = torch.zeros(outer, dtype=self.dtype, device=dev)
+        self.outer_gfull = torch.zeros(outer, dtype=grad_dtype, device=dev)
+        # this rank's shards of all units, back to back: what the optimizer owns
+        self.shard_off, total = {}, 0
+        for u in list(self.unit_names) + ([self.OUTER] if outer else []):
+            self.shard_off[u] = total
+            total += self.unit_size[u] // R
+        self.flat_param_shard = torch.zeros(total, dtype=self.dtype, device=dev)
+        self.flat_grad_shard = torch.zeros(total, dtype=grad_dtype, device=dev)
+        self._scratch = torch.zeros(max([self.unit_size[u] // R for u in self.unit_size] or [0]), dtype=grad_dtype, device=dev)
+
+        def alias(t):   # same memory, own version counter
+            return torch.empty(0, dtype=t.dtype, device=t.device).set_(t.untyped_storage(), 0, t.shape)
+        self._full_w = [alias(t) for t in self.full]
+        self._outer_w = alias(self.outer_full)
+        for u, specs in units.items():
+            buf, gbuf = self._buffers(u)
+            buf.zero_()
+            for name, shape, init, std in specs:
+                _, off, n = self.layout[name]
+                view = buf[off:off + n].view(shape)
+                if init == "normal":
+                    gen = torch.Generator(device=dev)
+                    gen.manual_seed(seed + zlib.crc32(name.encode()) + (0 if self.replicated[name] else 7919 * tp_rank))
+                    view.copy_(torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std)
+                elif init == "ones":
+                    view.fill_(1.0)
+                prm = nn.Parameter(view, requires_grad=True)
+                prm.main_grad = gbuf[off:off + n].view(shape)
+                self.params[name] = prm
+            self.param_shard(u).copy_(self._mine(buf, u))   # the values of the next unit overwrite the buffer
+        self.gather(self.OUTER)
+        return self
+
+    def _buffers(self, u):
+        if u == self.OUTER:
+            return self.outer_full, self.outer_gfull
+        k = self.unit_names.index(u) % 2
+        return self.full[k], self.gfull[k]
+
+    def _mine(self, buf, u):
+        n = self.unit_size[u] // self.ranks
+        return buf[self.rank * n:(self.rank + 1) * n]
+
+    def param_shard(self, u):
+        n = self.unit_size[u] // self.ranks
+        return self.flat_param_shard[self.shard_off[u]:self.shard_off[u] + n]
+
+    def grad_shard(self, u):
+        n = self.unit_size[u] // self.ranks
+        return self.flat_grad_shard[self.shard_off[u]:self.shard_off[u] + n]
+
+    def gather(self, u) -> None:
+        """Bring unit `u` together from the shards of all ranks, into the buffer whose turn it is."""
+        if u not in self.unit_size or self.unit_size[u] == 0:
+            return
+        target = self._outer_w if u == self.OUTER else self._full_w[self.unit_names.index(u) % 2]
+        out = target[:self.unit_size[u]]
+        with torch.no_grad():
+            if self.ranks == 1:
+                out.copy_(self.param_shard(u))
+            else:
+                self.comm.all_gather(self.param_shard(u), out)
+
+    def zero_unit_grads(self, u) -> None:
+        self._buffers(u)[1][:self.unit_size[u]].zero_()
+
+    def reduce_scatter_grads(self, u) -> None:
+        """Add the sum over all ranks of unit `u`'s gradients to the owners' shards."""
+        if u not in self.unit_size or self.unit_size[u] == 0:
+            return
+        g = self._buffers(u)[1][:self.unit_size[u]]
+        with torch.no_grad():
+            if self.ranks == 1:
+                self.grad_shard(u).add_(g)
+            else:
+                part = self._scratch[:self.unit_size[u] // self.ranks]
+                self.comm.reduce_scatter(g, part)
+                self.grad_shard(u).add_(part)
+
+
+class _FsdpEnter(torch.autograd.Function):
+    """Identity on the layer's inputs. Its backward runs when the layer's backward is complete: the layer's gradients
+    go to their owners."""
+
+    @staticmethod
+    def forward(ctx, store, unit, *xs):
+        ctx.store, ctx.unit = store, unit
+        return tuple(x.view_as(x) for x in xs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        ctx.store.reduce_scatter_grads(ctx.unit)
+        return (None, None, *gs)
+
+
+class _FsdpLeave(torch.autograd.Function):
+    """Identity on the layer's outputs. Its backward runs before any of the layer's: the parameters come back into the
+    buffer (another layer has used it since the forward) and the gradient buffer starts from zero."""
+
+    @staticmethod
+    def forward(ctx, store, unit, *xs):
+        ctx.store, ctx.unit = store, unit
+        return tuple(x.view_as(x) for x in xs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        ctx.store.gather(ctx.unit)
+        ctx.store.zero_unit_grads(ctx.unit)
+        return (None, None, *gs)
+
+
 class TransformerLayer(nn.Module):
     def __init__(self, cfg: GPTConfig, idx: int, store: ParamStore, tp):
         super().__init__()
@@ -234,7 +395,8 @@ class GPTStage(nn.Module):
     flat buffer whatever the schedule."""
 
     def __init__(self, cfg: GPTConfig, device, tp=None, first_layer=0, last_layer=None, pre=True, post=True,
-                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None, layer_ranges=None, cp=None):
+                 seed=1234, pad_to=1, layer_factory=None, ep_comm=None, layer_ranges=None, cp=None, fsdp_comm=None,
+                 fsdp: bool = False):
         """ep_comm: communicator of the expert-parallel group for a mixture-of-experts model (None: every expert is
         local). Expert weights that differ between the ranks of that group live in a second flat buffer pair,
         `expert_store`, which data parallelism must not reduce or gather."""
@@ -246,7 +408,10 @@ class GPTStage(nn.Module):
         last_layer = cfg.n_layer if last_layer is None else last_layer
         self.pre, self.post = pre, post
         tp_ = self.tp
-        store = ParamStore(cfg.dtype, device, pad_to)
+        # fsdp: parameters and gradients fully sharded over `fsdp_comm` (FsdpParamStore); a group of one still
+        # runs the same gather / scatter points
+        self.fsdp = bool(fsdp)
+        store = FsdpParamStore(cfg.dtype, device, fsdp_comm) if self.fsdp else ParamStore(cfg.dtype, device, pad_to)
         vshard = cfg.vocab // tp_.size
         assert cfg.vocab % tp_.size == 0
         if pre or post:
@@ -329,7 +494,10 @@ class GPTStage(nn.Module):
         else:
             x, delta = tokens_or_hidden
         for layer in (self.layers if chunk is None else self.chunks[chunk]):
-            x, delta = layer(x, delta, batch, seq)
+            if self.fsdp:
+                x, delta = self._sharded_layer(layer, x, delta, batch, seq)
+            else:
+                x, delta = layer(x, delta, batch, seq)
         if not self.chunk_is_last(chunk):
             return x, delta
         y, _ = fused.layer_norm(x, self.lnf_weight, self.lnf_bias, self.cfg.eps, residual=delta)
@@ -338,8 +506,25 @@ class GPTStage(nn.Module):
         logits = fused.linear(y, self.wte)
         return self.tp.vocab_parallel_cross_entropy(logits, targets.reshape(-1), loss_scale)
 
+    def _sharded_layer(self, layer, x, delta, batch, seq):
+        """One layer of a fully sharded stage: gather its parameters, run it between the two autograd markers that
+        place the backward's gather and reduce-scatter."""
+        store, unit = self.store, str(layer.idx)
+        store.gather(unit)
+        if torch.is_grad_enabled():
+            ins = _FsdpEnter.apply(store, unit, *((x,) if delta is None else (x, delta)))
+            x, delta = ins[0], (ins[1] if len(ins) > 1 else None)
+        x, delta = layer(x, delta, batch, seq)
+        if torch.is_grad_enabled():
+            x, delta = _FsdpLeave.apply(store, unit, x, delta)
+        return x, delta
+
     # ---- utilities
     def zero_grad_buffer(self):
+        if self.fsdp:
+            self.store.flat_grad_shard.zero_()
+            self.store.outer_gfull.zero_()
+            return
         self.store.flat_grad.zero_()
         if self.expert_store is not None:
             self.expert_store.flat_grad.zero_()

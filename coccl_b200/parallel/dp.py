@@ -120,3 +120,49 @@ class DistributedOptimizer:
         self._delta_state = None   # the replicas no longer match what the deltas were taken against: re-seed exactly
         if self.dp > 1 and not self.ddp:
             self.comm.all_gather(self.param_shard, self.flat_param)
+
+
+class FsdpOptimizer:
+    """AdamW over the shards of a fully sharded stage (models.gpt.FsdpParamStore): every rank updates the 1 / R of every
+    parameter it owns, from gradients that the backward pass has already reduce-scattered layer by layer. The step
+    reduces what is left (the gradients of the embeddings and the final LayerNorm, which stay resident for the whole
+    step), forms the global norm from the shards, applies the update and gathers the resident parameters again; the
+    layers' parameters are gathered by the next forward pass."""
+
+    def __init__(self, store, dp_comm=None, *, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_grad=1.0):
+        self.store, self.comm = store, dp_comm
+        self.dp = dp_comm.size if dp_comm is not None else 1
+        self.param_shard, self.grad_shard = store.flat_param_shard, store.flat_grad_shard
+        dev = self.param_shard.device
+        self.master = self.param_shard.float().clone()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
+        self.step_count = 0
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.ddp = False
+
+    def step(self, grad_scale: float = 1.0, coef=None):
+        self.step_count += 1
+        st = self.store
+        st.reduce_scatter_grads(st.OUTER)
+        fused.sum_squares(self.grad_shard, self._sumsq)
+        if self.dp > 1:
+            self.comm.all_reduce_small(self._sumsq)   # the shards of the ranks partition every gradient
+        fused.clip_coef(self._sumsq, self.clip, grad_scale, self._coef, self.grad_norm)
+        fused.adam_step(self.master, self.m, self.v, self.grad_shard, self.param_shard, lr=self.lr, beta1=self.betas[0],
+                        beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count, grad_scale=self._coef)
+        st.gather(st.OUTER)
+
+    def state_dict(self):
+        return {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count}
+
+    def load_state_dict(self, sd):
+        self.master.copy_(sd["master"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        self.step_count = int(sd["step"])
+        self.param_shard.copy_(self.master)
+        self.store.gather(self.store.OUTER)

@@ -49,7 +49,8 @@ def parse(argv=None):
     p.add_argument("--ep", type=int, default=1, help="expert parallelism: 1 or the data-parallel size")
     p.add_argument("--virtual-stages", type=int, default=1, help="model chunks per pipeline rank (interleaved 1F1B)")
     p.add_argument("--no-sequence-parallel", action="store_true")
-    p.add_argument("--dp-strategy", default="zero1", choices=["zero1", "ddp"])
+    p.add_argument("--dp-strategy", default="zero1", choices=["zero1", "ddp", "fsdp"],
+                   help="zero1: sharded optimizer; ddp: gradient all-reduce; fsdp: parameters, gradients and optimizer state sharded")
     c = ap.add_argument_group("collectives")
     c.add_argument("--policy", default=None, help="policy file (TOML); default: $COCCL_CONFIG_FILE, else the shipped training policy")
     c.add_argument("--no-compress", action="store_true", help="native collectives only (also COCCL_ENABLE=0)")

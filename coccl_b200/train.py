@@ -22,7 +22,9 @@ class ParallelConfig:
     pp: int = 1
     dp: int = 1
     sequence_parallel: bool = True
-    dp_strategy: str = "zero1"   # "zero1": sharded optimizer (reduce-scatter + all-gather); "ddp": gradient all-reduce
+    # "zero1": sharded optimizer (reduce-scatter + all-gather); "ddp": gradient all-reduce; "fsdp": parameters, gradients
+    # and optimizer state all sharded, a layer's parameters gathered while it runs (data parallelism only)
+    dp_strategy: str = "zero1"
     ep: int = 1   # expert parallelism of a mixture-of-experts model: 1 (every rank holds all experts) or dp
     virtual_stages: int = 1   # model chunks per pipeline rank; > 1 selects the interleaved 1F1B schedule
     cp: int = 1   # context parallelism: ranks that share every sequence, each holding seq_len / cp positions of it
@@ -65,7 +67,12 @@ class Trainer:
         replicas = dp * cp   # ranks that hold the same parameters: the gradient / optimizer-shard group
         ep_comm = getattr(g, "ep_comm", None) if g is not None else None
         assert self.parallel.ep == (ep_comm.size if ep_comm is not None else 1), "ParallelConfig.ep and the mesh disagree"
-        self.stage = GPTStage(cfg, device, tp=tp_ctx, layer_ranges=ranges,
+        self.fsdp = self.parallel.dp_strategy == "fsdp"
+        if self.fsdp:
+            assert self.parallel.tp == pp == cp == self.parallel.ep == 1 and cfg.n_experts == 0, \
+                "the fully sharded strategy is built for pure data parallelism of dense models"
+        self.stage = GPTStage(cfg, device, tp=tp_ctx, layer_ranges=ranges, fsdp=self.fsdp,
+                              fsdp_comm=(g.dp_comm if (g is not None and dp > 1) else None),
                               pre=(pp_rank == 0), post=(pp_rank == pp - 1), seed=seed, pad_to=8 * replicas * 2048,
                               ep_comm=ep_comm, cp=self.cp_ctx)
         # experts spread over the expert-parallel group: updated locally (never reduced or gathered), clipped with
@@ -75,13 +82,17 @@ class Trainer:
         if es is not None:
             self.expert_opt = DistributedOptimizer(es.flat_param, es.flat_grad, None, lr=lr, weight_decay=weight_decay,
                                                    clip_grad=clip_grad)
+        if self.fsdp:
+            from .parallel.dp import FsdpOptimizer
+            self.opt = FsdpOptimizer(self.stage.store, g.dp_comm if (g is not None and dp > 1) else None, lr=lr,
+                                     weight_decay=weight_decay, clip_grad=clip_grad)
         norm_groups = []
         if g is not None:
             if g.tp_comm is not None and g.tp_comm.size > 1:
                 norm_groups.append(g.tp_comm)
             if g.pp_comm is not None and g.pp_comm.size > 1:
                 norm_groups.append(g.pp_comm)
-        self.opt = DistributedOptimizer(self.stage.store.flat_param, self.stage.store.flat_grad,
+        self.opt = self.opt if self.fsdp else DistributedOptimizer(self.stage.store.flat_param, self.stage.store.flat_grad,
                                         g.dp_comm if (g is not None and replicas > 1) else None, lr=lr,
                                         weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups,
                                         norm_exclude=self.stage.store.norm_exclude_ranges(

@@ -44,7 +44,8 @@ def unshard_param(name: str, shards: list[torch.Tensor]) -> torch.Tensor:
 def save(trainer, directory: str, step: int, rank: int = 0, world: int = 1):
     os.makedirs(directory, exist_ok=True)
     sd = {
-        "flat_param": trainer.stage.store.flat_param.detach().cpu(),
+        # a fully sharded stage keeps only this rank's shards; every other layout keeps the stage's whole flat buffer
+        "flat_param": getattr(trainer.stage.store, "flat_param_shard", trainer.stage.store.flat_param).detach().cpu(),
         "optimizer": {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in trainer.opt.state_dict().items()},
         # experts of a mixture-of-experts model that are spread over the expert-parallel group (None otherwise)
         "expert_flat_param": (trainer.stage.expert_store.flat_param.detach().cpu()
@@ -82,7 +83,7 @@ def load(trainer, directory: str, rank: int = 0) -> int:
         # the layers a pipeline rank holds depend on the number of model chunks per rank
         raise ValueError(f"checkpoint was written with {man.get('virtual_stages', 1)} model chunk(s) per pipeline rank")
     sd = torch.load(os.path.join(directory, f"rank{rank:05d}.pt"), map_location="cpu", weights_only=False)
-    trainer.stage.store.flat_param.copy_(sd["flat_param"])
+    getattr(trainer.stage.store, "flat_param_shard", trainer.stage.store.flat_param).copy_(sd["flat_param"])
     trainer.opt.load_state_dict(sd["optimizer"])
     if sd.get("expert_flat_param") is not None:
         trainer.stage.expert_store.flat_param.copy_(sd["expert_flat_param"])

@@ -247,6 +247,58 @@ def test_moe_layouts_match_single_process(pp, dp):
     run_distributed(_moe_worker, pp * dp, "gloo", (pp, dp, params, ref))
 
 
+def _fsdp_worker(rank, world, ref_losses, ref_params):
+    """Fully sharded: a rank holds 1 / dp of every parameter, gradient and optimizer state; layers are gathered while
+    they run. Same losses and gradient norms as one process, and the shards really are shards."""
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = _cfg()
+    mesh = Mesh(tp=1, pp=1, dp=world, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, 1, world, dp_strategy="fsdp"), groups=mesh, lr=1e-2)
+    st = tr.stage.store
+    total = sum(st.unit_size.values())
+    assert st.flat_param_shard.numel() * world == total and tr.opt.master.numel() * world == total
+    assert st.full[0].numel() == max(st.unit_size[u] for u in st.unit_names) < total // 2   # two layer-sized buffers, not the model
+    # load the single-process model's initial weights: unit by unit through the buffers, own shard out
+    for u in list(st.unit_names) + [st.OUTER]:
+        buf = st._buffers(u)[0]
+        for name, (unit, off, n) in st.layout.items():
+            if unit == u:
+                buf[off:off + n].copy_(ref_params[name].reshape(-1))
+        st.param_shard(u).copy_(st._mine(buf, u))
+    st.gather(st.OUTER)
+    tr.opt.master.copy_(st.flat_param_shard.float())
+    tok = _data(cfg, 8)
+    per = 8 // world
+    mine = tok[rank * per:(rank + 1) * per]
+    for step, (ref, ref_norm) in enumerate(ref_losses):
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        assert abs(t.item() / world - ref) < 2e-3 * abs(ref) + 1e-4, (step, t.item() / world, ref)
+        assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6, (step, tr.opt.grad_norm.item(), ref_norm)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fully_sharded_strategy_matches_single_process(world):
+    tr, losses = _reference_losses()
+    tr2, _ = _reference_losses(steps=0)
+    params = {k: v.detach().clone() for k, v in tr2.stage.store.params.items()}
+    run_distributed(_fsdp_worker, world, "gloo", (losses, params))
+
+
+def test_fully_sharded_strategy_on_one_rank_is_the_plain_trainer():
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = _cfg()
+    tok = _data(cfg, 8)
+    plain = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2)
+    shard = Trainer(cfg, torch.device("cpu"), micro_batch=2, lr=1e-2, parallel=ParallelConfig(dp_strategy="fsdp"))
+    for _ in range(3):
+        a, b = plain.train_step(tok).item(), shard.train_step(tok).item()
+        assert abs(a - b) < 1e-5 * abs(a), (a, b)
+        assert abs(plain.opt.grad_norm.item() - shard.opt.grad_norm.item()) < 1e-5 * plain.opt.grad_norm.item()
+
+
 def _ddp_worker(rank, world, ref_losses, ref_params):
     import torch.distributed as dist
     from coccl_b200.parallel.mesh import Mesh

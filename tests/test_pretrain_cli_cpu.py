@@ -142,6 +142,26 @@ def test_expert_parallel_launch_saves_and_resumes(tmp_path):
         assert tail[s] == pytest.approx(full[s], rel=1e-4), (tail, full)
 
 
+def test_fully_sharded_launch_saves_and_resumes(tmp_path):
+    """--dp-strategy fsdp on two ranks: each rank's checkpoint holds its shards only, and the resumed run continues
+    the uninterrupted one."""
+    data = _token_file(tmp_path)
+    common = TINY + ["--data", data, "--global-batch", "8", "--dp-strategy", "fsdp", "--decay-steps", "6", "--heartbeat-stale-s", "20"]
+    full = {r["step"]: r["loss"] for r in _records(_launch(common + ["--steps", "6"], tmp_path)) if "step" in r}
+    ck = str(tmp_path / "ck")
+    _launch(common + ["--steps", "3", "--save", ck], tmp_path)
+    shard = torch.load(os.path.join(ck, "rank00001.pt"), map_location="cpu", weights_only=False)
+    tail = {r["step"]: r["loss"] for r in _records(_launch(common + ["--steps", "6", "--save", ck, "--resume"], tmp_path)) if "step" in r}
+    assert sorted(tail) == [4, 5, 6]
+    for s in tail:
+        assert tail[s] == pytest.approx(full[s], rel=1e-4), (tail, full)
+    assert full[6] < full[1]
+    # half of the model per rank (two ranks), not the model
+    from coccl_b200.models.gpt import GPTConfig
+    n = GPTConfig(n_layer=2, hidden=64, n_head=4, ffn=128, seq_len=32, vocab=128).num_params()
+    assert 0.45 * n < shard["flat_param"].numel() < 0.6 * n
+
+
 def test_example_launchers_parse_and_name_existing_modules():
     """The shell launchers under examples/ are syntactically valid and call modules and files that exist."""
     import importlib.util
