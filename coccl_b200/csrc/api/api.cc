@@ -363,8 +363,15 @@ void cocclApiGetStats(cocclApiStats* out) {
   out->compressedCalls = s.compressedCalls;
   out->deferredCalls = s.deferredCalls;
   out->policyLookups = s.policyLookups;
-  out->fusedCalls = state().executor ? state().executor->fusedCalls : 0;
-  out->stagedCalls = state().executor ? state().executor->stagedCalls : 0;
+  out->fusedCalls = state().executor ? state().executor->fusedCalls.load() : 0;
+  out->stagedCalls = state().executor ? state().executor->stagedCalls.load() : 0;
+}
+
+void cocclApiStagedReasons(unsigned long long* noFusedForm, unsigned long long* afterFailedSetup, unsigned long long* setupFailed) {
+  FusedExecutor* e = state().executor;
+  if (noFusedForm) *noFusedForm = e ? e->stagedNoFusedForm.load() : 0;
+  if (afterFailedSetup) *afterFailedSetup = e ? e->stagedAfterFailedSetup.load() : 0;
+  if (setupFailed) *setupFailed = e ? e->stagedSetupFailed.load() : 0;
 }
 
 unsigned long long cocclApiPeerExchangeCalls(void) { return (unsigned long long)PeerDataPath::calls(); }

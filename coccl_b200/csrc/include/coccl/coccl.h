@@ -70,6 +70,10 @@ typedef struct cocclApiStats {
 void cocclApiGetStats(cocclApiStats* out);
 // How many exchanges of encoded bytes of the staged pipeline (codecs without a fused kernel form: rANS, ZFP at rates
 // without one, third-party plugins) this process served by its own peer-memory kernel instead of a library collective.
+// Why compressed calls of this process ran through the staged pipeline instead of one fused kernel: the call has no
+// fused form (codec without a tile codec, datatype, hierarchical algorithm, more than one node); an earlier set-up of
+// the communicator had failed; this call's own set-up (mapping the peers' memory) failed.
+void cocclApiStagedReasons(unsigned long long* noFusedForm, unsigned long long* afterFailedSetup, unsigned long long* setupFailed);
 unsigned long long cocclApiPeerExchangeCalls(void);
 // Algorithm selection from measured times ([autotune] enabled = true): at the first all-reduce of a size bucket
 // (64 KiB - 256 MiB) that a fused kernel can serve, the one-shot and the two-shot kernel are timed on the call's own

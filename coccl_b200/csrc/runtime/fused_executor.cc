@@ -78,7 +78,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   cocclkCodec kc;
   const int op = fusedOperation(call, call.algorithm, &kc);
   const bool fusable = op >= 0;
-  if (!fusable) { ++stagedCalls; return StagedExecutor::execute(rt, call); }
+  if (!fusable) { ++stagedCalls; ++stagedNoFusedForm; return StagedExecutor::execute(rt, call); }
 
   FusedState* stp;
   {
@@ -89,7 +89,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
   // The set-up below blocks on the other ranks (host-level exchange). Ranks that live in one process as threads must
   // therefore not share a lock across it: each communicator has its own.
   std::unique_lock<std::mutex> lock(st.mutex);
-  if (st.broken) { lock.unlock(); ++stagedCalls; return StagedExecutor::execute(rt, call); }
+  if (st.broken) { lock.unlock(); ++stagedCalls; ++stagedAfterFailedSetup; return StagedExecutor::execute(rt, call); }
   const int n = comm->nRanks;
   const long count = (op == 0 || op == 1 || op == 2) ? (long)info.count : (op == 4 ? (long)(info.count / (size_t)n) : (long)info.count);
   const long slot = cocclkSlotBytes(&kc, count);
@@ -121,6 +121,7 @@ ncclResult_t FusedExecutor::execute(Runtime* rt, const PreparedCall& call) {
       st.half = 0;
       lock.unlock();
       ++stagedCalls;
+      ++stagedSetupFailed;
       return StagedExecutor::execute(rt, call);
     }
   }

@@ -14,6 +14,7 @@
 //   AllReduce two-shot     Compress(N) -> AllToAll -> DecompReduceComp(N) -> AllGather -> Decompress
 //   AllReduce triple-shot  hierarchical reduction (last encoder = default scope) -> AllGather -> Decompress
 #pragma once
+#include <atomic>
 #include "memory/buffer_manager.h"
 #include "pipeline/pipeline.h"
 #include "runtime/runtime.h"
@@ -47,7 +48,11 @@ class FusedExecutor : public StagedExecutor {
   // Status word of the communicator's last completed fused kernels (0 = fine; otherwise the {phase, peer, slice}
   // of the first bounded wait that ran out). Reads pinned host memory only.
   unsigned int asyncStatus(Comm* comm);
-  uint64_t fusedCalls = 0, stagedCalls = 0;
+  // ranks that are threads of one process share the executor
+  std::atomic<uint64_t> fusedCalls{0}, stagedCalls{0};
+  // why calls went to the staged pipeline: no fused form for the call (codec, datatype, algorithm, more than one node);
+  // the communicator's earlier set-up had failed; this call's set-up (mapping the peers' memory) failed
+  std::atomic<uint64_t> stagedNoFusedForm{0}, stagedAfterFailedSetup{0}, stagedSetupFailed{0};
 };
 
 }  // namespace coccl

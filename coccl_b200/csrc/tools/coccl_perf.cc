@@ -358,6 +358,11 @@ int main(int argc, char** argv) {
   cocclApiGetStats(&st);
   printf("# calls: compressed %llu (fused kernels %llu, staged pipeline %llu), native %llu\n", st.compressedCalls, st.fusedCalls,
          st.stagedCalls, st.nativeCalls);
+  if (st.stagedCalls) {
+    unsigned long long a = 0, b = 0, c = 0;
+    cocclApiStagedReasons(&a, &b, &c);
+    printf("# staged because: no fused form %llu, set-up failed %llu, after a failed set-up %llu\n", a, c, b);
+  }
   for (int i = 0; i < s.n; ++i) cocclApiCommDestroy(s.comms[i]);
   pthread_barrier_destroy(&s.barrier);
   if (bad) { fprintf(stderr, "coccl-perf: %d rank(s) failed\n", bad); return 1; }
