@@ -198,17 +198,17 @@ def _moe_worker(rank, world, pp, dp, ref_params, ref):
         assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6, (step, tr.opt.grad_norm.item(), ref_norm)
 
 
-def _moe_ep_worker(rank, world, ref_params, ref):
+def _moe_ep_worker(rank, world, ref_params, ref, pp=1):
     """Experts spread over the data-parallel group (ep = dp = 2): tokens travel to their experts and back, the experts
     live in their own flat buffers with their own optimizer, and the run still reproduces the single-process model."""
     import torch.distributed as dist
     from coccl_b200.parallel.mesh import Mesh
     from coccl_b200.train import ParallelConfig, Trainer
     cfg = _moe_cfg()
-    mesh = Mesh(tp=1, pp=1, dp=2, ep=2, device=torch.device("cpu"))
-    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, 1, 2, ep=2), groups=mesh, lr=1e-2)
+    mesh = Mesh(tp=1, pp=pp, dp=2, ep=2, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, pp, 2, ep=2), groups=mesh, lr=1e-2)
     es = tr.stage.expert_store
-    assert es is not None and len(es.params) == 2 * 2 * 3   # two MoE layers x two local experts x (up, bias, down)
+    assert es is not None and len(es.params) == (2 // pp) * 2 * 3   # MoE layers of this stage x two local experts x (up, bias, down)
     assert not any(".experts." in n for n in tr.stage.store.params)
     for store in (tr.stage.store, es):
         for name, p in store.params.items():
@@ -216,7 +216,7 @@ def _moe_ep_worker(rank, world, ref_params, ref):
     tr.opt.master.copy_(tr.opt.param_shard.float())
     tr.expert_opt.master.copy_(tr.expert_opt.param_shard.float())
     tok = _data(cfg, 8)
-    mine = tok[rank * 4:(rank + 1) * 4]
+    mine = tok[mesh.dp_rank * 4:(mesh.dp_rank + 1) * 4]
     for step, (ref_loss, ref_norm) in enumerate(ref):
         t = tr.train_step(mine).clone()
         dist.all_reduce(t)
@@ -226,9 +226,10 @@ def _moe_ep_worker(rank, world, ref_params, ref):
     assert (es.params[name].detach() - ref_params[name]).abs().max().item() > 0
 
 
-def test_expert_parallel_matches_single_process():
+@pytest.mark.parametrize("pp", [1, 2])
+def test_expert_parallel_matches_single_process(pp):
     params, ref = _moe_reference()
-    run_distributed(_moe_ep_worker, 2, "gloo", (params, ref))
+    run_distributed(_moe_ep_worker, 2 * pp, "gloo", (params, ref, pp))
 
 
 def test_moe_model_trains_and_counts_its_parameters():
