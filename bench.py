@@ -129,7 +129,8 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny"])
+    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "qwen2.5-7b", "llama3-8b"],
+                    help="the default is the benchmark's model; the llama-family presets are extras")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--parallelism", default=None, help="override as tp,pp,dp")
     ap.add_argument("--no-compress", action="store_true", help="route collectives through NCCL only")
@@ -161,7 +162,11 @@ def main():
 
     cfg = {"gpt-6.7b": GPTConfig(),
            "gpt-small": GPTConfig(n_layer=4, hidden=2048, n_head=16, ffn=8192, seq_len=2048, vocab=50304),
-           "gpt-tiny": GPTConfig(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)}[args.model]
+           "gpt-tiny": GPTConfig(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
+           "qwen2.5-7b": GPTConfig(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048,
+                                   vocab=152064, tie_embeddings=False, rope_theta=1.0e6, qkv_bias=True),
+           "llama3-8b": GPTConfig(arch="llama", n_layer=32, hidden=4096, n_head=32, n_kv_head=8, ffn=14336, seq_len=2048,
+                                  vocab=128256, tie_embeddings=False, rope_theta=5.0e5)}[args.model]
 
     mesh = None
     if n > 1:
@@ -235,7 +240,8 @@ def main():
             # the only published GPT-6.7B figure (163.2 model TFLOP/s per GPU, reference README.md:334-340) is for
             # 32 x H800 over InfiniBand: no number exists for this hardware, so no ratio is formed
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
-            "config": {"model": f"{args.model}: L{cfg.n_layer} h{cfg.hidden} heads{cfg.n_head} ffn{cfg.ffn} gelu "
+            "config": {"model": f"{args.model}: L{cfg.n_layer} h{cfg.hidden} heads{cfg.n_head} ffn{cfg.ffn} "
+                                f"{'gelu' if cfg.arch == 'gpt' else f'swiglu kv{cfg.kv_heads} rope rmsnorm'} "
                                 f"seq{cfg.seq_len} vocab{cfg.vocab}", "global_batch": global_batch,
                        "seq_len": cfg.seq_len, "micro_batch": 2, "parallelism": f"tp{tp}pp{pp}dp{dp}" + (f"v{par.virtual_stages}" if par.virtual_stages > 1 else ""),
                        "optimizer": "AdamW, fp32 master weights, sharded over DP",

@@ -41,6 +41,19 @@ class GPTConfig:
     n_experts: int = 0
     moe_top_k: int = 2
     moe_every: int = 1
+    # Model family. "gpt": LayerNorm, learned positions, biased linears, tanh-GELU MLP, output head tied to the word
+    # embedding. "llama": the Llama / Qwen family (coccl_b200.models.llama): RMSNorm, rotary positions, grouped-query
+    # attention with `n_kv_head` key/value heads, SwiGLU MLP of width `ffn`, no biases except (qkv_bias, as Qwen2.5)
+    # on the query / key / value projections, untied output head unless tie_embeddings.
+    arch: str = "gpt"
+    n_kv_head: int = 0              # 0: as many as n_head
+    rope_theta: float = 1.0e6
+    qkv_bias: bool = False
+    tie_embeddings: bool = True     # the llama presets set False
+
+    @property
+    def kv_heads(self) -> int:
+        return self.n_kv_head or self.n_head
 
     def is_moe_layer(self, idx: int) -> bool:
         return self.n_experts > 0 and (idx + 1) % max(self.moe_every, 1) == 0
@@ -51,6 +64,10 @@ class GPTConfig:
 
     def num_params(self) -> int:
         h, f = self.hidden, self.ffn
+        if self.arch == "llama":
+            qkv = (self.n_head + 2 * self.kv_heads) * self.head_dim
+            layer = qkv * h + (qkv if self.qkv_bias else 0) + h * h + 3 * h * f + 2 * h
+            return self.n_layer * layer + self.vocab * h * (1 if self.tie_embeddings else 2) + h
         attn = 4 * h * h + 4 * h + 4 * h           # qkv, proj, their biases, two LayerNorms
         mlp = 2 * h * f + f + h
         moe = self.n_experts * (2 * h * f + f) + self.n_experts * h        # experts (up, bias, down), router
@@ -61,6 +78,9 @@ class GPTConfig:
         """Training FLOPs per token (fwd+bwd = 3x fwd). Attention: QK^T and PV are 2*s*h each per token for full
         attention; a causal mask needs half of it, so 2*s*h per layer in total."""
         h, f, s = self.hidden, self.ffn, self.seq_len
+        if self.arch == "llama":
+            qkv = (self.n_head + 2 * self.kv_heads) * self.head_dim
+            return 3.0 * (self.n_layer * (2 * qkv * h + 2 * h * h + 2 * s * h + 2 * 3 * h * f) + 2 * h * self.vocab)
         attn = 2 * 4 * h * h + 2 * s * h
         n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
         dense = 2 * 2 * h * f
@@ -133,6 +153,24 @@ class ParamStore:
             self.params[name] = p
         self.offsets = {name: (off, n) for (name, _, _, _), off, n in zip(self.specs, offs, sizes)}
         return self
+
+    def span(self, names):
+        """One parameter over several named parameters that sit back to back in the flat buffers (same trailing shape,
+        added one after the other): the fused weight of a GEMM that computes all of them at once. Returns an
+        nn.Parameter whose rows are the rows of `names` in order and whose `main_grad` covers their gradients; the
+        optimizer, the checkpoint and the gradient reduction keep seeing the named parameters."""
+        first, last = self.offsets[names[0]], self.offsets[names[-1]]
+        tail = tuple(self.params[names[0]].shape[1:])
+        width = math.prod(tail) if tail else 1
+        at = first[0]
+        for n in names:   # back to back, whole rows
+            o, cnt = self.offsets[n]
+            assert o == at and cnt % 8 == 0 and tuple(self.params[n].shape[1:]) == tail, (n, "is not adjacent to its neighbours")
+            at += cnt
+        lo, hi = first[0], last[0] + last[1]
+        p = nn.Parameter(self.flat_param[lo:hi].view((hi - lo) // width, *tail), requires_grad=True)
+        p.main_grad = self.flat_grad[lo:hi].view((hi - lo) // width, *tail)
+        return p
 
     def norm_exclude_ranges(self, tp_rank: int, drop_wte: bool):
         """[lo, hi) ranges of the flat gradient that this rank must not count in the global gradient norm because
@@ -232,6 +270,21 @@ class FsdpParamStore(ParamStore):
             self.param_shard(u).copy_(self._mine(buf, u))   # the values of the next unit overwrite the buffer
         self.gather(self.OUTER)
         return self
+
+    def span(self, names):
+        """See ParamStore.span: here the named parameters sit back to back inside their unit's buffer."""
+        u, first, _ = self.layout[names[0]]
+        tail = tuple(self.params[names[0]].shape[1:])
+        width = math.prod(tail) if tail else 1
+        at = first
+        for n in names:
+            un, o, cnt = self.layout[n]
+            assert un == u and o == at and cnt % 8 == 0 and tuple(self.params[n].shape[1:]) == tail, (n, "is not adjacent to its neighbours")
+            at += cnt
+        buf, gbuf = self._buffers(u)
+        p = nn.Parameter(buf[first:at].view((at - first) // width, *tail), requires_grad=True)
+        p.main_grad = gbuf[first:at].view((at - first) // width, *tail)
+        return p
 
     def _buffers(self, u):
         if u == self.OUTER:
@@ -414,11 +467,13 @@ class GPTStage(nn.Module):
         store = FsdpParamStore(cfg.dtype, device, fsdp_comm) if self.fsdp else ParamStore(cfg.dtype, device, pad_to)
         vshard = cfg.vocab // tp_.size
         assert cfg.vocab % tp_.size == 0
-        if pre or post:
-            # the output head shares the word embedding; under pipeline parallelism the last stage keeps
+        llama = cfg.arch == "llama"
+        assert cfg.arch in ("gpt", "llama"), cfg.arch
+        if pre or (post and cfg.tie_embeddings):
+            # a tied output head shares the word embedding; under pipeline parallelism the last stage keeps
             # its own copy whose gradient is summed with the first stage's (see parallel/pp.py)
             store.add("wte", (vshard, cfg.hidden), "normal", cfg.init_std)
-        if pre:
+        if pre and not llama:
             store.add("wpe", (cfg.seq_len, cfg.hidden), "normal", cfg.init_std, replicated=True)
         self.ep_size = ep_comm.size if ep_comm is not None else 1
         # experts spread over several ranks are not replicas of one another: their own buffers. With one rank per
@@ -426,6 +481,10 @@ class GPTStage(nn.Module):
         expert_store = ParamStore(cfg.dtype, device, 8) if (cfg.n_experts > 0 and self.ep_size > 1) else None
 
         def default_layer(c, i, s, t):
+            if llama:
+                from .llama import LlamaLayer
+                assert c.n_experts == 0, "the llama family is built with dense layers"
+                return LlamaLayer(c, i, s, t)
             if c.is_moe_layer(i):
                 from .moe import MoETransformerLayer
                 assert t.size == 1, "mixture-of-experts layers are built for expert + data + pipeline parallelism (tp = 1)"
@@ -444,7 +503,10 @@ class GPTStage(nn.Module):
                 layer.cp = self.cp
         if post:
             store.add("lnf.weight", (cfg.hidden,), "ones", replicated=True)
-            store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
+            if not llama:
+                store.add("lnf.bias", (cfg.hidden,), "zeros", replicated=True)
+            if not cfg.tie_embeddings:
+                store.add("lm_head", (vshard, cfg.hidden), "normal", cfg.init_std)
         store.materialise(seed, tp_.rank)
         self.store = store
         self.expert_store = expert_store.materialise(seed, 0) if (expert_store is not None and expert_store.specs) else None
@@ -467,12 +529,16 @@ class GPTStage(nn.Module):
             mask = (local < 0) | (local >= self.wte.shape[0])
             e = F.embedding(local.masked_fill(mask, 0), self.wte)
             e = e.masked_fill(mask[:, None], 0)
-        first = self.cp.rank * s if self.cp is not None else 0   # s is this rank's part of the sequence
-        pos = self.wpe[first:first + s].unsqueeze(0).expand(b, s, cfg.hidden).reshape(b * s, cfg.hidden)
-        if tp.size > 1:
-            e = e + pos / tp.size  # the position term is summed over ranks below
-            e = tp.scatter_sum_tokens(e) if tp.sequence_parallel else tp.all_reduce_sum(e)
+        if hasattr(self, "wpe"):
+            first = self.cp.rank * s if self.cp is not None else 0   # s is this rank's part of the sequence
+            pos = self.wpe[first:first + s].unsqueeze(0).expand(b, s, cfg.hidden).reshape(b * s, cfg.hidden)
         else:
+            pos = None   # rotary positions are applied inside the attention
+        if tp.size > 1:
+            if pos is not None:
+                e = e + pos / tp.size  # the position term is summed over ranks below
+            e = tp.scatter_sum_tokens(e) if tp.sequence_parallel else tp.all_reduce_sum(e)
+        elif pos is not None:
             e = e + pos
         return e.to(cfg.dtype)
 
@@ -500,10 +566,14 @@ class GPTStage(nn.Module):
                 x, delta = layer(x, delta, batch, seq)
         if not self.chunk_is_last(chunk):
             return x, delta
-        y, _ = fused.layer_norm(x, self.lnf_weight, self.lnf_bias, self.cfg.eps, residual=delta)
+        if self.cfg.arch == "llama":
+            from .llama import rms_norm
+            y = rms_norm(x + delta if delta is not None else x, self.lnf_weight, self.cfg.eps)
+        else:
+            y, _ = fused.layer_norm(x, self.lnf_weight, self.lnf_bias, self.cfg.eps, residual=delta)
         y = self.tp.gather_tokens(y)
         y = self.tp.copy_to_tp(y)
-        logits = fused.linear(y, self.wte)
+        logits = fused.linear(y, self.wte if self.cfg.tie_embeddings else self.lm_head)
         return self.tp.vocab_parallel_cross_entropy(logits, targets.reshape(-1), loss_scale)
 
     def _sharded_layer(self, layer, x, delta, batch, seq):

@@ -100,7 +100,7 @@ class Mesh:
                 for g in grads:
                     g.copy_(flat[off:off + g.numel()].view_as(g))
                     off += g.numel()
-        if self.emb_group is not None and (stage.pre or stage.post):
+        if self.emb_group is not None and (stage.pre or stage.post) and stage.cfg.tie_embeddings:
             dist.all_reduce(store.params["wte"].main_grad, group=self.emb_group)
 
     def close(self):

@@ -30,6 +30,13 @@ MODELS = {
     "gpt-small": dict(n_layer=4, hidden=2048, n_head=16, ffn=8192),
     "gpt-tiny": dict(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
     "moe-tiny": dict(n_layer=4, hidden=512, n_head=8, ffn=1024, seq_len=256, vocab=8192, n_experts=4, moe_top_k=2, moe_every=2),
+    # the Llama / Qwen family (models/llama.py): RMSNorm, rotary positions, grouped-query attention, SwiGLU, untied head
+    "llama-tiny": dict(arch="llama", n_layer=2, hidden=512, n_head=8, n_kv_head=2, ffn=1536, seq_len=256, vocab=8192,
+                       tie_embeddings=False, rope_theta=1.0e4),
+    "llama3-8b": dict(arch="llama", n_layer=32, hidden=4096, n_head=32, n_kv_head=8, ffn=14336, seq_len=2048, vocab=128256,
+                      tie_embeddings=False, rope_theta=5.0e5),
+    "qwen2.5-7b": dict(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048, vocab=152064,
+                       tie_embeddings=False, rope_theta=1.0e6, qkv_bias=True),
 }
 
 
@@ -37,8 +44,8 @@ def parse(argv=None):
     ap = argparse.ArgumentParser(prog="python -m coccl_b200.pretrain", description=__doc__.split("\n\n")[0])
     m = ap.add_argument_group("model")
     m.add_argument("--model", default="gpt-tiny", choices=sorted(MODELS))
-    for name, typ in (("layers", int), ("hidden", int), ("heads", int), ("ffn", int), ("seq-len", int), ("vocab", int),
-                      ("experts", int), ("moe-top-k", int), ("moe-every", int)):
+    for name, typ in (("layers", int), ("hidden", int), ("heads", int), ("kv-heads", int), ("ffn", int), ("seq-len", int),
+                      ("vocab", int), ("experts", int), ("moe-top-k", int), ("moe-every", int), ("rope-theta", float)):
         m.add_argument(f"--{name}", type=typ, default=None, help="overrides the preset")
     m.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"], help="fp32 is for CPU runs")
     p = ap.add_argument_group("parallelism (tp * cp * pp * dp = world size)")
@@ -93,7 +100,8 @@ def model_config(args):
     from .models.gpt import GPTConfig
     kw = dict(MODELS[args.model])
     for flag, field in (("layers", "n_layer"), ("hidden", "hidden"), ("heads", "n_head"), ("ffn", "ffn"), ("seq_len", "seq_len"),
-                        ("vocab", "vocab"), ("experts", "n_experts"), ("moe_top_k", "moe_top_k"), ("moe_every", "moe_every")):
+                        ("vocab", "vocab"), ("experts", "n_experts"), ("moe_top_k", "moe_top_k"), ("moe_every", "moe_every"),
+                        ("kv_heads", "n_kv_head"), ("rope_theta", "rope_theta")):
         v = getattr(args, flag)
         if v is not None:
             kw[field] = v

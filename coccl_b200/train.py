@@ -97,7 +97,7 @@ class Trainer:
                                         weight_decay=weight_decay, clip_grad=clip_grad, norm_groups=norm_groups,
                                         norm_exclude=self.stage.store.norm_exclude_ranges(
                                             g.tp_rank if g is not None else 0,
-                                            drop_wte=(pp > 1 and pp_rank == pp - 1)),
+                                            drop_wte=(pp > 1 and pp_rank == pp - 1 and cfg.tie_embeddings)),
                                         extra_sumsq=(self.expert_opt.local_sum_squares if self.expert_opt is not None else None),
                                         strategy=self.parallel.dp_strategy)
         self.schedule = None

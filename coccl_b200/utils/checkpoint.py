@@ -14,8 +14,10 @@ import os
 
 import torch
 
-COLUMN_PARALLEL = ("qkv.weight", "qkv.bias", "fc1.weight", "fc1.bias", "wte")
-ROW_PARALLEL = ("proj.weight", "fc2.weight")
+# GPT names, then the llama family's (models/llama.py)
+COLUMN_PARALLEL = ("qkv.weight", "qkv.bias", "fc1.weight", "fc1.bias", "wte",
+                   ".q.weight", ".k.weight", ".v.weight", ".q.bias", ".k.bias", ".v.bias", "gate.weight", "up.weight", "lm_head")
+ROW_PARALLEL = ("proj.weight", "fc2.weight", ".o.weight", "down.weight")
 
 
 def shard_param(name: str, full: torch.Tensor, tp_rank: int, tp_size: int) -> torch.Tensor:
