@@ -129,7 +129,7 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "qwen2.5-7b", "llama3-8b"],
+    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "qwen2.5-7b", "qwen3-8b", "llama3-8b"],
                     help="the default is the benchmark's model; the llama-family presets are extras")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--parallelism", default=None, help="override as tp,pp,dp")
@@ -165,6 +165,8 @@ def main():
            "gpt-tiny": GPTConfig(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
            "qwen2.5-7b": GPTConfig(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048,
                                    vocab=152064, tie_embeddings=False, rope_theta=1.0e6, qkv_bias=True),
+           "qwen3-8b": GPTConfig(arch="llama", n_layer=36, hidden=4096, n_head=32, n_kv_head=8, ffn=12288, seq_len=2048,
+                                 vocab=151936, tie_embeddings=False, rope_theta=1.0e6, qk_norm=True),
            "llama3-8b": GPTConfig(arch="llama", n_layer=32, hidden=4096, n_head=32, n_kv_head=8, ffn=14336, seq_len=2048,
                                   vocab=128256, tie_embeddings=False, rope_theta=5.0e5)}[args.model]
 

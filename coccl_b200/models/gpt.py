@@ -49,6 +49,7 @@ class GPTConfig:
     n_kv_head: int = 0              # 0: as many as n_head
     rope_theta: float = 1.0e6
     qkv_bias: bool = False
+    qk_norm: bool = False           # RMSNorm over the head dimension of queries and keys before the rotation (Qwen3)
     tie_embeddings: bool = True     # the llama presets set False
 
     @property
@@ -66,7 +67,7 @@ class GPTConfig:
         h, f = self.hidden, self.ffn
         if self.arch == "llama":
             qkv = (self.n_head + 2 * self.kv_heads) * self.head_dim
-            layer = qkv * h + (qkv if self.qkv_bias else 0) + h * h + 3 * h * f + 2 * h
+            layer = qkv * h + (qkv if self.qkv_bias else 0) + h * h + 3 * h * f + 2 * h + (2 * self.head_dim if self.qk_norm else 0)
             return self.n_layer * layer + self.vocab * h * (1 if self.tie_embeddings else 2) + h
         attn = 4 * h * h + 4 * h + 4 * h           # qkv, proj, their biases, two LayerNorms
         mlp = 2 * h * f + f + h

@@ -1,5 +1,6 @@
 """The Llama / Qwen model family on the same trainer: RMSNorm, rotary positions, grouped-query attention, SwiGLU MLP,
-no biases (except, optionally, on the query / key / value projections as in Qwen2.5), untied output head.
+no biases (except, optionally, on the query / key / value projections as in Qwen2.5), optional RMSNorm of queries and
+keys per head (Qwen3), untied output head.
 
 The reference trains Qwen2.5 and Qwen3 through an external Megatron trainer
 (examples/training_scripts/train_qwen_coccl.sh:60-131; Qwen2.5-7B is one of its published end-to-end results,
@@ -98,6 +99,11 @@ class LlamaLayer(TransformerLayer):
             store.add(pre + "q.bias", (nh * d // t,), "zeros")
             store.add(pre + "k.bias", (nkv * d // t,), "zeros")
             store.add(pre + "v.bias", (nkv * d // t,), "zeros")
+        if cfg.qk_norm:
+            # one weight vector per layer, applied to every head: the ranks of a tensor-parallel group see different
+            # heads, so its gradient is a partial sum like that of any replicated parameter
+            store.add(pre + "q_norm.weight", (d,), "ones", replicated=True)
+            store.add(pre + "k_norm.weight", (d,), "ones", replicated=True)
         store.add(pre + "o.weight", (h, nh * d // t), "normal", out_std)
         store.add(pre + "ln2.weight", (h,), "ones", replicated=True)
         store.add(pre + "gate.weight", (f // t, h), "normal", cfg.init_std)
@@ -106,7 +112,8 @@ class LlamaLayer(TransformerLayer):
 
     def names(self):
         base = ["ln1.weight", "q.weight", "k.weight", "v.weight", "o.weight", "ln2.weight", "gate.weight", "up.weight", "down.weight"]
-        return base + (["q.bias", "k.bias", "v.bias"] if self.cfg.qkv_bias else [])
+        return (base + (["q.bias", "k.bias", "v.bias"] if self.cfg.qkv_bias else []) +
+                (["q_norm.weight", "k_norm.weight"] if self.cfg.qk_norm else []))
 
     def bind(self, params: dict, expert_params: dict | None = None):
         pre = self.prefix
@@ -121,8 +128,10 @@ class LlamaLayer(TransformerLayer):
         cfg, t = self.cfg, self.tp.size
         nh, nkv, d = cfg.n_head // t, cfg.kv_heads // t, cfg.head_dim
         q, k, v = qkv.split([nh * d, nkv * d, nkv * d], dim=-1)
-        q = q.reshape(batch, seq, nh, d)
-        kv = torch.stack([k.reshape(batch, seq, nkv, d), v.reshape(batch, seq, nkv, d)], 3).reshape(batch, seq, nkv, 2 * d)
+        q, k = q.reshape(batch, seq, nh, d), k.reshape(batch, seq, nkv, d)
+        if cfg.qk_norm:
+            q, k = rms_norm(q, self.q_norm_weight, cfg.eps), rms_norm(k, self.k_norm_weight, cfg.eps)
+        kv = torch.stack([k, v.reshape(batch, seq, nkv, d)], 3).reshape(batch, seq, nkv, 2 * d)
         cp = getattr(self, "cp", None)
         if cp is not None:
             # context parallelism: whole sequence, a share of the heads (keys and values of a head travel together)

@@ -35,6 +35,8 @@ MODELS = {
                        tie_embeddings=False, rope_theta=1.0e4),
     "llama3-8b": dict(arch="llama", n_layer=32, hidden=4096, n_head=32, n_kv_head=8, ffn=14336, seq_len=2048, vocab=128256,
                       tie_embeddings=False, rope_theta=5.0e5),
+    "qwen3-8b": dict(arch="llama", n_layer=36, hidden=4096, n_head=32, n_kv_head=8, ffn=12288, seq_len=2048, vocab=151936,
+                     tie_embeddings=False, rope_theta=1.0e6, qk_norm=True),
     "qwen2.5-7b": dict(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048, vocab=152064,
                        tie_embeddings=False, rope_theta=1.0e6, qkv_bias=True),
 }

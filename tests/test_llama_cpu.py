@@ -13,7 +13,7 @@ from dist_utils import run_distributed
 def _cfg(**kw):
     from coccl_b200.models.gpt import GPTConfig
     base = dict(arch="llama", n_layer=4, hidden=64, n_head=4, n_kv_head=2, ffn=128, seq_len=32, vocab=128, dtype=torch.float32,
-                qkv_bias=True, tie_embeddings=False, rope_theta=10000.0)
+                qkv_bias=True, qk_norm=True, tie_embeddings=False, rope_theta=10000.0)
     base.update(kw)
     return GPTConfig(**base)
 
@@ -62,6 +62,8 @@ def _plain_llama_forward(cfg, p, tokens):
         q = (y @ p[pre + "q.weight"].t() + p[pre + "q.bias"]).view(b, s, nh, d)
         k = (y @ p[pre + "k.weight"].t() + p[pre + "k.bias"]).view(b, s, nkv, d)
         v = (y @ p[pre + "v.weight"].t() + p[pre + "v.bias"]).view(b, s, nkv, d)
+        if cfg.qk_norm:
+            q, k = F.rms_norm(q, (d,), p[pre + "q_norm.weight"], cfg.eps), F.rms_norm(k, (d,), p[pre + "k_norm.weight"], cfg.eps)
         q, k = rope(q), rope(k)
         outs = []
         for hd in range(nh):
@@ -81,7 +83,7 @@ def test_model_equals_a_plain_restatement():
     stage = GPTStage(cfg, torch.device("cpu"))
     p = {k: v.detach() for k, v in stage.store.params.items()}
     for name in p:     # biases and norm weights away from their trivial initial values
-        if name.endswith(".bias") or ".ln" in name or name.startswith("lnf"):
+        if name.endswith(".bias") or ".ln" in name or name.startswith("lnf") or "_norm" in name:
             p[name].add_(torch.randn_like(p[name]) * 0.1)
     tok = _data(cfg, 2)
     inp, tgt = tok[:, :-1], tok[:, 1:]
