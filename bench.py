@@ -129,7 +129,7 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "qwen2.5-7b", "qwen3-8b", "llama3-8b"],
+    ap.add_argument("--model", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-2.7b", "gpt-13b", "gpt-small", "gpt-tiny", "qwen2.5-7b", "qwen3-8b", "llama3-8b"],
                     help="the default is the benchmark's model; the llama-family presets are extras")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--parallelism", default=None, help="override as tp,pp,dp")
@@ -161,6 +161,8 @@ def main():
     assert tp * pp * dp == n
 
     cfg = {"gpt-6.7b": GPTConfig(),
+           "gpt-2.7b": GPTConfig(n_layer=32, hidden=2560, n_head=32, ffn=10240),
+           "gpt-13b": GPTConfig(n_layer=40, hidden=5120, n_head=40, ffn=20480),
            "gpt-small": GPTConfig(n_layer=4, hidden=2048, n_head=16, ffn=8192, seq_len=2048, vocab=50304),
            "gpt-tiny": GPTConfig(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
            "qwen2.5-7b": GPTConfig(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048,

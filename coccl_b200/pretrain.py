@@ -27,6 +27,8 @@ import torch.distributed as dist
 MODELS = {
     "gpt-6.7b": dict(),
     "gpt-1.3b": dict(n_layer=24, hidden=2048, n_head=16, ffn=8192),
+    "gpt-2.7b": dict(n_layer=32, hidden=2560, n_head=32, ffn=10240),
+    "gpt-13b": dict(n_layer=40, hidden=5120, n_head=40, ffn=20480),
     "gpt-small": dict(n_layer=4, hidden=2048, n_head=16, ffn=8192),
     "gpt-tiny": dict(n_layer=2, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192),
     "moe-tiny": dict(n_layer=4, hidden=512, n_head=8, ffn=1024, seq_len=256, vocab=8192, n_experts=4, moe_top_k=2, moe_every=2),
