@@ -141,8 +141,7 @@ def _worker(rank, world, tp, pp, dp, cp, chunks, strategy, ref, ref_params):
 
 
 @pytest.mark.parametrize("tp,pp,dp,cp,chunks,strategy", [
-    (2, 1, 1, 1, 1, "zero1"), (1, 2, 1, 1, 1, "zero1"), (1, 1, 2, 1, 1, "zero1"), (1, 1, 1, 2, 1, "zero1"),
-    (2, 2, 1, 1, 2, "zero1"), (1, 1, 2, 1, 1, "fsdp")])
+    (2, 1, 1, 1, 1, "zero1"), (1, 1, 1, 2, 1, "zero1"), (2, 2, 1, 1, 2, "zero1"), (1, 1, 2, 1, 1, "fsdp")])
 def test_parallel_layouts_match_single_process(tp, pp, dp, cp, chunks, strategy):
     params, ref = _reference(_cfg())
     run_distributed(_worker, tp * pp * dp * cp, "gloo", (tp, pp, dp, cp, chunks, strategy, ref, params))

@@ -66,7 +66,7 @@ def test_parallel_layouts_match_single_process(tp, pp, dp):
     run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params))
 
 
-@pytest.mark.parametrize("tp,pp,dp,chunks", [(1, 2, 1, 2), (1, 2, 2, 2), (2, 2, 1, 2), (1, 4, 1, 1)])
+@pytest.mark.parametrize("tp,pp,dp,chunks", [(1, 2, 1, 2), (2, 2, 1, 2), (1, 4, 1, 1)])
 def test_interleaved_pipeline_matches_single_process(tp, pp, dp, chunks):
     """Two model chunks per pipeline rank (virtual stages c * pp + rank): same losses and gradient norms as one process."""
     tr, losses = _reference_losses()
@@ -75,7 +75,7 @@ def test_interleaved_pipeline_matches_single_process(tp, pp, dp, chunks):
     run_distributed(_worker, tp * pp * dp, "gloo", (tp, pp, dp, losses, params, chunks))
 
 
-@pytest.mark.parametrize("tp,pp,dp,cp", [(1, 1, 1, 2), (2, 1, 1, 2), (1, 2, 1, 2), (1, 1, 2, 2), (1, 1, 1, 4)])
+@pytest.mark.parametrize("tp,pp,dp,cp", [(1, 1, 1, 2), (2, 1, 1, 2), (1, 2, 1, 2), (1, 1, 2, 2)])
 def test_context_parallel_layouts_match_single_process(tp, pp, dp, cp):
     """Every sequence split over cp ranks, whole-sequence attention by head exchange: same losses and gradient norms."""
     tr, losses = _reference_losses()
