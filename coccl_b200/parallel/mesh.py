@@ -92,7 +92,15 @@ class Mesh:
             names = [n for n in store.params if store.replicated.get(n)]
             if not self.sequence_parallel:
                 names = [n for n in names if not (".ln" in n or n.startswith("lnf"))]
-            if names:
+            offsets = getattr(store, "offsets", None)
+            if names and self.sequence_parallel and offsets is not None:
+                # the store keeps replicated parameters together at the end of the flat buffers: one all-reduce on
+                # that slice of the gradient buffer, nothing gathered or copied (the gaps between them are zero padding)
+                lo = min(offsets[n][0] for n in names)
+                hi = max(offsets[n][0] + offsets[n][1] for n in names)
+                assert all(store.replicated[n] for n, (o, _) in offsets.items() if lo <= o < hi)
+                dist.all_reduce(store.flat_grad[lo:hi], group=self.tp_group)
+            elif names:
                 grads = [store.params[n].main_grad for n in names]
                 flat = torch.cat([g.reshape(-1) for g in grads])
                 dist.all_reduce(flat, group=self.tp_group)
