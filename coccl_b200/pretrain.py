@@ -52,6 +52,8 @@ def parse(argv=None):
                       ("vocab", int), ("experts", int), ("moe-top-k", int), ("moe-every", int), ("rope-theta", float)):
         m.add_argument(f"--{name}", type=typ, default=None, help="overrides the preset")
     m.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"], help="fp32 is for CPU runs")
+    m.add_argument("--hf-model", default=None, metavar="DIR",
+                   help="start from a Hugging Face checkpoint of the Llama / Qwen family (configuration and weights; overrides --model)")
     p = ap.add_argument_group("parallelism (tp * cp * pp * dp = world size)")
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--pp", type=int, default=1)
@@ -102,6 +104,11 @@ def learning_rate(step: int, *, peak: float, floor: float, warmup: int, decay: i
 
 def model_config(args):
     from .models.gpt import GPTConfig
+    if args.hf_model:
+        import transformers
+        from .utils import hf
+        return hf.config_from_hf(transformers.AutoConfig.from_pretrained(args.hf_model), seq_len=args.seq_len,
+                                 dtype=torch.bfloat16 if args.dtype == "bf16" else torch.float32)
     kw = dict(MODELS[args.model])
     for flag, field in (("layers", "n_layer"), ("hidden", "hidden"), ("heads", "n_head"), ("ffn", "ffn"), ("seq_len", "seq_len"),
                         ("vocab", "vocab"), ("experts", "n_experts"), ("moe_top_k", "moe_top_k"), ("moe_every", "moe_every"),
@@ -161,7 +168,20 @@ def main(argv=None) -> int:
         raise SystemExit("interleaved 1F1B needs the micro-batches per step to be a multiple of --pp")
 
     start = 0
-    if args.resume and args.save and os.path.exists(os.path.join(args.save, "manifest.json")):
+    resuming = bool(args.resume and args.save and os.path.exists(os.path.join(args.save, "manifest.json")))
+    if args.hf_model and not resuming:
+        import transformers
+        from .utils import hf
+        assert not trainer.fsdp, "--hf-model loads into whole (or tensor-parallel) parameters; the fully sharded layout is not covered"
+        sd = transformers.AutoModelForCausalLM.from_pretrained(args.hf_model, torch_dtype=cfg.dtype).state_dict()
+        missing = hf.load_state_dict(trainer.stage, sd, tp_rank=mesh.tp_rank if mesh else 0, tp_size=args.tp)
+        if missing:
+            raise SystemExit(f"{args.hf_model} does not provide {missing[:4]}{' ...' if len(missing) > 4 else ''}")
+        del sd
+        trainer.opt.master.copy_(trainer.opt.param_shard.float())   # the optimizer's fp32 copy follows the loaded weights
+        if rank == 0:
+            print(f"loaded weights from {args.hf_model}", flush=True)
+    if resuming:
         start = checkpoint.load(trainer, args.save, rank=rank)
         if rank == 0:
             print(f"resumed from {args.save} at step {start}", flush=True)

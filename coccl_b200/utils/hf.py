@@ -1,0 +1,94 @@
+"""Bridge to Hugging Face checkpoints of the Llama / Qwen family: a model configuration from a `transformers` config,
+parameter names, and loading a state dict into a (tensor- and pipeline-parallel) stage of this trainer.
+
+The reference's launcher starts from such checkpoints (`--load` of a converted Qwen2.5 / Qwen3 model,
+examples/training_scripts/train_qwen_coccl.sh:37-55, training_envs.sh:8-12). Here the names map one to one
+(models/llama.py keeps q / k / v and gate / up as separate named parameters; the fused GEMM weights are views that span
+them), so loading is a renaming plus the tensor-parallel slicing of utils.checkpoint.shard_param.
+"""
+from __future__ import annotations
+
+import re
+
+import torch
+
+from ..models.gpt import GPTConfig
+from .checkpoint import shard_param
+
+_LAYER = {
+    "input_layernorm.weight": "ln1.weight", "post_attention_layernorm.weight": "ln2.weight",
+    "self_attn.q_proj.weight": "q.weight", "self_attn.k_proj.weight": "k.weight", "self_attn.v_proj.weight": "v.weight",
+    "self_attn.q_proj.bias": "q.bias", "self_attn.k_proj.bias": "k.bias", "self_attn.v_proj.bias": "v.bias",
+    "self_attn.q_norm.weight": "q_norm.weight", "self_attn.k_norm.weight": "k_norm.weight",
+    "self_attn.o_proj.weight": "o.weight",
+    "mlp.gate_proj.weight": "gate.weight", "mlp.up_proj.weight": "up.weight", "mlp.down_proj.weight": "down.weight",
+}
+_TOP = {"model.embed_tokens.weight": "wte", "model.norm.weight": "lnf.weight", "lm_head.weight": "lm_head"}
+
+
+def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> GPTConfig:
+    """GPTConfig(arch="llama") for a transformers LlamaConfig / Qwen2Config / Qwen3Config."""
+    kind = getattr(hf, "model_type", "")
+    if kind not in ("llama", "qwen2", "qwen3"):
+        raise ValueError(f"model type {kind!r} is not of the Llama / Qwen family")
+    head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
+    if head_dim * hf.num_attention_heads != hf.hidden_size:
+        raise ValueError("a head dimension other than hidden_size / heads is not supported")
+    theta = getattr(hf, "rope_theta", None)
+    if theta is None:   # newer configs keep it in a dictionary
+        theta = (getattr(hf, "rope_parameters", None) or {}).get("rope_theta", 1.0e4)
+    return GPTConfig(arch="llama", n_layer=hf.num_hidden_layers, hidden=hf.hidden_size, n_head=hf.num_attention_heads,
+                     n_kv_head=getattr(hf, "num_key_value_heads", None) or hf.num_attention_heads,
+                     ffn=hf.intermediate_size, seq_len=seq_len or min(hf.max_position_embeddings, 2048),
+                     vocab=hf.vocab_size, eps=hf.rms_norm_eps, rope_theta=float(theta),
+                     qkv_bias=(kind == "qwen2") or bool(getattr(hf, "attention_bias", False)), qk_norm=(kind == "qwen3"),
+                     tie_embeddings=bool(getattr(hf, "tie_word_embeddings", False)), dtype=dtype)
+
+
+def rename(hf_name: str) -> str | None:
+    """This package's name of a Hugging Face parameter (None: a buffer that is not a parameter here)."""
+    if hf_name in _TOP:
+        return _TOP[hf_name]
+    m = re.match(r"model\.layers\.(\d+)\.(.+)$", hf_name)
+    if m and m.group(2) in _LAYER:
+        return f"layers.{m.group(1)}.{_LAYER[m.group(2)]}"
+    return None
+
+
+def load_state_dict(stage, state_dict: dict, *, tp_rank: int = 0, tp_size: int = 1) -> list[str]:
+    """Copy a Hugging Face state dict into the parameters `stage` holds (a pipeline stage takes its own layers, a
+    tensor-parallel rank its own slices). Returns the names of the stage's parameters that the state dict did not
+    provide; a tensor whose shape does not fit is an error."""
+    params = stage.store.params
+    seen = set()
+    with torch.no_grad():
+        for hf_name, value in state_dict.items():
+            name = rename(hf_name)
+            if name == "lm_head" and stage.cfg.tie_embeddings:
+                continue
+            if name is None or name not in params:
+                continue
+            piece = shard_param(name, value, tp_rank, tp_size)
+            if tuple(piece.shape) != tuple(params[name].shape):
+                raise ValueError(f"{hf_name}: shape {tuple(piece.shape)} does not fit {name} {tuple(params[name].shape)}")
+            params[name].copy_(piece.to(params[name].dtype))
+            seen.add(name)
+    return sorted(n for n in params if n not in seen)
+
+
+def export_state_dict(stages, cfg: GPTConfig) -> dict:
+    """The opposite direction for unsharded stages (tensor-parallel size 1): Hugging Face names for the parameters of
+    the given pipeline stages."""
+    back = {v: k for k, v in _LAYER.items()}
+    top = {v: k for k, v in _TOP.items()}
+    out = {}
+    for stage in stages:
+        for name, p in stage.store.params.items():
+            m = re.match(r"layers\.(\d+)\.(.+)$", name)
+            if m:
+                out[f"model.layers.{m.group(1)}.{back[m.group(2)]}"] = p.detach().clone()
+            elif name in top:
+                out[top[name]] = p.detach().clone()
+    if cfg.tie_embeddings and "model.embed_tokens.weight" in out:
+        out["lm_head.weight"] = out["model.embed_tokens.weight"]
+    return out
