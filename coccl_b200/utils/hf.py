@@ -45,6 +45,54 @@ def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> G
                      tie_embeddings=bool(getattr(hf, "tie_word_embeddings", False)), dtype=dtype)
 
 
+def gpt2_config(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> GPTConfig:
+    """GPTConfig(arch="gpt") for a transformers GPT2Config: the same architecture as this package's GPT (pre-LayerNorm,
+    learned positions, tanh-GELU MLP, tied output head)."""
+    if getattr(hf, "model_type", "") != "gpt2":
+        raise ValueError("not a GPT-2 configuration")
+    if hf.activation_function not in ("gelu_new", "gelu_pytorch_tanh"):
+        raise ValueError("this package's GPT uses the tanh form of GELU")
+    return GPTConfig(n_layer=hf.n_layer, hidden=hf.n_embd, n_head=hf.n_head, ffn=hf.n_inner or 4 * hf.n_embd,
+                     seq_len=seq_len or hf.n_positions, vocab=hf.vocab_size, eps=hf.layer_norm_epsilon, dtype=dtype)
+
+
+def gpt2_to_local(state_dict: dict, cfg: GPTConfig) -> dict:
+    """A GPT-2 state dict under this package's names and layouts. GPT-2 stores its linear layers as [in, out] and the
+    fused projection as (q | k | v) x heads; here weights are [out, in] and the projection is heads x (q | k | v), so
+    that a tensor-parallel rank's rows are whole heads."""
+    nh, d, h = cfg.n_head, cfg.head_dim, cfg.hidden
+    out = {"wte": state_dict["transformer.wte.weight"], "wpe": state_dict["transformer.wpe.weight"][:cfg.seq_len],
+           "lnf.weight": state_dict["transformer.ln_f.weight"], "lnf.bias": state_dict["transformer.ln_f.bias"]}
+    for i in range(cfg.n_layer):
+        src, dst = f"transformer.h.{i}.", f"layers.{i}."
+        for a, b in (("ln_1", "ln1"), ("ln_2", "ln2")):
+            out[dst + b + ".weight"], out[dst + b + ".bias"] = state_dict[src + a + ".weight"], state_dict[src + a + ".bias"]
+        w = state_dict[src + "attn.c_attn.weight"].t()                                   # [3h, h], rows (which, head, d)
+        out[dst + "qkv.weight"] = w.reshape(3, nh, d, h).permute(1, 0, 2, 3).reshape(3 * h, h).contiguous()
+        out[dst + "qkv.bias"] = state_dict[src + "attn.c_attn.bias"].reshape(3, nh, d).permute(1, 0, 2).reshape(3 * h).contiguous()
+        out[dst + "proj.weight"] = state_dict[src + "attn.c_proj.weight"].t().contiguous()
+        out[dst + "proj.bias"] = state_dict[src + "attn.c_proj.bias"]
+        out[dst + "fc1.weight"] = state_dict[src + "mlp.c_fc.weight"].t().contiguous()
+        out[dst + "fc1.bias"] = state_dict[src + "mlp.c_fc.bias"]
+        out[dst + "fc2.weight"] = state_dict[src + "mlp.c_proj.weight"].t().contiguous()
+        out[dst + "fc2.bias"] = state_dict[src + "mlp.c_proj.bias"]
+    return out
+
+
+def load_local(stage, local: dict, *, tp_rank: int = 0, tp_size: int = 1) -> list[str]:
+    """Copy parameters given under this package's names (whole, tensor-parallel size 1) into the ones `stage` holds."""
+    params, seen = stage.store.params, set()
+    with torch.no_grad():
+        for name, value in local.items():
+            if name in params:
+                piece = shard_param(name, value, tp_rank, tp_size)
+                if tuple(piece.shape) != tuple(params[name].shape):
+                    raise ValueError(f"{name}: shape {tuple(piece.shape)} does not fit {tuple(params[name].shape)}")
+                params[name].copy_(piece.to(params[name].dtype))
+                seen.add(name)
+    return sorted(n for n in params if n not in seen)
+
+
 def rename(hf_name: str) -> str | None:
     """This package's name of a Hugging Face parameter (None: a buffer that is not a parameter here)."""
     if hf_name in _TOP:

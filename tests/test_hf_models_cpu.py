@@ -1,4 +1,4 @@
-"""The Llama / Qwen family against Hugging Face transformers on CPU: a randomly initialised tiny LlamaForCausalLM /
+"""The model families against Hugging Face transformers on CPU: a randomly initialised tiny GPT2LMHeadModel, LlamaForCausalLM /
 Qwen2ForCausalLM / Qwen3ForCausalLM is loaded into this package's stage through utils/hf.py, and both must give the
 same loss and the same gradients."""
 import pytest
@@ -102,3 +102,37 @@ def test_launcher_starts_from_a_hugging_face_checkpoint(tmp_path, capsys):
     logits = model(input_ids=batch[:, :-1]).logits
     ref = F.cross_entropy(logits.reshape(-1, 128), batch[:, 1:].reshape(-1)).item()
     assert abs(rec["loss"] - ref) < 1e-3 * ref, (rec, ref)
+
+
+def test_gpt_equals_transformers_gpt2():
+    """The benchmark's model family: this package's GPT is GPT-2's architecture, so a GPT2LMHeadModel loaded through
+    utils/hf.py must give the same loss and gradients."""
+    from coccl_b200.models.gpt import GPTStage
+    from coccl_b200.utils import hf
+    torch.manual_seed(0)
+    hf_cfg = transformers.GPT2Config(vocab_size=128, n_positions=32, n_embd=64, n_layer=3, n_head=4, activation_function="gelu_new",
+                                     resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    model = transformers.GPT2LMHeadModel(hf_cfg).float().train()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "ln_" in n or n.endswith(".bias"):
+                p.add_(torch.randn_like(p) * 0.1)
+    cfg = hf.gpt2_config(hf_cfg, dtype=torch.float32)
+    stage = GPTStage(cfg, torch.device("cpu"))
+    local = hf.gpt2_to_local(model.state_dict(), cfg)
+    assert hf.load_local(stage, local) == []
+    assert cfg.num_params() == sum(p.numel() for p in model.parameters())
+    tok = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=torch.Generator().manual_seed(3))
+    inp, tgt = tok[:, :-1], tok[:, 1:]
+    loss = stage(inp, tgt, 1.0)
+    logits = model(input_ids=inp).logits
+    ref = F.cross_entropy(logits.reshape(-1, cfg.vocab), tgt.reshape(-1), reduction="sum")
+    assert abs(loss.item() - ref.item()) < 2e-4 * abs(ref.item()), (loss.item(), ref.item())
+    stage.zero_grad_buffer()
+    loss.backward()
+    stage.post_backward_sync_autograd_grads()
+    ref.backward()
+    theirs = hf.gpt2_to_local({n: p.grad for n, p in model.named_parameters()} | {"lm_head.weight": None}, cfg)
+    for name, p in stage.store.params.items():
+        a, b = p.main_grad, theirs[name]
+        assert torch.allclose(a, b, atol=2e-4 * b.abs().max().item() + 1e-6), (name, (a - b).abs().max().item())
