@@ -55,7 +55,8 @@ class PipelineSchedule:
         if first:
             out = self.stage(mb[:, :-1], tgt, scale, chunk=chunk)
         else:
-            inp.requires_grad_(True)
+            if torch.is_grad_enabled():
+                inp.requires_grad_(True)
             out = self.stage((inp, None), tgt, scale, batch=b, seq=s, chunk=chunk)
         if last:
             loss_acc += out.detach()
@@ -71,6 +72,21 @@ class PipelineSchedule:
         else:
             torch.autograd.backward(out, out_grad)
         return inp.grad if inp is not None else None
+
+    def run_forward_only(self, tokens, n_micro: int, scale: float, loss_acc):
+        """Evaluation: every micro-batch walks through the (virtual) stages once, no gradients, one tensor in flight
+        per stage boundary. A chain of matching blocking sends and receives, so nothing can wait in a cycle."""
+        chunks = len(self.stage.chunks)
+        ring = list(self.mesh.pp_ranks)
+        last_vs = self.pp_size * chunks - 1
+        with torch.no_grad():
+            for m in range(n_micro):
+                for c in range(chunks):
+                    vs = c * self.pp_size + self.pp_rank
+                    inp = self._p2p(recv_from=ring[(self.pp_rank - 1) % self.pp_size]) if vs > 0 else None
+                    y, _ = self._forward(tokens, m, inp, scale, loss_acc, chunk=c if chunks > 1 else None)
+                    if vs < last_vs:
+                        self._p2p(send=y, send_to=ring[(self.pp_rank + 1) % self.pp_size])
 
     def run(self, tokens, n_micro: int, scale: float, loss_acc):
         prev, nxt = self.prev, self.next

@@ -81,6 +81,9 @@ def parse(argv=None):
     d = ap.add_argument_group("data")
     d.add_argument("--data", default=None, help="flat token file (uint16 / uint32, or .npy); default: synthetic ids")
     d.add_argument("--data-dtype", default="auto", choices=["auto", "uint16", "uint32"])
+    d.add_argument("--eval-data", default=None, help="held-out token file; its loss is logged as val_loss")
+    d.add_argument("--eval-interval", type=int, default=0, help="steps between evaluations (0: never)")
+    d.add_argument("--eval-batches", type=int, default=4, help="global batches per evaluation")
     k = ap.add_argument_group("checkpoints and logs")
     k.add_argument("--save", default=None, metavar="DIR")
     k.add_argument("--save-interval", type=int, default=0, help="0: only at the end")
@@ -194,6 +197,23 @@ def main(argv=None) -> int:
         heartbeat = Heartbeat(default_store(), rank, world, stale_after_s=args.heartbeat_stale_s)
         heartbeat.beat(start - 1)   # a resumed run has the steps before `start` behind it
 
+    eval_source = None
+    if args.eval_interval > 0:
+        eval_source = TokenFile(args.eval_data, args.data_dtype) if args.eval_data else SyntheticTokens(cfg.vocab, seed=args.seed + 1)
+
+    def evaluate():
+        """Mean loss over the first --eval-batches global batches of the held-out stream (the same ones every time)."""
+        ev = BatchLoader(eval_source, seq_len=cfg.seq_len, global_batch=global_batch, dp_rank=mesh.dp_rank if mesh else 0,
+                         dp_size=dp, seed=args.seed + 1, vocab=cfg.vocab, depth=2)
+        total = torch.zeros(1, dtype=torch.float32, device=dev)
+        for _ in range(args.eval_batches):
+            total += trainer.eval_step(ev.next())
+            ev.copied()
+        ev.close()
+        if world > 1:
+            dist.all_reduce(total)
+        return total.item() / (loss_group_size * args.eval_batches)
+
     decay = args.decay_steps or args.steps
     tokens_per_step = global_batch * cfg.seq_len
     loss_group_size = args.tp * dp   # ranks of the last pipeline stage that hold a loss
@@ -253,6 +273,14 @@ def main(argv=None) -> int:
                 trainer.check_health(wait=True)
                 window_loss.zero_()
                 window_steps, t_window = 0, time.time()
+            if eval_source is not None and (done % args.eval_interval == 0 or done == args.steps):
+                val = evaluate()
+                if rank == 0:
+                    rec = {"step": done, "val_loss": round(val, 5)}
+                    print(json.dumps(rec), flush=True)
+                    if args.log_json:
+                        with open(args.log_json, "a") as f:
+                            f.write(json.dumps(rec) + "\n")
             if args.save_interval and done % args.save_interval == 0 and done != args.steps:
                 save(done)
         save(args.steps)

@@ -152,6 +152,31 @@ class Trainer:
             c.post_status_read()
         return self._loss_acc * self.parallel.dp  # this rank's mean loss
 
+    @torch.no_grad()
+    def eval_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Mean token loss of `tokens` [n_seq, seq_len + 1] under the current parameters: forward passes only, no
+        gradient, no update. Same conventions as train_step: each data-parallel rank passes its own sequences, and
+        the returned values add up over the ranks that hold a loss exactly as train_step's do."""
+        cfg = self.cfg
+        n_seq = tokens.shape[0]
+        assert n_seq % self.micro_batch == 0
+        n_micro = n_seq // self.micro_batch
+        if tokens.device != self.device:
+            tokens = tokens.to(self.device, non_blocking=True)
+        if self.cp_ctx is not None:
+            s_local = cfg.seq_len // self.parallel.cp
+            lo = self.cp_ctx.rank * s_local
+            tokens = tokens[:, lo:lo + s_local + 1]
+        acc = torch.zeros(1, dtype=torch.float32, device=self.device)
+        scale = 1.0 / (n_seq * cfg.seq_len * self.parallel.dp)
+        if self.schedule is not None:
+            self.schedule.run_forward_only(tokens, n_micro, scale, acc)
+        else:
+            for i in range(n_micro):
+                mb = tokens[i * self.micro_batch:(i + 1) * self.micro_batch]
+                acc += self.stage(mb[:, :-1], mb[:, 1:], scale)
+        return acc * self.parallel.dp
+
     def _comms(self):
         g = self.groups
         return [c for c in ((g.tp_comm, g.dp_comm, g.pp_comm, getattr(g, "ep_comm", None), getattr(g, "cp_comm", None))

@@ -46,6 +46,10 @@ def _worker(rank, world, tp, pp, dp, ref_losses, ref_params, virtual_stages=1, c
     per = 8 // dp
     mine = tok[mesh.dp_rank * per:(mesh.dp_rank + 1) * per]
     for step, (ref, ref_norm) in enumerate(ref_losses):
+        # evaluation (forward passes only, also through the pipeline schedules) sees the loss the training step reports
+        held = tr.eval_step(mine).clone()
+        dist.all_reduce(held)
+        assert abs(held.item() / (tp * dp) - ref) < 2e-3 * abs(ref) + 1e-4, (step, held.item() / (tp * dp), ref)
         loss = tr.train_step(mine)
         # the global gradient norm counts every parameter once, whatever the layout: replicated parameters on one
         # tensor-parallel rank only, the shared embedding on one pipeline stage only

@@ -113,6 +113,19 @@ def test_two_rank_launch_matches_one_process(tmp_path, capsys):
         assert two[s] == pytest.approx(one[s], rel=2e-3), (two, one)
 
 
+def test_validation_loss_is_logged_and_falls(tmp_path, capsys):
+    from coccl_b200.pretrain import main
+    data = _token_file(tmp_path)
+    common = TINY + ["--data", data, "--eval-data", data, "--global-batch", "4", "--eval-interval", "4", "--eval-batches", "2"]
+    main(common + ["--steps", "12", "--decay-steps", "12"])
+    vals = [r["val_loss"] for r in _records(capsys.readouterr().out) if "val_loss" in r]
+    assert len(vals) == 3 and vals[-1] < vals[0] - 0.2, vals
+    # without updates the held-out batches give the same loss every time
+    main(common + ["--steps", "8", "--lr", "0", "--min-lr", "0", "--warmup-steps", "0"])
+    vals = [r["val_loss"] for r in _records(capsys.readouterr().out) if "val_loss" in r]
+    assert len(vals) == 2 and vals[0] == vals[1], vals
+
+
 def _launch(argv, tmp_path, nproc=2):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
