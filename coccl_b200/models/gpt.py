@@ -47,6 +47,7 @@ class GPTConfig:
     # on the query / key / value projections, untied output head unless tie_embeddings.
     arch: str = "gpt"
     n_kv_head: int = 0              # 0: as many as n_head
+    kv_channels: int = 0            # width of one attention head; 0: hidden / n_head (Qwen3 sets 128 whatever the hidden size)
     rope_theta: float = 1.0e6
     qkv_bias: bool = False
     qk_norm: bool = False           # RMSNorm over the head dimension of queries and keys before the rotation (Qwen3)
@@ -61,14 +62,16 @@ class GPTConfig:
 
     @property
     def head_dim(self) -> int:
-        return self.hidden // self.n_head
+        return self.kv_channels or self.hidden // self.n_head
 
     def num_params(self) -> int:
         h, f = self.hidden, self.ffn
         if self.arch == "llama":
             qkv = (self.n_head + 2 * self.kv_heads) * self.head_dim
-            layer = qkv * h + (qkv if self.qkv_bias else 0) + h * h + 3 * h * f + 2 * h + (2 * self.head_dim if self.qk_norm else 0)
-            return self.n_layer * layer + self.vocab * h * (1 if self.tie_embeddings else 2) + h
+            attn = qkv * h + (qkv if self.qkv_bias else 0) + self.n_head * self.head_dim * h + 2 * h + (2 * self.head_dim if self.qk_norm else 0)
+            n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
+            mlps = (self.n_layer - n_moe) * 3 * h * f + n_moe * (self.n_experts * 3 * h * f + self.n_experts * h)
+            return self.n_layer * attn + mlps + self.vocab * h * (1 if self.tie_embeddings else 2) + h
         attn = 4 * h * h + 4 * h + 4 * h           # qkv, proj, their biases, two LayerNorms
         mlp = 2 * h * f + f + h
         moe = self.n_experts * (2 * h * f + f) + self.n_experts * h        # experts (up, bias, down), router
@@ -81,7 +84,10 @@ class GPTConfig:
         h, f, s = self.hidden, self.ffn, self.seq_len
         if self.arch == "llama":
             qkv = (self.n_head + 2 * self.kv_heads) * self.head_dim
-            return 3.0 * (self.n_layer * (2 * qkv * h + 2 * h * h + 2 * s * h + 2 * 3 * h * f) + 2 * h * self.vocab)
+            n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
+            mlps = (self.n_layer - n_moe) * 2 * 3 * h * f + n_moe * (self.moe_top_k * 2 * 3 * h * f + 2 * h * self.n_experts)
+            ao = self.n_head * self.head_dim   # width of the attention output
+            return 3.0 * (self.n_layer * (2 * qkv * h + 2 * ao * h + 2 * s * ao) + mlps + 2 * h * self.vocab)
         attn = 2 * 4 * h * h + 2 * s * h
         n_moe = sum(self.is_moe_layer(i) for i in range(self.n_layer))
         dense = 2 * 2 * h * f
@@ -483,8 +489,9 @@ class GPTStage(nn.Module):
 
         def default_layer(c, i, s, t):
             if llama:
-                from .llama import LlamaLayer
-                assert c.n_experts == 0, "the llama family is built with dense layers"
+                from .llama import LlamaLayer, LlamaMoELayer
+                if c.is_moe_layer(i):
+                    return LlamaMoELayer(c, i, s, t, ep_comm, expert_store)
                 return LlamaLayer(c, i, s, t)
             if c.is_moe_layer(i):
                 from .moe import MoETransformerLayer

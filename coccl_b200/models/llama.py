@@ -106,12 +106,19 @@ class LlamaLayer(TransformerLayer):
             store.add(pre + "k_norm.weight", (d,), "ones", replicated=True)
         store.add(pre + "o.weight", (h, nh * d // t), "normal", out_std)
         store.add(pre + "ln2.weight", (h,), "ones", replicated=True)
+        self.add_mlp_params(store, out_std)
+
+    MLP_NAMES = ("gate.weight", "up.weight", "down.weight")
+
+    def add_mlp_params(self, store, out_std: float):
+        cfg, pre, t = self.cfg, self.prefix, self.tp.size
+        h, f = cfg.hidden, cfg.ffn
         store.add(pre + "gate.weight", (f // t, h), "normal", cfg.init_std)
         store.add(pre + "up.weight", (f // t, h), "normal", cfg.init_std)
         store.add(pre + "down.weight", (h, f // t), "normal", out_std)
 
     def names(self):
-        base = ["ln1.weight", "q.weight", "k.weight", "v.weight", "o.weight", "ln2.weight", "gate.weight", "up.weight", "down.weight"]
+        base = ["ln1.weight", "q.weight", "k.weight", "v.weight", "o.weight", "ln2.weight", *self.MLP_NAMES]
         return (base + (["q.bias", "k.bias", "v.bias"] if self.cfg.qkv_bias else []) +
                 (["q_norm.weight", "k_norm.weight"] if self.cfg.qk_norm else []))
 
@@ -122,7 +129,10 @@ class LlamaLayer(TransformerLayer):
         st = self._store
         self.wqkv = st.span([pre + "q.weight", pre + "k.weight", pre + "v.weight"])
         self.bqkv = st.span([pre + "q.bias", pre + "k.bias", pre + "v.bias"]) if self.cfg.qkv_bias else None
-        self.w_gate_up = st.span([pre + "gate.weight", pre + "up.weight"])
+        self.bind_mlp(params, expert_params)
+
+    def bind_mlp(self, params, expert_params):
+        self.w_gate_up = self._store.span([self.prefix + "gate.weight", self.prefix + "up.weight"])
 
     def attention(self, qkv, batch, seq):
         cfg, t = self.cfg, self.tp.size
@@ -161,3 +171,48 @@ class LlamaLayer(TransformerLayer):
         qkv = tp.gather_linear(rms_norm(x, self.ln1_weight, cfg.eps), self.wqkv, self.bqkv)
         x = x + tp.linear_scatter(self.attention(qkv, batch, seq), self.o_weight, None)
         return x, self.mlp(rms_norm(x, self.ln2_weight, cfg.eps))
+
+
+class LlamaMoELayer(LlamaLayer):
+    """The family's mixture-of-experts layer (Qwen3-MoE, Mixtral style): attention as in LlamaLayer, then a top-k router
+    over `n_experts` SwiGLU experts of width `ffn`, weights = softmax over the chosen experts' logits. Tokens travel to
+    the experts' ranks and back through the same exchange as the GPT mixture-of-experts layer (models/moe.py: FP8
+    dispatch, bf16 combine over the expert-parallel group); with expert parallelism a rank allocates only its own
+    experts, in `expert_store`."""
+
+    MLP_NAMES = ("router.weight",)
+
+    def __init__(self, cfg, idx, store, tp, ep_comm, expert_store):
+        assert tp.size == 1, "mixture-of-experts layers are built for expert + data + pipeline parallelism (tp = 1)"
+        self.ep_comm, self._expert_store = ep_comm, expert_store
+        super().__init__(cfg, idx, store, tp)
+
+    def add_mlp_params(self, store, out_std: float):
+        cfg, pre = self.cfg, self.prefix
+        h, f, e_all = cfg.hidden, cfg.ffn, cfg.n_experts
+        ep = self.ep_comm.size if self.ep_comm is not None else 1
+        assert e_all % ep == 0, "n_experts must be a multiple of the expert-parallel size"
+        first = (self.ep_comm.rank if self.ep_comm is not None else 0) * (e_all // ep)
+        self.expert_ids = list(range(first, first + e_all // ep))
+        store.add(pre + "router.weight", (e_all, h), "normal", cfg.init_std)
+        target = self._expert_store if self._expert_store is not None else store
+        for e in self.expert_ids:
+            target.add(f"{pre}experts.{e}.gate.weight", (f, h), "normal", cfg.init_std)
+            target.add(f"{pre}experts.{e}.up.weight", (f, h), "normal", cfg.init_std)
+            target.add(f"{pre}experts.{e}.down.weight", (h, f), "normal", out_std)
+
+    def bind_mlp(self, params, expert_params):
+        from .moe import MoELayer
+        src = expert_params if self._expert_store is not None else params
+        gates, ups, downs = [], [], []
+        for e in self.expert_ids:
+            for kind, bucket in (("gate", gates), ("up", ups), ("down", downs)):
+                p = src[f"{self.prefix}experts.{e}.{kind}.weight"]
+                self.register_parameter(f"experts_{e}_{kind}_weight", p)
+                bucket.append(p)
+        cfg = self.cfg
+        self.moe = MoELayer.over(self.ep_comm, cfg.hidden, cfg.ffn, cfg.n_experts, cfg.moe_top_k, self.router_weight,
+                                 ups, [None] * len(ups), downs, w_gate=gates)
+
+    def mlp(self, y):
+        return self.moe.forward(y)

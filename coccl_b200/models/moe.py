@@ -90,19 +90,31 @@ class MoELayer:
             self.w_down.append((torch.randn(hidden, ffn, generator=ge) * 0.02).to(dev, torch.bfloat16))
 
     @classmethod
-    def over(cls, comm, hidden: int, ffn: int, n_experts: int, topk: int, router, w_up, b_up, w_down):
+    def over(cls, comm, hidden: int, ffn: int, n_experts: int, topk: int, router, w_up, b_up, w_down, w_gate=None):
         """The layer over parameters that somebody else owns (a trainer's flat buffers): `w_up`, `b_up`, `w_down`
-        list this rank's experts in order of their global index; comm None means every expert is local."""
+        list this rank's experts in order of their global index; comm None means every expert is local. With
+        `w_gate` the experts are SwiGLU MLPs (silu(x W_gate^T) * (x W_up^T)) W_down^T without biases (the Llama / Qwen
+        family); without it GELU MLPs with a bias on the first projection."""
         self = cls.__new__(cls)
         self.comm = comm if comm is not None else _Solo()
         assert n_experts % self.comm.size == 0 and len(w_up) == n_experts // self.comm.size
         self.hidden, self.ffn, self.n_experts, self.topk = hidden, ffn, n_experts, topk
         self.local = n_experts // self.comm.size
         self.router, self.w_up, self.b_up, self.w_down = router, list(w_up), list(b_up), list(w_down)
+        self.w_gate = list(w_gate) if w_gate is not None else None
         return self
 
     def parameters(self):
-        return [self.router, *self.w_up, *self.b_up, *self.w_down]
+        return [self.router, *self.w_up, *[b for b in self.b_up if b is not None], *self.w_down, *(self.w_gate or [])]
+
+    def expert(self, le: int, x: torch.Tensor) -> torch.Tensor:
+        """Local expert `le` on rows x."""
+        gate = getattr(self, "w_gate", None)
+        if gate is not None:
+            h = torch.nn.functional.silu(fused.linear(x, gate[le])) * fused.linear(x, self.w_up[le])
+        else:
+            h = fused.linear(x, self.w_up[le], self.b_up[le], gelu=True)
+        return fused.linear(h, self.w_down[le])
 
     def requires_grad_(self, on: bool = True):
         for p in self.parameters():
@@ -122,8 +134,7 @@ class MoELayer:
         for le in range(self.local):
             lo, hi = offsets[le], offsets[le + 1]
             if hi > lo:
-                h = fused.linear(rows[lo:hi], self.w_up[le], self.b_up[le], gelu=True)
-                outs.append(fused.linear(h, self.w_down[le]))
+                outs.append(self.expert(le, rows[lo:hi]))
         used = offsets[self.local]
         if used < total:  # unused tail of the receive buffer
             outs.append(rows.new_zeros(total - used, rows.shape[1]))
@@ -146,8 +157,7 @@ class MoELayer:
             for j in range(self.topk):
                 tok = (ids[:, j] == e).nonzero()[:, 0]
                 if tok.numel():
-                    h = fused.linear(x[tok].contiguous(), self.w_up[e], self.b_up[e], gelu=True)
-                    y = fused.linear(h, self.w_down[e])
+                    y = self.expert(e, x[tok].contiguous())
                     out = out.index_add(0, tok, gates[tok, j:j + 1] * y.float())
         return out.to(x.dtype)
 

@@ -29,19 +29,28 @@ _TOP = {"model.embed_tokens.weight": "wte", "model.norm.weight": "lnf.weight", "
 def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> GPTConfig:
     """GPTConfig(arch="llama") for a transformers LlamaConfig / Qwen2Config / Qwen3Config."""
     kind = getattr(hf, "model_type", "")
-    if kind not in ("llama", "qwen2", "qwen3"):
+    if kind not in ("llama", "qwen2", "qwen3", "qwen3_moe"):
         raise ValueError(f"model type {kind!r} is not of the Llama / Qwen family")
+    moe = {}
+    if kind == "qwen3_moe":
+        if not hf.norm_topk_prob:
+            raise ValueError("the router here weighs the chosen experts by a softmax over their logits (norm_topk_prob = true)")
+        if getattr(hf, "mlp_only_layers", None):
+            raise ValueError("dense layers at listed positions (mlp_only_layers) are not supported; use decoder_sparse_step")
+        if hf.decoder_sparse_step != 1 and hf.intermediate_size != hf.moe_intermediate_size:
+            raise ValueError("dense and expert MLPs of different widths are not supported")
+        moe = dict(n_experts=hf.num_experts, moe_top_k=hf.num_experts_per_tok, moe_every=hf.decoder_sparse_step)
     head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
-    if head_dim * hf.num_attention_heads != hf.hidden_size:
-        raise ValueError("a head dimension other than hidden_size / heads is not supported")
     theta = getattr(hf, "rope_theta", None)
     if theta is None:   # newer configs keep it in a dictionary
         theta = (getattr(hf, "rope_parameters", None) or {}).get("rope_theta", 1.0e4)
     return GPTConfig(arch="llama", n_layer=hf.num_hidden_layers, hidden=hf.hidden_size, n_head=hf.num_attention_heads,
                      n_kv_head=getattr(hf, "num_key_value_heads", None) or hf.num_attention_heads,
-                     ffn=hf.intermediate_size, seq_len=seq_len or min(hf.max_position_embeddings, 2048),
+                     kv_channels=0 if head_dim * hf.num_attention_heads == hf.hidden_size else head_dim,
+                     ffn=hf.moe_intermediate_size if kind == "qwen3_moe" else hf.intermediate_size,
+                     seq_len=seq_len or min(hf.max_position_embeddings, 2048), **moe,
                      vocab=hf.vocab_size, eps=hf.rms_norm_eps, rope_theta=float(theta),
-                     qkv_bias=(kind == "qwen2") or bool(getattr(hf, "attention_bias", False)), qk_norm=(kind == "qwen3"),
+                     qkv_bias=(kind == "qwen2") or bool(getattr(hf, "attention_bias", False)), qk_norm=kind in ("qwen3", "qwen3_moe"),
                      tie_embeddings=bool(getattr(hf, "tie_word_embeddings", False)), dtype=dtype)
 
 
@@ -93,10 +102,37 @@ def load_local(stage, local: dict, *, tp_rank: int = 0, tp_size: int = 1) -> lis
     return sorted(n for n in params if n not in seen)
 
 
+def split_experts(state_dict: dict) -> dict:
+    """Mixture-of-experts checkpoints keep all experts of a layer in two tensors (gate_up_proj [experts, 2 * width,
+    hidden] with the gate rows first, down_proj [experts, hidden, width]); this package names every expert's three
+    matrices. Returns the state dict with those tensors replaced by per-expert entries under Hugging Face style names
+    that `rename` understands; the router (`mlp.gate.weight`) keeps its name."""
+    out = {}
+    for k, v in state_dict.items():
+        m = re.match(r"(model\.layers\.\d+\.mlp\.experts)\.(gate_up_proj|down_proj)$", k)
+        if not m:
+            out[k] = v
+            continue
+        for e in range(v.shape[0]):
+            if m.group(2) == "gate_up_proj":
+                half = v.shape[1] // 2
+                out[f"{m.group(1)}.{e}.gate_proj.weight"] = v[e, :half]
+                out[f"{m.group(1)}.{e}.up_proj.weight"] = v[e, half:]
+            else:
+                out[f"{m.group(1)}.{e}.down_proj.weight"] = v[e]
+    return out
+
+
 def rename(hf_name: str) -> str | None:
     """This package's name of a Hugging Face parameter (None: a buffer that is not a parameter here)."""
     if hf_name in _TOP:
         return _TOP[hf_name]
+    m = re.match(r"model\.layers\.(\d+)\.mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$", hf_name)
+    if m:
+        return f"layers.{m.group(1)}.experts.{m.group(2)}.{m.group(3)}.weight"
+    m = re.match(r"model\.layers\.(\d+)\.mlp\.gate\.weight$", hf_name)
+    if m:
+        return f"layers.{m.group(1)}.router.weight"
     m = re.match(r"model\.layers\.(\d+)\.(.+)$", hf_name)
     if m and m.group(2) in _LAYER:
         return f"layers.{m.group(1)}.{_LAYER[m.group(2)]}"
@@ -107,10 +143,12 @@ def load_state_dict(stage, state_dict: dict, *, tp_rank: int = 0, tp_size: int =
     """Copy a Hugging Face state dict into the parameters `stage` holds (a pipeline stage takes its own layers, a
     tensor-parallel rank its own slices). Returns the names of the stage's parameters that the state dict did not
     provide; a tensor whose shape does not fit is an error."""
-    params = stage.store.params
+    params = dict(stage.store.params)
+    if getattr(stage, "expert_store", None) is not None:
+        params.update(stage.expert_store.params)      # this rank's experts under expert parallelism
     seen = set()
     with torch.no_grad():
-        for hf_name, value in state_dict.items():
+        for hf_name, value in split_experts(state_dict).items():
             name = rename(hf_name)
             if name == "lm_head" and stage.cfg.tie_embeddings:
                 continue

@@ -18,7 +18,7 @@ def _hf_model(kind):
     if kind == "qwen2":
         cfg = transformers.Qwen2Config(rope_theta=1.0e6, **common)
         return transformers.Qwen2ForCausalLM(cfg)
-    cfg = transformers.Qwen3Config(rope_theta=1.0e6, head_dim=16, **common)
+    cfg = transformers.Qwen3Config(rope_theta=1.0e6, head_dim=32, **common)   # heads wider than hidden / heads, as Qwen3
     return transformers.Qwen3ForCausalLM(cfg)
 
 
@@ -136,3 +136,40 @@ def test_gpt_equals_transformers_gpt2():
     for name, p in stage.store.params.items():
         a, b = p.main_grad, theirs[name]
         assert torch.allclose(a, b, atol=2e-4 * b.abs().max().item() + 1e-6), (name, (a - b).abs().max().item())
+
+
+def test_mixture_of_experts_equals_transformers_qwen3_moe():
+    from coccl_b200.models.gpt import GPTStage
+    from coccl_b200.utils import hf
+    torch.manual_seed(0)
+    hf_cfg = transformers.Qwen3MoeConfig(vocab_size=128, hidden_size=64, intermediate_size=96, moe_intermediate_size=96,
+                                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                         max_position_embeddings=64, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
+                                         decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False, rope_theta=1.0e6,
+                                         rms_norm_eps=1e-5, router_aux_loss_coef=0.0, output_router_logits=False)
+    model = transformers.Qwen3MoeForCausalLM(hf_cfg).float().train()
+    with torch.no_grad():   # the expert tensors and the router start uninitialised / zero
+        for n, p in model.named_parameters():
+            if "experts" in n or n.endswith("mlp.gate.weight"):
+                p.copy_(torch.randn_like(p) * 0.05)
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    cfg = hf.config_from_hf(hf_cfg, seq_len=32, dtype=torch.float32)
+    assert (cfg.n_experts, cfg.moe_top_k, cfg.moe_every, cfg.qk_norm, cfg.ffn) == (4, 2, 1, True, 96)
+    stage = GPTStage(cfg, torch.device("cpu"))
+    assert hf.load_state_dict(stage, model.state_dict()) == []
+    assert cfg.num_params() == sum(p.numel() for p in model.parameters())
+    tok = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=torch.Generator().manual_seed(3))
+    inp, tgt = tok[:, :-1], tok[:, 1:]
+    loss = stage(inp, tgt, 1.0)
+    logits = model(input_ids=inp).logits
+    ref = F.cross_entropy(logits.reshape(-1, cfg.vocab), tgt.reshape(-1), reduction="sum")
+    assert abs(loss.item() - ref.item()) < 2e-4 * abs(ref.item()), (loss.item(), ref.item())
+    stage.zero_grad_buffer()
+    loss.backward()
+    stage.post_backward_sync_autograd_grads()
+    ref.backward()
+    theirs = {hf.rename(k): v for k, v in hf.split_experts({n: p.grad for n, p in model.named_parameters()}).items()}
+    for name, p in stage.store.params.items():
+        a, b = p.main_grad, theirs[name]
+        assert torch.allclose(a, b, atol=3e-4 * b.abs().max().item() + 1e-6), (name, (a - b).abs().max().item(), b.abs().max().item())

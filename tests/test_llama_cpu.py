@@ -155,3 +155,36 @@ def test_training_lowers_the_loss_on_structured_tokens():
     tok = ids.view(8, 33)
     losses = [tr.train_step(tok).item() for _ in range(12)]
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+# ---------------------------------------------------------------------------- mixture of experts in the family
+def _moe_cfg():
+    return _cfg(n_layer=2, n_experts=4, moe_top_k=2, moe_every=1, qkv_bias=False)
+
+
+def _moe_ep_worker(rank, world, ref, ref_params):
+    import torch.distributed as dist
+    from coccl_b200.parallel.mesh import Mesh
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = _moe_cfg()
+    mesh = Mesh(tp=1, pp=1, dp=2, ep=2, device=torch.device("cpu"))
+    tr = Trainer(cfg, torch.device("cpu"), micro_batch=2, parallel=ParallelConfig(1, 1, 2, ep=2), groups=mesh, lr=1e-2)
+    es = tr.stage.expert_store
+    assert es is not None and len(es.params) == 2 * 2 * 3 and not any(".experts." in n for n in tr.stage.store.params)
+    for store in (tr.stage.store, es):
+        for name, p in store.params.items():
+            p.data.copy_(ref_params[name])
+    tr.opt.master.copy_(tr.opt.param_shard.float())
+    tr.expert_opt.master.copy_(tr.expert_opt.param_shard.float())
+    tok = _data(cfg, 8)
+    mine = tok[rank * 4:(rank + 1) * 4]
+    for step, (ref_loss, ref_norm) in enumerate(ref):
+        t = tr.train_step(mine).clone()
+        dist.all_reduce(t)
+        assert abs(t.item() / 2 - ref_loss) < 2e-3 * abs(ref_loss) + 1e-4, (step, t.item() / 2, ref_loss)
+        assert abs(tr.opt.grad_norm.item() - ref_norm) < 2e-3 * ref_norm + 1e-6, (step, tr.opt.grad_norm.item(), ref_norm)
+
+
+def test_mixture_of_experts_with_expert_parallelism_matches_single_process():
+    params, ref = _reference(_moe_cfg())
+    run_distributed(_moe_ep_worker, 2, "gloo", (ref, params))
