@@ -1,6 +1,8 @@
 #!/usr/bin/env bash
 # 3-D parallel GPT pre-training with compressed collectives, one process per GPU.
 #   examples/train_gpt.sh <model> [nnodes] [gpus-per-node] [node-rank]       e.g.  examples/train_gpt.sh gpt-6.7b 1 8 0
+# <model>: gpt-2.7b | gpt-6.7b | gpt-13b | qwen2.5-7b | qwen3-8b | llama3-8b | qwen3-30b-a3b (with EP) | ... (python -m coccl_b200.pretrain -h);
+# HF_MODEL=<directory> starts from a Hugging Face checkpoint of the Llama / Qwen family instead.
 # Variables: TP (2), PP (2), EP (1), VIRTUAL_STAGES (1), GLOBAL_BATCH (0 = 8 sequences per data-parallel rank),
 # MICRO_BATCH (2), STEPS (1000), LR (3e-4), DATA (flat token file; empty = synthetic ids), SAVE (checkpoint directory,
 # resumed when it already holds one), SAVE_INTERVAL (500), MASTER_ADDR (127.0.0.1), MASTER_PORT (29500),
@@ -21,6 +23,7 @@ args=(--model "$model" --tp "${TP:-2}" --pp "${PP:-2}" --ep "${EP:-1}" --virtual
       --global-batch "${GLOBAL_BATCH:-0}" --micro-batch "${MICRO_BATCH:-2}" --steps "${STEPS:-1000}" --lr "${LR:-3e-4}"
       --log-interval "${LOG_INTERVAL:-10}")
 [[ -n "${DATA:-}" ]] && args+=(--data "$DATA")
+[[ -n "${HF_MODEL:-}" ]] && args+=(--hf-model "$HF_MODEL")
 [[ -n "${SAVE:-}" ]] && args+=(--save "$SAVE" --save-interval "${SAVE_INTERVAL:-500}" --resume)
 cd "$root"
 exec python -m torch.distributed.run --nnodes "$nnodes" --nproc-per-node "$gpus" --node-rank "$node_rank" \
