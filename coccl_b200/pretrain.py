@@ -41,6 +41,8 @@ MODELS = {
                            tie_embeddings=False, rope_theta=1.0e6, qk_norm=True, n_experts=8, moe_top_k=2, moe_every=1),
     "qwen3-30b-a3b": dict(arch="llama", n_layer=48, hidden=2048, n_head=32, n_kv_head=4, kv_channels=128, ffn=768, seq_len=2048, vocab=151936,
                           tie_embeddings=False, rope_theta=1.0e6, qk_norm=True, n_experts=128, moe_top_k=8, moe_every=1),
+    "mixtral-8x7b": dict(arch="llama", n_layer=32, hidden=4096, n_head=32, n_kv_head=8, ffn=14336, seq_len=2048, vocab=32000,
+                         tie_embeddings=False, rope_theta=1.0e6, n_experts=8, moe_top_k=2, moe_every=1),
     "qwen3-8b": dict(arch="llama", n_layer=36, hidden=4096, n_head=32, n_kv_head=8, ffn=12288, seq_len=2048, vocab=151936,
                      tie_embeddings=False, rope_theta=1.0e6, qk_norm=True),
     "qwen2.5-7b": dict(arch="llama", n_layer=28, hidden=3584, n_head=28, n_kv_head=4, ffn=18944, seq_len=2048, vocab=152064,

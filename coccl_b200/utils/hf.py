@@ -27,9 +27,9 @@ _TOP = {"model.embed_tokens.weight": "wte", "model.norm.weight": "lnf.weight", "
 
 
 def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> GPTConfig:
-    """GPTConfig(arch="llama") for a transformers LlamaConfig / Qwen2Config / Qwen3Config."""
+    """GPTConfig(arch="llama") for a transformers LlamaConfig / Qwen2Config / Qwen3Config / Qwen3MoeConfig / MixtralConfig."""
     kind = getattr(hf, "model_type", "")
-    if kind not in ("llama", "qwen2", "qwen3", "qwen3_moe"):
+    if kind not in ("llama", "qwen2", "qwen3", "qwen3_moe", "mixtral"):
         raise ValueError(f"model type {kind!r} is not of the Llama / Qwen family")
     moe = {}
     if kind == "qwen3_moe":
@@ -40,6 +40,10 @@ def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> G
         if hf.decoder_sparse_step != 1 and hf.intermediate_size != hf.moe_intermediate_size:
             raise ValueError("dense and expert MLPs of different widths are not supported")
         moe = dict(n_experts=hf.num_experts, moe_top_k=hf.num_experts_per_tok, moe_every=hf.decoder_sparse_step)
+    if kind == "mixtral":   # every layer is a mixture of experts, the chosen experts' weights are renormalised
+        if getattr(hf, "sliding_window", None):
+            raise ValueError("sliding-window attention is not supported")
+        moe = dict(n_experts=hf.num_local_experts, moe_top_k=hf.num_experts_per_tok, moe_every=1)
     head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
     theta = getattr(hf, "rope_theta", None)
     if theta is None:   # newer configs keep it in a dictionary

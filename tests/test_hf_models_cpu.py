@@ -138,16 +138,22 @@ def test_gpt_equals_transformers_gpt2():
         assert torch.allclose(a, b, atol=2e-4 * b.abs().max().item() + 1e-6), (name, (a - b).abs().max().item())
 
 
-def test_mixture_of_experts_equals_transformers_qwen3_moe():
+@pytest.mark.parametrize("kind", ["qwen3_moe", "mixtral"])
+def test_mixture_of_experts_equals_transformers(kind):
     from coccl_b200.models.gpt import GPTStage
     from coccl_b200.utils import hf
     torch.manual_seed(0)
-    hf_cfg = transformers.Qwen3MoeConfig(vocab_size=128, hidden_size=64, intermediate_size=96, moe_intermediate_size=96,
-                                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
-                                         max_position_embeddings=64, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
-                                         decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False, rope_theta=1.0e6,
-                                         rms_norm_eps=1e-5, router_aux_loss_coef=0.0, output_router_logits=False)
-    model = transformers.Qwen3MoeForCausalLM(hf_cfg).float().train()
+    common = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=64, num_experts_per_tok=2, tie_word_embeddings=False,
+                  rope_theta=1.0e6, rms_norm_eps=1e-5, router_aux_loss_coef=0.0, output_router_logits=False)
+    if kind == "qwen3_moe":
+        hf_cfg = transformers.Qwen3MoeConfig(moe_intermediate_size=96, head_dim=16, num_experts=4, norm_topk_prob=True,
+                                             decoder_sparse_step=1, mlp_only_layers=[], **common)
+        model = transformers.Qwen3MoeForCausalLM(hf_cfg)
+    else:
+        hf_cfg = transformers.MixtralConfig(num_local_experts=4, sliding_window=None, **common)
+        model = transformers.MixtralForCausalLM(hf_cfg)
+    model = model.float().train()
     with torch.no_grad():   # the expert tensors and the router start uninitialised / zero
         for n, p in model.named_parameters():
             if "experts" in n or n.endswith("mlp.gate.weight"):
@@ -155,7 +161,7 @@ def test_mixture_of_experts_equals_transformers_qwen3_moe():
             if "norm" in n:
                 p.add_(torch.randn_like(p) * 0.1)
     cfg = hf.config_from_hf(hf_cfg, seq_len=32, dtype=torch.float32)
-    assert (cfg.n_experts, cfg.moe_top_k, cfg.moe_every, cfg.qk_norm, cfg.ffn) == (4, 2, 1, True, 96)
+    assert (cfg.n_experts, cfg.moe_top_k, cfg.moe_every, cfg.qk_norm, cfg.ffn) == (4, 2, 1, kind == "qwen3_moe", 96)
     stage = GPTStage(cfg, torch.device("cpu"))
     assert hf.load_state_dict(stage, model.state_dict()) == []
     assert cfg.num_params() == sum(p.numel() for p in model.parameters())
