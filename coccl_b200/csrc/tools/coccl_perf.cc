@@ -11,7 +11,7 @@
 // call of every size is compared with a host-computed reference and the relative RMS error is printed.
 //
 // Timing: a barrier between the threads, then -n calls bracketed by CUDA events on every rank's stream; the reported
-// time is the slowest rank's average.
+// time is the slowest rank's average. With -F 1 every call is timed on its own after a 256 MiB write (cold L2).
 #include <cuda_runtime.h>
 #include <math.h>
 #include <pthread.h>
@@ -33,7 +33,7 @@ enum class Entry { Standard, OneShot, TwoShot, TripleShot, Explicit };
 struct Options {
   Op op = Op::AllReduce;
   Entry entry = Entry::Standard;
-  int gpus = 0, warmup = 5, iters = 20, check = 0;
+  int gpus = 0, warmup = 5, iters = 20, check = 0, flush = 0;
   size_t minBytes = 1u << 20, maxBytes = 64u << 20;
   double factor = 2.0;
   ncclDataType_t dtype = ncclFloat32;
@@ -60,9 +60,10 @@ int usage(const char* why) {
   if (why) fprintf(stderr, "coccl-perf: %s\n", why);
   fprintf(stderr,
           "usage: coccl-perf [-o all_reduce|reduce_scatter|all_gather|alltoall] [-x standard|oneshot|twoshot|tripleshot|explicit]\n"
-          "                  [-g gpus] [-b min] [-e max] [-f factor] [-d float|half|bfloat16] [-w warmup] [-n iterations] [-c 0|1]\n"
+          "                  [-g gpus] [-b min] [-e max] [-f factor] [-d float|half|bfloat16] [-w warmup] [-n iterations] [-c 0|1] [-F 0|1]\n"
           "  sizes take K, M, G suffixes; -x oneshot/twoshot/tripleshot select cocclAllReduceComp* / cocclReduceScatterComp*,\n"
-          "  -x explicit selects cocclAllGatherComp / cocclAllToAllComp; policy from COCCL_ENABLE / COCCL_CONFIG_FILE\n");
+          "  -x explicit selects cocclAllGatherComp / cocclAllToAllComp; policy from COCCL_ENABLE / COCCL_CONFIG_FILE\n"
+          "  -F 1 writes a 256 MiB buffer before every timed call (cold L2) and times each call on its own\n");
   return 2;
 }
 
@@ -91,6 +92,7 @@ bool parse(int argc, char** argv, Options* o, const char** error) {
     else if (a == "-w") o->warmup = atoi(v);
     else if (a == "-n") o->iters = atoi(v);
     else if (a == "-c") o->check = atoi(v);
+    else if (a == "-F") o->flush = atoi(v);
     else if (a == "-f") o->factor = atof(v);
     else if (a == "-b") { if (!parseSize(v, &o->minBytes)) { *error = "bad -b"; return false; } }
     else if (a == "-e") { if (!parseSize(v, &o->maxBytes)) { *error = "bad -e"; return false; } }
@@ -247,7 +249,9 @@ void* worker(void* arg) {
     if (sc > maxSend) maxSend = sc;
     if (rc > maxRecv) maxRecv = rc;
   }
-  void *send = nullptr, *recv = nullptr;
+  void *send = nullptr, *recv = nullptr, *flushBuffer = nullptr;
+  const size_t kFlushBytes = 256u << 20;
+  if (o.flush && cudaMalloc(&flushBuffer, kFlushBytes) != cudaSuccess) fail("cudaMalloc", 0);
   const size_t w = widthOf(o.dtype);
   if (cudaMalloc(&send, maxSend * w) != cudaSuccess || cudaMalloc(&recv, maxRecv * w) != cudaSuccess) fail("cudaMalloc", 0);
   std::vector<float> host;
@@ -286,12 +290,29 @@ void* worker(void* arg) {
     }
     cudaStreamSynchronize(stream);
     pthread_barrier_wait(&s.barrier);
-    cudaEventRecord(e0, stream);
-    for (int i = 0; i < o.iters && rcode == ncclSuccess; ++i) rcode = issue(o, send, recv, a, s.comms[rank], stream);
-    cudaEventRecord(e1, stream);
-    if (cudaEventSynchronize(e1) != cudaSuccess) fail("cudaEventSynchronize", 0);
     float ms = 0;
-    cudaEventElapsedTime(&ms, e0, e1);
+    if (o.flush && flushBuffer != nullptr) {
+      // cold L2: a buffer twice the size of the L2 is overwritten before every call, the ranks meet, and the call
+      // is timed on its own; every thread runs all iterations (also after a failure) so that the barriers match
+      for (int i = 0; i < o.iters; ++i) {
+        cudaMemsetAsync(flushBuffer, i & 0xff, kFlushBytes, stream);
+        cudaStreamSynchronize(stream);
+        pthread_barrier_wait(&s.barrier);
+        cudaEventRecord(e0, stream);
+        if (rcode == ncclSuccess) rcode = issue(o, send, recv, a, s.comms[rank], stream);
+        cudaEventRecord(e1, stream);
+        if (cudaEventSynchronize(e1) != cudaSuccess) fail("cudaEventSynchronize", 0);
+        float one = 0;
+        cudaEventElapsedTime(&one, e0, e1);
+        ms += one;
+      }
+    } else {
+      cudaEventRecord(e0, stream);
+      for (int i = 0; i < o.iters && rcode == ncclSuccess; ++i) rcode = issue(o, send, recv, a, s.comms[rank], stream);
+      cudaEventRecord(e1, stream);
+      if (cudaEventSynchronize(e1) != cudaSuccess) fail("cudaEventSynchronize", 0);
+      cudaEventElapsedTime(&ms, e0, e1);
+    }
     s.ms[rank * sizes.size() + k] = ms / o.iters;
     if (rcode != ncclSuccess) fail(cocclApiGetErrorString(rcode), (int)rcode);
     ncclResult_t async = ncclSuccess;
@@ -299,6 +320,7 @@ void* worker(void* arg) {
   }
   if (send) cudaFree(send);
   if (recv) cudaFree(recv);
+  if (flushBuffer) cudaFree(flushBuffer);
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   cudaStreamDestroy(stream);
