@@ -147,7 +147,7 @@ def main() -> int:
     ap.add_argument("--depth", type=int, default=4)
     ap.add_argument("--threshold", type=int, default=8 << 20)
     ap.add_argument("--case-limit-s", type=int, default=240)
-    ap.add_argument("--budget-s", type=int, default=1500, help="stop starting new cases after this many seconds")
+    ap.add_argument("--time-limit-s", type=int, default=1500, help="stop starting new cases after this many seconds")
     ap.add_argument("--out", default="")
     ap.add_argument("--log", default="")
     a = ap.parse_args()
@@ -179,8 +179,8 @@ def main() -> int:
                 key = (codec, op)
                 if closed_reason(codec, op) is not None:
                     reason, res, tail = closed_reason(codec, op), None, ""
-                elif time.time() - t_start > a.budget_s:
-                    reason = "not run: time budget of this call used up"
+                elif time.time() - t_start > a.time_limit_s:
+                    reason = "not run: the time limit of this call was reached"
                     res, tail = None, ""
                 elif key in dead:
                     reason, res, tail = dead[key], None, ""
