@@ -195,6 +195,8 @@ def main(argv=None) -> int:
         if rank == 0:
             print(f"resumed from {args.save} at step {start}", flush=True)
 
+    if args.data_dtype == "auto" and cfg.vocab > 65536 and not (args.data or "").endswith(".npy"):
+        args.data_dtype = "uint32"   # ids of such a vocabulary do not fit 16 bits
     source = TokenFile(args.data, args.data_dtype) if args.data else SyntheticTokens(cfg.vocab, seed=args.seed)
     loader = BatchLoader(source, seq_len=cfg.seq_len, global_batch=global_batch, dp_rank=mesh.dp_rank if mesh else 0,
                          dp_size=dp, seed=args.seed, start_step=start, vocab=cfg.vocab)
