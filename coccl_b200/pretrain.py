@@ -94,6 +94,8 @@ def parse(argv=None):
     k.add_argument("--save", default=None, metavar="DIR")
     k.add_argument("--save-interval", type=int, default=0, help="0: only at the end")
     k.add_argument("--resume", action="store_true", help="continue from --save if it holds a checkpoint")
+    k.add_argument("--export-hf", default=None, metavar="DIR",
+                   help="write the final weights as a Hugging Face checkpoint (dense models, one rank holding the whole model)")
     k.add_argument("--log-interval", type=int, default=10)
     k.add_argument("--log-json", default=None, metavar="FILE", help="rank 0 appends one JSON line per log interval")
     k.add_argument("--heartbeat-stale-s", type=float, default=120.0, help="a peer silent for this long counts as lost; 0: off")
@@ -292,6 +294,13 @@ def main(argv=None) -> int:
             if args.save_interval and done % args.save_interval == 0 and done != args.steps:
                 save(done)
         save(args.steps)
+        if args.export_hf:
+            if args.tp * args.pp > 1 or trainer.fsdp:
+                raise SystemExit("--export-hf needs the whole model on a rank (tp = pp = 1, not fully sharded)")
+            if rank == 0:
+                from .utils import hf
+                hf.export_pretrained(trainer.stage, args.export_hf)
+                print(f"exported to {args.export_hf}", flush=True)
     finally:
         loader.close()
         if heartbeat is not None:

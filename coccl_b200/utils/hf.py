@@ -182,3 +182,63 @@ def export_state_dict(stages, cfg: GPTConfig) -> dict:
     if cfg.tie_embeddings and "model.embed_tokens.weight" in out:
         out["lm_head.weight"] = out["model.embed_tokens.weight"]
     return out
+
+
+def local_to_gpt2(params: dict, cfg: GPTConfig) -> dict:
+    """The opposite of gpt2_to_local: this package's GPT parameters (whole, tensor-parallel size 1) under GPT-2's names
+    and layouts."""
+    nh, d, h = cfg.n_head, cfg.head_dim, cfg.hidden
+    out = {"transformer.wte.weight": params["wte"], "transformer.wpe.weight": params["wpe"],
+           "transformer.ln_f.weight": params["lnf.weight"], "transformer.ln_f.bias": params["lnf.bias"], "lm_head.weight": params["wte"]}
+    for i in range(cfg.n_layer):
+        src, dst = f"layers.{i}.", f"transformer.h.{i}."
+        for a, b in (("ln1", "ln_1"), ("ln2", "ln_2")):
+            out[dst + b + ".weight"], out[dst + b + ".bias"] = params[src + a + ".weight"], params[src + a + ".bias"]
+        w = params[src + "qkv.weight"].reshape(nh, 3, d, h).permute(1, 0, 2, 3).reshape(3 * h, h)     # rows (which, head, d)
+        out[dst + "attn.c_attn.weight"] = w.t().contiguous()
+        out[dst + "attn.c_attn.bias"] = params[src + "qkv.bias"].reshape(nh, 3, d).permute(1, 0, 2).reshape(3 * h).contiguous()
+        out[dst + "attn.c_proj.weight"] = params[src + "proj.weight"].t().contiguous()
+        out[dst + "attn.c_proj.bias"] = params[src + "proj.bias"]
+        out[dst + "mlp.c_fc.weight"] = params[src + "fc1.weight"].t().contiguous()
+        out[dst + "mlp.c_fc.bias"] = params[src + "fc1.bias"]
+        out[dst + "mlp.c_proj.weight"] = params[src + "fc2.weight"].t().contiguous()
+        out[dst + "mlp.c_proj.bias"] = params[src + "fc2.bias"]
+    return {k: v.detach().clone() for k, v in out.items()}
+
+
+def hf_config(cfg: GPTConfig):
+    """A transformers configuration for `cfg` (dense models: GPT-2, Llama, Qwen2, Qwen3 by their distinguishing marks)."""
+    import transformers
+    if cfg.n_experts:
+        raise ValueError("export covers dense models")
+    if cfg.arch == "gpt":
+        return transformers.GPT2Config(vocab_size=cfg.vocab, n_positions=cfg.seq_len, n_embd=cfg.hidden, n_layer=cfg.n_layer,
+                                       n_head=cfg.n_head, n_inner=cfg.ffn, activation_function="gelu_new",
+                                       layer_norm_epsilon=cfg.eps, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    common = dict(vocab_size=cfg.vocab, hidden_size=cfg.hidden, intermediate_size=cfg.ffn, num_hidden_layers=cfg.n_layer,
+                  num_attention_heads=cfg.n_head, num_key_value_heads=cfg.kv_heads, max_position_embeddings=cfg.seq_len,
+                  rms_norm_eps=cfg.eps, rope_theta=cfg.rope_theta, tie_word_embeddings=cfg.tie_embeddings)
+    if cfg.qk_norm:
+        return transformers.Qwen3Config(head_dim=cfg.head_dim, attention_bias=cfg.qkv_bias, **common)
+    if cfg.kv_channels:
+        raise ValueError("a head width other than hidden / heads needs a configuration with head_dim (Qwen3)")
+    if cfg.qkv_bias:
+        return transformers.Qwen2Config(**common)
+    return transformers.LlamaConfig(attention_bias=False, **common)
+
+
+def export_pretrained(stage, directory: str) -> None:
+    """Write the parameters of an unsharded single-stage model as a Hugging Face checkpoint (`save_pretrained`)."""
+    import transformers
+    cfg = stage.cfg
+    assert stage.pre and stage.post and stage.tp.size == 1 and not getattr(stage, "fsdp", False), \
+        "export needs the whole model in one stage (tensor- and pipeline-parallel size 1)"
+    conf = hf_config(cfg)
+    model = transformers.AutoModelForCausalLM.from_config(conf)
+    sd = local_to_gpt2(stage.store.params, cfg) if cfg.arch == "gpt" else export_state_dict([stage], cfg)
+    missing = model.load_state_dict({k: v.float() for k, v in sd.items()}, strict=False)
+    left = [k for k in missing.missing_keys if "inv_freq" not in k and "rotary" not in k and not k.endswith(".attn.bias")
+            and not k.endswith("masked_bias")]
+    if left or missing.unexpected_keys:
+        raise RuntimeError(f"export does not match the transformers model: missing {left[:4]}, unexpected {missing.unexpected_keys[:4]}")
+    model.to(cfg.dtype).save_pretrained(directory, safe_serialization=True)

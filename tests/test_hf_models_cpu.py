@@ -179,3 +179,32 @@ def test_mixture_of_experts_equals_transformers(kind):
     for name, p in stage.store.params.items():
         a, b = p.main_grad, theirs[name]
         assert torch.allclose(a, b, atol=3e-4 * b.abs().max().item() + 1e-6), (name, (a - b).abs().max().item(), b.abs().max().item())
+
+
+@pytest.mark.parametrize("model", ["gpt-tiny", "llama-tiny"])
+def test_trained_weights_leave_as_a_hugging_face_checkpoint(tmp_path, capsys, model):
+    """Train a few steps here, export, load with transformers: its loss on a batch equals this package's."""
+    from coccl_b200.models.gpt import GPTStage
+    from coccl_b200.pretrain import main
+    from coccl_b200.utils import hf
+    out = tmp_path / "exported"
+    main(["--model", model, "--hidden", "64", "--heads", "4", "--ffn", "128", "--seq-len", "32", "--vocab", "128", "--layers", "2",
+          "--device", "cpu", "--steps", "3", "--lr", "1e-2", "--global-batch", "4", "--export-hf", str(out)] +
+         (["--kv-heads", "2"] if model == "llama-tiny" else []))
+    assert "exported to" in capsys.readouterr().out
+    theirs = transformers.AutoModelForCausalLM.from_pretrained(out).float().eval()
+    if model == "gpt-tiny":
+        cfg = hf.gpt2_config(theirs.config, dtype=torch.float32)
+        stage = GPTStage(cfg, torch.device("cpu"))
+        assert hf.load_local(stage, hf.gpt2_to_local(theirs.state_dict(), cfg)) == []
+    else:
+        cfg = hf.config_from_hf(theirs.config, seq_len=32, dtype=torch.float32)
+        stage = GPTStage(cfg, torch.device("cpu"))
+        assert hf.load_state_dict(stage, theirs.state_dict()) == []
+    tok = torch.randint(0, 128, (2, 33), generator=torch.Generator().manual_seed(5))
+    ours = stage(tok[:, :-1], tok[:, 1:], 1.0).item()
+    ref = F.cross_entropy(theirs(input_ids=tok[:, :-1]).logits.reshape(-1, 128), tok[:, 1:].reshape(-1), reduction="sum").item()
+    assert abs(ours - ref) < 1e-3 * abs(ref), (ours, ref)
+    # and the exported model is the TRAINED one, not a fresh initialisation
+    fresh = GPTStage(cfg, torch.device("cpu"))
+    assert (fresh.store.params["layers.0.ln1.weight"] - stage.store.params["layers.0.ln1.weight"]).abs().max().item() > 1e-4
