@@ -46,8 +46,12 @@ def config_from_hf(hf, *, seq_len: int | None = None, dtype=torch.bfloat16) -> G
         moe = dict(n_experts=hf.num_local_experts, moe_top_k=hf.num_experts_per_tok, moe_every=1)
     head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
     theta = getattr(hf, "rope_theta", None)
+    rope = getattr(hf, "rope_parameters", None) or getattr(hf, "rope_scaling", None) or {}
     if theta is None:   # newer configs keep it in a dictionary
-        theta = (getattr(hf, "rope_parameters", None) or {}).get("rope_theta", 1.0e4)
+        theta = rope.get("rope_theta", 1.0e4)
+    kind_of_rope = rope.get("rope_type", rope.get("type", "default")) if isinstance(rope, dict) else "default"
+    if kind_of_rope not in ("default", None):
+        raise ValueError(f"rotary embedding of type {kind_of_rope!r} (scaled frequencies) is not supported; plain rotary positions only")
     return GPTConfig(arch="llama", n_layer=hf.num_hidden_layers, hidden=hf.hidden_size, n_head=hf.num_attention_heads,
                      n_kv_head=getattr(hf, "num_key_value_heads", None) or hf.num_attention_heads,
                      kv_channels=0 if head_dim * hf.num_attention_heads == hf.hidden_size else head_dim,
