@@ -13,7 +13,7 @@ def test_first_loss_matches_cpu_and_training_lowers_it(moe):
     kw = dict(arch="llama", n_layer=2, hidden=512, n_head=8, n_kv_head=2, ffn=1536, seq_len=256, vocab=8192, qkv_bias=True,
               qk_norm=True, tie_embeddings=False, rope_theta=1.0e4)
     if moe:
-        kw.update(ffn=512, n_experts=8, moe_top_k=2, moe_every=1, qkv_bias=False)
+        kw.update(ffn=512, n_experts=4, moe_top_k=2, moe_every=1, qkv_bias=False)
     dev = torch.device("cuda", 0)
     tr = Trainer(GPTConfig(**kw), dev, micro_batch=2, lr=1e-3)
     ids = (torch.arange(8 * 257) * 7) % 8192          # every id determines its successor
@@ -26,6 +26,6 @@ def test_first_loss_matches_cpu_and_training_lowers_it(moe):
     losses = [tr.train_step(tok).item() for _ in range(8)]
     tr.check_health()
     assert abs(losses[0] - want) < 2e-2 * want, (losses[0], want)
-    assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.3, losses
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
     held = tr.eval_step(tok).item()
     assert held < losses[0]
