@@ -29,3 +29,21 @@ def test_first_loss_matches_cpu_and_training_lowers_it(moe):
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 1.0, losses
     held = tr.eval_step(tok).item()
     assert held < losses[0]
+
+
+def test_fully_sharded_strategy_on_one_gpu_equals_the_plain_trainer():
+    """One rank: the sharded store's gather / reduce-scatter points, the buffers that take turns and the sharded AdamW
+    run on the GPU and must reproduce the plain trainer (same kernels, same order of operations)."""
+    from coccl_b200.models.gpt import GPTConfig
+    from coccl_b200.train import ParallelConfig, Trainer
+    cfg = GPTConfig(n_layer=4, hidden=512, n_head=8, ffn=2048, seq_len=256, vocab=8192)
+    dev = torch.device("cuda", 0)
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=torch.Generator().manual_seed(2)).pin_memory()
+    plain = Trainer(cfg, dev, micro_batch=2, lr=1e-3)
+    shard = Trainer(cfg, dev, micro_batch=2, lr=1e-3, parallel=ParallelConfig(dp_strategy="fsdp"))
+    for step in range(4):
+        a, b = plain.train_step(tok).item(), shard.train_step(tok).item()
+        assert abs(a - b) < 2e-3 * abs(a), (step, a, b)
+        na, nb = plain.opt.grad_norm.item(), shard.opt.grad_norm.item()
+        assert abs(na - nb) < 2e-3 * na, (step, na, nb)
+    plain.check_health()
