@@ -1,4 +1,4 @@
-"""The Llama / Qwen family on one GPU (bf16, tcgen05 GEMMs for every projection): the first loss agrees with the fp32 CPU
+"""The Llama / Qwen family and the fully sharded strategy on one GPU (bf16, tcgen05 GEMMs): the first loss agrees with the fp32 CPU
 model built from the same parameters, and training lowers it. Runs last in the suite."""
 import pytest
 import torch
