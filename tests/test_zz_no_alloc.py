@@ -5,7 +5,7 @@ Some callers of this library cannot allocate device memory (a callback running w
 framework's allocator must not be touched, a process with a fixed memory budget), so the
 variant keeps its scratch inside the library image. Two calls in a row check that the shared
 scratch, which keeps the previous call's contents, does not leak into the next result.
-This file is collected last so that a failure here cannot hide any other test.
+This file is collected near the end so that a failure here hides as few other tests as possible.
 """
 import ctypes as C
 
